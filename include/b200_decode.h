@@ -1,0 +1,164 @@
+/*
+ * C ABI of the B200 (sm_100a) decode-step kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches on that
+ * stream, never synchronises, never allocates, and returns 0 or a negative B200_ERR_* code
+ * (no exceptions, no exit, no trap).  All tensors are row-major and dense unless a leading
+ * dimension is passed.  "bf16" means CUDA __nv_bfloat16 bits.
+ *
+ * Each declaration cites the reference (Megatron Core 0.15) call it replaces, by path inside
+ * the reference project.
+ */
+#ifndef B200_DECODE_H_
+#define B200_DECODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* b200_stream_t; /* same type as cudaStream_t */
+
+enum {
+  B200_OK = 0,
+  B200_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad size, unsupported head dim ...            */
+  B200_ERR_ALIGNMENT = -2,        /* pointer or leading dimension not 16-byte aligned            */
+  B200_ERR_WORKSPACE = -3,        /* workspace too small                                         */
+  B200_ERR_LAUNCH = -4,           /* the CUDA runtime refused the launch                         */
+  B200_ERR_DRIVER = -5,           /* tensor-map encode entry point missing or failed             */
+  B200_ERR_DEVICE_TIMEOUT = -6    /* a bounded device-side wait gave up (see b200_device_status) */
+};
+
+/* Library / ABI version (major*1000 + minor). */
+int b200_version(void);
+const char* b200_error_string(int code);
+
+/*
+ * Status word that kernels set when a bounded wait (mbarrier) ran out.  Reading it copies one
+ * int from the device (this call synchronises the device); `reset` != 0 clears it afterwards.
+ * 0 = no kernel has given up since the last reset.
+ */
+int b200_device_status(int reset, int* status_out);
+
+/* ---------------------------------------------------------------------------------------
+ * Embedding / row gather.  out[i, :] = table[ids[i] - vocab_start, :] if vocab_start <= ids[i]
+ * < vocab_end else 0.
+ * Replaces VocabParallelEmbedding.forward (megatron/core/tensor_parallel/layers.py:262-295,
+ * masked lookup before the all-reduce) and the last-token gather of
+ * DynamicInferenceContext.last_token_logits (megatron/core/inference/contexts/dynamic_context.py:890-918).
+ * Optional `add_table`/`add_ids`: a second table gathered and added in bf16 (learned absolute
+ * position embedding, megatron/core/models/common/embeddings/language_model_embedding.py:99-149).
+ */
+int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int n_rows, int row_elems,
+                          int64_t vocab_start, int64_t vocab_end, const void* add_table,
+                          const int64_t* add_ids, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused residual add + RMSNorm / LayerNorm over rows of `hidden` elements.
+ *   h = x (+ bias, bf16 add) (+ residual, bf16 add);  if hidden_out: hidden_out = h
+ *   normed_out = bf16( normalise_fp32(h) * gamma (+ beta) )
+ * beta == NULL selects RMSNorm, otherwise LayerNorm.  normed_out may be NULL (residual add only).
+ * Replaces bias_dropout_add (megatron/core/fusions/fused_bias_dropout.py:11-57, eval mode) followed by
+ * WrappedTorchNorm (megatron/core/transformer/torch_norm.py:38-51) / TENorm
+ * (megatron/core/extensions/transformer_engine.py:204-238).
+ */
+int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma,
+                       const void* beta, void* hidden_out, void* normed_out, int rows, int hidden, float eps,
+                       b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Activation between fc1 and fc2.
+ *   kind 0 (SwiGLU): in [rows, 2*F] = [gate | up]; out[r, f] = bf16(bf16(silu(gate)) * up)
+ *                    (megatron/core/fusions/fused_bias_swiglu.py:15-26, eager bf16 rounding points)
+ *   kind 1 (GELU):   in [rows, F] (+ bias[F]); out = bf16(gelu_erf(in + bias))
+ *                    (megatron/core/transformer/mlp.py:200-213)
+ */
+int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind,
+                         b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * y[M, N] = x[M, K] * w[N, K]^T (+ bias[N]), bf16 in, fp32 accumulate in tensor memory (tcgen05),
+ * bf16 out.  x row stride ldx elements, y row stride ldy elements; w is dense.
+ * Replaces ColumnParallelLinear.forward / RowParallelLinear.forward local GEMM
+ * (megatron/core/tensor_parallel/layers.py:317-336, 946-1043, 1225-1281; torch.matmul(x, W.t())).
+ * The all-reduce of the row-parallel variant stays with the caller.
+ * `workspace`: split-K partial sums + tile counters, see b200_gemm_bf16_workspace_bytes; the
+ * counter region (the first 64 KiB) must be zero before the first call and is left zero.
+ */
+size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K);
+int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M,
+                   int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Paged-KV attention for the dynamic context.
+ *
+ * qkv        [T, nkv, (g+2)*d] bf16: per KV group g query heads, then the key, then the value
+ *            (layout of SelfAttention.get_query_key_value_tensors, megatron/core/transformer/attention.py:985-1021)
+ * k_cache/v_cache  [n_chunks, chunk, nkv, d] bf16: one layer of the context's memory_buffer
+ *            (megatron/core/inference/contexts/dynamic_context.py:296-308, 547-564)
+ * block_table [rows, max_chunks] int32, kv_seq_lengths [T] int32 (kv length INCLUDING this step's token),
+ * row_of_token [T] int32 or NULL (NULL: token t uses block-table row t)
+ * out        [T, nq*d] bf16
+ *
+ * b200_rope_append: RoPE on q (in place in qkv) and k, then scatter k, v into the cache at
+ *   (token_to_chunk_idx[t], token_to_local_pos[t]).  Replaces apply_rotary_emb_key/query + append_key_value_cache
+ *   (dynamic_context.py:511-545, 566-631; megatron/core/models/common/embeddings/rope_utils.py:92-126).
+ *   cos/sin: bf16 tables [max_pos, d/2] or NULL for no RoPE.
+ * b200_paged_attention: softmax(q k^T / sqrt(d)) v over each row's paged KV; replaces
+ *   flash_attn_with_kvcache / flash_attn_varlen_func with block_table
+ *   (megatron/core/transformer/attention.py:470-601).  With fuse_rope_append != 0 it also does the work of
+ *   b200_rope_append for decode steps (one new token per request) inside the same kernel.
+ *   num_splits > 1 splits every row's context into that many ranges (flash-decoding) and needs
+ *   `workspace` of b200_paged_attention_workspace_bytes.
+ */
+typedef struct {
+  const void* qkv;
+  void* k_cache;
+  void* v_cache;
+  const int32_t* block_table;
+  const int32_t* kv_seq_lengths;
+  const int32_t* row_of_token;
+  const int64_t* token_to_pos_ids;          /* RoPE position of q  */
+  const int64_t* token_to_pos_in_request;   /* RoPE position of k  */
+  const int64_t* token_to_chunk_idx;
+  const int64_t* token_to_local_pos;
+  const void* rope_cos;
+  const void* rope_sin;
+  void* out;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t num_tokens;     /* T */
+  int32_t num_q_heads;    /* nq (this rank) */
+  int32_t num_kv_heads;   /* nkv (this rank) */
+  int32_t head_dim;       /* 64 or 128 */
+  int32_t chunk_size;     /* tokens per chunk, multiple of 64 */
+  int32_t num_chunks;     /* chunks in the pool */
+  int32_t max_chunks_per_row; /* block_table row stride */
+  int32_t num_splits;
+  int32_t fuse_rope_append;
+  float softmax_scale;    /* 0 = 1/sqrt(d) */
+} b200_attention_args;
+
+size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);
+int b200_rope_append(const b200_attention_args* args, b200_stream_t stream);
+int b200_paged_attention(const b200_attention_args* args, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Sampling over [rows, vocab] bf16 logits (row stride ld elements).
+ * b200_argmax_bf16: greedy token (smallest index among equal maxima) -> int64; replaces torch.argmax in
+ *   TextGenerationController.sample_from_logits (megatron/core/inference/text_generation_controllers/
+ *   text_generation_controller.py:288-290).
+ * b200_topk_probs_bf16: temperature, keep logits >= k-th largest, softmax -> fp32 probs [rows, vocab];
+ *   replaces modify_logits_for_top_k_filtering + softmax (same file :216-219, 292-305).  The draw itself
+ *   (torch.multinomial on the controller's generator) stays with the caller.
+ */
+int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int vocab, b200_stream_t stream);
+int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,
+                         float temperature, b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_DECODE_H_ */

@@ -1,0 +1,114 @@
+"""ctypes binding of ``libb200_decode.so`` (declarations in ``include/b200_decode.h``).
+
+There is no fallback: if the library is missing the import of any op fails with a clear
+error.  The library is built in-tree by ``megatron_mixtera_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+from .build import LIB_PATH
+
+EXPORTED_SYMBOLS = (
+    "b200_version",
+    "b200_error_string",
+    "b200_device_status",
+    "b200_gather_rows_bf16",
+    "b200_add_norm_bf16",
+    "b200_activation_bf16",
+    "b200_gemm_bf16_workspace_bytes",
+    "b200_gemm_bf16",
+    "b200_paged_attention_workspace_bytes",
+    "b200_rope_append",
+    "b200_paged_attention",
+    "b200_argmax_bf16",
+    "b200_topk_probs_bf16",
+)
+
+
+class AttentionArgs(ctypes.Structure):
+    """Mirror of ``b200_attention_args``."""
+
+    _fields_ = [
+        ("qkv", c_void_p),
+        ("k_cache", c_void_p),
+        ("v_cache", c_void_p),
+        ("block_table", c_void_p),
+        ("kv_seq_lengths", c_void_p),
+        ("row_of_token", c_void_p),
+        ("token_to_pos_ids", c_void_p),
+        ("token_to_pos_in_request", c_void_p),
+        ("token_to_chunk_idx", c_void_p),
+        ("token_to_local_pos", c_void_p),
+        ("rope_cos", c_void_p),
+        ("rope_sin", c_void_p),
+        ("out", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_size_t),
+        ("num_tokens", c_int32),
+        ("num_q_heads", c_int32),
+        ("num_kv_heads", c_int32),
+        ("head_dim", c_int32),
+        ("chunk_size", c_int32),
+        ("num_chunks", c_int32),
+        ("max_chunks_per_row", c_int32),
+        ("num_splits", c_int32),
+        ("fuse_rope_append", c_int32),
+        ("softmax_scale", c_float),
+    ]
+
+
+class B200Error(RuntimeError):
+    """A C-ABI entry point returned a negative code."""
+
+    def __init__(self, fn: str, code: int, text: str):
+        super().__init__(f"{fn} failed: {text} ({code})")
+        self.code = code
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load (once) and type the shared library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m megatron_mixtera_b200.build` "
+            "(there is no CPU or PyTorch fallback for the decode kernels)"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.b200_version.restype = c_int
+    lib.b200_error_string.restype = c_char_p
+    lib.b200_error_string.argtypes = [c_int]
+    lib.b200_device_status.argtypes = [c_int, POINTER(c_int)]
+    lib.b200_gather_rows_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p,
+                                          c_void_p, c_void_p]
+    lib.b200_add_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_int, c_float, c_void_p]
+    lib.b200_activation_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_gemm_bf16_workspace_bytes.restype = c_size_t
+    lib.b200_gemm_bf16_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.b200_gemm_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
+                                   c_void_p, c_size_t, c_void_p]
+    lib.b200_paged_attention_workspace_bytes.restype = c_size_t
+    lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
+    lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]
+    lib.b200_paged_attention.argtypes = [POINTER(AttentionArgs), c_void_p]
+    lib.b200_argmax_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_topk_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    for name in EXPORTED_SYMBOLS:
+        fn = getattr(lib, name)
+        if fn.restype is c_int or name.startswith("b200_") and fn.restype not in (c_char_p, c_size_t):
+            fn.restype = c_int
+    _lib = lib
+    return lib
+
+
+def check(fn_name: str, code: int) -> None:
+    if code != 0:
+        raise B200Error(fn_name, code, load().b200_error_string(code).decode())

@@ -1,0 +1,7 @@
+// Single translation unit of libb200_decode.so: the kernels share one device status word and
+// one tensor-map cache, so they are compiled together instead of being device-linked.
+#include "common.cu"
+#include "gemm_bf16.cu"
+#include "attention.cu"
+#include "elementwise.cu"
+#include "sampling.cu"

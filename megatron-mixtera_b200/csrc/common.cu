@@ -1,0 +1,138 @@
+// Host-side plumbing shared by the kernels: error strings, the device status word,
+// tensor-map (TMA descriptor) encoding with a small cache, device properties.
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  uint64_t words[16];
+  bool operator==(const MapKey& o) const { return std::memcmp(words, o.words, sizeof(words)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t w : k.words) {
+      h ^= w;
+      h *= 1099511628211ull;
+    }
+    return static_cast<size_t>(h);
+  }
+};
+
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
+
+}  // namespace
+
+const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                                  const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2) {
+  if (rank < 1 || rank > 4) return nullptr;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key.words[0] = reinterpret_cast<uint64_t>(base);
+  key.words[1] = (static_cast<uint64_t>(rank) << 32) | (static_cast<uint64_t>(swizzle) << 16) |
+                 (static_cast<uint64_t>(l2) << 8) | static_cast<uint64_t>(dev);
+  for (int i = 0; i < rank; ++i) {
+    key.words[2 + i] = dims[i];
+    key.words[6 + i] = i + 1 < rank ? strides_bytes[i] : 0;
+    key.words[10 + i] = box[i];
+  }
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) return it->second;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return nullptr;
+  // cudaMalloc-free: the descriptor is a 128-byte host object passed to kernels by value.
+  CUtensorMap* m = static_cast<CUtensorMap*>(aligned_alloc(64, sizeof(CUtensorMap)));
+  if (!m) return nullptr;
+  cuuint64_t gdims[4];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[4];
+  cuuint32_t estrides[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
+                  gstrides, gbox, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, l2,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    free(m);
+    return nullptr;
+  }
+  g_maps.emplace(key, m);
+  return m;
+}
+
+int sm_count() {
+  static int cached[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_version(void) { return 1000; }
+
+const char* b200_error_string(int code) {
+  switch (code) {
+    case B200_OK: return "ok";
+    case B200_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case B200_ERR_ALIGNMENT: return "pointer or leading dimension not 16-byte aligned";
+    case B200_ERR_WORKSPACE: return "workspace too small";
+    case B200_ERR_LAUNCH: return "kernel launch failed";
+    case B200_ERR_DRIVER: return "tensor map could not be encoded";
+    case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown error";
+  }
+}
+
+int b200_device_status(int reset, int* status_out) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, b200::g_device_status, sizeof(int)) != cudaSuccess) return B200_ERR_LAUNCH;
+  if (status_out) *status_out = v;
+  if (reset) {
+    int z = 0;
+    if (cudaMemcpyToSymbol(b200::g_device_status, &z, sizeof(int)) != cudaSuccess) return B200_ERR_LAUNCH;
+  }
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,263 @@
+// Memory-bound row kernels of the decode step: embedding / row gather, fused residual-add +
+// RMSNorm / LayerNorm, SwiGLU / GELU.  All use 16-byte vector accesses; one CTA per token row.
+#include "common.cuh"
+
+namespace b200 {
+namespace ew {
+
+struct alignas(16) Vec8 {
+  uint32_t w[4];  // 8 bf16
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // protect `red` against the previous use
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// out[i] = table[ids[i] - lo] (zero outside [lo, hi)) (+ add_table[add_ids[i]], bf16 add)
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ ids,
+                                   __nv_bfloat16* __restrict__ out, int row_elems, int64_t lo, int64_t hi,
+                                   const __nv_bfloat16* __restrict__ add_table, const int64_t* __restrict__ add_ids) {
+  const int r = blockIdx.x;
+  const int64_t id = ids[r];
+  const bool in_range = id >= lo && id < hi;
+  const Vec8* src = reinterpret_cast<const Vec8*>(table + (in_range ? (id - lo) : 0) * row_elems);
+  const Vec8* add = add_table ? reinterpret_cast<const Vec8*>(add_table + add_ids[r] * row_elems) : nullptr;
+  Vec8* dst = reinterpret_cast<Vec8*>(out + static_cast<int64_t>(r) * row_elems);
+  for (int i = threadIdx.x; i < row_elems / 8; i += blockDim.x) {
+    Vec8 v;
+    if (in_range) {
+      v = src[i];
+    } else {
+      v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
+    }
+    if (add) {
+      const Vec8 a = add[i];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        v.w[k] = pack_bf16x2(bf16_lo(v.w[k]) + bf16_lo(a.w[k]), bf16_hi(v.w[k]) + bf16_hi(a.w[k]));
+    }
+    dst[i] = v;
+  }
+}
+
+// h = x (+bias) (+residual) with a bf16 rounding after each add; normed = norm(h) * gamma (+beta).
+// kMaxVec: vectors of 8 elements cached per thread so that the row is read once.
+template <int kMaxVec>
+__global__ void __launch_bounds__(256)
+add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
+                const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
+                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
+                __nv_bfloat16* __restrict__ normed_out, int hidden, float eps) {
+  __shared__ float red[32];
+  const int64_t off = static_cast<int64_t>(blockIdx.x) * hidden;
+  const Vec8* xv = reinterpret_cast<const Vec8*>(x + off);
+  const Vec8* rv = residual ? reinterpret_cast<const Vec8*>(residual + off) : nullptr;
+  const Vec8* bv = bias ? reinterpret_cast<const Vec8*>(bias) : nullptr;
+  const int nvec = hidden / 8;
+  float vals[kMaxVec][8];
+  float sum = 0.f, sumsq = 0.f;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) {
+      Vec8 v = xv[i];
+      float f[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        f[2 * k] = bf16_lo(v.w[k]);
+        f[2 * k + 1] = bf16_hi(v.w[k]);
+      }
+      if (bv) {
+        const Vec8 b = bv[i];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          f[2 * k] = bf16_round(f[2 * k] + bf16_lo(b.w[k]));
+          f[2 * k + 1] = bf16_round(f[2 * k + 1] + bf16_hi(b.w[k]));
+        }
+      }
+      if (rv) {
+        const Vec8 r = rv[i];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          f[2 * k] = bf16_round(f[2 * k] + bf16_lo(r.w[k]));
+          f[2 * k + 1] = bf16_round(f[2 * k + 1] + bf16_hi(r.w[k]));
+        }
+      }
+      if (hidden_out) {
+        Vec8 o;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o.w[k] = pack_bf16x2(f[2 * k], f[2 * k + 1]);
+        reinterpret_cast<Vec8*>(hidden_out + off)[i] = o;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        vals[it][k] = f[k];
+        sum += f[k];
+        sumsq += f[k] * f[k];
+      }
+    }
+  }
+  if (normed_out == nullptr) return;
+  float mean = 0.f, rstd;
+  if (beta != nullptr) {  // LayerNorm: two-pass variance on the cached values
+    mean = block_sum(sum, red) / hidden;
+    float var = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxVec; ++it) {
+      const int i = threadIdx.x + it * blockDim.x;
+      if (i < nvec) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float d = vals[it][k] - mean;
+          var += d * d;
+        }
+      }
+    }
+    rstd = rsqrtf(block_sum(var, red) / hidden + eps);
+  } else {
+    rstd = rsqrtf(block_sum(sumsq, red) / hidden + eps);
+  }
+  const Vec8* gv = reinterpret_cast<const Vec8*>(gamma);
+  const Vec8* betav = beta ? reinterpret_cast<const Vec8*>(beta) : nullptr;
+#pragma unroll
+  for (int it = 0; it < kMaxVec; ++it) {
+    const int i = threadIdx.x + it * blockDim.x;
+    if (i < nvec) {
+      const Vec8 g = gv[i];
+      Vec8 o;
+      float y[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        y[2 * k] = (vals[it][2 * k] - mean) * rstd * bf16_lo(g.w[k]);
+        y[2 * k + 1] = (vals[it][2 * k + 1] - mean) * rstd * bf16_hi(g.w[k]);
+      }
+      if (betav) {
+        const Vec8 b = betav[i];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          y[2 * k] += bf16_lo(b.w[k]);
+          y[2 * k + 1] += bf16_hi(b.w[k]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) o.w[k] = pack_bf16x2(y[2 * k], y[2 * k + 1]);
+      reinterpret_cast<Vec8*>(normed_out + off)[i] = o;
+    }
+  }
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+// kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
+__global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
+                                  __nv_bfloat16* __restrict__ out, int F, int kind) {
+  const int r = blockIdx.x;
+  const int nvec = F / 8;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  Vec8 o;
+  if (kind == 0) {
+    const Vec8* row = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * 2 * F);
+    const Vec8 g = row[i];
+    const Vec8 u = row[nvec + i];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float a = bf16_round(silu_f(bf16_lo(g.w[k]))) * bf16_lo(u.w[k]);
+      const float b = bf16_round(silu_f(bf16_hi(g.w[k]))) * bf16_hi(u.w[k]);
+      o.w[k] = pack_bf16x2(a, b);
+    }
+  } else {
+    const Vec8 v = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * F)[i];
+    Vec8 b;
+    b.w[0] = b.w[1] = b.w[2] = b.w[3] = 0u;
+    if (bias) b = reinterpret_cast<const Vec8*>(bias)[i];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float lo = bf16_lo(v.w[k]), hi = bf16_hi(v.w[k]);
+      if (bias) {
+        lo = bf16_round(lo + bf16_lo(b.w[k]));
+        hi = bf16_round(hi + bf16_hi(b.w[k]));
+      }
+      o.w[k] = pack_bf16x2(gelu_erf_f(lo), gelu_erf_f(hi));
+    }
+  }
+  reinterpret_cast<Vec8*>(out + static_cast<int64_t>(r) * F)[i] = o;
+}
+
+}  // namespace ew
+}  // namespace b200
+
+extern "C" {
+
+int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int n_rows, int row_elems,
+                          int64_t vocab_start, int64_t vocab_end, const void* add_table, const int64_t* add_ids,
+                          b200_stream_t stream) {
+  using namespace b200;
+  if (!table || !ids || !out || n_rows <= 0 || row_elems <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if ((add_table == nullptr) != (add_ids == nullptr)) return B200_ERR_INVALID_ARGUMENT;
+  if (row_elems % 8 != 0 || !aligned16(table) || !aligned16(out) || (add_table && !aligned16(add_table)))
+    return B200_ERR_ALIGNMENT;
+  int threads = row_elems / 8;
+  threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
+  ew::gather_rows_kernel<<<n_rows, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), row_elems, vocab_start,
+      vocab_end, static_cast<const __nv_bfloat16*>(add_table), add_ids);
+  return launch_status();
+}
+
+int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                       void* hidden_out, void* normed_out, int rows, int hidden, float eps, b200_stream_t stream) {
+  using namespace b200;
+  if (!x || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (normed_out && !gamma) return B200_ERR_INVALID_ARGUMENT;
+  if (!normed_out && !hidden_out) return B200_ERR_INVALID_ARGUMENT;
+  if (hidden % 8 != 0) return B200_ERR_ALIGNMENT;
+  const void* ptrs[] = {x, bias, residual, gamma, beta, hidden_out, normed_out};
+  for (const void* q : ptrs)
+    if (q && !aligned16(q)) return B200_ERR_ALIGNMENT;
+  const int nvec = hidden / 8;
+  int threads = nvec >= 256 ? 256 : ((nvec + 31) / 32) * 32;
+  const int per_thread = (nvec + threads - 1) / threads;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto B = static_cast<const __nv_bfloat16*>(bias);
+  auto R = static_cast<const __nv_bfloat16*>(residual);
+  auto Gm = static_cast<const __nv_bfloat16*>(gamma);
+  auto Bt = static_cast<const __nv_bfloat16*>(beta);
+  auto H = static_cast<__nv_bfloat16*>(hidden_out);
+  auto Nn = static_cast<__nv_bfloat16*>(normed_out);
+  if (per_thread <= 1)
+    ew::add_norm_kernel<1><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+  else if (per_thread <= 2)
+    ew::add_norm_kernel<2><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+  else if (per_thread <= 4)
+    ew::add_norm_kernel<4><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+  else if (per_thread <= 8)
+    ew::add_norm_kernel<8><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+  else
+    return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
+  return launch_status();
+}
+
+int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind,
+                         b200_stream_t stream) {
+  using namespace b200;
+  if (!in || !out || rows <= 0 || F <= 0 || (kind != 0 && kind != 1)) return B200_ERR_INVALID_ARGUMENT;
+  if (F % 8 != 0 || !aligned16(in) || !aligned16(out) || (bias && !aligned16(bias))) return B200_ERR_ALIGNMENT;
+  const int nvec = F / 8;
+  dim3 grid(rows, (nvec + 255) / 256);
+  ew::activation_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
+      static_cast<__nv_bfloat16*>(out), F, kind);
+  return launch_status();
+}
+
+}  // extern "C"

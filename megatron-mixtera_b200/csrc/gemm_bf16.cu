@@ -1,0 +1,313 @@
+// y[M, N] = x[M, K] * w[N, K]^T (+ bias): weight-streaming GEMM for decode on tcgen05 / TMEM.
+//
+// Decode has few tokens (M = 8 ... 256) and large weights, so the kernel is bound by streaming w
+// from HBM once.  The roles of the two operands are swapped with respect to the usual GEMM: a tile
+// of 128 weight rows is the UMMA "M" side (one TMEM lane per output feature) and the tokens are the
+// UMMA "N" side (one TMEM column per token, 32 ... 256).  Each CTA owns one (128-feature tile,
+// token block, K range) unit:
+//
+//   warp 0 / lane 0 : TMA producer  - w tile [128 x 64] and x tile [BT x 64] per stage, 128B swizzle
+//   warp 1 / lane 0 : UMMA issuer   - 4 x tcgen05.mma (K = 16 each) per stage, fp32 accumulate in TMEM
+//   warps 0-3       : epilogue      - tcgen05.ld, then either bf16 store or split-K partial store
+//
+// Small N (e.g. out-proj, 32 tiles) cannot fill 148 SMs with whole-K units, so K is split across
+// CTAs.  Partials go to an fp32 workspace; the CTA that arrives last on the tile's counter sums the
+// partials in split order (deterministic, no spinning) and writes bf16.
+#include "common.cuh"
+
+namespace b200 {
+namespace gemm {
+
+constexpr int kTileN = 128;   // weight rows per CTA (UMMA M)
+constexpr int kTileK = 64;    // bf16 elements per stage along K = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 128;
+constexpr int kCounterBytes = 64 * 1024;
+constexpr int kMaxSplits = 32;
+
+template <int BT>
+struct Config {
+  static constexpr int kStageBytesW = kTileN * kTileK * 2;
+  static constexpr int kStageBytesX = BT * kTileK * 2;
+  static constexpr int kStageBytes = kStageBytesW + kStageBytesX;
+  // ~96 KiB of tiles per CTA so that two CTAs are resident per SM.
+  static constexpr int kStages = (BT <= 64) ? 4 : (BT <= 128 ? 3 : 2);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = BT < 32 ? 32 : BT;
+};
+
+struct Params {
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  float* partials;      // [splits][M][N] fp32 (split-K only)
+  int* counters;        // one per (n tile, m block)
+  int64_t ldy;
+  int M, N, K;
+  int num_k_blocks;     // ceil(K / 64)
+  int k_blocks_per_split;
+  int num_splits;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Params p) {
+  using C = Config<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* accum_bar = empty_bar + C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n_tile = blockIdx.x;
+  const int split = blockIdx.y;
+  const int m_block = blockIdx.z;
+  const int n0 = n_tile * kTileN;
+  const int m0 = m_block * BT;
+  const int kb_begin = split * p.k_blocks_per_split;
+  const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
+        uint8_t* stage = smem + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+        const int k0 = (kb_begin + i) * kTileK;
+        tma_load_2d(stage, &map_w, &full_bar[s], k0, n0);
+        tma_load_2d(stage + C::kStageBytesW, &map_x, &full_bar[s], k0, m0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- UMMA issuer ----------------
+      constexpr uint32_t idesc = umma_idesc_bf16(kTileN, BT < 16 ? 16 : BT);
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusGemmTimeout);
+        tcgen05_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+        const uint32_t b_addr = a_addr + C::kStageBytesW;
+        const uint64_t a_desc = umma_desc_k_major_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_major_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kTileK / kUmmaK; ++k) {
+          // 32 bytes per K step inside the 128-byte swizzle row -> +2 in the encoded start address
+          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // frees the stage when these UMMAs have read it
+      }
+      umma_commit(accum_bar);        // accumulator complete
+    }
+    __syncwarp();
+  }
+
+  // ---------------- epilogue: all four warps ----------------
+  mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
+  tcgen05_fence_after_sync();
+
+  const int n = n0 + warp * 32 + lane;          // output feature held by this thread (TMEM lane)
+  const bool n_ok = n < p.N;
+  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+
+  if (p.num_splits == 1) {
+    const float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BT; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(lane_addr + c0, r);
+      tmem_ld_wait();
+      if (n_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int m = m0 + c0 + j;
+          if (m < p.M) {
+            float v = __uint_as_float(r[j]);
+            // bias is added to the bf16-rounded product, as `matmul(x, w.t()) + bias` does
+            if (p.bias != nullptr) v = bf16_round(v) + b;
+            p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  } else {
+    float* part = p.partials + static_cast<int64_t>(split) * p.M * p.N;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BT; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(lane_addr + c0, r);
+      tmem_ld_wait();
+      if (n_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int m = m0 + c0 + j;
+          if (m < p.M) __stcg(&part[static_cast<int64_t>(m) * p.N + n], __uint_as_float(r[j]));
+        }
+      }
+    }
+    // Publish the partial tile, then count arrivals; the last CTA of this tile reduces.
+    __threadfence();
+    __syncthreads();
+    int* counter = p.counters + (m_block * gridDim.x + n_tile);
+    if (tid == 0) {
+      const int prev = atomicAdd(counter, 1);
+      *last_flag = (prev == p.num_splits - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (*last_flag) {
+      __threadfence();
+      const int nn = n0 + tid;  // coalesced: consecutive threads, consecutive features
+      if (nn < p.N) {
+        const float b = p.bias != nullptr ? __bfloat162float(p.bias[nn]) : 0.f;
+        const int m_end = min(p.M, m0 + BT);
+        for (int m = m0; m < m_end; ++m) {
+          float acc = 0.f;
+          for (int s = 0; s < p.num_splits; ++s)
+            acc += __ldcg(&p.partials[(static_cast<int64_t>(s) * p.M + m) * p.N + nn]);
+          if (p.bias != nullptr) acc = bf16_round(acc) + b;
+          p.y[static_cast<int64_t>(m) * p.ldy + nn] = __float2bfloat16_rn(acc);
+        }
+      }
+      if (tid == 0) *counter = 0;  // leave the counters zero for the next launch
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+// Number of K splits: fill ~2 CTAs per SM when there are too few output tiles, keep >= 4 K blocks
+// per split.
+static int choose_splits(int tiles, int num_k_blocks) {
+  const int slots = 2 * sm_count();
+  if (tiles * 2 > slots) return 1;
+  int s = slots / tiles;
+  if (s > kMaxSplits) s = kMaxSplits;
+  if (s > num_k_blocks / 4) s = num_k_blocks / 4;
+  if (s < 1) s = 1;
+  // drop empty trailing splits
+  const int per = (num_k_blocks + s - 1) / s;
+  s = (num_k_blocks + per - 1) / per;
+  return s;
+}
+
+static int pick_bt(int M) {
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+template <int BT>
+static int launch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
+                  int K, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  using C = Config<BT>;
+  const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+  const uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
+  const uint32_t wb[2] = {kTileK, kTileN};
+  const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+  const uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
+  const uint32_t xb[2] = {kTileK, BT};
+  const CUtensorMap* mw = get_tensor_map(w, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  const CUtensorMap* mx = get_tensor_map(x, 2, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  if (!mw || !mx) return B200_ERR_DRIVER;
+
+  const int n_tiles = (N + kTileN - 1) / kTileN;
+  const int m_blocks = (M + BT - 1) / BT;
+  const int num_kb = (K + kTileK - 1) / kTileK;
+  const int splits = choose_splits(n_tiles * m_blocks, num_kb);
+  Params p;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.ldy = ldy;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_k_blocks = num_kb;
+  p.k_blocks_per_split = (num_kb + splits - 1) / splits;
+  p.num_splits = splits;
+  p.partials = nullptr;
+  p.counters = nullptr;
+  if (splits > 1) {
+    const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
+    if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bf16_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+        cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  dim3 grid(n_tiles, splits, m_blocks);
+  gemm_bf16_kernel<BT><<<grid, kThreads, C::kSmemBytes, stream>>>(*mw, *mx, p);
+  return launch_status();
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" {
+
+size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int bt = pick_bt(M);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
+  const int splits = choose_splits(tiles, (K + kTileK - 1) / kTileK);
+  if (splits == 1) return static_cast<size_t>(kCounterBytes);
+  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
+}
+
+int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
+                   int K, void* workspace, size_t workspace_bytes, b200_stream_t stream) {
+  using namespace b200;
+  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return B200_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(w)) return B200_ERR_ALIGNMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch<32>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    case 64: return gemm::launch<64>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    case 128: return gemm::launch<128>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    default: return gemm::launch<256>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+  }
+}
+
+}  // extern "C"

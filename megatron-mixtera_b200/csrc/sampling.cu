@@ -1,0 +1,175 @@
+// Sampling over vocab-sized bf16 logit rows: greedy argmax and top-k filtered probabilities.
+// One CTA per row; rows are read once with 16-byte loads where the row start allows it.
+#include "common.cuh"
+
+namespace b200 {
+namespace sampling {
+
+constexpr int kThreads = 1024;
+
+// Order-preserving map of bf16 bits to unsigned: larger float <=> larger key.
+__device__ __forceinline__ uint32_t bf16_key(uint16_t b) { return (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u); }
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+
+// Greedy: largest value, smallest index among equal values (NaN never wins).
+__global__ void __launch_bounds__(kThreads)
+argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int64_t* __restrict__ out, int vocab) {
+  const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const float v = bf16_bits_to_float(row[i]);
+    if (v > best || (best_i == 0x7fffffff && v == best)) {  // strided scan visits indices in increasing order
+      best = v;
+      best_i = i;
+    }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = best_i;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    best = sv[lane];
+    best_i = si[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
+// Top-k: the k-th largest value is found exactly by a two-pass radix select on the 16-bit keys
+// (256-bin histograms in shared memory); logits below it become probability 0, the rest
+// softmax((logit / temperature)) in fp32.  Division by the temperature is rounded to bf16 first,
+// as the in-place `logits.div_(temperature)` on a bf16 tensor does.
+__global__ void __launch_bounds__(kThreads)
+topk_probs_kernel(const uint16_t* __restrict__ logits, int64_t ld, float* __restrict__ probs, int vocab, int top_k,
+                  float temperature) {
+  __shared__ int hist[256];
+  __shared__ int sel_bin, sel_rank;
+  __shared__ float red[32];
+  const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+  float* prow = probs + static_cast<int64_t>(blockIdx.x) * vocab;
+  const bool scale = temperature != 1.0f;
+
+  auto load_key = [&](int i) -> uint32_t {
+    uint16_t b = row[i];
+    if (scale) {
+      __nv_bfloat16 q = __float2bfloat16_rn(bf16_bits_to_float(b) / temperature);
+      b = *reinterpret_cast<uint16_t*>(&q);
+    }
+    return bf16_key(b);
+  };
+  auto key_to_float = [&](uint32_t key) -> float {
+    const uint16_t b = (key & 0x8000u) ? static_cast<uint16_t>(key & 0x7fffu) : static_cast<uint16_t>(~key & 0xffffu);
+    return bf16_bits_to_float(b);
+  };
+
+  // pass 1: high byte
+  for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < vocab; i += kThreads) atomicAdd(&hist[load_key(i) >> 8], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int need = top_k, b = 255;
+    for (; b > 0; --b) {
+      if (hist[b] >= need) break;
+      need -= hist[b];
+    }
+    sel_bin = b;
+    sel_rank = need;  // the threshold is the need-th largest key inside bin b
+  }
+  __syncthreads();
+  const int hi_bin = sel_bin;
+  const int need = sel_rank;
+  __syncthreads();
+  // pass 2: low byte inside the selected high bin
+  for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const uint32_t k = load_key(i);
+    if (static_cast<int>(k >> 8) == hi_bin) atomicAdd(&hist[k & 0xff], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = need, b = 255;
+    for (; b > 0; --b) {
+      if (hist[b] >= n) break;
+      n -= hist[b];
+    }
+    sel_bin = b;
+  }
+  __syncthreads();
+  const uint32_t thr_key = (static_cast<uint32_t>(hi_bin) << 8) | static_cast<uint32_t>(sel_bin);
+
+  // softmax over the kept entries: max is the largest key overall
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const uint32_t k = load_key(i);
+    if (k >= thr_key) mx = fmaxf(mx, key_to_float(k));
+  }
+  mx = warp_max(mx);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = warp_max(red[lane]);
+  __syncthreads();
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const uint32_t k = load_key(i);
+    if (k >= thr_key) sum += expf(key_to_float(k) - mx);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = warp_sum(red[lane]);
+  const float inv = 1.f / sum;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const uint32_t k = load_key(i);
+    prow[i] = k >= thr_key ? expf(key_to_float(k) - mx) * inv : 0.f;
+  }
+}
+
+}  // namespace sampling
+}  // namespace b200
+
+extern "C" {
+
+int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int vocab, b200_stream_t stream) {
+  using namespace b200;
+  if (!logits || !out || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
+  sampling::argmax_kernel<<<rows, sampling::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(logits), ld, out, vocab);
+  return launch_status();
+}
+
+int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,
+                         float temperature, b200_stream_t stream) {
+  using namespace b200;
+  if (!logits || !probs || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
+  if (top_k < 1 || top_k > vocab || !(temperature > 0.f)) return B200_ERR_INVALID_ARGUMENT;
+  sampling::topk_probs_kernel<<<rows, sampling::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(logits), ld, probs, vocab, top_k, temperature);
+  return launch_status();
+}
+
+}  // extern "C"

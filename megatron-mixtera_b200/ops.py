@@ -1,0 +1,193 @@
+"""Tensor-level wrappers over the C ABI (``include/b200_decode.h``).
+
+Each function checks dtype / device / contiguity on the host, passes raw device pointers and
+the current CUDA stream to the library and raises `B200Error` on a non-zero return code.
+Nothing here computes on the CPU or through PyTorch kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import AttentionArgs, B200Error, check  # noqa: F401  (re-exported)
+
+BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise B200Error(name, -1, f"{name} must be a CUDA tensor (no CPU fallback exists)")
+    if t.dtype != dtype:
+        raise B200Error(name, -1, f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise B200Error(name, -1, f"{name} must be contiguous")
+
+
+class _Workspace:
+    """Grow-only device scratch per (device, tag).  The first 64 KiB hold the split-K tile
+    counters, which the kernels leave zeroed, so a fresh buffer is zero-filled."""
+
+    def __init__(self):
+        self._buf = {}
+
+    def get(self, device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
+        key = (device.index, tag)
+        buf = self._buf.get(key)
+        if buf is None or buf.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise B200Error("workspace", -3, "workspace would have to grow during CUDA graph capture; "
+                                "run one eager warm-up step of the same shapes first")
+            buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self._buf[key] = buf
+        return buf
+
+
+_workspace = _Workspace()
+
+
+def device_status(reset: bool = False) -> int:
+    """Status word set by kernels whose bounded waits gave up (0 = healthy).  Synchronises."""
+    out = ctypes.c_int(0)
+    check("b200_device_status", _lib.load().b200_device_status(int(reset), ctypes.byref(out)))
+    return out.value
+
+
+def gather_rows(table, ids, *, vocab_start: int = 0, vocab_end: Optional[int] = None, add_table=None, add_ids=None,
+                out=None):
+    """out[i] = table[ids[i] - vocab_start] (0 when outside the shard) (+ add_table[add_ids[i]])."""
+    _need(table, BF16, "table")
+    _need(ids, torch.int64, "ids")
+    n, width = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((n, width), dtype=BF16, device=table.device)
+    if add_table is not None:
+        _need(add_table, BF16, "add_table")
+        _need(add_ids, torch.int64, "add_ids")
+    hi = vocab_start + table.shape[0] if vocab_end is None else vocab_end
+    check("b200_gather_rows_bf16", _lib.load().b200_gather_rows_bf16(
+        table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, width, vocab_start, hi, _p(add_table), _p(add_ids),
+        _stream()))
+    return out
+
+
+def add_norm(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5, want_hidden: bool = False,
+             want_normed: bool = True) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """h = x (+bias) (+residual); returns (h or None, norm(h) * gamma (+beta) or None)."""
+    _need(x, BF16, "x")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    h = torch.empty_like(x) if want_hidden else None
+    y = torch.empty_like(x) if want_normed else None
+    check("b200_add_norm_bf16", _lib.load().b200_add_norm_bf16(
+        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps, _stream()))
+    return h, y
+
+
+def activation(x, kind: str, bias=None):
+    """kind 'swiglu': x [rows, 2F] -> [rows, F]; kind 'gelu': x [rows, F] (+bias) -> [rows, F]."""
+    _need(x, BF16, "x")
+    rows = x.numel() // x.shape[-1]
+    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.device)
+    check("b200_activation_bf16", _lib.load().b200_activation_bf16(
+        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, 0 if kind == "swiglu" else 1, _stream()))
+    return out
+
+
+def gemm(x, w, bias=None, out=None):
+    """y[M, N] = x[M, K] @ w[N, K].T (+ bias), bf16 with fp32 accumulation on tcgen05."""
+    _need(x, BF16, "x")
+    _need(w, BF16, "w")
+    K = x.shape[-1]
+    M = x.numel() // K
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise B200Error("gemm", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.shape)}")
+    if out is None:
+        out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.device)
+    lib = _lib.load()
+    nbytes = lib.b200_gemm_bf16_workspace_bytes(M, N, K)
+    ws = _workspace.get(x.device, "gemm", nbytes)
+    check("b200_gemm_bf16", lib.b200_gemm_bf16(x.data_ptr(), K, w.data_ptr(), _p(bias), out.data_ptr(), N, M, N, K,
+                                               ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
+def attention_workspace(device, num_tokens: int, num_q_heads: int, head_dim: int, num_splits: int):
+    nbytes = _lib.load().b200_paged_attention_workspace_bytes(num_tokens, num_q_heads, head_dim, num_splits)
+    return _workspace.get(device, "attn", nbytes) if nbytes else None
+
+
+def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, out, num_q_heads: int,
+                        num_kv_heads: int, head_dim: int, chunk_size: int, token_to_pos_ids=None,
+                        token_to_pos_in_request=None, token_to_chunk_idx=None, token_to_local_pos=None,
+                        row_of_token=None, rope_cos=None, rope_sin=None, num_splits: int = 1,
+                        fuse_rope_append: bool = False, softmax_scale: float = 0.0) -> AttentionArgs:
+    T = qkv.shape[0]
+    a = AttentionArgs()
+    a.qkv = qkv.data_ptr()
+    a.k_cache = k_cache.data_ptr()
+    a.v_cache = v_cache.data_ptr()
+    a.block_table = block_table.data_ptr()
+    a.kv_seq_lengths = kv_seq_lengths.data_ptr()
+    a.row_of_token = _p(row_of_token)
+    a.token_to_pos_ids = _p(token_to_pos_ids)
+    a.token_to_pos_in_request = _p(token_to_pos_in_request)
+    a.token_to_chunk_idx = _p(token_to_chunk_idx)
+    a.token_to_local_pos = _p(token_to_local_pos)
+    a.rope_cos = _p(rope_cos)
+    a.rope_sin = _p(rope_sin)
+    a.out = _p(out)
+    a.num_tokens = T
+    a.num_q_heads = num_q_heads
+    a.num_kv_heads = num_kv_heads
+    a.head_dim = head_dim
+    a.chunk_size = chunk_size
+    a.num_chunks = k_cache.shape[0]
+    a.max_chunks_per_row = block_table.shape[1]
+    a.num_splits = num_splits
+    a.fuse_rope_append = int(fuse_rope_append)
+    a.softmax_scale = softmax_scale
+    ws = attention_workspace(qkv.device, T, num_q_heads, head_dim, num_splits) if out is not None else None
+    a.workspace = _p(ws)
+    a.workspace_bytes = 0 if ws is None else ws.numel()
+    return a
+
+
+def rope_append(args: AttentionArgs) -> None:
+    check("b200_rope_append", _lib.load().b200_rope_append(ctypes.byref(args), _stream()))
+
+
+def paged_attention(args: AttentionArgs) -> None:
+    check("b200_paged_attention", _lib.load().b200_paged_attention(ctypes.byref(args), _stream()))
+
+
+def argmax(logits):
+    """Greedy token per row of bf16 logits [rows, vocab] -> int64 [rows]."""
+    _need(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    out = torch.empty((rows,), dtype=torch.int64, device=logits.device)
+    check("b200_argmax_bf16", _lib.load().b200_argmax_bf16(logits.data_ptr(), logits.stride(0), out.data_ptr(), rows,
+                                                            vocab, _stream()))
+    return out
+
+
+def topk_probs(logits, top_k: int, temperature: float = 1.0):
+    """fp32 probabilities after temperature and top-k filtering, [rows, vocab]."""
+    _need(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    probs = torch.empty((rows, vocab), dtype=torch.float32, device=logits.device)
+    check("b200_topk_probs_bf16", _lib.load().b200_topk_probs_bf16(
+        logits.data_ptr(), logits.stride(0), probs.data_ptr(), rows, vocab, top_k, float(temperature), _stream()))
+    return probs

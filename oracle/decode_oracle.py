@@ -491,8 +491,11 @@ def sample(logits: torch.Tensor, top_k: int = 1, top_p: float = 0.0, temperature
     return torch.multinomial(probs, num_samples=1, generator=generator).view(-1)
 
 
-def filtered_probabilities(logits, top_k: int, top_p: float, temperature: float) -> torch.Tensor:
-    """The probability vector handed to multinomial (exact support; used for top-k/top-p parity)."""
+def filtered_probabilities(logits, top_k: int, top_p: float, temperature: float, softmax_dtype=None) -> torch.Tensor:
+    """The probability vector handed to multinomial (exact support; used for top-k/top-p parity).
+
+    The reference takes the final softmax in the logits' dtype; ``softmax_dtype=torch.float32``
+    gives the same distribution before that last rounding."""
     x = logits.clone()
     if temperature != 1.0:
         x.div_(temperature)
@@ -507,7 +510,7 @@ def filtered_probabilities(logits, top_k: int, top_p: float, temperature: float)
         f[..., 0] = 0
         f = f.scatter(1, si, f)
         x.masked_fill_(f, float("-inf"))
-    return x.softmax(dim=-1)
+    return (x if softmax_dtype is None else x.to(softmax_dtype)).softmax(dim=-1)
 
 
 def decode_loop(model: GPTOracle, prompts, num_tokens_to_generate, arrival=None, termination_id=-1, on_step=None):

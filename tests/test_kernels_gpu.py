@@ -1,0 +1,316 @@
+"""Kernel-level parity: every C-ABI entry point against the CPU oracle on seeded inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import decode_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from megatron_mixtera_b200 import build, ops as _ops
+
+    build.build()
+    yield _ops
+    torch.cuda.synchronize()
+    assert _ops.device_status() == 0, "a kernel abandoned a bounded wait"
+
+
+def rel_l2(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def randn(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(BF16)
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize(
+    "M,N,K,bias",
+    [
+        (8, 256, 256, False),      # one tile, BT=32 with zero-filled token rows
+        (64, 1024, 512, True),     # split-K (8 tiles only)
+        (64, 1000, 576, False),    # ragged N tile, K not a multiple of the split
+        (33, 384, 1024, True),     # BT=64 with ragged M
+        (128, 512, 256, False),    # BT=128
+        (300, 640, 512, True),     # BT=256, two token blocks, ragged
+        (64, 6144, 4096, False),   # Llama-3-8B QKV projection at decode
+        (64, 4096, 14336, False),  # Llama-3-8B fc2 at decode (long K, deep split)
+        (16, 20000, 512, False),   # many tiles: no split
+    ],
+)
+def test_gemm_matches_fp32_matmul(ops, M, N, K, bias):
+    x = randn((M, K), 1)
+    w = randn((N, K), 2, 0.05)
+    b = randn((N,), 3) if bias else None
+    y = ops.gemm(x.cuda(), w.cuda(), None if b is None else b.cuda())
+    ref = x.float() @ w.float().t()
+    if b is not None:
+        ref = ref.to(BF16).float() + b.float()  # layers.py:333-335: bf16 matmul result, then bias add
+    assert y.shape == (M, N) and y.dtype == BF16
+    err = rel_l2(y, ref)
+    assert err < 3e-3, err
+    # run again: the split-K tile counters must have been left at zero
+    y2 = ops.gemm(x.cuda(), w.cuda(), None if b is None else b.cuda())
+    assert torch.equal(y, y2)
+
+
+def test_gemm_is_deterministic_and_linear(ops):
+    # size-independent properties at a full-size shape: repeatability and y(2x) = 2 y(x) exactly
+    x = randn((64, 4096), 5).cuda()
+    w = randn((4096, 4096), 6, 0.02).cuda()
+    y1 = ops.gemm(x, w)
+    y2 = ops.gemm(x * 2, w)
+    assert torch.equal(ops.gemm(x, w), y1)
+    assert torch.equal(y2.float(), y1.float() * 2)
+
+
+def test_gemm_rejects_bad_arguments(ops):
+    x = randn((8, 100), 1).cuda()  # K not a multiple of 8
+    w = randn((16, 100), 2).cuda()
+    with pytest.raises(ops.B200Error):
+        ops.gemm(x, w)
+    with pytest.raises(ops.B200Error):
+        ops.gemm(randn((8, 128), 1), randn((16, 128), 2))  # CPU tensors: no fallback
+
+
+# ------------------------------------------------------------------------------------------
+# Norm / activation / gather
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,hidden", [(5, 256), (64, 4096), (3, 8192), (7, 512)])
+def test_rmsnorm_with_residual(ops, rows, hidden):
+    x, r = randn((rows, hidden), 1), randn((rows, hidden), 2)
+    g = (1 + randn((hidden,), 3, 0.02).float()).to(BF16)
+    h, y = ops.add_norm(x.cuda(), g.cuda(), residual=r.cuda(), want_hidden=True)
+    h_ref = x + r
+    y_ref = F.rms_norm(h_ref, (hidden,), g, 1e-5)
+    assert torch.equal(h.cpu(), h_ref)
+    mism = (y.cpu() != y_ref).float().mean().item()
+    assert mism < 2e-3 and rel_l2(y, y_ref) < 1e-3, (mism, rel_l2(y, y_ref))
+    _, y0 = ops.add_norm(x.cuda(), g.cuda())
+    assert rel_l2(y0, F.rms_norm(x, (hidden,), g, 1e-5)) < 1e-3
+
+
+def test_layernorm_with_bias_and_residual(ops):
+    rows, hidden = 9, 256
+    x, r, b = randn((rows, hidden), 1), randn((rows, hidden), 2), randn((hidden,), 3, 0.1)
+    g, beta = (1 + randn((hidden,), 4, 0.02).float()).to(BF16), randn((hidden,), 5, 0.1)
+    h, y = ops.add_norm(x.cuda(), g.cuda(), bias=b.cuda(), residual=r.cuda(), beta=beta.cuda(), want_hidden=True)
+    h_ref = (x + b) + r
+    assert torch.equal(h.cpu(), h_ref)
+    assert rel_l2(y, F.layer_norm(h_ref, (hidden,), g, beta, 1e-5)) < 2e-3
+
+
+def test_swiglu_and_gelu(ops):
+    x = randn((17, 2 * 1024), 1, 2.0)
+    y = ops.activation(x.cuda(), "swiglu")
+    a, b = torch.chunk(x, 2, dim=-1)
+    ref = F.silu(a) * b
+    assert (y.cpu() != ref).float().mean().item() < 2e-3 and rel_l2(y, ref) < 1e-3
+    x = randn((17, 1024), 2, 2.0)
+    bias = randn((1024,), 3, 0.1)
+    y = ops.activation(x.cuda(), "gelu", bias.cuda())
+    assert rel_l2(y, F.gelu(x + bias)) < 2e-3
+
+
+def test_gather_rows(ops):
+    table = randn((100, 256), 1)
+    pos = randn((64, 256), 2)
+    ids = torch.tensor([0, 99, 5, 5, 42, 77], dtype=torch.int64)
+    pid = torch.tensor([0, 1, 2, 3, 63, 10], dtype=torch.int64)
+    assert torch.equal(ops.gather_rows(table.cuda(), ids.cuda()).cpu(), table[ids])
+    out = ops.gather_rows(table.cuda(), ids.cuda(), add_table=pos.cuda(), add_ids=pid.cuda())
+    assert torch.equal(out.cpu(), table[ids] + pos[pid])
+    # vocab shard [40, 80): ids outside give zero rows (layers.py:262-295)
+    out = ops.gather_rows(table[40:80].contiguous().cuda(), ids.cuda(), vocab_start=40, vocab_end=80)
+    ref = torch.zeros(6, 256, dtype=BF16)
+    ref[4], ref[5] = table[42], table[77]
+    assert torch.equal(out.cpu(), ref)
+
+
+# ------------------------------------------------------------------------------------------
+# Sampling
+# ------------------------------------------------------------------------------------------
+def test_argmax_ties_pick_first(ops):
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn((9, 128256), generator=g).to(BF16)
+    logits[0, 1000] = logits[0, 77000] = 50.0   # tie: the smaller index wins
+    logits[1, :] = 0.0                           # all equal
+    logits[2, -1] = 60.0                         # last element
+    got = ops.argmax(logits.cuda()).cpu()
+    assert got.tolist() == torch.argmax(logits.float(), dim=-1).tolist()
+    assert got[0] == 1000 and got[1] == 0 and got[2] == 128255
+    # strided rows (a slice of padded logits)
+    wide = torch.randn((4, 1100), generator=g).to(BF16).cuda()
+    assert ops.argmax(wide[:, :1000].contiguous()).tolist() == torch.argmax(wide[:, :1000].float(), -1).tolist()
+
+
+@pytest.mark.parametrize("top_k,temperature", [(2, 1.0), (40, 0.7), (1000, 1.3)])
+def test_topk_probabilities(ops, top_k, temperature):
+    g = torch.Generator().manual_seed(1)
+    logits = (torch.randn((5, 32000), generator=g) * 3).to(BF16)
+    probs = ops.topk_probs(logits.cuda(), top_k, temperature).cpu()
+    ref = O.filtered_probabilities(logits, top_k, 0.0, temperature, softmax_dtype=torch.float32)
+    assert torch.equal(probs > 0, ref > 0)  # exact support
+    assert int((ref > 0).sum(-1).min()) >= top_k
+    assert float((probs - ref).abs().max()) < 1e-5
+    # and within bf16 rounding of what the reference hands to multinomial
+    assert float((probs - O.filtered_probabilities(logits, top_k, 0.0, temperature).float()).abs().max()) < 2.5e-3
+    assert torch.allclose(probs.sum(-1), torch.ones(5), atol=1e-4)
+
+
+# ------------------------------------------------------------------------------------------
+# Paged attention
+# ------------------------------------------------------------------------------------------
+def make_paged_case(*, T, nkv, G, D, chunk, kv_lens, seed, rope=True, max_pos=None):
+    """Random pool + block tables with shuffled chunk ids; the last token of every row is 'new'."""
+    g = torch.Generator().manual_seed(seed)
+    nq = nkv * G
+    max_chunks = max(1, max(math.ceil(k / chunk) for k in kv_lens)) + 1
+    n_chunks = sum(math.ceil(k / chunk) for k in kv_lens) + 3
+    perm = torch.randperm(n_chunks - 1, generator=g).tolist()  # last chunk = dummy
+    k_cache = (torch.randn((n_chunks, chunk, nkv, D), generator=g)).to(BF16)
+    v_cache = (torch.randn((n_chunks, chunk, nkv, D), generator=g)).to(BF16)
+    block_table = torch.zeros((T, max_chunks), dtype=torch.int32)
+    chunk_idx = torch.full((T,), n_chunks - 1, dtype=torch.int64)
+    local = torch.zeros((T,), dtype=torch.int64)
+    pos = torch.zeros((T,), dtype=torch.int64)
+    it = iter(perm)
+    for r, kl in enumerate(kv_lens):
+        nb = math.ceil(kl / chunk)
+        ids = [next(it) for _ in range(nb)]
+        block_table[r, :nb] = torch.tensor(ids, dtype=torch.int32)
+        if kl > 0:
+            chunk_idx[r] = ids[(kl - 1) // chunk]
+            local[r] = (kl - 1) % chunk
+            pos[r] = kl - 1
+    qkv = torch.randn((T, nkv, (G + 2) * D), generator=g).to(BF16)
+    max_pos = max_pos or (max(kv_lens) + 1)
+    freqs = O.rope_freqs(max_pos, D, 500000.0) if rope else None
+    return dict(T=T, nkv=nkv, G=G, D=D, nq=nq, chunk=chunk, kv_lens=torch.tensor(kv_lens, dtype=torch.int32),
+                k_cache=k_cache, v_cache=v_cache, block_table=block_table, chunk_idx=chunk_idx, local=local, pos=pos,
+                qkv=qkv, freqs=freqs)
+
+
+def oracle_decode_attention(c):
+    """dynamic_context.py:511-631 + attention.py:588-600 restated: rope, append, paged attention."""
+    T, nkv, G, D = c["T"], c["nkv"], c["G"], c["D"]
+    qkv = c["qkv"]
+    q = qkv[..., : G * D].reshape(T, nkv * G, D)
+    k = qkv[..., G * D : (G + 1) * D]
+    v = qkv[..., (G + 1) * D :]
+    if c["freqs"] is not None:
+        k = O.apply_rope(k, c["freqs"][c["pos"]])
+        q = O.apply_rope(q, c["freqs"][c["pos"]])
+    kc, vc = c["k_cache"].clone(), c["v_cache"].clone()
+    kc[c["chunk_idx"], c["local"]] = k
+    vc[c["chunk_idx"], c["local"]] = v
+    out = O.paged_attention(q, kc, vc, c["kv_lens"], c["block_table"].numpy())
+    return out, kc, vc
+
+
+def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None):
+    dev = "cuda"
+    D = c["D"]
+    cos = sin = None
+    if c["freqs"] is not None:
+        half = c["freqs"][:, : D // 2]
+        cos, sin = torch.cos(half).to(BF16).to(dev), torch.sin(half).to(BF16).to(dev)
+    kc, vc = c["k_cache"].clone().to(dev), c["v_cache"].clone().to(dev)
+    out = torch.full((c["T"], c["nq"] * D), float("nan"), dtype=BF16, device=dev)
+    # the argument struct holds raw pointers only: keep every device tensor alive in `d`
+    d = {k: c[k].to(dev) for k in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
+    d["row"] = None if row_of_token is None else row_of_token.to(dev)
+    args = ops.make_attention_args(
+        qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
+        num_q_heads=c["nq"], num_kv_heads=c["nkv"], head_dim=D, chunk_size=c["chunk"], token_to_pos_ids=d["pos"],
+        token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
+        rope_cos=cos, rope_sin=sin, num_splits=num_splits, fuse_rope_append=fused, row_of_token=d["row"])
+    if not fused:
+        ops.rope_append(args)
+    ops.paged_attention(args)
+    torch.cuda.synchronize()
+    return out.cpu().view(c["T"], c["nq"], D), kc.cpu(), vc.cpu()
+
+
+@pytest.mark.parametrize(
+    "nkv,G,D,chunk,kv_lens,splits",
+    [
+        (2, 4, 128, 64, [1, 64, 65, 130, 0, 300, 17, 256], 1),
+        (2, 4, 128, 64, [1, 64, 65, 130, 0, 300, 17, 256], 4),
+        (1, 8, 128, 256, [1000, 257, 512, 3], 3),
+        (8, 4, 128, 256, [2304, 128, 700, 1216, 0, 0], 4),     # Llama-3-8B head geometry
+        (4, 1, 64, 64, [33, 200, 64], 2),                       # MHA, head dim 64
+        (2, 2, 64, 128, [129, 5], 1),
+    ],
+)
+@pytest.mark.parametrize("fused", [True, False])
+def test_paged_decode_attention(ops, nkv, G, D, chunk, kv_lens, splits, fused):
+    c = make_paged_case(T=len(kv_lens), nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=kv_lens, seed=11)
+    ref, kc_ref, vc_ref = oracle_decode_attention(c)
+    out, kc, vc = run_cuda_attention(ops, c, num_splits=splits, fused=fused)
+    # KV-slot indexing and contents: bit-exact (bf16 RoPE rounding points reproduced)
+    live = [r for r, kl in enumerate(kv_lens) if kl > 0]
+    for r in live:
+        ci, lp = int(c["chunk_idx"][r]), int(c["local"][r])
+        assert torch.equal(kc[ci, lp], kc_ref[ci, lp]), r
+        assert torch.equal(vc[ci, lp], vc_ref[ci, lp]), r
+    if fused:
+        # nothing but the new slots was written
+        mask = torch.ones(kc.shape[:2], dtype=torch.bool)
+        mask[c["chunk_idx"][live], c["local"][live]] = False
+        assert torch.equal(kc[mask], c["k_cache"][mask]) and torch.equal(vc[mask], c["v_cache"][mask])
+    assert not torch.isnan(out.float()).any()
+    for r, kl in enumerate(kv_lens):
+        if kl == 0:
+            assert torch.all(out[r] == 0)
+    err = rel_l2(out, ref)
+    assert err < 5e-3, err
+
+
+def test_paged_attention_prefill_rows_via_row_of_token(ops):
+    # One request of 70 prompt tokens processed as 70 rows sharing block-table row 1: row t sees t+1 keys.
+    nkv, G, D, chunk, n = 2, 4, 128, 64, 70
+    c = make_paged_case(T=n, nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=[n] * n, seed=3, max_pos=128)
+    ids = c["block_table"][0].clone()
+    c["block_table"] = torch.stack([torch.zeros_like(ids), ids])
+    pos = torch.arange(n, dtype=torch.int64)
+    c["pos"], c["local"] = pos, pos % chunk
+    c["chunk_idx"] = ids[(pos // chunk)].long()
+    c["kv_lens"] = (pos + 1).int()
+    row_of_token = torch.ones(n, dtype=torch.int32)
+    out, kc, vc = run_cuda_attention(ops, c, num_splits=2, fused=False, row_of_token=row_of_token)
+    # oracle: same thing expressed as one varlen request (cu_q = [0, n]) over block-table row 1
+    T = n
+    qkv = c["qkv"]
+    q = O.apply_rope(qkv[..., : G * D].reshape(T, nkv * G, D), c["freqs"][pos])
+    k = O.apply_rope(qkv[..., G * D : (G + 1) * D], c["freqs"][pos])
+    kc_ref, vc_ref = c["k_cache"].clone(), c["v_cache"].clone()
+    kc_ref[c["chunk_idx"], c["local"]] = k
+    vc_ref[c["chunk_idx"], c["local"]] = qkv[..., (G + 1) * D :]
+    ref = O.paged_attention(q, kc_ref, vc_ref, torch.tensor([n]), c["block_table"][1:2].numpy(),
+                            cu_q=torch.tensor([0, n]))
+    assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    assert rel_l2(out, ref) < 5e-3
+
+
+def test_attention_split_invariance_at_long_context(ops):
+    # size-independent property at a long context: the result does not depend on the split count
+    kv_lens = [32768 + 77, 9000]
+    c = make_paged_case(T=2, nkv=1, G=4, D=128, chunk=256, kv_lens=kv_lens, seed=5)
+    o1, _, _ = run_cuda_attention(ops, c, num_splits=1, fused=True)
+    o16, _, _ = run_cuda_attention(ops, c, num_splits=16, fused=True)
+    assert rel_l2(o16, o1) < 2e-3
+    ref, _, _ = oracle_decode_attention(c)
+    assert rel_l2(o16, ref) < 5e-3
