@@ -188,16 +188,74 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __syncthreads();
     if (*last_flag) {
       __threadfence();
-      const int nn = n0 + tid;  // coalesced: consecutive threads, consecutive features
-      if (nn < p.N) {
-        const float b = p.bias != nullptr ? __bfloat162float(p.bias[nn]) : 0.f;
-        const int m_end = min(p.M, m0 + BT);
-        for (int m = m0; m < m_end; ++m) {
-          float acc = 0.f;
-          for (int s = 0; s < p.num_splits; ++s)
-            acc += __ldcg(&p.partials[(static_cast<int64_t>(s) * p.M + m) * p.N + nn]);
-          if (p.bias != nullptr) acc = bf16_round(acc) + b;
-          p.y[static_cast<int64_t>(m) * p.ldy + nn] = __float2bfloat16_rn(acc);
+      // Sum the splits in order.  Lanes cover 4 consecutive features each (16-byte loads), the four
+      // warps take different token rows, and four rows are in flight per thread so that the L2
+      // latency of the S x rows loads is overlapped instead of serialised.
+      const int m_end = min(p.M, m0 + BT);
+      if ((p.N & 3) == 0) {
+        const int nn = n0 + lane * 4;
+        if (nn < p.N) {
+          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.bias != nullptr)
+            bv = make_float4(__bfloat162float(p.bias[nn]), __bfloat162float(p.bias[nn + 1]),
+                             __bfloat162float(p.bias[nn + 2]), __bfloat162float(p.bias[nn + 3]));
+          const int64_t split_stride = static_cast<int64_t>(p.M) * p.N;
+          for (int mb = m0 + warp; mb < m_end; mb += 16) {
+            float4 acc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < p.num_splits; ++s) {
+              const float* base = p.partials + s * split_stride + nn;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int m = mb + j * 4;
+                if (m < m_end) {
+                  const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(m) * p.N));
+                  acc[j].x += v.x;
+                  acc[j].y += v.y;
+                  acc[j].z += v.z;
+                  acc[j].w += v.w;
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int m = mb + j * 4;
+              if (m < m_end) {
+                float4 a = acc[j];
+                if (p.bias != nullptr) {
+                  a.x = bf16_round(a.x) + bv.x;
+                  a.y = bf16_round(a.y) + bv.y;
+                  a.z = bf16_round(a.z) + bv.z;
+                  a.w = bf16_round(a.w) + bv.w;
+                }
+                __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + nn;
+                if ((p.ldy & 3) == 0) {
+                  uint2 o;
+                  o.x = pack_bf16x2(a.x, a.y);
+                  o.y = pack_bf16x2(a.z, a.w);
+                  *reinterpret_cast<uint2*>(dst) = o;
+                } else {
+                  dst[0] = __float2bfloat16_rn(a.x);
+                  dst[1] = __float2bfloat16_rn(a.y);
+                  dst[2] = __float2bfloat16_rn(a.z);
+                  dst[3] = __float2bfloat16_rn(a.w);
+                }
+              }
+            }
+          }
+        }
+      } else {
+        const int nn = n0 + tid;  // coalesced: consecutive threads, consecutive features
+        if (nn < p.N) {
+          const float b = p.bias != nullptr ? __bfloat162float(p.bias[nn]) : 0.f;
+          for (int m = m0; m < m_end; ++m) {
+            float acc = 0.f;
+            for (int s = 0; s < p.num_splits; ++s)
+              acc += __ldcg(&p.partials[(static_cast<int64_t>(s) * p.M + m) * p.N + nn]);
+            if (p.bias != nullptr) acc = bf16_round(acc) + b;
+            p.y[static_cast<int64_t>(m) * p.ldy + nn] = __float2bfloat16_rn(acc);
+          }
         }
       }
       if (tid == 0) *counter = 0;  // leave the counters zero for the next launch

@@ -1,0 +1,124 @@
+"""Tensor-parallel linear layers and embedding backed by the sm_100a kernels.
+
+Constructor arguments, parameter names / shapes (``weight [out/tp, in]`` or ``[out, in/tp]``, ``bias``)
+and the ``forward(x) -> (output, bias_or_None)`` contract follow the reference's
+``ColumnParallelLinear`` / ``RowParallelLinear`` / ``VocabParallelEmbedding``
+(``megatron/core/tensor_parallel/layers.py:158-295, 743-1057, 1060-1303``), so a state dict of one loads
+into the other.  Only the inference forward exists: there is no autograd path.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops, parallel_state
+from .mappings import gather_from_tensor_model_parallel_region, reduce_from_tensor_model_parallel_region
+
+
+def _device():
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
+class _ParallelLinearBase(torch.nn.Module):
+    def get_extra_state(self):
+        return None
+
+    def set_extra_state(self, state):
+        pass
+
+
+class ColumnParallelLinear(_ParallelLinearBase):
+    """Y = X A^T + b with A split along its output rows: rank r holds rows [r*out/tp, (r+1)*out/tp)."""
+
+    def __init__(self, input_size, output_size, *, config, init_method=None, bias=True, gather_output=False,
+                 skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None,
+                 skip_weight_param_allocation=False, stride=1, **_):
+        super().__init__()
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        assert output_size % tp == 0, f"output_size {output_size} not divisible by tp {tp}"
+        self.input_size, self.output_size = input_size, output_size
+        self.output_size_per_partition = output_size // tp
+        self.gather_output, self.skip_bias_add, self.tp_group = gather_output, skip_bias_add, tp_group
+        self.config = config
+        dt, dev = config.params_dtype, _device()
+        self.weight = None
+        if not skip_weight_param_allocation:
+            self.weight = torch.nn.Parameter(torch.empty(self.output_size_per_partition, input_size, dtype=dt, device=dev),
+                                             requires_grad=False)
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=dt, device=dev), requires_grad=False)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, input_, weight: Optional[torch.Tensor] = None, runtime_gather_output: Optional[bool] = None):
+        """``input_`` [..., in] -> ([..., out/tp] or gathered [..., out], bias if ``skip_bias_add``)."""
+        w = self.weight if weight is None else weight
+        fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add) else None
+        out = ops.gemm(input_, w, fuse_bias)
+        gather = self.gather_output if runtime_gather_output is None else runtime_gather_output
+        if gather:
+            out = gather_from_tensor_model_parallel_region(out, self.tp_group)
+        return out, (self.bias if self.skip_bias_add else None)
+
+
+class RowParallelLinear(_ParallelLinearBase):
+    """Y = X A^T + b with A split along its input columns; partial products are all-reduced."""
+
+    def __init__(self, input_size, output_size, *, config, init_method=None, bias=True, input_is_parallel=True,
+                 skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None, **_):
+        super().__init__()
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        assert input_size % tp == 0, f"input_size {input_size} not divisible by tp {tp}"
+        assert input_is_parallel, "the decode path always feeds the row-parallel layer its own shard"
+        self.input_size, self.output_size = input_size, output_size
+        self.input_size_per_partition = input_size // tp
+        self.skip_bias_add, self.tp_group, self.config = skip_bias_add, tp_group, config
+        dt, dev = config.params_dtype, _device()
+        self.weight = torch.nn.Parameter(torch.empty(output_size, self.input_size_per_partition, dtype=dt, device=dev),
+                                         requires_grad=False)
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(output_size, dtype=dt, device=dev), requires_grad=False)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, input_):
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        # The bias must be added once, after the reduction: fuse it into the GEMM only at TP=1.
+        fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add and tp == 1) else None
+        out = ops.gemm(input_, self.weight, fuse_bias)
+        if tp > 1:
+            out = reduce_from_tensor_model_parallel_region(out, self.tp_group)
+            if self.bias is not None and not self.skip_bias_add:
+                out, _ = ops.add_norm(out, None, bias=self.bias, want_hidden=True, want_normed=False)
+        return out, (self.bias if self.skip_bias_add else None)
+
+
+class VocabParallelEmbedding(torch.nn.Module):
+    """Embedding split along the vocabulary: masked local lookup, then all-reduce
+    (reference ``layers.py:158-295``)."""
+
+    def __init__(self, num_embeddings, embedding_dim, *, config, init_method=None, tp_group=None, **_):
+        super().__init__()
+        tp, rank = parallel_state.get_tensor_model_parallel_world_size(), parallel_state.get_tensor_model_parallel_rank()
+        assert num_embeddings % tp == 0
+        per = num_embeddings // tp
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.vocab_start_index, self.vocab_end_index = rank * per, (rank + 1) * per
+        self.tp_group = tp_group
+        self.weight = torch.nn.Parameter(torch.empty(per, embedding_dim, dtype=config.params_dtype, device=_device()),
+                                         requires_grad=False)
+
+    def forward(self, input_ids, add_table=None, add_ids=None):
+        """``input_ids`` int64 [..]; returns [n, H].  ``add_table[add_ids]`` (position embedding) is
+        added in the same kernel at TP=1 and after the reduction otherwise."""
+        ids = input_ids.reshape(-1)
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        if tp == 1:
+            return ops.gather_rows(self.weight, ids, add_table=add_table, add_ids=add_ids)
+        out = ops.gather_rows(self.weight, ids, vocab_start=self.vocab_start_index, vocab_end=self.vocab_end_index)
+        out = reduce_from_tensor_model_parallel_region(out, self.tp_group)
+        if add_table is not None:
+            pos = ops.gather_rows(add_table, add_ids.reshape(-1))
+            out, _ = ops.add_norm(out, None, residual=pos, want_hidden=True, want_normed=False)
+        return out

@@ -1,0 +1,48 @@
+"""Configuration of the decoder stack: the fields of the reference's ``TransformerConfig``
+(``megatron/core/transformer/transformer_config.py``) that the dynamic decode path reads."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class TransformerConfig:
+    num_layers: int
+    hidden_size: int
+    num_attention_heads: int
+    num_query_groups: Optional[int] = None      # None: multi-head attention
+    kv_channels: Optional[int] = None           # None: hidden_size // num_attention_heads
+    ffn_hidden_size: Optional[int] = None       # None: 4 * hidden_size
+    normalization: str = "LayerNorm"            # "LayerNorm" | "RMSNorm"
+    layernorm_epsilon: float = 1e-5
+    gated_linear_unit: bool = False             # True + activation "silu" = SwiGLU
+    activation: str = "gelu"                    # "gelu" | "silu"
+    add_bias_linear: bool = True
+    params_dtype: torch.dtype = torch.bfloat16
+    tensor_model_parallel_size: int = 1
+    enable_cuda_graph: bool = False
+    inference_sampling_seed: int = 42
+    init_method_std: float = 0.02
+    fp8: Optional[str] = None                   # None | "mxfp8" | "blockwise"
+
+    def __post_init__(self):
+        if self.num_query_groups is None:
+            self.num_query_groups = self.num_attention_heads
+        if self.kv_channels is None:
+            self.kv_channels = self.hidden_size // self.num_attention_heads
+        if self.ffn_hidden_size is None:
+            self.ffn_hidden_size = 4 * self.hidden_size
+        if self.params_dtype != torch.bfloat16:
+            raise ValueError("the sm_100a decode kernels compute in bf16 (fp32 accumulation); params_dtype must be bfloat16")
+        tp = self.tensor_model_parallel_size
+        if self.num_attention_heads % tp or self.num_query_groups % tp:
+            raise ValueError("attention heads and query groups must be divisible by the tensor parallel size")
+        if self.num_attention_heads % self.num_query_groups:
+            raise ValueError("num_attention_heads must be a multiple of num_query_groups")
+        if self.gated_linear_unit and self.activation != "silu":
+            raise NotImplementedError("gated MLPs are supported as SwiGLU only")
+        if not self.gated_linear_unit and self.activation != "gelu":
+            raise NotImplementedError("ungated MLPs are supported with GELU only")

@@ -1,0 +1,324 @@
+"""Host bookkeeping of the shipped DynamicInferenceContext against the reference's own fixtures
+(bit-exact block tables, KV slots, chunk stack) and the reference's unit-test goldens."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from megatron_mixtera_b200.inference.contexts.dynamic_context import (
+    ChunkOverflowError,
+    ContextOverflowError,
+    DynamicInferenceContext,
+    MaxSequenceLengthOverflowError,
+    RequestOverflowError,
+    TokenOverflowError,
+)
+
+
+def set_rounder(v):
+    DynamicInferenceContext.TOKEN_ROUNDER = v
+    DynamicInferenceContext.REQUEST_ROUNDER = v
+
+
+@pytest.fixture(autouse=True)
+def _restore_rounders():
+    yield
+    DynamicInferenceContext.TOKEN_ROUNDER = 64
+    DynamicInferenceContext.REQUEST_ROUNDER = 4
+
+
+def make_ctx(**kw):
+    base = dict(params_dtype=torch.float32, num_layers=4, kv_channels=8, num_attention_heads=2,
+                max_sequence_length=512, buffer_size_gb=0.03, buffer_guaranteed_fraction=0.1, chunk_size_tokens=128,
+                tensor_model_parallel_size=1, device="cpu", allocate_memory_buffer=False)
+    base.update(kw)
+    return DynamicInferenceContext(**base)
+
+
+def snapshot(c):
+    a, pa, t = c.active_token_count, c.padded_active_token_count, c.total_request_count
+    d = {
+        "counts": np.array([t, c.paused_request_count, a, pa, c.padded_active_request_count, int(c.is_decode_only()),
+                            c.chunk_allocator.chunk_count_avail]),
+        "input_ids": c.token_to_input_ids[:a], "pos_ids": c.token_to_pos_ids[:a],
+        "request_idx": c.token_to_request_idx[:a], "chunk_idx": c.token_to_chunk_idx[:pa],
+        "local_pos": c.token_to_local_position_within_kv_chunk[:pa],
+        "pos_in_request": c.token_to_position_in_request[:pa],
+        "kv_seq_lengths": c.kv_seq_lengths, "block_table": c.block_table,
+    }
+    for k in ("request_ids", "request_query_lengths", "request_output_lengths", "request_kv_length_offsets",
+              "request_kv_chunk_counts", "request_last_kv_chunk_id", "request_last_kv_chunk_offset",
+              "request_to_kv_chunk_ids"):
+        d[k] = getattr(c, k)[:t]
+    return {k: np.asarray(torch.as_tensor(v).cpu()) for k, v in d.items()}
+
+
+def check_snapshot(z, step, c):
+    for k, v in snapshot(c).items():
+        ref = z[f"s{step}_{k}"]
+        assert np.array_equal(v.astype(np.int64), ref.astype(np.int64)), (step, k, v, ref)
+    avail = c.chunk_allocator.chunk_count_avail
+    assert np.array_equal(c.chunk_allocator.chunk_bag.numpy()[:avail], z[f"s{step}_chunk_bag"][:avail]), step
+    if not c.is_decode_only():
+        assert np.array_equal(c.cu_query_seq_lengths.cpu().numpy(), z[f"s{step}_cu_query_seq_lengths"])
+        assert np.array_equal(c.cu_kv_seq_lengths.cpu().numpy(), z[f"s{step}_cu_kv_seq_lengths"])
+        # the per-token view used by the token-as-row prefill attention
+        a = c.active_token_count
+        rows = c.token_to_block_table_row[:a].numpy()
+        assert np.array_equal(rows, z[f"s{step}_request_idx"] - c.paused_request_count)
+        assert np.array_equal(c.token_kv_lengths[:a].numpy(), z[f"s{step}_pos_in_request"][:a] + 1)
+    assert [c.max_seqlen_q, c.max_seqlen_k] == z[f"s{step}_max_seqlen"].tolist()
+
+
+@pytest.mark.parametrize("name", ["ctx_scenario_a", "ctx_scenario_b"])
+def test_context_matches_reference_scenario(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    meta = json.loads(str(z["meta"]))
+    cfg = meta["cfg"]
+    set_rounder(meta["rounder"])
+    c = DynamicInferenceContext(params_dtype=torch.float32, device="cpu", allocate_memory_buffer=False, **cfg)
+    assert [c.max_requests, c.max_tokens, c.chunk_allocator.chunk_count_total, c.gtd_chunk_count, c.gtd_request_count,
+            c.max_kv_chunk_count, c.chunk_size_bytes] == z["init"].tolist()
+    rng = np.random.RandomState(meta["seed"])
+    events = iter(meta["events"])
+    total_steps = max(e[1] for e in meta["events"]) + 1
+    names = {"ok": None, "RequestOverflowError": RequestOverflowError, "ChunkOverflowError": ChunkOverflowError,
+             "TokenOverflowError": TokenOverflowError}
+    next_id = 0
+    for step in range(total_steps):
+        n_add = int(rng.randint(0, 4)) if step < total_steps * 2 // 3 else 0
+        for _ in range(n_add):
+            plen = int(rng.randint(1, cfg["max_sequence_length"] // 2))
+            ngen = int(rng.randint(1, cfg["max_sequence_length"] - plen))
+            toks = torch.from_numpy(rng.randint(0, 1000, size=plen).astype(np.int64))
+            ev = next(events)
+            assert ev[:5] == ["add", step, next_id, plen, ngen]
+            try:
+                c.add_request(next_id, toks, ngen)
+                assert ev[5] == "ok", ev
+            except ContextOverflowError as e:
+                assert type(e) is names[ev[5]], (ev, e)
+                assert e.is_transient
+            next_id += 1
+        ev = next(events)
+        if c.active_token_count == 0:
+            assert ev[0] == "idle"
+            continue
+        c.initialize_attention_state()
+        check_snapshot(z, step, c)
+        n_active = c.total_request_count - c.paused_request_count
+        new_tokens = rng.randint(0, 1000, size=n_active).astype(np.int64)
+        _ = rng.rand(n_active)
+        newly = c.update_requests(torch.from_numpy(z[f"s{step}_mask"]), torch.from_numpy(new_tokens))
+        got = np.zeros(0, np.int64) if newly is None else newly.numpy().astype(np.int64)
+        assert np.array_equal(got, z[f"s{step}_newly_paused"]), step
+
+
+def test_initialize_dynamic_context():
+    # reference tests/unit_tests/inference/contexts/test_dynamic_context.py:66-90
+    set_rounder(64)
+    c = make_ctx()
+    assert c.gtd_chunk_count == 48
+    assert c.gtd_request_count == 12
+    assert c.chunk_allocator.chunk_count_total == 491
+    assert c.max_requests == 128
+    assert c.max_tokens == 62848
+    assert torch.all(c.request_ids == -1)
+    assert not c.is_static_batching()
+
+
+def test_is_memory_available():
+    # :108-133
+    c = make_ctx(num_layers=2, kv_channels=64, num_attention_heads=8, buffer_size_gb=1.0)
+    c.chunk_allocator.chunk_count_avail = 10
+    assert c.chunk_allocator.is_memory_available(10)
+    assert not c.chunk_allocator.is_memory_available(11)
+    assert c.chunk_allocator.is_memory_available(1)
+    c.chunk_allocator.chunk_count_avail = 0
+    assert not c.chunk_allocator.is_memory_available(1)
+    c.chunk_allocator.chunk_count_avail = 10
+    c.chunk_allocator.gtd_chunk_count = 5
+    assert c.chunk_allocator.is_memory_available(6)
+    assert not c.chunk_allocator.is_memory_available(6, safe=True)
+
+
+def test_request_overflow():
+    # :136-153
+    set_rounder(1)
+    c = make_ctx(num_layers=2, kv_channels=64, num_attention_heads=8, max_sequence_length=128, buffer_size_gb=0.01,
+                 chunk_size_tokens=32)
+    with pytest.raises(RequestOverflowError):
+        for i in range(c.max_requests + 1):
+            c.add_request(i, torch.zeros(10, dtype=torch.int64))
+
+
+def test_token_overflow_error():
+    # :156-178
+    set_rounder(1)
+    c = make_ctx(num_layers=2, kv_channels=64, num_attention_heads=8, buffer_size_gb=0.1, buffer_overflow_factor=1.0,
+                 max_requests_override=2, max_tokens_override=20)
+    with pytest.raises(TokenOverflowError):
+        c.add_request(1, torch.arange(0, 25))
+
+
+def test_max_sequence_length_overflow_is_permanent_and_leaks_nothing():
+    c = make_ctx()
+    avail = c.chunk_allocator.chunk_count_avail
+    with pytest.raises(MaxSequenceLengthOverflowError) as e:
+        c.add_request(0, torch.arange(0, 500), 100)
+    assert not e.value.is_transient
+    assert c.chunk_allocator.chunk_count_avail == avail
+
+
+def test_reset():
+    # :181-243
+    c = make_ctx(num_layers=2, kv_channels=64, num_attention_heads=8, max_sequence_length=128, buffer_size_gb=1.0)
+    c.add_request(0, torch.arange(0, 100), 10)
+    c.initialize_attention_state()
+    c.total_request_count = 10
+    c.active_token_count = 10
+    c.paused_request_count = 5
+    c.paused_tokens = torch.tensor([1, 2, 3])
+    for t in (c.request_ids, c.request_query_lengths, c.request_kv_length_offsets, c.request_kv_chunk_counts,
+              c.request_last_kv_chunk_id, c.request_last_kv_chunk_offset, c.request_to_kv_chunk_ids):
+        t.fill_(1)
+    c.chunk_allocator.chunk_count_avail = 5
+    c.reset()
+    assert c.total_request_count == 0 and c.active_token_count == 0 and c.paused_request_count == 0
+    assert c.padded_active_token_count == 0 and c.padded_active_request_count == 0
+    assert c.paused_tokens is None
+    assert torch.all(c.request_ids == -1)
+    assert torch.all(c.request_query_lengths == 0)
+    assert torch.all(c.request_kv_length_offsets == 0)
+    assert torch.all(c.request_kv_chunk_counts == 0)
+    assert torch.all(c.request_last_kv_chunk_id == -1)
+    assert torch.all(c.request_last_kv_chunk_offset == 0)
+    assert torch.all(c.token_to_input_ids == 0) and torch.all(c.token_to_pos_ids == 0)
+    assert torch.all(c.token_to_request_idx == -1) and torch.all(c.token_to_chunk_idx == -1)
+    assert torch.all(c.token_to_position_in_request == 0)
+    assert torch.all(c.token_to_local_position_within_kv_chunk == 0)
+    assert c.chunk_allocator.chunk_count_avail == c.chunk_allocator.chunk_count_total - 1
+    assert torch.all(c.request_to_kv_chunk_ids == -1)
+
+
+def test_allocate_and_release_memory_chunks():
+    # :246-279
+    set_rounder(64)
+    c = make_ctx()
+    assert c.chunk_allocator.allocate_memory_chunks(4).tolist() == [486, 487, 488, 489]
+    assert c.chunk_allocator.chunk_count_avail == 486
+    c.chunk_allocator.release_memory_chunks(torch.tensor([488, 489]))
+    assert c.chunk_allocator.chunk_count_avail == 488
+    assert c.chunk_allocator.allocate_memory_chunks(1).item() == 489
+    assert c.chunk_allocator.chunk_count_avail == 487
+    assert c.chunk_allocator.allocate_memory_chunks(c.chunk_allocator.chunk_count_avail + 100) is None
+
+
+def test_add_request():
+    # :282-345
+    set_rounder(64)
+    c = make_ctx()
+    n = 144
+    c.add_request(request_id=0, tokens=torch.arange(0, n, dtype=torch.long))
+    assert c.total_request_count == 1 and c.active_token_count == n
+    assert c.request_ids[0] == 0 and torch.all(c.request_ids[1:] == -1)
+    assert c.request_query_lengths[0] == n and c.request_kv_length_offsets[0] == 0
+    assert c.request_to_kv_chunk_ids[0].tolist() == [488, 489, -1, -1]
+    assert c.request_kv_chunk_counts[0] == 2 and c.request_last_kv_chunk_id[0] == 489
+    assert c.request_last_kv_chunk_offset[0].item() == 15
+    ar = torch.arange(0, n, dtype=torch.long)
+    assert torch.all(c.token_to_pos_ids[:n] == ar) and torch.all(c.token_to_input_ids[:n] == ar)
+    assert torch.all(c.token_to_position_in_request[:n] == ar)
+    assert torch.all(c.token_to_chunk_idx[:128] == 488) and torch.all(c.token_to_chunk_idx[128:n] == 489)
+    assert torch.all(c.token_to_local_position_within_kv_chunk[:n] == ar % 128)
+
+
+def test_update_request():
+    # :348-515
+    set_rounder(64)
+    c = make_ctx()
+    c.paused_request_count = 0
+    c.total_request_count = 3
+    c.request_kv_chunk_counts[0:3] = 1
+    c.request_to_kv_chunk_ids[0:3, 0] = c.chunk_allocator.allocate_memory_chunks(3, safe=True)
+    c.update_requests(active_requests_mask=torch.Tensor([0, 0, 0]), new_tokens=torch.tensor([0, 1, 2]))
+    assert c.total_request_count == 0
+
+    c = make_ctx()
+    mask = torch.Tensor([1, 0, 1, 1, 1, 0, 0, 1]).int()
+    next_tokens = torch.arange(2, 10).int()
+    c.paused_request_count = 2
+    c.paused_tokens = torch.Tensor([0, 1]).int()
+    c.total_request_count = 5
+    with pytest.raises(AssertionError):
+        c.update_requests(active_requests_mask=mask, new_tokens=next_tokens)
+    n = 10
+    c.chunk_allocator.chunk_count_avail -= 11
+    c.total_request_count = n
+    avail = c.chunk_allocator.chunk_count_avail
+    c.request_to_kv_chunk_ids[0:n, 0] = torch.arange(avail, avail + 10, dtype=torch.int32)
+    c.request_to_kv_chunk_ids[3][1] = avail
+    c.request_kv_length_offsets[0:n] = 10
+    c.request_kv_length_offsets[0:2] = c.chunk_size_tokens - 1
+    c.request_kv_length_offsets[5:7] = c.chunk_size_tokens - 1
+    c.request_kv_length_offsets[3] = c.chunk_size_bytes + 10
+    c.request_query_lengths[0:n] = 1
+    c.request_ids[0:n] = torch.arange(0, n, dtype=torch.int32)
+    c.request_kv_chunk_counts[0:n] = 1
+    c.request_kv_chunk_counts[3] = 2
+    c.request_last_kv_chunk_id[0:n] = torch.arange(0, n, dtype=torch.int32)
+    c.request_last_kv_chunk_id[3] = 11
+    c.request_last_kv_chunk_offset[0:n] = 10
+    c.request_last_kv_chunk_offset[0:2] = c.chunk_size_tokens - 1
+    c.request_last_kv_chunk_offset[5:7] = c.chunk_size_tokens - 1
+    c.update_requests(active_requests_mask=mask, new_tokens=next_tokens)
+    assert c.paused_request_count == 0 and c.total_request_count == 7 and c.active_token_count == 7
+    assert c.request_last_kv_chunk_offset[0:10].tolist() == [0, 0, 0, 0, 11, 11, 11, 10, 10, 10]
+    assert c.token_to_input_ids[:7].tolist() == [0, 1, 5, 6, 4, 2, 9]
+    assert c.token_to_pos_ids[:7].tolist() == [128, 128, 128, 128, 11, 11, 11]
+    assert c.request_to_kv_chunk_ids[0:10].tolist() == [
+        [479, 482, -1, -1], [480, 479, -1, -1], [484, 486, -1, -1], [485, 487, -1, -1], [483, -1, -1, -1],
+        [481, -1, -1, -1], [488, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1]]
+
+
+def test_release_memory_chunks_for_finished_requests():
+    # :517-571 and :573-630
+    c = make_ctx()
+    chunks = c.chunk_allocator.allocate_memory_chunks(5, safe=True)
+    c.total_request_count = 5
+    avail0 = c.chunk_allocator.chunk_count_avail
+    for i in range(5):
+        c.request_to_kv_chunk_ids[i, 0] = chunks[i]
+        c.request_query_lengths[i] = 1
+        c.request_ids[i] = i
+    c.update_requests(torch.tensor([0, 1, 0, 1, 0]), torch.tensor([10, 11, 12, 13, 14]))
+    assert c.total_request_count == 2 and c.active_token_count == 2
+    assert c.chunk_allocator.chunk_count_avail == avail0 + 3
+
+    c = make_ctx()
+    chunks = c.chunk_allocator.allocate_memory_chunks(6, safe=True)
+    c.total_request_count = 3
+    avail0 = c.chunk_allocator.chunk_count_avail
+    c.request_to_kv_chunk_ids[0, 0] = chunks[0]
+    c.request_to_kv_chunk_ids[1, :2] = chunks[1:3]
+    c.request_to_kv_chunk_ids[2, :3] = chunks[3:6]
+    c.request_kv_chunk_counts[:3] = torch.tensor([1, 2, 3], dtype=torch.int32)
+    c.request_query_lengths[:3] = 1
+    c.request_ids[:3] = torch.arange(3, dtype=torch.int32)
+    c.update_requests(torch.tensor([0, 0, 0]), torch.tensor([10, 11, 12]))
+    assert c.total_request_count == 0 and c.active_token_count == 0
+    assert c.chunk_allocator.chunk_count_avail == avail0 + 6
+
+
+def test_cuda_graph_token_counts():
+    # size tables of the reference's engine tests (tests/unit_tests/inference/engines/test_dynamic_engine.py:496-522)
+    set_rounder(4)
+    c = make_ctx(max_requests_override=64, num_cuda_graphs=4)
+    assert c.cuda_graph_token_counts == [64, 48, 32, 16]
+    c = make_ctx(max_requests_override=64, num_cuda_graphs=1)
+    assert c.cuda_graph_token_counts == [64]
+    c = make_ctx(max_requests_override=60, num_cuda_graphs=16)
+    assert c.cuda_graph_token_counts == [60, 56, 48, 40, 32, 24, 16, 8]
