@@ -1,0 +1,177 @@
+"""GPT decoder model for the dynamic inference path.
+
+Module tree and ``state_dict`` keys follow the reference's ``GPTModel``
+(``megatron/core/models/gpt/gpt_model.py``): ``embedding.word_embeddings``,
+``embedding.position_embeddings`` (learned absolute positions only), ``decoder.layers.N.*``,
+``decoder.final_layernorm``, ``output_layer``.  ``forward`` has the reference's signature and returns
+``[1, rows, vocab]`` logits (``gpt_model.py:344, 509-560``).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops, parallel_state
+from ..spec_provider import get_gpt_layer_b200_spec
+from ..tensor_parallel.layers import ColumnParallelLinear, VocabParallelEmbedding
+from ..transformer.transformer_block import TransformerBlock
+from ..transformer.transformer_config import TransformerConfig
+
+
+def rope_tables(max_seq_len: int, dim: int, base: float, dtype: torch.dtype, device) -> tuple:
+    """cos / sin of ``pos * base^(-2i/dim)`` as ``[max_seq_len, dim/2]`` tables in ``dtype``.
+
+    The angles are formed in fp32 exactly as ``RotaryEmbedding.forward`` does
+    (``megatron/core/models/common/embeddings/rotary_pos_embedding.py:79-81, 150-181``) and the cast to
+    the activation dtype happens before use, as ``_apply_rotary_pos_emb_bshd`` does
+    (``rope_utils.py:122-123``).  Computed on the host so that the values do not depend on the device's
+    trigonometric routines.
+    """
+    inv_freq = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    freqs = torch.outer(torch.arange(max_seq_len, dtype=torch.float32), inv_freq)
+    return torch.cos(freqs).to(dtype).to(device).contiguous(), torch.sin(freqs).to(dtype).to(device).contiguous()
+
+
+class _PositionEmbedding(torch.nn.Module):
+    def __init__(self, n, h, dtype, device):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.empty(n, h, dtype=dtype, device=device), requires_grad=False)
+
+
+class LanguageModelEmbedding(torch.nn.Module):
+    """Word (+ learned position) embeddings (reference ``language_model_embedding.py:99-149``)."""
+
+    def __init__(self, config, vocab_size, max_sequence_length, position_embedding_type):
+        super().__init__()
+        self.word_embeddings = VocabParallelEmbedding(vocab_size, config.hidden_size, config=config)
+        self.add_position_embedding = position_embedding_type == "learned_absolute"
+        if self.add_position_embedding:
+            self.position_embeddings = _PositionEmbedding(max_sequence_length, config.hidden_size, config.params_dtype,
+                                                          self.word_embeddings.weight.device)
+
+    def forward(self, input_ids, position_ids):
+        if self.add_position_embedding:
+            return self.word_embeddings(input_ids, self.position_embeddings.weight, position_ids.reshape(-1))
+        return self.word_embeddings(input_ids)
+
+
+class GPTModel(torch.nn.Module):
+    def __init__(self, config: TransformerConfig, transformer_layer_spec=None, vocab_size: int = None,
+                 max_sequence_length: int = None, pre_process: bool = True, post_process: bool = True,
+                 parallel_output: bool = True, share_embeddings_and_output_weights: bool = False,
+                 position_embedding_type: str = "learned_absolute", rotary_base: float = 10000.0, **_):
+        super().__init__()
+        assert pre_process and post_process, "pipeline stages are outside the decode path built here"
+        self.config, self.vocab_size, self.max_sequence_length = config, vocab_size, max_sequence_length
+        self.position_embedding_type = position_embedding_type
+        self.share_embeddings_and_output_weights = share_embeddings_and_output_weights
+        if transformer_layer_spec is None:
+            transformer_layer_spec = get_gpt_layer_b200_spec(config.normalization)
+        self.embedding = LanguageModelEmbedding(config, vocab_size, max_sequence_length, position_embedding_type)
+        self.decoder = TransformerBlock(config, transformer_layer_spec)
+        self.output_layer = ColumnParallelLinear(
+            config.hidden_size, vocab_size, config=config, bias=False, gather_output=not parallel_output,
+            skip_bias_add=False, skip_weight_param_allocation=share_embeddings_and_output_weights)
+        self.rotary_pos_cos = self.rotary_pos_sin = None
+        if position_embedding_type == "rope":
+            self.rotary_pos_cos, self.rotary_pos_sin = rope_tables(
+                max_sequence_length, config.kv_channels, rotary_base, config.params_dtype,
+                self.embedding.word_embeddings.weight.device)
+
+    # ------------------------------------------------------------------------------------------
+    def forward_rows(self, input_ids, position_ids, inference_context, row_indices=None,
+                     runtime_gather_output: Optional[bool] = None):
+        """Logits ``[rows, vocab]``: every token row when ``row_indices`` is None, else the given rows
+        (int64 device tensor) of the final hidden states."""
+        hidden = self.embedding(input_ids.reshape(-1), position_ids)
+        hidden = self.decoder(hidden, inference_context=inference_context, rotary_pos_cos=self.rotary_pos_cos,
+                              rotary_pos_sin=self.rotary_pos_sin)
+        if row_indices is not None:
+            hidden = ops.gather_rows(hidden, row_indices)
+        weight = self.embedding.word_embeddings.weight if self.share_embeddings_and_output_weights else None
+        logits, _ = self.output_layer(hidden, weight=weight, runtime_gather_output=runtime_gather_output)
+        return logits
+
+    def forward(self, input_ids, position_ids, attention_mask=None, decoder_input=None, labels=None,
+                inference_context=None, runtime_gather_output: Optional[bool] = None, **_):
+        """``input_ids`` / ``position_ids`` ``[1, T]`` of the context's padded step.  Returns
+        ``[1, active requests, vocab]`` when the context materialises last-token logits only, else
+        ``[1, T, vocab]``."""
+        ctx = inference_context
+        if ctx is None or labels is not None:
+            raise NotImplementedError("only inference with a dynamic context is implemented")
+        if ctx.materialize_only_last_token_logits:
+            n_req = ctx.total_request_count - ctx.paused_request_count
+            if ctx.is_decode_only():
+                logits = self.forward_rows(input_ids, position_ids, ctx, None, runtime_gather_output)[:n_req]
+            else:
+                idx = torch.from_numpy(ctx.last_token_indices()).to(input_ids.device)
+                logits = self.forward_rows(input_ids, position_ids, ctx, idx, runtime_gather_output)
+        else:
+            logits = self.forward_rows(input_ids, position_ids, ctx, None, runtime_gather_output)
+        return logits.unsqueeze(0)
+
+    # ------------------------------------------------------------------------------------------
+    def full_parameter_shapes(self) -> Dict[str, tuple]:
+        """``state_dict`` key -> UNSHARDED shape (what a TP=1 model of the reference holds)."""
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        out = {}
+        for k, v in self.state_dict().items():
+            if v is None or k.endswith("_extra_state"):
+                continue
+            shape = list(v.shape)
+            dim = _partition_dim(k)
+            if dim is not None:
+                shape[dim] *= tp
+            out[k] = tuple(shape)
+        return out
+
+    def load_full_state_dict(self, full: Dict[str, torch.Tensor]) -> None:
+        """Load UNSHARDED tensors, keeping this rank's shard of each (see `shard_for_rank`)."""
+        tp, rank = parallel_state.get_tensor_model_parallel_world_size(), parallel_state.get_tensor_model_parallel_rank()
+        own = self.state_dict()
+        for k, dst in own.items():
+            if dst is None or k.endswith("_extra_state"):
+                continue
+            dst.copy_(shard_for_rank(k, full[k], rank, tp, gated=self.config.gated_linear_unit))
+
+    def init_synthetic_weights(self, seed: int = 0, std: float = 0.02, device=None) -> None:
+        """Seeded N(0, std) weights (norm scales 1 + N(0, std)), identical across TP sizes."""
+        from ..synthetic import canonical_tensor
+
+        tp, rank = parallel_state.get_tensor_model_parallel_world_size(), parallel_state.get_tensor_model_parallel_rank()
+        own = self.state_dict()
+        for k, shape in self.full_parameter_shapes().items():
+            dev = own[k].device if device is None else device
+            full = canonical_tensor(k, shape, seed=seed, std=std, dtype=self.config.params_dtype, device=dev)
+            own[k].copy_(shard_for_rank(k, full, rank, tp, gated=self.config.gated_linear_unit))
+            del full
+
+
+def _partition_dim(key: str) -> Optional[int]:
+    """Dimension along which tensor parallelism splits the tensor behind ``key`` (None: replicated)."""
+    if key.endswith(("linear_qkv.weight", "linear_qkv.bias", "linear_fc1.weight", "linear_fc1.bias",
+                     "output_layer.weight", "word_embeddings.weight")):
+        return 0
+    if key.endswith(("linear_proj.weight", "linear_fc2.weight")):
+        return 1
+    return None
+
+
+def shard_for_rank(key: str, full: torch.Tensor, rank: int, tp: int, *, gated: bool) -> torch.Tensor:
+    """This rank's shard of an unsharded tensor.
+
+    QKV rows are grouped per KV group ``[q_0..q_{g-1}, k, v]`` (``attention.py:992-1021``), so the
+    contiguous row split is a split by KV group.  For a gated MLP, fc1 holds ``[gate ; up]`` and rank r
+    takes ``[gate_r ; up_r]``, the layout checkpoints use (``mlp.py:260-297``); a plain contiguous split
+    would change the function with the TP size.  fc2 / out-proj split along the input dimension;
+    embedding and LM head split contiguously along the vocabulary (``layers.py:223-228``).
+    """
+    dim = _partition_dim(key)
+    if dim is None or tp == 1:
+        return full
+    if gated and key.endswith(("linear_fc1.weight", "linear_fc1.bias")):
+        gate, up = torch.chunk(full, 2, dim=0)
+        return torch.cat([torch.chunk(gate, tp, dim=0)[rank], torch.chunk(up, tp, dim=0)[rank]], dim=0)
+    return torch.chunk(full, tp, dim=dim)[rank]

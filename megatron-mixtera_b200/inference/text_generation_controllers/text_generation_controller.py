@@ -1,0 +1,134 @@
+"""Text generation controller of the dynamic path: forward -> last-token logits -> sample ->
+finished mask -> context update (reference
+``megatron/core/inference/text_generation_controllers/text_generation_controller.py:172-315, 410-565``).
+"""
+from __future__ import annotations
+
+import asyncio
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from ... import ops
+from ..sampling_params import SamplingParams
+
+
+def get_asyncio_loop():
+    try:
+        return asyncio.get_running_loop()
+    except RuntimeError:
+        try:
+            loop = asyncio.get_event_loop_policy().get_event_loop()
+        except RuntimeError:
+            loop = asyncio.new_event_loop()
+            asyncio.set_event_loop(loop)
+        return loop
+
+
+class TextGenerationController:
+    def __init__(self, inference_wrapped_model, tokenizer, pp_group=None):
+        self.inference_wrapped_model = inference_wrapped_model
+        self.tokenizer = tokenizer
+        self.pp_group = pp_group
+        self.model_is_pipeline_parallel = False
+        cfg = inference_wrapped_model.model.config
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        self.sampling_rng = torch.Generator(device=dev)
+        self.sampling_rng.manual_seed(cfg.inference_sampling_seed)
+
+    # --------------------------------------------------------------------------------------------
+    def tokenize_prompt(self, prompt: str, add_BOS: bool = False):
+        tokens = self.tokenizer.tokenize(prompt)
+        return [self.tokenizer.bos] + tokens if add_BOS else tokens
+
+    # --------------------------------------------------------------------------------------------
+    def sample_from_logits(self, last_token_logits: torch.Tensor, sampling_params: Optional[SamplingParams] = None,
+                           vocab_size: Optional[int] = None, **kwargs) -> torch.Tensor:
+        """Sample one token per row of ``last_token_logits [batch, vocab]`` (bf16, on the device).
+
+        ``top_k == 1``: greedy, the argmax kernel (ties go to the smallest index).  ``top_k > 1``: the
+        top-k kernel produces the filtered, temperature-scaled probabilities and ``torch.multinomial``
+        draws from them with the controller's generator, as the reference does (:292-309).  ``top_k == 0``
+        with ``top_p == 0`` keeps the whole vocabulary.  top-p (sort-based) sampling is rejected: it is not
+        part of the decode path built here.
+        """
+        if kwargs.get("common_inference_params"):
+            sampling_params = kwargs["common_inference_params"]
+        top_p, top_k, temperature = sampling_params.top_p, sampling_params.top_k, sampling_params.temperature
+        assert isinstance(top_p, float) and isinstance(top_k, int)
+        assert not (top_k > 0 and top_p > 0.0), "Cannot have top-p and top-k both greater than zero"
+        assert top_p <= 1.0, "top-p should be in (0,1]"
+        if sampling_params.top_n_logprobs > 0:
+            raise NotImplementedError("top-n log-probabilities are outside the decode path built here")
+        if top_k == 1:
+            return ops.argmax(last_token_logits)
+        if top_k > 1 or (top_k == 0 and top_p == 0.0):
+            if top_k > 1:
+                assert top_k <= last_token_logits.size(1), "top-k is larger than logit size."
+                if vocab_size:
+                    assert top_k < vocab_size, "top-k is larger than vocab size."
+            keep = top_k if top_k > 1 else last_token_logits.size(1)
+            probs = ops.topk_probs(last_token_logits, keep, temperature)
+            sampled = torch.multinomial(probs, num_samples=1, generator=self.sampling_rng).view(-1)
+            if vocab_size:
+                sampled = torch.clamp(sampled, min=0, max=vocab_size - 1)
+            return sampled
+        raise NotImplementedError("top-p sampling is outside the decode path built here")
+
+    # --------------------------------------------------------------------------------------------
+    @torch.inference_mode()
+    async def async_generate_output_tokens_dynamic_batch(self, sampling_params: SamplingParams, termination_id: int) -> Optional[Dict]:
+        """One engine step; returns the dict of the reference (:548-555) or None when idle.
+
+        The sampled tokens are read back once (the only device->host transfer of the step); the finished
+        mask and the context update then run on the host.  ``sample`` and the id tensors in the result
+        are host tensors.
+        """
+        context = self.inference_wrapped_model.inference_context
+        materialize_last = context.materialize_only_last_token_logits
+        if sampling_params.return_log_probs:
+            skip = getattr(sampling_params, "skip_prompt_log_probs_for_dynamic_inference", False)
+            assert skip or materialize_last is False, "Materialize only last token logits must be false for returning log probs"
+        if context.active_token_count == 0:
+            return None
+
+        context.initialize_attention_state()
+        cuda_graph_request_count = context.padded_active_request_count if context.is_decode_only() else None
+        input_ids, position_ids = context.current_input_and_position_ids()
+        logits = self.inference_wrapped_model.run_one_forward_step(
+            {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None})
+        await asyncio.sleep(0)  # the forward is enqueued; let other coroutines run
+
+        last_token_logits = logits.squeeze(0) if materialize_last else context.last_token_logits(logits)
+        vocab_size = self.inference_wrapped_model.inference_wrapper_config.padded_vocab_size
+        new_sample_dev = self.sample_from_logits(last_token_logits.contiguous(), sampling_params, vocab_size=vocab_size)
+        new_sample = new_sample_dev.cpu()  # the step's one synchronising read
+
+        p, t = context.paused_request_count, context.total_request_count
+        active_request_ids = context.request_ids[p:t].long().clone()
+        active_sequence_lengths = context.get_active_sequence_lengths() + 1
+        max_sequence_lengths = context.get_max_sequence_lengths()
+        active_request_mask = (new_sample != termination_id).byte() & torch.less(active_sequence_lengths, max_sequence_lengths).byte()
+        finished_idxs = torch.nonzero(active_request_mask == 0, as_tuple=True)[0] + p
+        finished_request_ids = context.request_ids[finished_idxs].clone()
+
+        log_probs = None
+        if sampling_params.return_log_probs:
+            log_probs = context.calculate_log_probs(logits, new_sample_dev, only_last_token_logits=materialize_last)
+
+        newly_paused_request_ids = context.update_requests(active_request_mask, new_sample.clone())
+        return {
+            "active_request_ids": active_request_ids,
+            "newly_paused_request_ids": newly_paused_request_ids,
+            "finished_request_ids": finished_request_ids,
+            "sample": new_sample,
+            "log_probs": log_probs,
+            "cuda_graph_request_count": cuda_graph_request_count,
+        }
+
+    @torch.inference_mode()
+    def generate_output_tokens_dynamic_batch(self, sampling_params: SamplingParams, termination_id: int):
+        """Synchronous wrapper of `async_generate_output_tokens_dynamic_batch`."""
+        return get_asyncio_loop().run_until_complete(
+            self.async_generate_output_tokens_dynamic_batch(sampling_params, termination_id))

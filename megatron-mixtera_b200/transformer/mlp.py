@@ -1,0 +1,40 @@
+"""Feed-forward block: fc1 -> SwiGLU or bias+GELU -> fc2 (reference ``megatron/core/transformer/mlp.py:140-234``).
+fc1's weight holds ``[gate ; up]`` halves per rank for the gated case (``fused_bias_swiglu.py:25``)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Union
+
+import torch
+
+from .. import ops
+from .spec_utils import ModuleSpec, build_module
+
+
+@dataclass
+class MLPSubmodules:
+    linear_fc1: Union[ModuleSpec, type] = None
+    linear_fc2: Union[ModuleSpec, type] = None
+
+
+class MLP(torch.nn.Module):
+    def __init__(self, config, submodules: MLPSubmodules, **_):
+        super().__init__()
+        self.config = config
+        ffn = config.ffn_hidden_size * (2 if config.gated_linear_unit else 1)
+        self.linear_fc1 = build_module(submodules.linear_fc1, config.hidden_size, ffn, config=config,
+                                       bias=config.add_bias_linear, gather_output=False, skip_bias_add=True,
+                                       tp_comm_buffer_name="fc1")
+        self.linear_fc2 = build_module(submodules.linear_fc2, config.ffn_hidden_size, config.hidden_size, config=config,
+                                       bias=config.add_bias_linear, input_is_parallel=True, skip_bias_add=True,
+                                       tp_comm_buffer_name="fc2")
+
+    def forward(self, hidden_states):
+        inter, bias = self.linear_fc1(hidden_states)
+        if self.config.gated_linear_unit:
+            if bias is not None:
+                raise NotImplementedError("SwiGLU with an fc1 bias")
+            inter = ops.activation(inter, "swiglu")
+        else:
+            inter = ops.activation(inter, "gelu", bias)
+        return self.linear_fc2(inter)

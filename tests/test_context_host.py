@@ -67,9 +67,9 @@ def check_snapshot(z, step, c):
         assert np.array_equal(c.cu_kv_seq_lengths.cpu().numpy(), z[f"s{step}_cu_kv_seq_lengths"])
         # the per-token view used by the token-as-row prefill attention
         a = c.active_token_count
-        rows = c.token_to_block_table_row[:a].numpy()
+        rows = c.token_to_block_table_row[:a].cpu().numpy()
         assert np.array_equal(rows, z[f"s{step}_request_idx"] - c.paused_request_count)
-        assert np.array_equal(c.token_kv_lengths[:a].numpy(), z[f"s{step}_pos_in_request"][:a] + 1)
+        assert np.array_equal(c.token_kv_lengths[:a].cpu().numpy(), z[f"s{step}_pos_in_request"][:a] + 1)
     assert [c.max_seqlen_q, c.max_seqlen_k] == z[f"s{step}_max_seqlen"].tolist()
 
 
