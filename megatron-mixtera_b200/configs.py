@@ -1,0 +1,41 @@
+"""Named model / workload shapes of the decode benchmark (synthetic weights, synthetic prompts)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Tuple
+
+
+@dataclass(frozen=True)
+class Workload:
+    name: str
+    num_layers: int
+    hidden_size: int
+    num_attention_heads: int
+    num_query_groups: int
+    kv_channels: int
+    ffn_hidden_size: int
+    vocab_size: int
+    num_requests: int
+    prompt_len_range: Tuple[int, int]
+    num_tokens_to_generate: int
+    chunk_size_tokens: int = 256
+    rotary_base: float = 500000.0
+    log_uniform_lengths: bool = False
+
+    @property
+    def max_sequence_length(self) -> int:
+        return self.prompt_len_range[1] + self.num_tokens_to_generate
+
+
+# Llama-3-8B-shaped bf16 decode, 64 concurrent requests, prompts uniform in [128, 2048], 256 output tokens.
+LLAMA3_8B_BF16_64REQ = Workload(
+    name="llama3-8b-shape bf16 decode, 64 requests, prompt U[128,2048], 256 greedy tokens, KV chunk 256",
+    num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
+    ffn_hidden_size=14336, vocab_size=128256, num_requests=64, prompt_len_range=(128, 2048),
+    num_tokens_to_generate=256)
+
+# A few-layer cut of the same shape for smoke tests.
+LLAMA3_8B_SHAPE_2LAYER = Workload(
+    name="llama3-8b-shape, 2 layers, 8 requests", num_layers=2, hidden_size=4096, num_attention_heads=32,
+    num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256, num_requests=8,
+    prompt_len_range=(128, 700), num_tokens_to_generate=16)

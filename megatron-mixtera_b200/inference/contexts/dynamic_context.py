@@ -265,6 +265,7 @@ class DynamicInferenceContext(BaseInferenceContext):
         self._h_bt_np = self._h_bt.numpy()
         self._copy_event = torch.cuda.Event() if pin else None
         self._copies_pending = False
+        self.h2d_bytes = 0  # bytes mirrored host -> device so far (benchmark accounting)
 
         # ---- guaranteed-request reserve (reference :384-401) ----
         gtd_chunk_count = min(int(buffer_guaranteed_fraction * chunk_count_total), chunk_count_total)
@@ -353,6 +354,7 @@ class DynamicInferenceContext(BaseInferenceContext):
             return
         for r in rows:
             self._d_tok[r, lo:hi].copy_(self._h_tok[r, lo:hi], non_blocking=True)
+            self.h2d_bytes += (hi - lo) * 8
         self._mark_copies()
 
     # ------------------------------------------------------------------ attention state
@@ -463,6 +465,7 @@ class DynamicInferenceContext(BaseInferenceContext):
             bt[n_req:n_rows] = 0
         self.request_to_kv_chunk_ids_cudagraph_only[:dev_rows].copy_(self._h_bt[:dev_rows], non_blocking=True)
         self.block_table = self.request_to_kv_chunk_ids_cudagraph_only[:n_rows]
+        self.h2d_bytes += dev_rows * (8 + 4 * self.max_kv_chunk_count) + (0 if decode else 8 * (n_rows + 1) + 8 * padded)
         self._mark_copies()
 
     def reset(self) -> None:

@@ -12,7 +12,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import AttentionArgs, B200Error, check  # noqa: F401  (re-exported)
+from ._lib import AttentionArgs, B200Error  # noqa: F401  (re-exported)
 
 BF16 = torch.bfloat16
 
@@ -54,6 +54,20 @@ class _Workspace:
 
 
 _workspace = _Workspace()
+
+# Kernel launches issued through this module since import (attention with splits counts two).
+launch_count = 0
+
+
+_NOT_A_LAUNCH = ("b200_device_status",)
+
+
+def check(fn_name: str, code: int) -> None:
+    """Raise on a non-zero return code; count the kernel launch otherwise."""
+    global launch_count
+    _lib.check(fn_name, code)
+    if fn_name not in _NOT_A_LAUNCH:
+        launch_count += 1
 
 
 def device_status(reset: bool = False) -> int:
@@ -170,7 +184,10 @@ def rope_append(args: AttentionArgs) -> None:
 
 
 def paged_attention(args: AttentionArgs) -> None:
+    global launch_count
     check("b200_paged_attention", _lib.load().b200_paged_attention(ctypes.byref(args), _stream()))
+    if args.num_splits > 1:
+        launch_count += 1  # the split-combine kernel
 
 
 def argmax(logits):
