@@ -6,7 +6,7 @@
 //     {d, head, token}, 128-byte swizzle), completion on mbarriers;
 //   * four consumer warps each take a 16-token slice of every tile: S = Q K^T with mma.sync
 //     (the M side is the group's 4-8 query heads padded to 16), online softmax with warp shuffles
-//     in the exp2 domain, O += P V (P as a hi + lo bf16 pair); per-warp (max, sum, O) states are
+//     in the exp2 domain, O += P V (P as a sum of three bf16 terms); per-warp (max, sum, O) states are
 //     merged through shared memory at the end.
 // RoPE of the query heads is applied while staging Q.  In decode steps (fuse_rope_append) the unit
 // whose range contains the new token also rotates the new key, writes key and value into the pool
@@ -86,6 +86,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
+  pdl_launch_dependents();
   const int unit = blockIdx.x;
   const int split = unit % p.num_splits;
   const int h = (unit / p.num_splits) % p.nkv;
@@ -95,6 +96,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   if (kv_len <= 0) {  // padding row: flash-attn returns zeros for it
     if (p.num_splits == 1) {
+      pdl_wait();
       __nv_bfloat16* o = p.out + (static_cast<int64_t>(t) * p.nq + h * G) * D;
       for (int i = tid; i < G * D; i += kThreads) o[i] = __float2bfloat16_rn(0.f);
     }
@@ -129,6 +131,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (warp == kConsumerWarps) {
     // ------------------------------- producer warp -------------------------------
     if (lane == 0) {
+      // Decode steps: the pool holds only what earlier steps wrote (this step's key/value is patched
+      // in by the consumers), so K/V streaming starts without waiting for the QKV GEMM before us.
+      // Prefill steps: the append kernel right before us writes the pool, so wait for it.
+      if (!p.fused) pdl_wait();
       const int32_t* bt_row = p.block_table + static_cast<int64_t>(row) * p.max_chunks;
       int cur_c = -1;
       int cur_id = 0;
@@ -161,6 +167,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int tig = lane & 3;
   const __nv_bfloat16* qkv_t = p.qkv + (static_cast<int64_t>(t) * p.nkv + h) * (G + 2) * D;
 
+  pdl_wait();  // qkv is the previous kernel's output
   // Stage Q (with RoPE) as a zero-padded [16][D] tile.
   for (int i = tid; i < 16 * C::kQStride / 2; i += kConsumerThreads)
     reinterpret_cast<uint32_t*>(q_smem)[i] = 0u;
@@ -291,11 +298,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         m_run[r] = m_new;
         l_run[r] *= alpha[r];
       }
-      // P is fed to the tensor cores as hi + lo bf16 halves (two MMAs per V fragment): the bf16
-      // rounding of P alone would cost ~1e-3 relative accuracy per output, the pair keeps ~16 bits.
-      uint32_t pf[4], pl[4];
+      // P is fed to the tensor cores as a sum of three bf16 terms (three MMAs per V fragment): the
+      // bf16 rounding of P alone would cost ~1e-3 relative accuracy per output, the triple keeps all
+      // 24 bits, so the result is that of an fp32 softmax applied to bf16 V.
+      uint32_t pf[4], pl[4], pt[4];
       {
-        float pv[2][4], pr[2][4];
+        float pv[2][4], pr[2][4], pq[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
@@ -303,6 +311,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             pv[nt][c] = exp2f(sacc[nt][c] - m_use[c >> 1]);
             l_run[c >> 1] += pv[nt][c];
             pr[nt][c] = pv[nt][c] - bf16_round(pv[nt][c]);
+            pq[nt][c] = pr[nt][c] - bf16_round(pr[nt][c]);
           }
         }
         pf[0] = pack_bf16x2(pv[0][0], pv[0][1]);
@@ -313,6 +322,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         pl[1] = pack_bf16x2(pr[0][2], pr[0][3]);
         pl[2] = pack_bf16x2(pr[1][0], pr[1][1]);
         pl[3] = pack_bf16x2(pr[1][2], pr[1][3]);
+        pt[0] = pack_bf16x2(pq[0][0], pq[0][1]);
+        pt[1] = pack_bf16x2(pq[0][2], pq[0][3]);
+        pt[2] = pack_bf16x2(pq[1][0], pq[1][1]);
+        pt[3] = pack_bf16x2(pq[1][2], pq[1][3]);
       }
 #pragma unroll
       for (int i2 = 0; i2 < D / 8; ++i2) {
@@ -333,8 +346,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         ldmatrix_x4_trans(vbase + sub * C::kSubBytes + ((chunk16 ^ (v_row & 7)) << 4), b0, b1, b2, b3);
         mma_bf16_16816(oacc[dn * 2], pf, b0, b1);
         mma_bf16_16816(oacc[dn * 2], pl, b0, b1);
+        mma_bf16_16816(oacc[dn * 2], pt, b0, b1);
         mma_bf16_16816(oacc[dn * 2 + 1], pf, b2, b3);
         mma_bf16_16816(oacc[dn * 2 + 1], pl, b2, b3);
+        mma_bf16_16816(oacc[dn * 2 + 1], pt, b2, b3);
       }
     }
     __syncwarp();
@@ -397,6 +412,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 // Merge the splits of each (token, query head): out = sum_s 2^(lse_s - max) O_s / sum_s 2^(lse_s - max).
 template <int D>
 __global__ void __launch_bounds__(D) combine_kernel(Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int qh = blockIdx.x;  // t * nq + head
   const int t = qh / p.nq;
   const int d = threadIdx.x;
@@ -424,6 +441,8 @@ __global__ void __launch_bounds__(D) combine_kernel(Params p) {
 // Prefill / mixed steps: rotate k, then scatter k and v of every token into the pool.
 template <int D>
 __global__ void __launch_bounds__(128) rope_append_kernel(Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int G = p.G;
   const bool rope = p.cos != nullptr;
@@ -510,13 +529,10 @@ static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_
   }
   const int64_t units = static_cast<int64_t>(p.T) * p.nkv * p.num_splits;
   if (units > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
-  paged_attention_kernel<D><<<static_cast<unsigned>(units), kThreads, C::kSmemBytes, stream>>>(*mk, *mv, p);
-  int rc = launch_status();
+  int rc = launch_pdl(paged_attention_kernel<D>, dim3(static_cast<unsigned>(units)), dim3(kThreads), C::kSmemBytes,
+                      stream, *mk, *mv, p);
   if (rc != B200_OK) return rc;
-  if (p.num_splits > 1) {
-    combine_kernel<D><<<p.T * p.nq, D, 0, stream>>>(p);
-    rc = launch_status();
-  }
+  if (p.num_splits > 1) rc = launch_pdl(combine_kernel<D>, dim3(p.T * p.nq), dim3(D), 0, stream, p);
   return rc;
 }
 
@@ -538,11 +554,8 @@ int b200_rope_append(const b200_attention_args* a, b200_stream_t stream) {
   if (rc != B200_OK) return rc;
   if (!a->token_to_chunk_idx || !a->token_to_local_pos) return B200_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (a->head_dim == 128)
-    attn::rope_append_kernel<128><<<p.T, 128, 0, s>>>(p);
-  else
-    attn::rope_append_kernel<64><<<p.T, 128, 0, s>>>(p);
-  return launch_status();
+  if (a->head_dim == 128) return launch_pdl(attn::rope_append_kernel<128>, dim3(p.T), dim3(128), 0, s, p);
+  return launch_pdl(attn::rope_append_kernel<64>, dim3(p.T), dim3(128), 0, s, p);
 }
 
 int b200_paged_attention(const b200_attention_args* a, b200_stream_t stream) {

@@ -33,6 +33,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the library is launched with the
+// programmatic-stream-serialization attribute (see launch_pdl): it may start while the previous
+// kernel on the stream is still draining, does its set-up (and prefetches data no earlier kernel
+// writes, e.g. weights), and calls pdl_wait() before it touches anything a predecessor produced
+// or that a predecessor may still be reading.  pdl_launch_dependents() lets the NEXT kernel
+// start its own set-up early; it fires once every CTA of this grid has issued it or exited.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -238,6 +251,28 @@ namespace b200 {
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+// Launch with programmatic stream serialization allowed (see pdl_wait above).
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  return B200_OK;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -24,6 +24,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ ids,
                                    __nv_bfloat16* __restrict__ out, int row_elems, int64_t lo, int64_t hi,
                                    const __nv_bfloat16* __restrict__ add_table, const int64_t* __restrict__ add_ids) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int64_t id = ids[r];
   const bool in_range = id >= lo && id < hi;
@@ -56,6 +58,8 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
                 __nv_bfloat16* __restrict__ normed_out, int hidden, float eps) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t off = static_cast<int64_t>(blockIdx.x) * hidden;
   const Vec8* xv = reinterpret_cast<const Vec8*>(x + off);
   const Vec8* rv = residual ? reinterpret_cast<const Vec8*>(residual + off) : nullptr;
@@ -159,6 +163,8 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 // kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
                                   __nv_bfloat16* __restrict__ out, int F, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int nvec = F / 8;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
@@ -207,10 +213,9 @@ int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int 
     return B200_ERR_ALIGNMENT;
   int threads = row_elems / 8;
   threads = threads > 256 ? 256 : ((threads + 31) / 32) * 32;
-  ew::gather_rows_kernel<<<n_rows, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), row_elems, vocab_start,
-      vocab_end, static_cast<const __nv_bfloat16*>(add_table), add_ids);
-  return launch_status();
+  return launch_pdl(ew::gather_rows_kernel, dim3(n_rows), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), row_elems,
+                    vocab_start, vocab_end, static_cast<const __nv_bfloat16*>(add_table), add_ids);
 }
 
 int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
@@ -235,16 +240,14 @@ int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, co
   auto H = static_cast<__nv_bfloat16*>(hidden_out);
   auto Nn = static_cast<__nv_bfloat16*>(normed_out);
   if (per_thread <= 1)
-    ew::add_norm_kernel<1><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
   else if (per_thread <= 2)
-    ew::add_norm_kernel<2><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
   else if (per_thread <= 4)
-    ew::add_norm_kernel<4><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
   else if (per_thread <= 8)
-    ew::add_norm_kernel<8><<<rows, threads, 0, s>>>(X, B, R, Gm, Bt, H, Nn, hidden, eps);
-  else
-    return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
-  return launch_status();
+    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
+  return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
 }
 
 int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind,
@@ -254,10 +257,9 @@ int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, 
   if (F % 8 != 0 || !aligned16(in) || !aligned16(out) || (bias && !aligned16(bias))) return B200_ERR_ALIGNMENT;
   const int nvec = F / 8;
   dim3 grid(rows, (nvec + 255) / 256);
-  ew::activation_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<__nv_bfloat16*>(out), F, kind);
-  return launch_status();
+  return launch_pdl(ew::activation_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
+                    static_cast<__nv_bfloat16*>(out), F, kind);
 }
 
 }  // extern "C"

@@ -6,7 +6,9 @@
 // UMMA "N" side (one TMEM column per token, 32 ... 256).  Each CTA owns one (128-feature tile,
 // token block, K range) unit:
 //
-//   warp 0 / lane 0 : TMA producer  - w tile [128 x 64] and x tile [BT x 64] per stage, 128B swizzle
+//   warp 0 / lane 0 : TMA producer  - w tile [128 x 64] and x tile [BT x 64] per stage, 128B swizzle;
+//                                     the first w tiles are requested before the programmatic-launch
+//                                     wait, so weight streaming overlaps the previous kernel's tail
 //   warp 1 / lane 0 : UMMA issuer   - 4 x tcgen05.mma (K = 16 each) per stage, fp32 accumulate in TMEM
 //   warps 0-3       : epilogue      - tcgen05.ld, then either bf16 store or split-K partial store
 //
@@ -94,10 +96,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer ----------------
-      for (int i = 0; i < num_kb; ++i) {
+      // The weights are written by no kernel, so their first tiles are requested before waiting
+      // for the previous kernel on the stream; the activations (its output) only afterwards.
+      const int pre = num_kb < C::kStages ? num_kb : C::kStages;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full_bar[i], C::kStageBytes);
+        tma_load_2d(smem + i * C::kStageBytes, &map_w, &full_bar[i], (kb_begin + i) * kTileK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * C::kStageBytes + C::kStageBytesW, &map_x, &full_bar[i], (kb_begin + i) * kTileK, m0);
+      for (int i = pre; i < num_kb; ++i) {
         const int s = i % C::kStages;
         const uint32_t phase = (i / C::kStages) & 1;
         mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
@@ -135,6 +148,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 
   // ---------------- epilogue: all four warps ----------------
+  pdl_wait();  // outputs, partials and counters may still be in use by the previous kernel until here
   mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
   tcgen05_fence_after_sync();
 
@@ -334,8 +348,7 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
     attr_set = true;
   }
   dim3 grid(n_tiles, splits, m_blocks);
-  gemm_bf16_kernel<BT><<<grid, kThreads, C::kSmemBytes, stream>>>(*mw, *mx, p);
-  return launch_status();
+  return launch_pdl(gemm_bf16_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p);
 }
 
 }  // namespace gemm

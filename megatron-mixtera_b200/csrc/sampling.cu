@@ -14,6 +14,8 @@ __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_
 // Greedy: largest value, smallest index among equal values (NaN never wins).
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int64_t* __restrict__ out, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -67,6 +69,8 @@ topk_probs_kernel(const uint16_t* __restrict__ logits, int64_t ld, float* __rest
   __shared__ int hist[256];
   __shared__ int sel_bin, sel_rank;
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
   float* prow = probs + static_cast<int64_t>(blockIdx.x) * vocab;
   const bool scale = temperature != 1.0f;
@@ -157,9 +161,8 @@ extern "C" {
 int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int vocab, b200_stream_t stream) {
   using namespace b200;
   if (!logits || !out || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
-  sampling::argmax_kernel<<<rows, sampling::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(logits), ld, out, vocab);
-  return launch_status();
+  return launch_pdl(sampling::argmax_kernel, dim3(rows), dim3(sampling::kThreads), 0,
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, out, vocab);
 }
 
 int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,
@@ -167,9 +170,9 @@ int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows,
   using namespace b200;
   if (!logits || !probs || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
   if (top_k < 1 || top_k > vocab || !(temperature > 0.f)) return B200_ERR_INVALID_ARGUMENT;
-  sampling::topk_probs_kernel<<<rows, sampling::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(logits), ld, probs, vocab, top_k, temperature);
-  return launch_status();
+  return launch_pdl(sampling::topk_probs_kernel, dim3(rows), dim3(sampling::kThreads), 0,
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, probs, vocab,
+                    top_k, temperature);
 }
 
 }  // extern "C"

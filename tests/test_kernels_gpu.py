@@ -276,8 +276,9 @@ def test_paged_decode_attention(ops, nkv, G, D, chunk, kv_lens, splits, fused):
     for r, kl in enumerate(kv_lens):
         if kl == 0:
             assert torch.all(out[r] == 0)
+    # P is carried as three bf16 terms, so the output is that of an fp32 softmax up to the final rounding
     err = rel_l2(out, ref)
-    assert err < 5e-3, err
+    assert err < 1.5e-3, err
 
 
 def test_paged_attention_prefill_rows_via_row_of_token(ops):
