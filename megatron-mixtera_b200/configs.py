@@ -34,8 +34,8 @@ LLAMA3_8B_BF16_64REQ = Workload(
     ffn_hidden_size=14336, vocab_size=128256, num_requests=64, prompt_len_range=(128, 2048),
     num_tokens_to_generate=256)
 
-# A few-layer cut of the same shape for smoke tests.
+# Two layers of the same shape and batch: small enough for profiler captures (a few GB on the device).
 LLAMA3_8B_SHAPE_2LAYER = Workload(
-    name="llama3-8b-shape, 2 layers, 8 requests", num_layers=2, hidden_size=4096, num_attention_heads=32,
-    num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256, num_requests=8,
-    prompt_len_range=(128, 700), num_tokens_to_generate=16)
+    name="llama3-8b-shape cut to 2 layers, 64 requests, prompt U[128,2048]", num_layers=2, hidden_size=4096,
+    num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256,
+    num_requests=64, prompt_len_range=(128, 2048), num_tokens_to_generate=24)

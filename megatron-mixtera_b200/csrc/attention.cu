@@ -6,7 +6,7 @@
 //     {d, head, token}, 128-byte swizzle), completion on mbarriers;
 //   * four consumer warps each take a 16-token slice of every tile: S = Q K^T with mma.sync
 //     (the M side is the group's 4-8 query heads padded to 16), online softmax with warp shuffles
-//     in the exp2 domain, O += P V (P as a sum of three bf16 terms); per-warp (max, sum, O) states are
+//     in the exp2 domain, O += P V (P as hi + lo bf16 terms); per-warp (max, sum, O) states are
 //     merged through shared memory at the end.
 // RoPE of the query heads is applied while staging Q.  In decode steps (fuse_rope_append) the unit
 // whose range contains the new token also rotates the new key, writes key and value into the pool
@@ -298,12 +298,12 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         m_run[r] = m_new;
         l_run[r] *= alpha[r];
       }
-      // P is fed to the tensor cores as a sum of three bf16 terms (three MMAs per V fragment): the
-      // bf16 rounding of P alone would cost ~1e-3 relative accuracy per output, the triple keeps all
-      // 24 bits, so the result is that of an fp32 softmax applied to bf16 V.
-      uint32_t pf[4], pl[4], pt[4];
+      // P is fed to the tensor cores as hi + lo bf16 terms (two MMAs per V fragment): the bf16 rounding
+      // of P alone would cost ~2e-3 relative accuracy per output; the pair keeps 16 bits (~2e-4 after the
+      // output rounding).  A third term was measured: +5 us per launch for no visible gain downstream.
+      uint32_t pf[4], pl[4];
       {
-        float pv[2][4], pr[2][4], pq[2][4];
+        float pv[2][4], pr[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
@@ -311,7 +311,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             pv[nt][c] = exp2f(sacc[nt][c] - m_use[c >> 1]);
             l_run[c >> 1] += pv[nt][c];
             pr[nt][c] = pv[nt][c] - bf16_round(pv[nt][c]);
-            pq[nt][c] = pr[nt][c] - bf16_round(pr[nt][c]);
           }
         }
         pf[0] = pack_bf16x2(pv[0][0], pv[0][1]);
@@ -322,10 +321,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         pl[1] = pack_bf16x2(pr[0][2], pr[0][3]);
         pl[2] = pack_bf16x2(pr[1][0], pr[1][1]);
         pl[3] = pack_bf16x2(pr[1][2], pr[1][3]);
-        pt[0] = pack_bf16x2(pq[0][0], pq[0][1]);
-        pt[1] = pack_bf16x2(pq[0][2], pq[0][3]);
-        pt[2] = pack_bf16x2(pq[1][0], pq[1][1]);
-        pt[3] = pack_bf16x2(pq[1][2], pq[1][3]);
       }
 #pragma unroll
       for (int i2 = 0; i2 < D / 8; ++i2) {
@@ -346,10 +341,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         ldmatrix_x4_trans(vbase + sub * C::kSubBytes + ((chunk16 ^ (v_row & 7)) << 4), b0, b1, b2, b3);
         mma_bf16_16816(oacc[dn * 2], pf, b0, b1);
         mma_bf16_16816(oacc[dn * 2], pl, b0, b1);
-        mma_bf16_16816(oacc[dn * 2], pt, b0, b1);
         mma_bf16_16816(oacc[dn * 2 + 1], pf, b2, b3);
         mma_bf16_16816(oacc[dn * 2 + 1], pl, b2, b3);
-        mma_bf16_16816(oacc[dn * 2 + 1], pt, b2, b3);
       }
     }
     __syncwarp();

@@ -276,7 +276,7 @@ def test_paged_decode_attention(ops, nkv, G, D, chunk, kv_lens, splits, fused):
     for r, kl in enumerate(kv_lens):
         if kl == 0:
             assert torch.all(out[r] == 0)
-    # P is carried as three bf16 terms, so the output is that of an fp32 softmax up to the final rounding
+    # P is carried as hi + lo bf16 terms: close to an fp32 softmax, far inside flash-attn's own bf16-P error
     err = rel_l2(out, ref)
     assert err < 1.5e-3, err
 

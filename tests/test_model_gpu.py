@@ -170,7 +170,9 @@ def test_c0_tiny_gpt_matches_bf16_oracle():
     # config 0 (LayerNorm, learned positions, GELU, biases, MHA d=64).  The reference trace is fp32; the
     # CUDA path computes in bf16, so the checker here is the oracle run in bf16 on the same weights.
     z = np.load(os.path.join(GOLDEN, "c0_fp32.npz"))
-    meta = json.loads(str(z["meta"]))
+    # the fixture used 16-token chunks; the attention kernel streams 64-token tiles, so chunks are a
+    # multiple of 64 (the reference's flash-attn path needs a multiple of 256).  Chunking does not change logits.
+    meta = dict(json.loads(str(z["meta"])), chunk_size_tokens=64)
     oracle_model, _ = build_oracle_model(meta, torch.bfloat16)
     trace = {k: z[k] for k in z.files if k.startswith("prompt_")}
     prompts = [z[f"prompt_{i}"] for i in range(len(meta["prompt_lengths"]))]
