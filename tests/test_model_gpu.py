@@ -191,11 +191,14 @@ def test_c0_tiny_gpt_matches_bf16_oracle():
     assert max(state["rel"]) < 8e-3, state["rel"]  # bf16 rounding noise floor, see the llama test
     assert_flips_are_near_ties(state["flips"], 4 * 16)
     # and within the looser FP-format distance of the fp32 reference itself
+    # (only while the bf16 oracle still follows the fp32 run's token trajectory: afterwards the inputs differ)
     fp32_rel = []
     for s in range(16):
         ref = torch.from_numpy(z[f"s{s}_logits"])
-        fp32_rel.append(float((torch.from_numpy(trace[f"s{s}_logits"]) - ref).norm() / ref.norm()))
-    assert max(fp32_rel) < 2e-2
+        fp32_rel.append(float((state["logits"][s] - ref).norm() / ref.norm()))
+        if not np.array_equal(trace[f"s{s}_sample"], z[f"s{s}_sample"]):
+            break
+    assert len(fp32_rel) >= 4 and max(fp32_rel) < 2e-2, fp32_rel
 
 
 def test_engine_generate_free_running():
