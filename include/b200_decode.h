@@ -28,7 +28,8 @@ enum {
   B200_ERR_WORKSPACE = -3,        /* workspace too small                                         */
   B200_ERR_LAUNCH = -4,           /* the CUDA runtime refused the launch                         */
   B200_ERR_DRIVER = -5,           /* tensor-map encode entry point missing or failed             */
-  B200_ERR_DEVICE_TIMEOUT = -6    /* a bounded device-side wait gave up (see b200_device_status) */
+  B200_ERR_DEVICE_TIMEOUT = -6,   /* a bounded device-side wait gave up (see b200_device_status) */
+  B200_ERR_SCRATCH_LIMIT = -7     /* the problem needs more scratch than the library's built-in array */
 };
 
 /* Library / ABI version (major*1000 + minor). */
@@ -90,6 +91,30 @@ int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, 
 size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K);
 int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M,
                    int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
+/*
+ * The same GEMM for callers that cannot allocate device memory.  (No counterpart in the reference.)
+ *
+ * Who needs it: code that runs where cudaMalloc is not an option - a latency-critical serving loop that must
+ * not take the allocator's locks or its implicit synchronisation, a server that has given the whole device to
+ * its own memory pool, or a plugin that is handed nothing but input and output pointers.  The split-K scratch that b200_gemm_bf16 takes as `workspace` is here a fixed array inside
+ * the library (b200_gemm_bf16_static_scratch_limit() bytes: 64 KiB of tile counters + 16 MiB of partial sums,
+ * resident on every GPU that loads the library until the process exits).  The call performs no device or host
+ * allocation; the caller still owns x, w, bias and y.
+ *
+ *  - Limit: returns B200_ERR_SCRATCH_LIMIT when b200_gemm_bf16_workspace_bytes(M, N, K) exceeds the array
+ *    (decode shapes with few tokens fit; e.g. M = 256, N = 4096, K = 14336 does not).
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, once per
+ *    device, with that device current).  Make that first call outside any stream capture.
+ *  - Every call uses the same array and finds whatever the last call left in it.  The counter region is
+ *    cleared on `stream` at the start of each call; the partial sums are always fully overwritten before
+ *    they are read.  Two calls whose kernels can overlap on the GPU (different streams without an ordering
+ *    between them) race on the array: order them.
+ *  - Results are bit-identical to b200_gemm_bf16 for the same arguments.
+ */
+size_t b200_gemm_bf16_static_scratch_limit(void);
+int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy,
+                                  int M, int N, int K, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.

@@ -20,6 +20,8 @@ EXPORTED_SYMBOLS = (
     "b200_activation_bf16",
     "b200_gemm_bf16_workspace_bytes",
     "b200_gemm_bf16",
+    "b200_gemm_bf16_static_scratch_limit",
+    "b200_gemm_bf16_static_scratch",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -95,6 +97,10 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_bf16_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                    c_void_p, c_size_t, c_void_p]
+    lib.b200_gemm_bf16_static_scratch_limit.restype = c_size_t
+    lib.b200_gemm_bf16_static_scratch_limit.argtypes = []
+    lib.b200_gemm_bf16_static_scratch.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                                  c_int, c_void_p]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]

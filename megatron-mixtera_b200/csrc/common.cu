@@ -49,6 +49,26 @@ std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 
 }  // namespace
 
+bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
+                       CUtensorMapL2promotion l2) {
+  if (rank < 1 || rank > 4 || out == nullptr) return false;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdims[4];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[4];
+  cuuint32_t estrides[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
+            gstrides, gbox, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, l2,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                                   const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2) {
   if (rank < 1 || rank > 4) return nullptr;
@@ -67,24 +87,10 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
   std::lock_guard<std::mutex> lock(g_map_mutex);
   auto it = g_maps.find(key);
   if (it != g_maps.end()) return it->second;
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return nullptr;
-  // cudaMalloc-free: the descriptor is a 128-byte host object passed to kernels by value.
+  // The descriptor is a 128-byte host object passed to kernels by value; it is kept for the process lifetime.
   CUtensorMap* m = static_cast<CUtensorMap*>(aligned_alloc(64, sizeof(CUtensorMap)));
   if (!m) return nullptr;
-  cuuint64_t gdims[4];
-  cuuint64_t gstrides[4];
-  cuuint32_t gbox[4];
-  cuuint32_t estrides[4] = {1, 1, 1, 1};
-  for (int i = 0; i < rank; ++i) {
-    gdims[i] = dims[i];
-    gbox[i] = box[i];
-    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
-  }
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
-                  gstrides, gbox, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, l2,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
+  if (!encode_tensor_map(m, base, rank, dims, strides_bytes, box, swizzle, l2)) {
     free(m);
     return nullptr;
   }
@@ -120,6 +126,7 @@ const char* b200_error_string(int code) {
     case B200_ERR_LAUNCH: return "kernel launch failed";
     case B200_ERR_DRIVER: return "tensor map could not be encoded";
     case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case B200_ERR_SCRATCH_LIMIT: return "the problem needs more scratch than the library's built-in array holds";
     default: return "unknown error";
   }
 }

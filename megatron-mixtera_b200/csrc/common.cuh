@@ -282,6 +282,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                                   const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2);
 
+// Same encoding into caller-provided storage, without touching the cache (no host allocation).
+bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
+                       CUtensorMapL2promotion l2);
+
 int sm_count();
 
 }  // namespace b200

@@ -305,7 +305,7 @@ static int pick_bt(int M) {
 
 template <int BT>
 static int launch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
-                  int K, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                  int K, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool cache_maps = true) {
   using C = Config<BT>;
   const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
   const uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -313,9 +313,17 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
   const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
   const uint64_t xs[1] = {static_cast<uint64_t>(ldx) * 2};
   const uint32_t xb[2] = {kTileK, BT};
-  const CUtensorMap* mw = get_tensor_map(w, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-  const CUtensorMap* mx = get_tensor_map(x, 2, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-  if (!mw || !mx) return B200_ERR_DRIVER;
+  CUtensorMap local_w, local_x;  // used when the descriptor cache (a host allocation) must be avoided
+  const CUtensorMap* mw = &local_w;
+  const CUtensorMap* mx = &local_x;
+  if (cache_maps) {
+    mw = get_tensor_map(w, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    mx = get_tensor_map(x, 2, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (!mw || !mx) return B200_ERR_DRIVER;
+  } else if (!encode_tensor_map(&local_w, w, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+             !encode_tensor_map(&local_x, x, 2, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+    return B200_ERR_DRIVER;
+  }
 
   const int n_tiles = (N + kTileN - 1) / kTileN;
   const int m_blocks = (M + BT - 1) / BT;
@@ -378,6 +386,74 @@ int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, 
     case 64: return gemm::launch<64>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
     case 128: return gemm::launch<128>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
     default: return gemm::launch<256>(x, ldx, w, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+  }
+}
+
+}  // extern "C"
+
+// =============================================================================================
+// GEMM for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a GEMM: a
+// latency-critical serving loop that must not take the allocator's locks or its implicit
+// synchronisation, a server that has handed the whole device to a memory pool of its own, or a
+// plugin that only receives input and output pointers from its framework.  For them the split-K scratch (tile counters + fp32 partial sums)
+// lives in the fixed array below instead of a caller workspace.  Every GPU that loads the library
+// pays for the array once, until the process exits.
+// =============================================================================================
+namespace b200 {
+namespace gemm {
+
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(kCounterBytes) + (16u << 20);  // 64 KiB + 16 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// `g_static_scratch` is a device symbol: in host code its name is only a handle, so the device
+// address is looked up once per device (with that device current) and cached.
+static void* static_scratch_address() {
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  return addr[dev];
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" {
+
+size_t b200_gemm_bf16_static_scratch_limit(void) { return b200::gemm::kStaticScratchBytes; }
+
+int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy,
+                                  int M, int N, int K, b200_stream_t stream) {
+  using namespace b200;
+  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return B200_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(w)) return B200_ERR_ALIGNMENT;
+  const size_t need = b200_gemm_bf16_workspace_bytes(M, N, K);
+  if (need > gemm::kStaticScratchBytes) return B200_ERR_SCRATCH_LIMIT;
+  void* scratch = gemm::static_scratch_address();
+  if (scratch == nullptr) return B200_ERR_LAUNCH;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // The tile counters must be zero when the kernel starts.  Kernels leave them zero, but the array is
+  // shared by every call and survives a call that was cut short, so they are cleared each time.
+  if (cudaMemsetAsync(scratch, 0, gemm::kCounterBytes, s) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  const size_t bytes = gemm::kStaticScratchBytes;
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch<32>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);
+    case 64: return gemm::launch<64>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);
+    case 128: return gemm::launch<128>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);
+    default: return gemm::launch<256>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);
   }
 }
 
