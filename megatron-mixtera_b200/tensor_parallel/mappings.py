@@ -22,7 +22,7 @@ def gather_from_tensor_model_parallel_region(x: torch.Tensor, group=None) -> tor
         return x
     group = group or parallel_state.get_tensor_model_parallel_group()
     x = x.contiguous()
-    out = torch.empty((tp, *x.shape), dtype=x.dtype, device=x.device)
+    out = torch.empty((tp * x.shape[0], *x.shape[1:]), dtype=x.dtype, device=x.device)  # rank-major along dim 0
     torch.distributed.all_gather_into_tensor(out, x, group=group)
     # [tp, ..., n] -> [..., tp * n]
-    return out.movedim(0, -2).reshape(*x.shape[:-1], tp * x.shape[-1])
+    return out.view(tp, *x.shape).movedim(0, -2).reshape(*x.shape[:-1], tp * x.shape[-1])

@@ -35,7 +35,7 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         num_query_groups=meta.get("num_query_groups"), kv_channels=meta["kv_channels"],
         ffn_hidden_size=meta["ffn_hidden_size"], normalization="RMSNorm" if llama else "LayerNorm",
         gated_linear_unit=llama, activation="silu" if llama else "gelu", add_bias_linear=not llama,
-        enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0)
+        enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0, tensor_model_parallel_size=meta.get("tp", 1))
     model = GPTModel(cfg, vocab_size=meta["vocab_size"], max_sequence_length=meta["max_sequence_length"],
                      position_embedding_type="rope" if llama else "learned_absolute",
                      rotary_base=meta.get("rotary_base", 10000))
@@ -47,7 +47,8 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         num_attention_heads=cfg.num_query_groups, max_sequence_length=meta["max_sequence_length"],
         buffer_size_gb=meta["buffer_size_gb"], buffer_guaranteed_fraction=0.1,
         chunk_size_tokens=meta["chunk_size_tokens"], max_requests_override=meta["max_requests"],
-        max_tokens_override=meta["max_tokens"], tensor_model_parallel_size=1, num_cuda_graphs=num_cuda_graphs)
+        max_tokens_override=meta["max_tokens"], tensor_model_parallel_size=meta.get("tp", 1),
+        num_cuda_graphs=num_cuda_graphs)
     wrapper = GPTInferenceWrapper(model, InferenceWrapperConfig(hidden_size=cfg.hidden_size, params_dtype=torch.bfloat16,
                                                                 padded_vocab_size=meta["vocab_size"]), ctx)
     return model, ctx, wrapper, TextGenerationController
