@@ -14,7 +14,7 @@ from conftest import GOLDEN, ROOT
 WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 
-def _torchrun(n, mode, out, port, timeout=600):
+def _torchrun(n, mode, out, port, timeout=240):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", TORCHDYNAMO_DISABLE="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER, mode, out]

@@ -123,6 +123,8 @@ def cuda_mode(out_path):
         if ctx.active_token_count > 0:
             state["step"] = step
             ctl.generate_output_tokens_dynamic_batch(sp, -1)
+            if os.environ.get("TP_WORKER_VERBOSE"):
+                print(f"[rank {os.environ.get('RANK', '0')}] step {step} done, decode_only={ctx.is_decode_only()}", file=sys.stderr, flush=True)
         step += 1
     torch.cuda.synchronize()
     assert ops.device_status() == 0
@@ -138,8 +140,15 @@ def cuda_mode(out_path):
         np.savez(out_path, replays=wrapper.graph_replays, **out)
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+        # Not destroy_process_group(): tearing the NCCL communicator down while captured CUDA graphs still
+        # reference it blocks for ever (seen on torch 2.11 / NCCL 2.28); release the graphs and just exit.
+        wrapper._graphs.clear()
+        torch.cuda.synchronize()
 
 
 if __name__ == "__main__":
+    import faulthandler
+
+    # a stuck rank prints where it is and exits instead of waiting for the launcher's timeout
+    faulthandler.dump_traceback_later(int(os.environ.get("TP_WORKER_DEADLINE_S", "150")), exit=True)
     (host_mode if sys.argv[1] == "host" else cuda_mode)(sys.argv[2])
