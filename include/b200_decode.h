@@ -117,6 +117,36 @@ int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, con
                                   int M, int N, int K, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * MXFP8 linears: E4M3 values with one E8M0 (power-of-two) scale per 32 elements along K, for weights and
+ * activations alike; fp32 accumulation on tcgen05 (kind::mxf8f6f4.block_scale), bf16 output.
+ * Replaces the FP8 path of TELayerNormColumnParallelLinear / TERowParallelLinear under the `mxfp8` recipe
+ * (megatron/core/extensions/transformer_engine.py:453-640, 736-828; recipe choice megatron/core/fp8_utils.py:451-468;
+ * the arithmetic itself lives in Transformer Engine 2.7, absent from the reference tree).
+ *
+ * Scale storage ("tile layout"): for a [rows, K] matrix, b200_mxfp8_scale_bytes(rows, K) bytes arranged as
+ * [ceil(rows/128)][K/128][512]; inside a tile the scale of (row r, 32-block b) is byte
+ * (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4).  Scale byte e means 2^(e - 127); a block's scale is the smallest
+ * power of two >= amax / 448.  K must be a multiple of 128.
+ *
+ * b200_quantize_mxfp8    bf16 [rows, K] (row stride ldx) -> q [rows, K] + scales (weights at load; activations
+ *                        whose producer is not fused).
+ * b200_add_norm_mxfp8    b200_add_norm_bf16 whose normalised output is written as MXFP8 instead of bf16
+ *                        (the quantisation of the next linear's input fused into its producer).
+ * b200_activation_mxfp8  b200_activation_bf16 with MXFP8 output (input of fc2).
+ * b200_gemm_mxfp8        y[M, N] = dq(xq)[M, K] * dq(wq)[N, K]^T (+ bias); workspace as for b200_gemm_bf16.
+ */
+size_t b200_mxfp8_scale_bytes(int rows, int K);
+int b200_quantize_mxfp8(const void* x, int64_t ldx, void* q, void* sf, int rows, int K, b200_stream_t stream);
+int b200_add_norm_mxfp8(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                        void* hidden_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
+                        b200_stream_t stream);
+int b200_activation_mxfp8(const void* in, const void* bias, void* q_out, void* sf_out, int rows, int F, int kind,
+                          b200_stream_t stream);
+size_t b200_gemm_mxfp8_workspace_bytes(int M, int N, int K);
+int b200_gemm_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,
+                    int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.
  *
  * qkv        [T, nkv, (g+2)*d] bf16: per KV group g query heads, then the key, then the value

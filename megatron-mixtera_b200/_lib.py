@@ -22,6 +22,12 @@ EXPORTED_SYMBOLS = (
     "b200_gemm_bf16",
     "b200_gemm_bf16_static_scratch_limit",
     "b200_gemm_bf16_static_scratch",
+    "b200_mxfp8_scale_bytes",
+    "b200_quantize_mxfp8",
+    "b200_add_norm_mxfp8",
+    "b200_activation_mxfp8",
+    "b200_gemm_mxfp8_workspace_bytes",
+    "b200_gemm_mxfp8",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -101,6 +107,16 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_bf16_static_scratch_limit.argtypes = []
     lib.b200_gemm_bf16_static_scratch.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                                   c_int, c_void_p]
+    lib.b200_mxfp8_scale_bytes.restype = c_size_t
+    lib.b200_mxfp8_scale_bytes.argtypes = [c_int, c_int]
+    lib.b200_quantize_mxfp8.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_add_norm_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_float, c_void_p]
+    lib.b200_activation_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_gemm_mxfp8_workspace_bytes.restype = c_size_t
+    lib.b200_gemm_mxfp8_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.b200_gemm_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                    c_int, c_void_p, c_size_t, c_void_p]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]

@@ -2,6 +2,8 @@
 // one tensor-map cache, so they are compiled together instead of being device-linked.
 #include "common.cu"
 #include "gemm_bf16.cu"
+#include "gemm_mxfp8.cu"
+#include "quant.cu"
 #include "attention.cu"
 #include "elementwise.cu"
 #include "sampling.cu"

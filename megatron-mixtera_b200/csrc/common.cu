@@ -51,7 +51,7 @@ std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 
 bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                        const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
-                       CUtensorMapL2promotion l2) {
+                       CUtensorMapL2promotion l2, CUtensorMapDataType dtype) {
   if (rank < 1 || rank > 4 || out == nullptr) return false;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
@@ -64,13 +64,14 @@ bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint6
     gbox[i] = box[i];
     if (i + 1 < rank) gstrides[i] = strides_bytes[i];
   }
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
+  return fn(out, dtype, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims,
             gstrides, gbox, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, l2,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2) {
+                                  const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2,
+                                  CUtensorMapDataType dtype) {
   if (rank < 1 || rank > 4) return nullptr;
   MapKey key;
   std::memset(&key, 0, sizeof(key));
@@ -78,7 +79,7 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
   cudaGetDevice(&dev);
   key.words[0] = reinterpret_cast<uint64_t>(base);
   key.words[1] = (static_cast<uint64_t>(rank) << 32) | (static_cast<uint64_t>(swizzle) << 16) |
-                 (static_cast<uint64_t>(l2) << 8) | static_cast<uint64_t>(dev);
+                 (static_cast<uint64_t>(l2) << 8) | static_cast<uint64_t>(dev) | (static_cast<uint64_t>(dtype) << 40);
   for (int i = 0; i < rank; ++i) {
     key.words[2 + i] = dims[i];
     key.words[6 + i] = i + 1 < rank ? strides_bytes[i] : 0;
@@ -90,7 +91,7 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
   // The descriptor is a 128-byte host object passed to kernels by value; it is kept for the process lifetime.
   CUtensorMap* m = static_cast<CUtensorMap*>(aligned_alloc(64, sizeof(CUtensorMap)));
   if (!m) return nullptr;
-  if (!encode_tensor_map(m, base, rank, dims, strides_bytes, box, swizzle, l2)) {
+  if (!encode_tensor_map(m, base, rank, dims, strides_bytes, box, swizzle, l2, dtype)) {
     free(m);
     return nullptr;
   }

@@ -156,6 +156,47 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Block-scaled FP8 UMMA (kind::mxf8f6f4): D (+)= (A * 2^sfa) * (B * 2^sfb), one E8M0 scale per row per
+// 32 elements of K (= one instruction), scales read from tensor memory.
+__device__ __forceinline__ void umma_mxf8_block_scaled(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                       uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// Shared memory -> tensor memory copy of a 32-row x 16-byte scale-factor tile, replicated into the four
+// 32-lane quadrants.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Descriptor of such a tile: no swizzle, 8-row x 16-byte core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sf_tile(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;         // descriptor version
+  return d;
+}
+// Instruction descriptor for kind::mxf8f6f4.block_scale: E4M3 x E4M3, E8M0 scales, both operands K-major.
+// sf ids select which byte of the 32-bit scale column belongs to this instruction's 32-wide K block.
+__host__ __device__ constexpr uint32_t umma_idesc_mxf8(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24) |
+         (a_sf_id << 29);
+}
+// 1-D bulk copy global -> shared (16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // Arrives on `bar` once all previously issued UMMAs of this thread have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -280,12 +321,13 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Encodes (and caches per distinct argument set) a tiled tensor map.  Returns nullptr on failure.
 // dims/strides are innermost first; strides[i] is the byte stride of dimension i+1.
 const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                                  const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2);
+                                  const uint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion l2,
+                                  CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
 
 // Same encoding into caller-provided storage, without touching the cache (no host allocation).
 bool encode_tensor_map(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                        const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle,
-                       CUtensorMapL2promotion l2);
+                       CUtensorMapL2promotion l2, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
 
 int sm_count();
 

@@ -1,6 +1,7 @@
 // Memory-bound row kernels of the decode step: embedding / row gather, fused residual-add +
 // RMSNorm / LayerNorm, SwiGLU / GELU.  All use 16-byte vector accesses; one CTA per token row.
 #include "common.cuh"
+#include "quant.cuh"
 
 namespace b200 {
 namespace ew {
@@ -56,7 +57,8 @@ __global__ void __launch_bounds__(256)
 add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
                 const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
-                __nv_bfloat16* __restrict__ normed_out, int hidden, float eps) {
+                __nv_bfloat16* __restrict__ normed_out, int hidden, float eps, uint8_t* __restrict__ q_out,
+                uint8_t* __restrict__ sf_out) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -108,7 +110,7 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       }
     }
   }
-  if (normed_out == nullptr) return;
+  if (normed_out == nullptr && q_out == nullptr) return;
   float mean = 0.f, rstd;
   if (beta != nullptr) {  // LayerNorm: two-pass variance on the cached values
     mean = block_sum(sum, red) / hidden;
@@ -133,10 +135,10 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 #pragma unroll
   for (int it = 0; it < kMaxVec; ++it) {
     const int i = threadIdx.x + it * blockDim.x;
-    if (i < nvec) {
+    const bool valid = i < nvec;
+    float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (valid) {
       const Vec8 g = gv[i];
-      Vec8 o;
-      float y[8];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         y[2 * k] = (vals[it][2 * k] - mean) * rstd * bf16_lo(g.w[k]);
@@ -150,9 +152,17 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
           y[2 * k + 1] += bf16_hi(b.w[k]);
         }
       }
+      if (normed_out) {
+        Vec8 o;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) o.w[k] = pack_bf16x2(y[2 * k], y[2 * k + 1]);
-      reinterpret_cast<Vec8*>(normed_out + off)[i] = o;
+        for (int k = 0; k < 4; ++k) o.w[k] = pack_bf16x2(y[2 * k], y[2 * k + 1]);
+        reinterpret_cast<Vec8*>(normed_out + off)[i] = o;
+      }
+    }
+    if (q_out) {  // quantise the bf16-rounded normalised row (what an unfused quantiser would read)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = bf16_round(y[k]);
+      mx::quantize8(y, valid, blockIdx.x, i * 8, q_out, hidden, sf_out, hidden / 128);
     }
   }
 }
@@ -162,15 +172,18 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 
 // kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
-                                  __nv_bfloat16* __restrict__ out, int F, int kind) {
+                                  __nv_bfloat16* __restrict__ out, int F, int kind, uint8_t* __restrict__ q_out,
+                                  uint8_t* __restrict__ sf_out) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
   const int nvec = F / 8;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
-  if (i >= nvec) return;
+  const bool valid = i < nvec;
   Vec8 o;
-  if (kind == 0) {
+  o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0u;
+  if (!valid) {
+  } else if (kind == 0) {
     const Vec8* row = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * 2 * F);
     const Vec8 g = row[i];
     const Vec8 u = row[nvec + i];
@@ -195,7 +208,16 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __
       o.w[k] = pack_bf16x2(gelu_erf_f(lo), gelu_erf_f(hi));
     }
   }
-  reinterpret_cast<Vec8*>(out + static_cast<int64_t>(r) * F)[i] = o;
+  if (valid && out) reinterpret_cast<Vec8*>(out + static_cast<int64_t>(r) * F)[i] = o;
+  if (q_out) {
+    float y[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      y[2 * k] = bf16_lo(o.w[k]);
+      y[2 * k + 1] = bf16_hi(o.w[k]);
+    }
+    mx::quantize8(y, valid, r, i * 8, q_out, F, sf_out, F / 128);
+  }
 }
 
 }  // namespace ew
@@ -218,14 +240,16 @@ int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int 
                     vocab_start, vocab_end, static_cast<const __nv_bfloat16*>(add_table), add_ids);
 }
 
-int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
-                       void* hidden_out, void* normed_out, int rows, int hidden, float eps, b200_stream_t stream) {
+static int add_norm_impl(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                         void* hidden_out, void* normed_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
+                         b200_stream_t stream) {
   using namespace b200;
   if (!x || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
-  if (normed_out && !gamma) return B200_ERR_INVALID_ARGUMENT;
-  if (!normed_out && !hidden_out) return B200_ERR_INVALID_ARGUMENT;
-  if (hidden % 8 != 0) return B200_ERR_ALIGNMENT;
-  const void* ptrs[] = {x, bias, residual, gamma, beta, hidden_out, normed_out};
+  if ((normed_out || q_out) && !gamma) return B200_ERR_INVALID_ARGUMENT;
+  if (!normed_out && !hidden_out && !q_out) return B200_ERR_INVALID_ARGUMENT;
+  if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
+  if (hidden % 8 != 0 || (q_out && hidden % 128 != 0)) return B200_ERR_ALIGNMENT;
+  const void* ptrs[] = {x, bias, residual, gamma, beta, hidden_out, normed_out, q_out, sf_out};
   for (const void* q : ptrs)
     if (q && !aligned16(q)) return B200_ERR_ALIGNMENT;
   const int nvec = hidden / 8;
@@ -239,27 +263,54 @@ int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, co
   auto Bt = static_cast<const __nv_bfloat16*>(beta);
   auto H = static_cast<__nv_bfloat16*>(hidden_out);
   auto Nn = static_cast<__nv_bfloat16*>(normed_out);
+  auto Q = static_cast<uint8_t*>(q_out);
+  auto SF = static_cast<uint8_t*>(sf_out);
   if (per_thread <= 1)
-    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
   else if (per_thread <= 2)
-    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
   else if (per_thread <= 4)
-    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
   else if (per_thread <= 8)
-    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps);
+    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
   return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
 }
 
-int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind,
-                         b200_stream_t stream) {
+int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                       void* hidden_out, void* normed_out, int rows, int hidden, float eps, b200_stream_t stream) {
+  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, normed_out, nullptr, nullptr, rows, hidden, eps, stream);
+}
+
+int b200_add_norm_mxfp8(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                        void* hidden_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
+                        b200_stream_t stream) {
+  if (!q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, nullptr, q_out, sf_out, rows, hidden, eps, stream);
+}
+
+static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int rows, int F,
+                           int kind, b200_stream_t stream) {
   using namespace b200;
-  if (!in || !out || rows <= 0 || F <= 0 || (kind != 0 && kind != 1)) return B200_ERR_INVALID_ARGUMENT;
-  if (F % 8 != 0 || !aligned16(in) || !aligned16(out) || (bias && !aligned16(bias))) return B200_ERR_ALIGNMENT;
+  if (!in || (!out && !q_out) || rows <= 0 || F <= 0 || (kind != 0 && kind != 1)) return B200_ERR_INVALID_ARGUMENT;
+  if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
+  if (F % 8 != 0 || (q_out && F % 128 != 0) || !aligned16(in) || (out && !aligned16(out)) || (bias && !aligned16(bias)) ||
+      (q_out && (!aligned16(q_out) || !aligned16(sf_out))))
+    return B200_ERR_ALIGNMENT;
   const int nvec = F / 8;
   dim3 grid(rows, (nvec + 255) / 256);
   return launch_pdl(ew::activation_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
-                    static_cast<__nv_bfloat16*>(out), F, kind);
+                    static_cast<__nv_bfloat16*>(out), F, kind, static_cast<uint8_t*>(q_out), static_cast<uint8_t*>(sf_out));
+}
+
+int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind, b200_stream_t stream) {
+  return activation_impl(in, bias, out, nullptr, nullptr, rows, F, kind, stream);
+}
+
+int b200_activation_mxfp8(const void* in, const void* bias, void* q_out, void* sf_out, int rows, int F, int kind,
+                          b200_stream_t stream) {
+  if (!q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
+  return activation_impl(in, bias, nullptr, q_out, sf_out, rows, F, kind, stream);
 }
 
 }  // extern "C"

@@ -50,108 +50,17 @@ struct Params {
   int num_splits;
 };
 
+// Accumulator -> output.  TMEM lane = output feature, TMEM column = token.  Either rounds to bf16 and
+// stores (whole-K units), or stores the fp32 partial tile and lets the CTA that arrives last on the
+// tile's counter sum the partials in split order.
 template <int BT>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Params p) {
-  using C = Config<BT>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
-  uint64_t* empty_bar = full_bar + C::kStages;
-  uint64_t* accum_bar = empty_bar + C::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
-
+__device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, int* last_flag, int n_tile, int split,
+                                         int m_block) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int n_tile = blockIdx.x;
-  const int split = blockIdx.y;
-  const int m_block = blockIdx.z;
   const int n0 = n_tile * kTileN;
   const int m0 = m_block * BT;
-  const int kb_begin = split * p.k_blocks_per_split;
-  const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
-  const int num_kb = kb_end - kb_begin;
-
-  if (tid == 0) {
-    for (int s = 0; s < C::kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    mbar_init(accum_bar, 1);
-    *abort_flag = 0;
-    *last_flag = 0;
-    fence_barrier_init();
-    prefetch_tensormap(&map_w);
-    prefetch_tensormap(&map_x);
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish_alloc_permit();
-  }
-  tcgen05_fence_before_sync();
-  __syncthreads();
-  tcgen05_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  pdl_launch_dependents();
-  if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- TMA producer ----------------
-      // The weights are written by no kernel, so their first tiles are requested before waiting
-      // for the previous kernel on the stream; the activations (its output) only afterwards.
-      const int pre = num_kb < C::kStages ? num_kb : C::kStages;
-      for (int i = 0; i < pre; ++i) {
-        mbar_arrive_expect_tx(&full_bar[i], C::kStageBytes);
-        tma_load_2d(smem + i * C::kStageBytes, &map_w, &full_bar[i], (kb_begin + i) * kTileK, n0);
-      }
-      pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem + i * C::kStageBytes + C::kStageBytesW, &map_x, &full_bar[i], (kb_begin + i) * kTileK, m0);
-      for (int i = pre; i < num_kb; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t phase = (i / C::kStages) & 1;
-        mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
-        uint8_t* stage = smem + s * C::kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
-        const int k0 = (kb_begin + i) * kTileK;
-        tma_load_2d(stage, &map_w, &full_bar[s], k0, n0);
-        tma_load_2d(stage + C::kStageBytesW, &map_x, &full_bar[s], k0, m0);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ---------------- UMMA issuer ----------------
-      constexpr uint32_t idesc = umma_idesc_bf16(kTileN, BT < 16 ? 16 : BT);
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % C::kStages;
-        const uint32_t phase = (i / C::kStages) & 1;
-        mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusGemmTimeout);
-        tcgen05_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
-        const uint32_t b_addr = a_addr + C::kStageBytesW;
-        const uint64_t a_desc = umma_desc_k_major_sw128(a_addr);
-        const uint64_t b_desc = umma_desc_k_major_sw128(b_addr);
-#pragma unroll
-        for (int k = 0; k < kTileK / kUmmaK; ++k) {
-          // 32 bytes per K step inside the 128-byte swizzle row -> +2 in the encoded start address
-          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(&empty_bar[s]);  // frees the stage when these UMMAs have read it
-      }
-      umma_commit(accum_bar);        // accumulator complete
-    }
-    __syncwarp();
-  }
-
-  // ---------------- epilogue: all four warps ----------------
-  pdl_wait();  // outputs, partials and counters may still be in use by the previous kernel until here
-  mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
-  tcgen05_fence_after_sync();
-
   const int n = n0 + warp * 32 + lane;          // output feature held by this thread (TMEM lane)
   const bool n_ok = n < p.N;
   const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
@@ -275,6 +184,112 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (tid == 0) *counter = 0;  // leave the counters zero for the next launch
     }
   }
+
+}
+
+template <int BT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Params p) {
+  using C = Config<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* accum_bar = empty_bar + C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n_tile = blockIdx.x;
+  const int split = blockIdx.y;
+  const int m_block = blockIdx.z;
+  const int n0 = n_tile * kTileN;
+  const int m0 = m_block * BT;
+  const int kb_begin = split * p.k_blocks_per_split;
+  const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      // The weights are written by no kernel, so their first tiles are requested before waiting
+      // for the previous kernel on the stream; the activations (its output) only afterwards.
+      const int pre = num_kb < C::kStages ? num_kb : C::kStages;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full_bar[i], C::kStageBytes);
+        tma_load_2d(smem + i * C::kStageBytes, &map_w, &full_bar[i], (kb_begin + i) * kTileK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * C::kStageBytes + C::kStageBytesW, &map_x, &full_bar[i], (kb_begin + i) * kTileK, m0);
+      for (int i = pre; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
+        uint8_t* stage = smem + s * C::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+        const int k0 = (kb_begin + i) * kTileK;
+        tma_load_2d(stage, &map_w, &full_bar[s], k0, n0);
+        tma_load_2d(stage + C::kStageBytesW, &map_x, &full_bar[s], k0, m0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- UMMA issuer ----------------
+      constexpr uint32_t idesc = umma_idesc_bf16(kTileN, BT < 16 ? 16 : BT);
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusGemmTimeout);
+        tcgen05_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+        const uint32_t b_addr = a_addr + C::kStageBytesW;
+        const uint64_t a_desc = umma_desc_k_major_sw128(a_addr);
+        const uint64_t b_desc = umma_desc_k_major_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kTileK / kUmmaK; ++k) {
+          // 32 bytes per K step inside the 128-byte swizzle row -> +2 in the encoded start address
+          umma_f16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // frees the stage when these UMMAs have read it
+      }
+      umma_commit(accum_bar);        // accumulator complete
+    }
+    __syncwarp();
+  }
+
+  // ---------------- epilogue: all four warps ----------------
+  pdl_wait();  // outputs, partials and counters may still be in use by the previous kernel until here
+  mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
+  tcgen05_fence_after_sync();
+
+  epilogue<BT>(p, tmem_base, last_flag, n_tile, split, m_block);
 
   tcgen05_fence_before_sync();
   __syncthreads();

@@ -1,0 +1,266 @@
+// y[M, N] = dequant(xq, x_sf)[M, K] * dequant(wq, w_sf)[N, K]^T (+ bias): MXFP8 GEMM for decode.
+//
+// Both operands are E4M3 with one E8M0 (power-of-two) scale per 32 elements along K.  The kernel has
+// the structure of the bf16 weight-streaming GEMM (128-row weight tile = UMMA M side, tokens = UMMA
+// N side, TMA ring, split-K with last-arriver reduction, shared epilogue) with two differences:
+//   * one stage is 128 bytes of K per row (128 elements = four 32-wide scale blocks), and
+//   * the MMA is tcgen05.mma kind::mxf8f6f4.block_scale: the scales of a stage (a 512-byte tile per
+//     128 rows) arrive by a 1-D bulk copy, are moved to tensor memory with tcgen05.cp and applied by
+//     the tensor core; the four MMAs of a stage pick their byte of the scale column through the
+//     scale ids of the instruction descriptor.
+//
+// Scale-factor storage ("tile layout", also what the quantisation kernels write): for a matrix with R
+// rows, sf[ceil(R/128)][K/128][512]; inside a tile the scale of (row r, 32-block b) sits at byte
+// (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4) - i.e. the 32-lane x 16-byte image tensor memory wants.
+#include "common.cuh"
+
+namespace b200 {
+namespace gemm {
+
+constexpr int kFp8TileK = 128;  // bytes = elements of K per stage
+constexpr int kSfTileBytes = 512;
+
+template <int BT>
+struct Fp8Config {
+  static constexpr int kSfTilesX = BT > 128 ? 2 : 1;
+  static constexpr int kStageBytesW = kTileN * kFp8TileK;
+  static constexpr int kStageBytesX = BT * kFp8TileK;
+  static constexpr int kOffX = kStageBytesW;
+  static constexpr int kOffSfW = kOffX + kStageBytesX;
+  static constexpr int kOffSfX = kOffSfW + kSfTileBytes;
+  static constexpr int kTxBytes = kOffSfX + kSfTilesX * kSfTileBytes;
+  static constexpr int kStageBytes = (kTxBytes + 1023) / 1024 * 1024;
+  static constexpr int kStages = (BT <= 64) ? 4 : (BT <= 128 ? 3 : 2);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSfCols = 4 + 4 * kSfTilesX;  // tensor-memory columns of one stage's scales
+  static constexpr int kTmemNeeded = BT + kStages * kSfCols;
+  static constexpr int kTmemCols = kTmemNeeded <= 32 ? 32 : kTmemNeeded <= 64 ? 64 : kTmemNeeded <= 128 ? 128
+                                   : kTmemNeeded <= 256 ? 256 : 512;
+};
+
+struct Fp8Operands {
+  const uint8_t* w_sf;  // tile layout, [n tiles][K/128][512]
+  const uint8_t* x_sf;  // tile layout, [ceil(M/128)][K/128][512]
+  int k_tiles;          // K / 128
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Params p,
+                  Fp8Operands q) {
+  using C = Fp8Config<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* accum_bar = empty_bar + C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n_tile = blockIdx.x;
+  const int split = blockIdx.y;
+  const int m_block = blockIdx.z;
+  const int n0 = n_tile * kTileN;
+  const int m0 = m_block * BT;
+  const int kb_begin = split * p.k_blocks_per_split;
+  const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // scale tiles of this CTA: weights -> tile row n_tile; tokens -> tile row m0 / 128 (+1 for BT = 256)
+  const uint8_t* w_sf = q.w_sf + static_cast<int64_t>(n_tile) * q.k_tiles * kSfTileBytes;
+  const uint8_t* x_sf = q.x_sf + static_cast<int64_t>(m0 / 128) * q.k_tiles * kSfTileBytes;
+
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer ----------------
+      auto load_w = [&](int i, int s) {
+        uint8_t* stage = smem + s * C::kStageBytes;
+        tma_load_2d(stage, &map_w, &full_bar[s], (kb_begin + i) * kFp8TileK, n0);
+        bulk_load_1d(stage + C::kOffSfW, w_sf + static_cast<int64_t>(kb_begin + i) * kSfTileBytes, kSfTileBytes,
+                     &full_bar[s]);
+      };
+      auto load_x = [&](int i, int s) {
+        uint8_t* stage = smem + s * C::kStageBytes;
+        tma_load_2d(stage + C::kOffX, &map_x, &full_bar[s], (kb_begin + i) * kFp8TileK, m0);
+#pragma unroll
+        for (int t = 0; t < C::kSfTilesX; ++t)
+          bulk_load_1d(stage + C::kOffSfX + t * kSfTileBytes,
+                       x_sf + (static_cast<int64_t>(t) * q.k_tiles + kb_begin + i) * kSfTileBytes, kSfTileBytes,
+                       &full_bar[s]);
+      };
+      // weights and their scales are written by no kernel: request them before the programmatic wait
+      const int pre = num_kb < C::kStages ? num_kb : C::kStages;
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full_bar[i], C::kTxBytes);
+        load_w(i, i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) load_x(i, i);
+      for (int i = pre; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
+        mbar_arrive_expect_tx(&full_bar[s], C::kTxBytes);
+        load_w(i, s);
+        load_x(i, s);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- UMMA issuer ----------------
+      constexpr int kN = BT < 16 ? 16 : BT;
+      const uint32_t sf_base = tmem_base + BT;                       // scale slots live after the accumulator
+      const uint32_t sfb_col_off = static_cast<uint32_t>((m0 % 128) / 32);  // token rows inside their 128-row tile
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % C::kStages;
+        const uint32_t phase = (i / C::kStages) & 1;
+        mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusGemmTimeout);
+        tcgen05_fence_after_sync();
+        const uint32_t stage_addr = smem_u32(smem + s * C::kStageBytes);
+        const uint32_t sfa = sf_base + s * C::kSfCols;
+        const uint32_t sfb = sfa + 4;
+        tmem_cp_32x128b_warpx4(sfa, umma_desc_sf_tile(stage_addr + C::kOffSfW));
+#pragma unroll
+        for (int t = 0; t < C::kSfTilesX; ++t)
+          tmem_cp_32x128b_warpx4(sfb + 4 * t, umma_desc_sf_tile(stage_addr + C::kOffSfX + t * kSfTileBytes));
+        const uint64_t a_desc = umma_desc_k_major_sw128(stage_addr);
+        const uint64_t b_desc = umma_desc_k_major_sw128(stage_addr + C::kOffX);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // 32 elements = 32 bytes per K step inside the 128-byte swizzle row
+          umma_mxf8_block_scaled(tmem_base, a_desc + 2 * k, b_desc + 2 * k, umma_idesc_mxf8(kTileN, kN, k, k), sfa,
+                                 sfb + sfb_col_off, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  }
+
+  pdl_wait();
+  mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
+  tcgen05_fence_after_sync();
+  epilogue<BT>(p, tmem_base, last_flag, n_tile, split, m_block);
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+template <int BT>
+static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,
+                        int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  using C = Fp8Config<BT>;
+  const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+  const uint64_t ws[1] = {static_cast<uint64_t>(K)};
+  const uint32_t wb[2] = {kFp8TileK, kTileN};
+  const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+  const uint32_t xb[2] = {kFp8TileK, BT};
+  const CUtensorMap* mw = get_tensor_map(wq, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_DATA_TYPE_UINT8);
+  const CUtensorMap* mx = get_tensor_map(xq, 2, xd, ws, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_DATA_TYPE_UINT8);
+  if (!mw || !mx) return B200_ERR_DRIVER;
+  const int n_tiles = (N + kTileN - 1) / kTileN;
+  const int m_blocks = (M + BT - 1) / BT;
+  const int num_kb = K / kFp8TileK;
+  const int splits = choose_splits(n_tiles * m_blocks, num_kb);
+  Params p;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.ldy = ldy;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.num_k_blocks = num_kb;
+  p.k_blocks_per_split = (num_kb + splits - 1) / splits;
+  p.num_splits = splits;
+  p.partials = nullptr;
+  p.counters = nullptr;
+  if (splits > 1) {
+    const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
+    if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
+    p.counters = static_cast<int*>(workspace);
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+  }
+  Fp8Operands q;
+  q.w_sf = static_cast<const uint8_t*>(w_sf);
+  q.x_sf = static_cast<const uint8_t*>(x_sf);
+  q.k_tiles = num_kb;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_mxfp8_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+        cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  dim3 grid(n_tiles, splits, m_blocks);
+  return launch_pdl(gemm_mxfp8_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
+}
+
+}  // namespace gemm
+}  // namespace b200
+
+extern "C" {
+
+size_t b200_mxfp8_scale_bytes(int rows, int K) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0) return 0;
+  // whole 256-row groups, so that a 256-token block of the GEMM can always read two tiles
+  return static_cast<size_t>((rows + 255) / 256) * 2 * (K / 128) * b200::gemm::kSfTileBytes;
+}
+
+size_t b200_gemm_mxfp8_workspace_bytes(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int bt = pick_bt(M);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
+  const int splits = choose_splits(tiles, K / kFp8TileK);
+  if (splits == 1) return static_cast<size_t>(kCounterBytes);
+  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
+}
+
+int b200_gemm_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,
+                    int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream) {
+  using namespace b200;
+  if (!xq || !x_sf || !wq || !w_sf || !y || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 128 != 0 || ldy < N) return B200_ERR_ALIGNMENT;
+  if (!aligned16(xq) || !aligned16(wq) || !aligned16(x_sf) || !aligned16(w_sf)) return B200_ERR_ALIGNMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch_mxfp8<32>(xq, x_sf, wq, w_sf, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    case 64: return gemm::launch_mxfp8<64>(xq, x_sf, wq, w_sf, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    case 128: return gemm::launch_mxfp8<128>(xq, x_sf, wq, w_sf, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    default: return gemm::launch_mxfp8<256>(xq, x_sf, wq, w_sf, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+  }
+}
+
+}  // extern "C"

@@ -138,6 +138,72 @@ def gemm(x, w, bias=None, out=None):
     return out
 
 
+class Mxfp8Tensor:
+    """An MXFP8-quantised [rows, K] matrix: E4M3 bytes + E8M0 scales in the GEMM's tile layout."""
+
+    __slots__ = ("q", "sf", "shape")
+
+    def __init__(self, q: torch.Tensor, sf: torch.Tensor, shape):
+        self.q, self.sf, self.shape = q, sf, tuple(shape)
+
+
+def _mx_buffers(rows: int, K: int, device):
+    q = torch.empty((rows, K), dtype=torch.uint8, device=device)
+    sf = torch.empty((_lib.load().b200_mxfp8_scale_bytes(rows, K),), dtype=torch.uint8, device=device)
+    return q, sf
+
+
+def quantize_mxfp8(x) -> Mxfp8Tensor:
+    """bf16 [..., K] -> MXFP8 (K a multiple of 128)."""
+    _need(x, BF16, "x")
+    K = x.shape[-1]
+    rows = x.numel() // K
+    q, sf = _mx_buffers(rows, K, x.device)
+    check("b200_quantize_mxfp8", _lib.load().b200_quantize_mxfp8(x.data_ptr(), K, q.data_ptr(), sf.data_ptr(), rows, K,
+                                                                 _stream()))
+    return Mxfp8Tensor(q, sf, x.shape)
+
+
+def add_norm_mxfp8(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5, want_hidden: bool = False):
+    """`add_norm` whose normalised output is MXFP8: returns (h or None, Mxfp8Tensor)."""
+    _need(x, BF16, "x")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    h = torch.empty_like(x) if want_hidden else None
+    q, sf = _mx_buffers(rows, hidden, x.device)
+    check("b200_add_norm_mxfp8", _lib.load().b200_add_norm_mxfp8(
+        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(), rows, hidden, eps,
+        _stream()))
+    return h, Mxfp8Tensor(q, sf, x.shape)
+
+
+def activation_mxfp8(x, kind: str, bias=None) -> Mxfp8Tensor:
+    """`activation` with MXFP8 output."""
+    _need(x, BF16, "x")
+    rows = x.numel() // x.shape[-1]
+    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    q, sf = _mx_buffers(rows, F, x.device)
+    check("b200_activation_mxfp8", _lib.load().b200_activation_mxfp8(
+        x.data_ptr(), _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, 0 if kind == "swiglu" else 1, _stream()))
+    return Mxfp8Tensor(q, sf, (*x.shape[:-1], F))
+
+
+def gemm_mxfp8(x: Mxfp8Tensor, w: Mxfp8Tensor, bias=None, out=None):
+    """y = dq(x) @ dq(w).T (+ bias) on the block-scaled FP8 tensor cores; bf16 output."""
+    K = x.shape[-1]
+    M = x.q.shape[0]
+    N = w.q.shape[0]
+    if w.q.shape[1] != K:
+        raise B200Error("gemm_mxfp8", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.q.shape)}")
+    if out is None:
+        out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
+    lib = _lib.load()
+    ws = _workspace.get(x.q.device, "gemm", lib.b200_gemm_mxfp8_workspace_bytes(M, N, K))
+    check("b200_gemm_mxfp8", lib.b200_gemm_mxfp8(x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), _p(bias),
+                                                 out.data_ptr(), N, M, N, K, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
 def attention_workspace(device, num_tokens: int, num_q_heads: int, head_dim: int, num_splits: int):
     nbytes = _lib.load().b200_paged_attention_workspace_bytes(num_tokens, num_q_heads, head_dim, num_splits)
     return _workspace.get(device, "attn", nbytes) if nbytes else None

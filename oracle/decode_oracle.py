@@ -555,24 +555,39 @@ def _to_e4m3(x: torch.Tensor) -> torch.Tensor:
 
 
 def quantize_mxfp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """OCP MX: blocks of 32 along the last dim share a power-of-two scale 2^(e-127), stored E8M0.
+    """MX format: blocks of 32 along the last dim share a power-of-two scale 2^(e-127), stored E8M0.
 
-    Scale exponent = floor(log2(amax)) - 8 (8 = emax of E4M3), clamped to [-127, 127];
-    elements = RNE-saturate(x / scale).  Returns (e4m3 values, uint8 biased exponents).
+    The scale is the smallest power of two >= amax / 448 (rounding the exponent UP, so nothing saturates):
+    this is what Transformer Engine's MXFP8 recipe does; the OCP text rounds down and saturates.  The biased
+    exponent is read off the fp32 bits of amax / 448, +1 if any mantissa bit is set, clamped to 254.
+    elements = RNE-saturate(x / scale).  Returns (e4m3 values, uint8 biased exponents [..., K/32]).
     """
     shp = x.shape
     xb = x.float().reshape(*shp[:-1], shp[-1] // 32, 32)
     amax = xb.abs().amax(dim=-1)
-    e = torch.floor(torch.log2(amax.clamp_min(2.0**-127))) - 8
-    e = torch.where(amax == 0, torch.full_like(e, -127), e).clamp(-127, 127)
-    scale = torch.exp2(e)
-    q = _to_e4m3(xb / scale[..., None]).reshape(shp)
-    return q, (e + 127).to(torch.uint8)
+    bits = (amax / 448.0).view(torch.int32)
+    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).int()
+    e = e.clamp(max=254)
+    inv = torch.ldexp(torch.ones_like(amax), 127 - e)
+    q = _to_e4m3(xb * inv[..., None]).reshape(shp)
+    return q, e.to(torch.uint8)
+
+
+def mxfp8_scales_to_tile_layout(e8m0: torch.Tensor) -> torch.Tensor:
+    """[rows, K/32] scale bytes -> the GEMM's tile layout [ceil(rows/256)*2][K/128][512] (flattened)."""
+    rows, kb = e8m0.shape
+    tiles = -(-rows // 256) * 2
+    out = torch.zeros(tiles, kb // 4, 512, dtype=torch.uint8)
+    r = torch.arange(rows)
+    b = torch.arange(kb)
+    off = ((r % 32) * 16 + ((r % 128) // 32) * 4)[:, None] + (b % 4)[None, :]
+    out[(r // 128)[:, None].expand(rows, kb), (b // 4)[None, :].expand(rows, kb), off] = e8m0
+    return out.reshape(-1)
 
 
 def dequantize_mxfp8(q: torch.Tensor, e8m0: torch.Tensor) -> torch.Tensor:
     shp = q.shape
-    s = torch.exp2(e8m0.float() - 127.0)
+    s = torch.ldexp(torch.ones(e8m0.shape), e8m0.int() - 127)
     return (q.float().reshape(*shp[:-1], shp[-1] // 32, 32) * s[..., None]).reshape(shp)
 
 

@@ -1,0 +1,109 @@
+"""MXFP8 path: quantisers and the block-scaled tcgen05 GEMM against the CPU oracle's restatement
+(E4M3 values, E8M0 scale per 32 elements, scale = smallest power of two >= amax / 448)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import decode_oracle as O
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from megatron_mixtera_b200 import build, ops as _ops
+
+    build.build()
+    yield _ops
+    torch.cuda.synchronize()
+    assert _ops.device_status() == 0
+
+
+def randn(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(BF16)
+
+
+def rel_l2(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def check_quantised(t, x_ref_bf16, exact=True):
+    """`t` (Mxfp8Tensor on the device) against the oracle's quantisation of `x_ref_bf16` [rows, K]."""
+    rows, K = x_ref_bf16.shape
+    q_ref, e_ref = O.quantize_mxfp8(x_ref_bf16)
+    q = t.q.cpu().view(torch.float8_e4m3fn)
+    tiles = O.mxfp8_scales_to_tile_layout(e_ref)
+    sf = t.sf.cpu()
+    assert sf.numel() == tiles.numel()
+    # compare only the bytes that belong to real rows (the rest of a tile is never read for real outputs)
+    mask = O.mxfp8_scales_to_tile_layout(torch.ones_like(e_ref)).bool()
+    if exact:
+        assert torch.equal(sf[mask], tiles[mask])
+        assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    else:
+        assert (sf[mask] != tiles[mask]).float().mean() < 2e-3
+        assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 5e-3
+    return q_ref, e_ref
+
+
+@pytest.mark.parametrize("rows,K", [(1, 128), (64, 4096), (130, 512), (300, 1024)])
+def test_quantize_mxfp8_bit_exact(ops, rows, K):
+    x = randn((rows, K), 1, 3.0)
+    x[0, :32] = 0            # an all-zero block
+    x[-1, -32:] = 448.0      # exactly the E4M3 maximum: scale 2^0, no saturation
+    if rows > 2:
+        x[1, 0] = 1000.0     # forces the round-up of the scale exponent
+    t = ops.quantize_mxfp8(x.cuda())
+    q_ref, e_ref = check_quantised(t, x)
+    assert float(O.dequantize_mxfp8(q_ref, e_ref)[-1, -1]) == 448.0
+    assert rel_l2(O.dequantize_mxfp8(q_ref, e_ref), x) < 0.04
+
+
+@pytest.mark.parametrize(
+    "M,N,K,bias",
+    [
+        (8, 256, 256, False),
+        (64, 1024, 512, True),      # split-K
+        (33, 384, 1024, True),
+        (128, 512, 256, False),     # BT = 128
+        (200, 384, 1024, False),    # BT = 256: two scale tiles per stage
+        (300, 640, 512, True),      # two token blocks
+        (64, 6144, 4096, False),    # Llama-3-8B qkv at decode
+        (64, 4096, 14336, False),   # Llama-3-8B fc2 at decode
+        (16, 20000, 512, False),
+    ],
+)
+def test_gemm_mxfp8_matches_dequantised_product(ops, M, N, K, bias):
+    x, w = randn((M, K), 1), randn((N, K), 2, 0.05)
+    b = randn((N,), 3) if bias else None
+    xq, wq = ops.quantize_mxfp8(x.cuda()), ops.quantize_mxfp8(w.cuda())
+    y = ops.gemm_mxfp8(xq, wq, None if b is None else b.cuda())
+    xd = O.dequantize_mxfp8(*O.quantize_mxfp8(x))
+    wd = O.dequantize_mxfp8(*O.quantize_mxfp8(w))
+    ref = xd @ wd.t()
+    if b is not None:
+        ref = ref.to(BF16).float() + b.float()
+    assert y.shape == (M, N) and y.dtype == BF16
+    # exact products of exactly representable operands, fp32 accumulation: only the output rounding differs
+    assert rel_l2(y, ref) < 3e-3, rel_l2(y, ref)
+    assert (y.cpu() != ref.to(BF16)).float().mean() < 2e-3
+    # and the FP8 format itself stays within the stated 2e-2 of the bf16 product
+    assert rel_l2(y, x.float() @ w.float().t() + (0 if b is None else b.float())) < 4e-2
+    assert torch.equal(ops.gemm_mxfp8(xq, wq, None if b is None else b.cuda()), y)
+
+
+def test_fused_norm_and_activation_quantisers(ops):
+    rows, hidden = 64, 4096
+    x, r = randn((rows, hidden), 1), randn((rows, hidden), 2)
+    g = (1 + randn((hidden,), 3, 0.02).float()).to(BF16)
+    h, t = ops.add_norm_mxfp8(x.cuda(), g.cuda(), residual=r.cuda(), want_hidden=True)
+    assert torch.equal(h.cpu(), x + r)
+    check_quantised(t, F.rms_norm(x + r, (hidden,), g, 1e-5), exact=False)
+    y = randn((17, 2 * 1024), 4, 2.0)
+    a, b = torch.chunk(y, 2, dim=-1)
+    t = ops.activation_mxfp8(y.cuda(), "swiglu")
+    check_quantised(t, F.silu(a) * b, exact=False)
+    assert t.shape == (17, 1024)
