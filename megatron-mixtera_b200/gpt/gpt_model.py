@@ -72,7 +72,8 @@ class GPTModel(torch.nn.Module):
         self.decoder = TransformerBlock(config, transformer_layer_spec)
         self.output_layer = ColumnParallelLinear(
             config.hidden_size, vocab_size, config=config, bias=False, gather_output=not parallel_output,
-            skip_bias_add=False, skip_weight_param_allocation=share_embeddings_and_output_weights)
+            skip_bias_add=False, skip_weight_param_allocation=share_embeddings_and_output_weights,
+            fp8_enabled=False)  # the reference's output layer is a plain bf16 ColumnParallelLinear too
         self.rotary_pos_cos = self.rotary_pos_sin = None
         if position_embedding_type == "rope":
             self.rotary_pos_cos, self.rotary_pos_sin = rope_tables(
@@ -135,6 +136,13 @@ class GPTModel(torch.nn.Module):
             if dst is None or k.endswith("_extra_state"):
                 continue
             dst.copy_(shard_for_rank(k, full[k], rank, tp, gated=self.config.gated_linear_unit))
+        self.quantize_weights()
+
+    def quantize_weights(self) -> None:
+        """(Re)build the FP8 copies of the linear weights; a no-op for bf16 models."""
+        for m in self.modules():
+            if hasattr(m, "quantize_weights") and m is not self:
+                m.quantize_weights()
 
     def init_synthetic_weights(self, seed: int = 0, std: float = 0.02, device=None) -> None:
         """Seeded N(0, std) weights (norm scales 1 + N(0, std)), identical across TP sizes."""
@@ -147,6 +155,7 @@ class GPTModel(torch.nn.Module):
             full = canonical_tensor(k, shape, seed=seed, std=std, dtype=self.config.params_dtype, device=dev)
             own[k].copy_(shard_for_rank(k, full, rank, tp, gated=self.config.gated_linear_unit))
             del full
+        self.quantize_weights()
 
 
 def _partition_dim(key: str) -> Optional[int]:

@@ -21,11 +21,37 @@ def _device():
 
 
 class _ParallelLinearBase(torch.nn.Module):
+    """Shared by the column- and row-parallel linears: optional MXFP8 execution.
+
+    With ``config.fp8 == "mxfp8"`` (and ``fp8_enabled``) the bf16 ``weight`` parameter stays the checkpoint
+    format, and a quantised copy (E4M3 + E8M0 scales) is made by `quantize_weights` - called by the model
+    after weights are loaded, or lazily on the first forward - and streamed by the block-scaled GEMM.  The
+    input may arrive already quantised (`ops.Mxfp8Tensor`, from a producer kernel that fused the
+    quantisation) or as bf16, in which case it is quantised here.
+    """
+
+    fp8 = False
+    _wq = None
+
     def get_extra_state(self):
         return None
 
     def set_extra_state(self, state):
         pass
+
+    def quantize_weights(self) -> None:
+        if self.fp8 and self.weight is not None:
+            self._wq = ops.quantize_mxfp8(self.weight.data)
+
+    def _matmul(self, input_, weight, bias):
+        if self.fp8 and weight is self.weight:
+            if self._wq is None:
+                self.quantize_weights()
+            x = input_ if isinstance(input_, ops.Mxfp8Tensor) else ops.quantize_mxfp8(input_)
+            return ops.gemm_mxfp8(x, self._wq, bias)
+        if isinstance(input_, ops.Mxfp8Tensor):
+            raise ops.B200Error("linear", -1, "got an MXFP8 input but this layer runs in bf16")
+        return ops.gemm(input_, weight, bias)
 
 
 class ColumnParallelLinear(_ParallelLinearBase):
@@ -33,8 +59,9 @@ class ColumnParallelLinear(_ParallelLinearBase):
 
     def __init__(self, input_size, output_size, *, config, init_method=None, bias=True, gather_output=False,
                  skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None,
-                 skip_weight_param_allocation=False, stride=1, **_):
+                 skip_weight_param_allocation=False, stride=1, fp8_enabled=True, **_):
         super().__init__()
+        self.fp8 = fp8_enabled and getattr(config, "fp8", None) == "mxfp8"
         tp = parallel_state.get_tensor_model_parallel_world_size()
         assert output_size % tp == 0, f"output_size {output_size} not divisible by tp {tp}"
         self.input_size, self.output_size = input_size, output_size
@@ -55,7 +82,7 @@ class ColumnParallelLinear(_ParallelLinearBase):
         """``input_`` [..., in] -> ([..., out/tp] or gathered [..., out], bias if ``skip_bias_add``)."""
         w = self.weight if weight is None else weight
         fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add) else None
-        out = ops.gemm(input_, w, fuse_bias)
+        out = self._matmul(input_, w, fuse_bias)
         gather = self.gather_output if runtime_gather_output is None else runtime_gather_output
         if gather:
             out = gather_from_tensor_model_parallel_region(out, self.tp_group)
@@ -66,8 +93,9 @@ class RowParallelLinear(_ParallelLinearBase):
     """Y = X A^T + b with A split along its input columns; partial products are all-reduced."""
 
     def __init__(self, input_size, output_size, *, config, init_method=None, bias=True, input_is_parallel=True,
-                 skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None, **_):
+                 skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None, fp8_enabled=True, **_):
         super().__init__()
+        self.fp8 = fp8_enabled and getattr(config, "fp8", None) == "mxfp8"
         tp = parallel_state.get_tensor_model_parallel_world_size()
         assert input_size % tp == 0, f"input_size {input_size} not divisible by tp {tp}"
         assert input_is_parallel, "the decode path always feeds the row-parallel layer its own shard"
@@ -86,7 +114,7 @@ class RowParallelLinear(_ParallelLinearBase):
         tp = parallel_state.get_tensor_model_parallel_world_size()
         # The bias must be added once, after the reduction: fuse it into the GEMM only at TP=1.
         fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add and tp == 1) else None
-        out = ops.gemm(input_, self.weight, fuse_bias)
+        out = self._matmul(input_, self.weight, fuse_bias)
         if tp > 1:
             out = reduce_from_tensor_model_parallel_region(out, self.tp_group)
             if self.bias is not None and not self.skip_bias_add:

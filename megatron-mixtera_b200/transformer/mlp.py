@@ -31,10 +31,11 @@ class MLP(torch.nn.Module):
 
     def forward(self, hidden_states):
         inter, bias = self.linear_fc1(hidden_states)
+        act = ops.activation_mxfp8 if self.config.fp8 == "mxfp8" else ops.activation
         if self.config.gated_linear_unit:
             if bias is not None:
                 raise NotImplementedError("SwiGLU with an fc1 bias")
-            inter = ops.activation(inter, "swiglu")
+            inter = act(inter, "swiglu")
         else:
-            inter = ops.activation(inter, "gelu", bias)
+            inter = act(inter, "gelu", bias)
         return self.linear_fc2(inter)

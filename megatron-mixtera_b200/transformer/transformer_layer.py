@@ -37,12 +37,13 @@ class TransformerLayer(torch.nn.Module):
     def forward_fused(self, hidden, branch, branch_bias, **attn_kwargs):
         """``hidden`` [T, H] residual stream; ``branch`` the previous layer's MLP output not yet added
         (None for the first layer).  Returns (hidden after the attention residual, MLP output, MLP bias)."""
+        fp8 = self.config.fp8 == "mxfp8"  # the norms then emit the FP8 input of the linear that follows
         if branch is None:
-            normed = self.input_layernorm(hidden)
+            normed = self.input_layernorm(hidden, quantize=fp8)
         else:
-            hidden, normed = self.input_layernorm.add_and_norm(branch, hidden, branch_bias)
+            hidden, normed = self.input_layernorm.add_and_norm(branch, hidden, branch_bias, quantize=fp8)
         attn_out, attn_bias = self.self_attention(normed, **attn_kwargs)
-        hidden, normed = self.pre_mlp_layernorm.add_and_norm(attn_out, hidden, attn_bias)
+        hidden, normed = self.pre_mlp_layernorm.add_and_norm(attn_out, hidden, attn_bias, quantize=fp8)
         mlp_out, mlp_bias = self.mlp(normed)
         return hidden, mlp_out, mlp_bias
 

@@ -407,8 +407,14 @@ def paged_attention(q, k_cache, v_cache, kv_lens, block_table, cu_q=None):
 class GPTOracle:
     """Forward of the local-spec GPT over a ContextOracle (gpt_model.py:279-560, transformer_layer.py:433-660)."""
 
-    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype):
+    def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype,
+                 fp8: Optional[str] = None):
+        """``fp8="mxfp8"``: every decoder linear multiplies MXFP8-quantised inputs by MXFP8-quantised weights
+        with fp32 accumulation (the TE ``mxfp8`` recipe under ``fp8_autocast``, transformer_block.py:629-643);
+        embedding, norms, attention and the output layer stay in ``dtype``."""
         self.s, self.w, self.ctx, self.dtype = spec, weights, ctx, dtype
+        self.fp8 = fp8
+        self._wdq: Dict[str, torch.Tensor] = {}
         nkv = spec.num_query_groups
         self.k_cache = torch.full(
             (spec.num_layers, ctx.chunk_count_total, ctx.chunk_size_tokens, nkv, spec.kv_channels), -1.0, dtype=dtype
@@ -423,7 +429,12 @@ class GPTOracle:
         return F.layer_norm(x, (s.hidden_size,), self.w[prefix + ".weight"], self.w[prefix + ".bias"], s.eps)
 
     def _linear(self, x, prefix, add_bias=True):
-        y = torch.matmul(x, self.w[prefix + ".weight"].t())  # layers.py:333
+        if self.fp8 == "mxfp8":
+            if prefix not in self._wdq:
+                self._wdq[prefix] = dequantize_mxfp8(*quantize_mxfp8(self.w[prefix + ".weight"]))
+            y = torch.matmul(dequantize_mxfp8(*quantize_mxfp8(x)), self._wdq[prefix].t()).to(x.dtype)
+        else:
+            y = torch.matmul(x, self.w[prefix + ".weight"].t())  # layers.py:333
         b = self.w.get(prefix + ".bias")
         if add_bias and b is not None:
             y = y + b
