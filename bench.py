@@ -128,7 +128,7 @@ def build_stack(w, tp: int, seed: int = 0):
         num_layers=w.num_layers, hidden_size=w.hidden_size, num_attention_heads=w.num_attention_heads,
         num_query_groups=w.num_query_groups, kv_channels=w.kv_channels, ffn_hidden_size=w.ffn_hidden_size,
         normalization="RMSNorm", gated_linear_unit=True, activation="silu", add_bias_linear=False,
-        tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed)
+        tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8)
     model = GPTModel(cfg, vocab_size=w.vocab_size, max_sequence_length=w.max_sequence_length,
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
@@ -149,7 +149,9 @@ def build_stack(w, tp: int, seed: int = 0):
     return model, ctx, wrapper, ctl, engine
 
 
-def algorithmic_gemm_bytes(M, N, K):
+def algorithmic_gemm_bytes(M, N, K, fp8=False):
+    if fp8:  # E4M3 operands + one scale byte per 32 elements, bf16 output
+        return (N * K + M * K) * (1.0 + 1.0 / 32.0) + 2.0 * M * N
     return 2.0 * (N * K + M * K + M * N)
 
 
@@ -181,12 +183,14 @@ def kernel_rooflines(model, ctx, T, peak_gbs):
     gemm_bytes = gemm_time = 0.0
     for name, get in (("linear_qkv", lambda l: l.self_attention.linear_qkv), ("linear_proj", lambda l: l.self_attention.linear_proj),
                       ("linear_fc1", lambda l: l.mlp.linear_fc1), ("linear_fc2", lambda l: l.mlp.linear_fc2)):
-        wts = [get(l).weight for l in layers]
-        N, K = wts[0].shape
+        mods = [get(l) for l in layers]
+        N, K = mods[0].weight.shape
+        fp8 = bool(mods[0].fp8)
         x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
-        y = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
-        sec = sweep(lambda: [ops.gemm(x, wt, out=y) for wt in wts])
-        b = algorithmic_gemm_bytes(T, N, K)
+        if fp8:
+            x = ops.quantize_mxfp8(x)
+        sec = sweep(lambda: [m._matmul(x, m.weight, None) for m in mods])
+        b = algorithmic_gemm_bytes(T, N, K, fp8)
         out[name] = {"us": sec * 1e6, "GB/s": b / sec / 1e9, "frac": b / sec / 1e9 / peak_gbs, "shape": [T, N, K]}
         gemm_bytes += b
         gemm_time += sec
@@ -388,7 +392,7 @@ def run_ours(args, w):
     line = {
         "metric": METRIC, "value": B * steps / dev_s, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": dev_s / steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": "mxfp8 linears (fp32 accumulate), bf16 elsewhere" if w.fp8 else "bf16", "data": "synthetic",
         "config": {"workload": w.name, "concurrent_requests": B, "padded_tokens": T, "parallelism": f"tp{tp}",
                    "l2": "per-step inputs (weights + KV pool) far exceed the 126 MB L2; no flush needed",
                    "mean_context_tokens": float(ctx.kv_seq_lengths_cudagraph_only[:B].float().mean())},
@@ -397,7 +401,7 @@ def run_ours(args, w):
                 "p50_step_ms": statistics.median(step_ms)},
         "gpu_launches": int((graph_launches + 1) * steps),
         "launches_per_step": {"graph_forward": graph_launches, "eager_outside_graph": eager_launches_per_step},
-        "roofline": {"bound": "hbm", "kernel": f"gemm_bf16_kernel (tcgen05, {len(model.decoder.layers)} layers x qkv/proj/fc1/fc2)",
+        "roofline": {"bound": "hbm", "kernel": f"{'gemm_mxfp8_kernel' if w.fp8 else 'gemm_bf16_kernel'} (tcgen05, {len(model.decoder.layers)} layers x qkv/proj/fc1/fc2)",
                      "achieved": g["bytes"] / g["sec"] / 1e9, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": g["bytes"] / g["sec"] / 1e9 / peak, "traffic": GEMM_DRAM_TRAFFIC_PER_LAYER},
         "kernels": kern,
@@ -420,7 +424,8 @@ def step_bytes(w, ctx, B, tp):
     """Algorithmic HBM bytes of one decode step per GPU: every weight once + the resident KV once."""
     H, F, d = w.hidden_size, w.ffn_hidden_size, w.kv_channels
     per_layer = ((w.num_attention_heads + 2 * w.num_query_groups) * d * H + w.num_attention_heads * d * H + 3 * F * H) // tp
-    weights = 2.0 * (w.num_layers * per_layer + w.vocab_size * H // tp)
+    bytes_per_weight = (1.0 + 1.0 / 32.0) if w.fp8 else 2.0
+    weights = bytes_per_weight * w.num_layers * per_layer + 2.0 * (w.vocab_size * H // tp)
     kv = float(ctx.kv_seq_lengths_cudagraph_only[:B].sum()) * 2 * (w.num_query_groups // tp) * d * 2 * w.num_layers
     return weights + kv
 
@@ -431,12 +436,13 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "smoke"])
+    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "smoke"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     from megatron_mixtera_b200 import configs
 
-    w = configs.LLAMA3_8B_BF16_64REQ if args.workload == "llama3_8b" else configs.LLAMA3_8B_SHAPE_2LAYER
+    w = {"llama3_8b": configs.LLAMA3_8B_BF16_64REQ, "llama3_8b_mxfp8": configs.LLAMA3_8B_MXFP8_128REQ,
+         "smoke": configs.LLAMA3_8B_SHAPE_2LAYER}[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
     else:

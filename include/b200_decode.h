@@ -85,8 +85,9 @@ int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, 
  * Replaces ColumnParallelLinear.forward / RowParallelLinear.forward local GEMM
  * (megatron/core/tensor_parallel/layers.py:317-336, 946-1043, 1225-1281; torch.matmul(x, W.t())).
  * The all-reduce of the row-parallel variant stays with the caller.
- * `workspace`: split-K partial sums + tile counters, see b200_gemm_bf16_workspace_bytes; the
- * counter region (the first 64 KiB) must be zero before the first call and is left zero.
+ * `workspace`: split-K partial sums (fp32), see b200_gemm_bf16_workspace_bytes; its contents need no
+ * initialisation (the first 64 KiB are reserved).  When K is split a second kernel on the same stream sums the
+ * partials in a fixed order, so results are deterministic.
  */
 size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K);
 int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M,
@@ -98,7 +99,7 @@ int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, 
  * Who needs it: code that runs where cudaMalloc is not an option - a latency-critical serving loop that must
  * not take the allocator's locks or its implicit synchronisation, a server that has given the whole device to
  * its own memory pool, or a plugin that is handed nothing but input and output pointers.  The split-K scratch that b200_gemm_bf16 takes as `workspace` is here a fixed array inside
- * the library (b200_gemm_bf16_static_scratch_limit() bytes: 64 KiB of tile counters + 16 MiB of partial sums,
+ * the library (b200_gemm_bf16_static_scratch_limit() bytes: 64 KiB reserved + 16 MiB of partial sums,
  * resident on every GPU that loads the library until the process exits).  The call performs no device or host
  * allocation; the caller still owns x, w, bias and y.
  *
@@ -106,9 +107,8 @@ int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, 
  *    (decode shapes with few tokens fit; e.g. M = 256, N = 4096, K = 14336 does not).
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, once per
  *    device, with that device current).  Make that first call outside any stream capture.
- *  - Every call uses the same array and finds whatever the last call left in it.  The counter region is
- *    cleared on `stream` at the start of each call; the partial sums are always fully overwritten before
- *    they are read.  Two calls whose kernels can overlap on the GPU (different streams without an ordering
+ *  - Every call uses the same array and finds whatever the last call left in it.  Nothing in it has to start
+ *    at zero: the partial sums of a call are always fully overwritten before they are read.  Two calls whose kernels can overlap on the GPU (different streams without an ordering
  *    between them) race on the array: order them.
  *  - Results are bit-identical to b200_gemm_bf16 for the same arguments.
  */

@@ -21,6 +21,7 @@ class Workload:
     chunk_size_tokens: int = 256
     rotary_base: float = 500000.0
     log_uniform_lengths: bool = False
+    fp8: str = None  # None (bf16 linears) or "mxfp8"
 
     @property
     def max_sequence_length(self) -> int:
@@ -39,3 +40,11 @@ LLAMA3_8B_SHAPE_2LAYER = Workload(
     name="llama3-8b-shape cut to 2 layers, 64 requests, prompt U[128,2048]", num_layers=2, hidden_size=4096,
     num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256,
     num_requests=64, prompt_len_range=(128, 2048), num_tokens_to_generate=24)
+
+# The same shape with MXFP8 linears (E4M3 values, E8M0 scale per 32-element block), bf16 KV cache,
+# 128 concurrent requests, prompts uniform in [256, 4096].
+LLAMA3_8B_MXFP8_128REQ = Workload(
+    name="llama3-8b-shape MXFP8 linears + bf16 KV decode, 128 requests, prompt U[256,4096], 256 greedy tokens, KV chunk 256",
+    num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
+    ffn_hidden_size=14336, vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096),
+    num_tokens_to_generate=256, fp8="mxfp8")

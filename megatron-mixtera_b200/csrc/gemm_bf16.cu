@@ -13,8 +13,9 @@
 //   warps 0-3       : epilogue      - tcgen05.ld, then either bf16 store or split-K partial store
 //
 // Small N (e.g. out-proj, 32 tiles) cannot fill 148 SMs with whole-K units, so K is split across
-// CTAs.  Partials go to an fp32 workspace; the CTA that arrives last on the tile's counter sums the
-// partials in split order (deterministic, no spinning) and writes bf16.
+// CTAs.  Partials go to an fp32 workspace and a second, fully parallel kernel sums them in split
+// order (deterministic) and writes bf16.  (A "last CTA to arrive reduces its tile" scheme was tried
+// first: correct, but the single reducing CTA cost 3 - 6 us per GEMM.)
 #include "common.cuh"
 
 namespace b200 {
@@ -50,9 +51,67 @@ struct Params {
   int num_splits;
 };
 
+// Sum of the split-K partial tiles: y[m, n] = bf16(sum_s partial[s][m][n]) (+ bias), splits added in order
+// (deterministic).  One thread per four consecutive features; all CTAs of the grid work in parallel, which
+// is what a single "last arriver" CTA cannot offer.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partials, int splits, int M, int N, const __nv_bfloat16* __restrict__ bias,
+                     __nv_bfloat16* __restrict__ y, int64_t ldy) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t split_stride = static_cast<int64_t>(M) * N;
+  if ((N & 3) == 0) {
+    const int nq = N >> 2;
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<int64_t>(M) * nq) return;
+    const int m = static_cast<int>(idx / nq);
+    const int n = static_cast<int>(idx - static_cast<int64_t>(m) * nq) * 4;
+    const float* src = partials + static_cast<int64_t>(m) * N + n;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + s * split_stride));
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    if (bias != nullptr) {  // bias is added to the bf16-rounded product, as `matmul(x, w.t()) + bias` does
+      acc.x = bf16_round(acc.x) + __bfloat162float(bias[n]);
+      acc.y = bf16_round(acc.y) + __bfloat162float(bias[n + 1]);
+      acc.z = bf16_round(acc.z) + __bfloat162float(bias[n + 2]);
+      acc.w = bf16_round(acc.w) + __bfloat162float(bias[n + 3]);
+    }
+    __nv_bfloat16* dst = y + static_cast<int64_t>(m) * ldy + n;
+    if ((ldy & 3) == 0) {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    } else {
+      dst[0] = __float2bfloat16_rn(acc.x);
+      dst[1] = __float2bfloat16_rn(acc.y);
+      dst[2] = __float2bfloat16_rn(acc.z);
+      dst[3] = __float2bfloat16_rn(acc.w);
+    }
+  } else {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= split_stride) return;
+    const int m = static_cast<int>(idx / N);
+    const int n = static_cast<int>(idx - static_cast<int64_t>(m) * N);
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += __ldcg(partials + s * split_stride + idx);
+    if (bias != nullptr) acc = bf16_round(acc) + __bfloat162float(bias[n]);
+    y[static_cast<int64_t>(m) * ldy + n] = __float2bfloat16_rn(acc);
+  }
+}
+
+static int launch_splitk_reduce(const Params& p, cudaStream_t stream) {
+  const int64_t work = (p.N & 3) == 0 ? static_cast<int64_t>(p.M) * (p.N >> 2) : static_cast<int64_t>(p.M) * p.N;
+  const unsigned blocks = static_cast<unsigned>((work + 255) / 256);
+  return launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(p.partials),
+                    p.num_splits, p.M, p.N, p.bias, p.y, p.ldy);
+}
+
 // Accumulator -> output.  TMEM lane = output feature, TMEM column = token.  Either rounds to bf16 and
-// stores (whole-K units), or stores the fp32 partial tile and lets the CTA that arrives last on the
-// tile's counter sum the partials in split order.
+// stores (whole-K units), or stores the fp32 partial tile for splitk_reduce_kernel.
 template <int BT>
 __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, int* last_flag, int n_tile, int split,
                                          int m_block) {
@@ -100,89 +159,8 @@ __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, in
         }
       }
     }
-    // Publish the partial tile, then count arrivals; the last CTA of this tile reduces.
-    __threadfence();
-    __syncthreads();
-    int* counter = p.counters + (m_block * gridDim.x + n_tile);
-    if (tid == 0) {
-      const int prev = atomicAdd(counter, 1);
-      *last_flag = (prev == p.num_splits - 1) ? 1 : 0;
-    }
-    __syncthreads();
-    if (*last_flag) {
-      __threadfence();
-      // Sum the splits in order.  Lanes cover 4 consecutive features each (16-byte loads), the four
-      // warps take different token rows, and four rows are in flight per thread so that the L2
-      // latency of the S x rows loads is overlapped instead of serialised.
-      const int m_end = min(p.M, m0 + BT);
-      if ((p.N & 3) == 0) {
-        const int nn = n0 + lane * 4;
-        if (nn < p.N) {
-          float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.bias != nullptr)
-            bv = make_float4(__bfloat162float(p.bias[nn]), __bfloat162float(p.bias[nn + 1]),
-                             __bfloat162float(p.bias[nn + 2]), __bfloat162float(p.bias[nn + 3]));
-          const int64_t split_stride = static_cast<int64_t>(p.M) * p.N;
-          for (int mb = m0 + warp; mb < m_end; mb += 16) {
-            float4 acc[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < p.num_splits; ++s) {
-              const float* base = p.partials + s * split_stride + nn;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int m = mb + j * 4;
-                if (m < m_end) {
-                  const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(m) * p.N));
-                  acc[j].x += v.x;
-                  acc[j].y += v.y;
-                  acc[j].z += v.z;
-                  acc[j].w += v.w;
-                }
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int m = mb + j * 4;
-              if (m < m_end) {
-                float4 a = acc[j];
-                if (p.bias != nullptr) {
-                  a.x = bf16_round(a.x) + bv.x;
-                  a.y = bf16_round(a.y) + bv.y;
-                  a.z = bf16_round(a.z) + bv.z;
-                  a.w = bf16_round(a.w) + bv.w;
-                }
-                __nv_bfloat16* dst = p.y + static_cast<int64_t>(m) * p.ldy + nn;
-                if ((p.ldy & 3) == 0) {
-                  uint2 o;
-                  o.x = pack_bf16x2(a.x, a.y);
-                  o.y = pack_bf16x2(a.z, a.w);
-                  *reinterpret_cast<uint2*>(dst) = o;
-                } else {
-                  dst[0] = __float2bfloat16_rn(a.x);
-                  dst[1] = __float2bfloat16_rn(a.y);
-                  dst[2] = __float2bfloat16_rn(a.z);
-                  dst[3] = __float2bfloat16_rn(a.w);
-                }
-              }
-            }
-          }
-        }
-      } else {
-        const int nn = n0 + tid;  // coalesced: consecutive threads, consecutive features
-        if (nn < p.N) {
-          const float b = p.bias != nullptr ? __bfloat162float(p.bias[nn]) : 0.f;
-          for (int m = m0; m < m_end; ++m) {
-            float acc = 0.f;
-            for (int s = 0; s < p.num_splits; ++s)
-              acc += __ldcg(&p.partials[(static_cast<int64_t>(s) * p.M + m) * p.N + nn]);
-            if (p.bias != nullptr) acc = bf16_round(acc) + b;
-            p.y[static_cast<int64_t>(m) * p.ldy + nn] = __float2bfloat16_rn(acc);
-          }
-        }
-      }
-      if (tid == 0) *counter = 0;  // leave the counters zero for the next launch
-    }
+    // The partial tile is complete once this kernel ends; splitk_reduce_kernel (launched right behind) sums
+    // the splits of every output element in split order.
   }
 
 }
@@ -371,7 +349,9 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
     attr_set = true;
   }
   dim3 grid(n_tiles, splits, m_blocks);
-  return launch_pdl(gemm_bf16_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p);
+  const int rc = launch_pdl(gemm_bf16_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p);
+  if (rc != B200_OK || splits == 1) return rc;
+  return launch_splitk_reduce(p, stream);
 }
 
 }  // namespace gemm
@@ -457,12 +437,8 @@ int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, con
   void* scratch = gemm::static_scratch_address();
   if (scratch == nullptr) return B200_ERR_LAUNCH;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // The tile counters must be zero when the kernel starts.  Kernels leave them zero, but the array is
-  // shared by every call and survives a call that was cut short, so they are cleared each time.
-  if (cudaMemsetAsync(scratch, 0, gemm::kCounterBytes, s) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return B200_ERR_LAUNCH;
-  }
+  // Nothing in the array has to start at zero: the partial sums of a call are completely written by the
+  // GEMM kernel before the reduction kernel of the same call reads them (the first 64 KiB are reserved).
   const size_t bytes = gemm::kStaticScratchBytes;
   switch (gemm::pick_bt(M)) {
     case 32: return gemm::launch<32>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);

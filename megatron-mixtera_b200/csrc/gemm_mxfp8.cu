@@ -224,7 +224,9 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
     attr_set = true;
   }
   dim3 grid(n_tiles, splits, m_blocks);
-  return launch_pdl(gemm_mxfp8_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
+  const int rc = launch_pdl(gemm_mxfp8_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
+  if (rc != B200_OK || splits == 1) return rc;
+  return launch_splitk_reduce(p, stream);
 }
 
 }  // namespace gemm

@@ -35,8 +35,7 @@ def _need(t: torch.Tensor, dtype, name: str) -> None:
 
 
 class _Workspace:
-    """Grow-only device scratch per (device, tag).  The first 64 KiB hold the split-K tile
-    counters, which the kernels leave zeroed, so a fresh buffer is zero-filled."""
+    """Grow-only device scratch per (device, tag) (split-K partial sums, attention split partials)."""
 
     def __init__(self):
         self._buf = {}
