@@ -147,6 +147,28 @@ int b200_gemm_mxfp8(const void* xq, const void* x_sf, const void* wq, const void
                     int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Block-scaled FP8 linears with fp32 scales: E4M3 weights with one scale per 128 x 128 block
+ * (w_scale [ceil(N/128)][K/128]) and E4M3 activations with one scale per token per 128 elements of K
+ * (x_scale [K/128][m_pad], m_pad >= M a multiple of 4); scale = amax / 448, value = RNE-saturate(x / scale).
+ * Replaces the FP8 path of the TE linears under the `blockwise` recipe (Float8BlockScaling,
+ * megatron/core/fp8_utils.py:451-468; arithmetic in Transformer Engine 2.7, absent from the reference tree).
+ * Each 128-wide K block is multiplied on tcgen05 (kind::f8f6f4) into its own TMEM accumulator and promoted
+ * with w_scale * x_scale[token] in fp32 registers.  K must be a multiple of 128.
+ */
+int b200_quantize_fp8_weight_block128(const void* w, void* q, float* scale, int N, int K, b200_stream_t stream);
+int b200_quantize_fp8_rowblock(const void* x, int64_t ldx, void* q, float* scale, int rows, int K, int m_pad,
+                               b200_stream_t stream);
+int b200_add_norm_fp8_rowblock(const void* x, const void* bias, const void* residual, const void* gamma,
+                               const void* beta, void* hidden_out, void* q_out, float* scale_out, int m_pad, int rows,
+                               int hidden, float eps, b200_stream_t stream);
+int b200_activation_fp8_rowblock(const void* in, const void* bias, void* q_out, float* scale_out, int m_pad, int rows,
+                                 int F, int kind, b200_stream_t stream);
+size_t b200_gemm_fp8_block_workspace_bytes(int M, int N, int K);
+int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
+                        const void* bias, void* y, int64_t ldy, int M, int N, int K, void* workspace,
+                        size_t workspace_bytes, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.
  *
  * qkv        [T, nkv, (g+2)*d] bf16: per KV group g query heads, then the key, then the value

@@ -28,6 +28,12 @@ EXPORTED_SYMBOLS = (
     "b200_activation_mxfp8",
     "b200_gemm_mxfp8_workspace_bytes",
     "b200_gemm_mxfp8",
+    "b200_quantize_fp8_weight_block128",
+    "b200_quantize_fp8_rowblock",
+    "b200_add_norm_fp8_rowblock",
+    "b200_activation_fp8_rowblock",
+    "b200_gemm_fp8_block_workspace_bytes",
+    "b200_gemm_fp8_block",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -117,6 +123,16 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_mxfp8_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                     c_int, c_void_p, c_size_t, c_void_p]
+    lib.b200_quantize_fp8_weight_block128.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_quantize_fp8_rowblock.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_add_norm_fp8_rowblock.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200_activation_fp8_rowblock.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                 c_void_p]
+    lib.b200_gemm_fp8_block_workspace_bytes.restype = c_size_t
+    lib.b200_gemm_fp8_block_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.b200_gemm_fp8_block.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                        c_int, c_int, c_void_p, c_size_t, c_void_p]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]

@@ -3,6 +3,7 @@
 #include "common.cu"
 #include "gemm_bf16.cu"
 #include "gemm_mxfp8.cu"
+#include "gemm_fp8_block.cu"
 #include "quant.cu"
 #include "attention.cu"
 #include "elementwise.cu"

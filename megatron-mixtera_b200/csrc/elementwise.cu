@@ -58,7 +58,7 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
                 __nv_bfloat16* __restrict__ normed_out, int hidden, float eps, uint8_t* __restrict__ q_out,
-                uint8_t* __restrict__ sf_out) {
+                void* __restrict__ sf_out, int q_mode, int m_pad) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -162,7 +162,7 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     if (q_out) {  // quantise the bf16-rounded normalised row (what an unfused quantiser would read)
 #pragma unroll
       for (int k = 0; k < 8; ++k) y[k] = bf16_round(y[k]);
-      mx::quantize8(y, valid, blockIdx.x, i * 8, q_out, hidden, sf_out, hidden / 128);
+      mx::quantize8_any(q_mode, y, valid, blockIdx.x, i * 8, q_out, hidden, sf_out, hidden / 128, m_pad);
     }
   }
 }
@@ -173,7 +173,7 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 // kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
                                   __nv_bfloat16* __restrict__ out, int F, int kind, uint8_t* __restrict__ q_out,
-                                  uint8_t* __restrict__ sf_out) {
+                                  void* __restrict__ sf_out, int q_mode, int m_pad) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
@@ -216,7 +216,7 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __
       y[2 * k] = bf16_lo(o.w[k]);
       y[2 * k + 1] = bf16_hi(o.w[k]);
     }
-    mx::quantize8(y, valid, r, i * 8, q_out, F, sf_out, F / 128);
+    mx::quantize8_any(q_mode, y, valid, r, i * 8, q_out, F, sf_out, F / 128, m_pad);
   }
 }
 
@@ -241,8 +241,8 @@ int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int 
 }
 
 static int add_norm_impl(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
-                         void* hidden_out, void* normed_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
-                         b200_stream_t stream) {
+                         void* hidden_out, void* normed_out, void* q_out, void* sf_out, int q_mode, int m_pad, int rows,
+                         int hidden, float eps, b200_stream_t stream) {
   using namespace b200;
   if (!x || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
   if ((normed_out || q_out) && !gamma) return B200_ERR_INVALID_ARGUMENT;
@@ -264,32 +264,40 @@ static int add_norm_impl(const void* x, const void* bias, const void* residual, 
   auto H = static_cast<__nv_bfloat16*>(hidden_out);
   auto Nn = static_cast<__nv_bfloat16*>(normed_out);
   auto Q = static_cast<uint8_t*>(q_out);
-  auto SF = static_cast<uint8_t*>(sf_out);
   if (per_thread <= 1)
-    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
+    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
   else if (per_thread <= 2)
-    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
+    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
   else if (per_thread <= 4)
-    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
+    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
   else if (per_thread <= 8)
-    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, SF);
+    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
   return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
 }
 
 int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
                        void* hidden_out, void* normed_out, int rows, int hidden, float eps, b200_stream_t stream) {
-  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, normed_out, nullptr, nullptr, rows, hidden, eps, stream);
+  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, normed_out, nullptr, nullptr, 0, 0, rows, hidden, eps, stream);
 }
 
 int b200_add_norm_mxfp8(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
                         void* hidden_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
                         b200_stream_t stream) {
   if (!q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
-  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, nullptr, q_out, sf_out, rows, hidden, eps, stream);
+  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, nullptr, q_out, sf_out, b200::mx::kQuantMx, 0, rows, hidden,
+                       eps, stream);
 }
 
-static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int rows, int F,
-                           int kind, b200_stream_t stream) {
+int b200_add_norm_fp8_rowblock(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
+                               void* hidden_out, void* q_out, float* scale_out, int m_pad, int rows, int hidden, float eps,
+                               b200_stream_t stream) {
+  if (!q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, nullptr, q_out, scale_out, b200::mx::kQuantBlock128, m_pad,
+                       rows, hidden, eps, stream);
+}
+
+static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int q_mode, int m_pad,
+                           int rows, int F, int kind, b200_stream_t stream) {
   using namespace b200;
   if (!in || (!out && !q_out) || rows <= 0 || F <= 0 || (kind != 0 && kind != 1)) return B200_ERR_INVALID_ARGUMENT;
   if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
@@ -300,17 +308,23 @@ static int activation_impl(const void* in, const void* bias, void* out, void* q_
   dim3 grid(rows, (nvec + 255) / 256);
   return launch_pdl(ew::activation_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
-                    static_cast<__nv_bfloat16*>(out), F, kind, static_cast<uint8_t*>(q_out), static_cast<uint8_t*>(sf_out));
+                    static_cast<__nv_bfloat16*>(out), F, kind, static_cast<uint8_t*>(q_out), sf_out, q_mode, m_pad);
 }
 
 int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind, b200_stream_t stream) {
-  return activation_impl(in, bias, out, nullptr, nullptr, rows, F, kind, stream);
+  return activation_impl(in, bias, out, nullptr, nullptr, 0, 0, rows, F, kind, stream);
 }
 
 int b200_activation_mxfp8(const void* in, const void* bias, void* q_out, void* sf_out, int rows, int F, int kind,
                           b200_stream_t stream) {
   if (!q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
-  return activation_impl(in, bias, nullptr, q_out, sf_out, rows, F, kind, stream);
+  return activation_impl(in, bias, nullptr, q_out, sf_out, b200::mx::kQuantMx, 0, rows, F, kind, stream);
+}
+
+int b200_activation_fp8_rowblock(const void* in, const void* bias, void* q_out, float* scale_out, int m_pad, int rows, int F,
+                                 int kind, b200_stream_t stream) {
+  if (!q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+  return activation_impl(in, bias, nullptr, q_out, scale_out, b200::mx::kQuantBlock128, m_pad, rows, F, kind, stream);
 }
 
 }  // extern "C"

@@ -49,5 +49,39 @@ __device__ __forceinline__ void quantize8(const float (&v)[8], bool valid, int r
   if ((col0 & 31) == 0) sf[sf_offset(row, col0 >> 5, k_tiles)] = static_cast<uint8_t>(e);
 }
 
+// The 128-block recipe: one fp32 scale = amax / 448 per token per 128 elements of K, stored as
+// scale[K/128][m_pad] (block-major, so that the GEMM fetches the scales of a token block with one copy).
+// Lanes 16j .. 16j+15 of the warp hold one 128-element block, 8 consecutive values each.
+__device__ __forceinline__ void quantize8_block128(const float (&v)[8], bool valid, int row, int col0, uint8_t* q,
+                                                   int64_t ldq, float* scale, int m_pad) {
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!valid) return;
+  const float sc = fmaxf(amax / 448.0f, 1e-30f);
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h] / sc, v[4 * h + 1] / sc), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h + 2] / sc, v[4 * h + 3] / sc), __NV_SATFINITE, __NV_E4M3);
+    w[h] = lo | (hi << 16);
+  }
+  *reinterpret_cast<uint2*>(q + static_cast<int64_t>(row) * ldq + col0) = make_uint2(w[0], w[1]);
+  if ((col0 & 127) == 0) scale[static_cast<int64_t>(col0 >> 7) * m_pad + row] = sc;
+}
+
+enum : int { kQuantMx = 1, kQuantBlock128 = 2 };
+
+// Dispatch used by the fused producers: `sf` is the E8M0 tile buffer (mode 1) or the fp32 scale matrix (mode 2).
+__device__ __forceinline__ void quantize8_any(int mode, const float (&v)[8], bool valid, int row, int col0, uint8_t* q,
+                                              int64_t ldq, void* sf, int k_tiles, int m_pad) {
+  if (mode == kQuantMx)
+    quantize8(v, valid, row, col0, q, ldq, static_cast<uint8_t*>(sf), k_tiles);
+  else
+    quantize8_block128(v, valid, row, col0, q, ldq, static_cast<float*>(sf), m_pad);
+}
+
 }  // namespace mx
 }  // namespace b200

@@ -203,6 +203,82 @@ def gemm_mxfp8(x: Mxfp8Tensor, w: Mxfp8Tensor, bias=None, out=None):
     return out
 
 
+class Fp8BlockTensor:
+    """FP8 matrix of the 128-block recipe.  Activations: q [rows, K] + scale [K/128, m_pad] (per token per 128
+    of K); weights: q [N, K] + scale [ceil(N/128), K/128] (per 128 x 128 block)."""
+
+    __slots__ = ("q", "scale", "shape", "m_pad")
+
+    def __init__(self, q, scale, shape, m_pad=0):
+        self.q, self.scale, self.shape, self.m_pad = q, scale, tuple(shape), m_pad
+
+
+def _rowblock_buffers(rows: int, K: int, device):
+    m_pad = (rows + 3) // 4 * 4
+    q = torch.empty((rows, K), dtype=torch.uint8, device=device)
+    scale = torch.empty((K // 128, m_pad), dtype=torch.float32, device=device)
+    return q, scale, m_pad
+
+
+def quantize_fp8_weight_block128(w) -> Fp8BlockTensor:
+    _need(w, BF16, "w")
+    N, K = w.shape
+    q = torch.empty((N, K), dtype=torch.uint8, device=w.device)
+    scale = torch.empty(((N + 127) // 128, K // 128), dtype=torch.float32, device=w.device)
+    check("b200_quantize_fp8_weight_block128", _lib.load().b200_quantize_fp8_weight_block128(
+        w.data_ptr(), q.data_ptr(), scale.data_ptr(), N, K, _stream()))
+    return Fp8BlockTensor(q, scale, w.shape)
+
+
+def quantize_fp8_rowblock(x) -> Fp8BlockTensor:
+    _need(x, BF16, "x")
+    K = x.shape[-1]
+    rows = x.numel() // K
+    q, scale, m_pad = _rowblock_buffers(rows, K, x.device)
+    check("b200_quantize_fp8_rowblock", _lib.load().b200_quantize_fp8_rowblock(
+        x.data_ptr(), K, q.data_ptr(), scale.data_ptr(), rows, K, m_pad, _stream()))
+    return Fp8BlockTensor(q, scale, x.shape, m_pad)
+
+
+def add_norm_fp8_rowblock(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5, want_hidden: bool = False):
+    """`add_norm` whose normalised output is FP8 with per-token 1 x 128 scales."""
+    _need(x, BF16, "x")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    h = torch.empty_like(x) if want_hidden else None
+    q, scale, m_pad = _rowblock_buffers(rows, hidden, x.device)
+    check("b200_add_norm_fp8_rowblock", _lib.load().b200_add_norm_fp8_rowblock(
+        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), scale.data_ptr(), m_pad, rows,
+        hidden, eps, _stream()))
+    return h, Fp8BlockTensor(q, scale, x.shape, m_pad)
+
+
+def activation_fp8_rowblock(x, kind: str, bias=None) -> Fp8BlockTensor:
+    _need(x, BF16, "x")
+    rows = x.numel() // x.shape[-1]
+    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    q, scale, m_pad = _rowblock_buffers(rows, F, x.device)
+    check("b200_activation_fp8_rowblock", _lib.load().b200_activation_fp8_rowblock(
+        x.data_ptr(), _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, 0 if kind == "swiglu" else 1, _stream()))
+    return Fp8BlockTensor(q, scale, (*x.shape[:-1], F), m_pad)
+
+
+def gemm_fp8_block(x: Fp8BlockTensor, w: Fp8BlockTensor, bias=None, out=None):
+    """y = dq(x) @ dq(w).T (+ bias) for the 128-block recipe (fp32 scales promoted per K block)."""
+    K = x.shape[-1]
+    M, N = x.q.shape[0], w.q.shape[0]
+    if w.q.shape[1] != K:
+        raise B200Error("gemm_fp8_block", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.q.shape)}")
+    if out is None:
+        out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
+    lib = _lib.load()
+    ws = _workspace.get(x.q.device, "gemm", lib.b200_gemm_fp8_block_workspace_bytes(M, N, K))
+    check("b200_gemm_fp8_block", lib.b200_gemm_fp8_block(
+        x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), _p(bias), out.data_ptr(), N, M, N,
+        K, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
 def attention_workspace(device, num_tokens: int, num_q_heads: int, head_dim: int, num_splits: int):
     nbytes = _lib.load().b200_paged_attention_workspace_bytes(num_tokens, num_q_heads, head_dim, num_splits)
     return _workspace.get(device, "attn", nbytes) if nbytes else None

@@ -107,3 +107,61 @@ def test_fused_norm_and_activation_quantisers(ops):
     t = ops.activation_mxfp8(y.cuda(), "swiglu")
     check_quantised(t, F.silu(a) * b, exact=False)
     assert t.shape == (17, 1024)
+
+
+# ------------------------------------------------------------------------------------------
+# 128-block recipe (fp32 scales: 128 x 128 weight blocks, 1 x 128 per-token activation blocks)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,K", [(3, 128), (64, 4096), (130, 512)])
+def test_rowblock_quantiser_bit_exact(ops, rows, K):
+    x = randn((rows, K), 1, 3.0)
+    x[0, :128] = 0
+    t = ops.quantize_fp8_rowblock(x.cuda())
+    q_ref, s_ref = O.quantize_fp8_rowblock(x, 128)
+    assert torch.equal(t.q.cpu(), q_ref.view(torch.uint8))
+    assert torch.equal(t.scale.cpu()[:, :rows].t().contiguous(), s_ref)
+
+
+@pytest.mark.parametrize("N,K", [(128, 128), (300, 512), (4096, 4096)])
+def test_weight_block_quantiser_bit_exact(ops, N, K):
+    w = randn((N, K), 2, 0.05)
+    t = ops.quantize_fp8_weight_block128(w.cuda())
+    q_ref, s_ref = O.quantize_fp8_block_weight(w, 128)
+    assert torch.equal(t.scale.cpu(), s_ref)
+    assert torch.equal(t.q.cpu(), q_ref.view(torch.uint8))
+
+
+@pytest.mark.parametrize(
+    "M,N,K,bias",
+    [(8, 256, 256, False), (64, 1024, 512, True), (33, 384, 1024, True), (128, 512, 256, False), (300, 640, 512, True),
+     (64, 6144, 4096, False), (64, 4096, 14336, False), (256, 8192 // 8 * 10 // 8 * 8, 8192, False)],
+)
+def test_gemm_fp8_block_matches_dequantised_product(ops, M, N, K, bias):
+    x, w = randn((M, K), 1), randn((N, K), 2, 0.05)
+    b = randn((N,), 3) if bias else None
+    xq, wq = ops.quantize_fp8_rowblock(x.cuda()), ops.quantize_fp8_weight_block128(w.cuda())
+    y = ops.gemm_fp8_block(xq, wq, None if b is None else b.cuda())
+    xd = O.dequantize_fp8_rowblock(*O.quantize_fp8_rowblock(x, 128), 128)
+    wd = O.dequantize_fp8_block_weight(*O.quantize_fp8_block_weight(w, 128), 128)
+    ref = xd @ wd.t()
+    if b is not None:
+        ref = ref.to(BF16).float() + b.float()
+    assert rel_l2(y, ref) < 3e-3, rel_l2(y, ref)
+    assert rel_l2(y, x.float() @ w.float().t() + (0 if b is None else b.float())) < 4e-2
+    assert torch.equal(ops.gemm_fp8_block(xq, wq, None if b is None else b.cuda()), y)
+
+
+def test_fused_rowblock_quantisers(ops):
+    rows, hidden = 64, 4096
+    x, r = randn((rows, hidden), 1), randn((rows, hidden), 2)
+    g = (1 + randn((hidden,), 3, 0.02).float()).to(BF16)
+    h, t = ops.add_norm_fp8_rowblock(x.cuda(), g.cuda(), residual=r.cuda(), want_hidden=True)
+    assert torch.equal(h.cpu(), x + r)
+    q_ref, s_ref = O.quantize_fp8_rowblock(F.rms_norm(x + r, (hidden,), g, 1e-5), 128)
+    assert (t.q.cpu() != q_ref.view(torch.uint8)).float().mean() < 5e-3
+    assert torch.allclose(t.scale.cpu()[:, :rows].t(), s_ref, rtol=1e-2)
+    y = randn((17, 2 * 1024), 4, 2.0)
+    a, b = torch.chunk(y, 2, dim=-1)
+    t = ops.activation_fp8_rowblock(y.cuda(), "swiglu")
+    q_ref, s_ref = O.quantize_fp8_rowblock(F.silu(a) * b, 128)
+    assert (t.q.cpu() != q_ref.view(torch.uint8)).float().mean() < 5e-3
