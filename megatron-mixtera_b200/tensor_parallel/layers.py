@@ -23,14 +23,15 @@ def _device():
 class _ParallelLinearBase(torch.nn.Module):
     """Shared by the column- and row-parallel linears: optional MXFP8 execution.
 
-    With ``config.fp8 == "mxfp8"`` (and ``fp8_enabled``) the bf16 ``weight`` parameter stays the checkpoint
-    format, and a quantised copy (E4M3 + E8M0 scales) is made by `quantize_weights` - called by the model
-    after weights are loaded, or lazily on the first forward - and streamed by the block-scaled GEMM.  The
-    input may arrive already quantised (`ops.Mxfp8Tensor`, from a producer kernel that fused the
-    quantisation) or as bf16, in which case it is quantised here.
+    With ``config.fp8`` set ("mxfp8": E8M0 scale per 32 elements; "blockwise": fp32 scale per 128 x 128 weight
+    block and per token per 128 of K) and ``fp8_enabled``, the bf16 ``weight`` parameter stays the checkpoint
+    format and a quantised copy is made by `quantize_weights` - called by the model after weights are loaded,
+    or lazily on the first forward - and streamed by the FP8 GEMM.  The input may arrive already quantised
+    (`ops.Mxfp8Tensor` / `ops.Fp8BlockTensor`, from a producer kernel that fused the quantisation) or as
+    bf16, in which case it is quantised here.
     """
 
-    fp8 = False
+    fp8 = None
     _wq = None
 
     def get_extra_state(self):
@@ -41,16 +42,21 @@ class _ParallelLinearBase(torch.nn.Module):
 
     def quantize_weights(self) -> None:
         if self.fp8 and self.weight is not None:
-            self._wq = ops.quantize_mxfp8(self.weight.data)
+            fn = ops.quantize_mxfp8 if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
+            self._wq = fn(self.weight.data)
 
     def _matmul(self, input_, weight, bias):
+        quantised_input = isinstance(input_, (ops.Mxfp8Tensor, ops.Fp8BlockTensor))
         if self.fp8 and weight is self.weight:
             if self._wq is None:
                 self.quantize_weights()
-            x = input_ if isinstance(input_, ops.Mxfp8Tensor) else ops.quantize_mxfp8(input_)
-            return ops.gemm_mxfp8(x, self._wq, bias)
-        if isinstance(input_, ops.Mxfp8Tensor):
-            raise ops.B200Error("linear", -1, "got an MXFP8 input but this layer runs in bf16")
+            if self.fp8 == "mxfp8":
+                x = input_ if quantised_input else ops.quantize_mxfp8(input_)
+                return ops.gemm_mxfp8(x, self._wq, bias)
+            x = input_ if quantised_input else ops.quantize_fp8_rowblock(input_)
+            return ops.gemm_fp8_block(x, self._wq, bias)
+        if quantised_input:
+            raise ops.B200Error("linear", -1, "got an FP8 input but this layer runs in bf16")
         return ops.gemm(input_, weight, bias)
 
 
@@ -61,7 +67,7 @@ class ColumnParallelLinear(_ParallelLinearBase):
                  skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None,
                  skip_weight_param_allocation=False, stride=1, fp8_enabled=True, **_):
         super().__init__()
-        self.fp8 = fp8_enabled and getattr(config, "fp8", None) == "mxfp8"
+        self.fp8 = getattr(config, "fp8", None) if fp8_enabled else None
         tp = parallel_state.get_tensor_model_parallel_world_size()
         assert output_size % tp == 0, f"output_size {output_size} not divisible by tp {tp}"
         self.input_size, self.output_size = input_size, output_size
@@ -95,7 +101,7 @@ class RowParallelLinear(_ParallelLinearBase):
     def __init__(self, input_size, output_size, *, config, init_method=None, bias=True, input_is_parallel=True,
                  skip_bias_add=False, is_expert=False, tp_comm_buffer_name=None, tp_group=None, fp8_enabled=True, **_):
         super().__init__()
-        self.fp8 = fp8_enabled and getattr(config, "fp8", None) == "mxfp8"
+        self.fp8 = getattr(config, "fp8", None) if fp8_enabled else None
         tp = parallel_state.get_tensor_model_parallel_world_size()
         assert input_size % tp == 0, f"input_size {input_size} not divisible by tp {tp}"
         assert input_is_parallel, "the decode path always feeds the row-parallel layer its own shard"

@@ -31,7 +31,7 @@ class MLP(torch.nn.Module):
 
     def forward(self, hidden_states):
         inter, bias = self.linear_fc1(hidden_states)
-        act = ops.activation_mxfp8 if self.config.fp8 == "mxfp8" else ops.activation
+        act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[self.config.fp8]
         if self.config.gated_linear_unit:
             if bias is not None:
                 raise NotImplementedError("SwiGLU with an fc1 bias")

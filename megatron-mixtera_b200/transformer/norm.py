@@ -22,15 +22,17 @@ class B200Norm(torch.nn.Module):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x, quantize: bool = False):
-        """Normalised rows; with ``quantize`` the output is an `ops.Mxfp8Tensor` for an FP8 linear."""
-        if quantize:
-            return ops.add_norm_mxfp8(x, self.weight, beta=self.bias, eps=self.eps)[1]
-        return ops.add_norm(x, self.weight, beta=self.bias, eps=self.eps)[1]
+    @staticmethod
+    def _op(quantize):
+        return {None: ops.add_norm, False: ops.add_norm, "mxfp8": ops.add_norm_mxfp8,
+                "blockwise": ops.add_norm_fp8_rowblock}[quantize]
 
-    def add_and_norm(self, x, residual, bias=None, quantize: bool = False):
+    def forward(self, x, quantize=None):
+        """Normalised rows; ``quantize`` ("mxfp8" | "blockwise") makes the output the FP8 input of a linear."""
+        return self._op(quantize)(x, self.weight, beta=self.bias, eps=self.eps)[1]
+
+    def add_and_norm(self, x, residual, bias=None, quantize=None):
         """(hidden, normed) with hidden = x (+bias) + residual: the bias-dropout-add of the
         reference (``fused_bias_dropout.py:11-57``, eval mode) fused with the norm that follows it
-        and, with ``quantize``, with the MXFP8 quantisation of the next linear's input."""
-        fn = ops.add_norm_mxfp8 if quantize else ops.add_norm
-        return fn(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps, want_hidden=True)
+        and, with ``quantize``, with the FP8 quantisation of the next linear's input."""
+        return self._op(quantize)(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps, want_hidden=True)

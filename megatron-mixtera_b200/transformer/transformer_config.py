@@ -26,7 +26,7 @@ class TransformerConfig:
     enable_cuda_graph: bool = False
     inference_sampling_seed: int = 42
     init_method_std: float = 0.02
-    fp8: Optional[str] = None                   # None | "mxfp8" (E4M3 + E8M0 scale per 32, weights and activations)
+    fp8: Optional[str] = None                   # None | "mxfp8" (E8M0 scale per 32) | "blockwise" (fp32, 128x128 / 1x128)
 
     def __post_init__(self):
         if self.num_query_groups is None:
@@ -37,8 +37,8 @@ class TransformerConfig:
             self.ffn_hidden_size = 4 * self.hidden_size
         if self.params_dtype != torch.bfloat16:
             raise ValueError("the sm_100a decode kernels compute in bf16 (fp32 accumulation); params_dtype must be bfloat16")
-        if self.fp8 not in (None, "mxfp8"):
-            raise NotImplementedError(f"fp8 recipe {self.fp8!r} (supported: 'mxfp8')")
+        if self.fp8 not in (None, "mxfp8", "blockwise"):
+            raise NotImplementedError(f"fp8 recipe {self.fp8!r} (supported: 'mxfp8', 'blockwise')")
         tp = self.tensor_model_parallel_size
         if self.num_attention_heads % tp or self.num_query_groups % tp:
             raise ValueError("attention heads and query groups must be divisible by the tensor parallel size")

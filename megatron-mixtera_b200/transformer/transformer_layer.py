@@ -37,7 +37,7 @@ class TransformerLayer(torch.nn.Module):
     def forward_fused(self, hidden, branch, branch_bias, **attn_kwargs):
         """``hidden`` [T, H] residual stream; ``branch`` the previous layer's MLP output not yet added
         (None for the first layer).  Returns (hidden after the attention residual, MLP output, MLP bias)."""
-        fp8 = self.config.fp8 == "mxfp8"  # the norms then emit the FP8 input of the linear that follows
+        fp8 = self.config.fp8  # with an FP8 recipe the norms emit the quantised input of the linear that follows
         if branch is None:
             normed = self.input_layernorm(hidden, quantize=fp8)
         else:

@@ -409,8 +409,9 @@ class GPTOracle:
 
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype,
                  fp8: Optional[str] = None):
-        """``fp8="mxfp8"``: every decoder linear multiplies MXFP8-quantised inputs by MXFP8-quantised weights
-        with fp32 accumulation (the TE ``mxfp8`` recipe under ``fp8_autocast``, transformer_block.py:629-643);
+        """``fp8="mxfp8"`` / ``"blockwise"``: every decoder linear multiplies FP8-quantised inputs by FP8-quantised
+        weights with fp32 accumulation (the TE recipes of those names under ``fp8_autocast``,
+        transformer_block.py:629-643; E8M0 scale per 32 elements, resp. fp32 scale per 128 x 128 / 1 x 128 block);
         embedding, norms, attention and the output layer stay in ``dtype``."""
         self.s, self.w, self.ctx, self.dtype = spec, weights, ctx, dtype
         self.fp8 = fp8
@@ -433,6 +434,10 @@ class GPTOracle:
             if prefix not in self._wdq:
                 self._wdq[prefix] = dequantize_mxfp8(*quantize_mxfp8(self.w[prefix + ".weight"]))
             y = torch.matmul(dequantize_mxfp8(*quantize_mxfp8(x)), self._wdq[prefix].t()).to(x.dtype)
+        elif self.fp8 == "blockwise":
+            if prefix not in self._wdq:
+                self._wdq[prefix] = dequantize_fp8_block_weight(*quantize_fp8_block_weight(self.w[prefix + ".weight"]))
+            y = torch.matmul(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x)), self._wdq[prefix].t()).to(x.dtype)
         else:
             y = torch.matmul(x, self.w[prefix + ".weight"].t())  # layers.py:333
         b = self.w.get(prefix + ".bias")

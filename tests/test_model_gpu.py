@@ -226,10 +226,11 @@ def oracle_trace(meta, dtype, fp8=None):
 FP8_LOGIT_TOLERANCE = 2e-2  # stated bar for FP8 logits (relative L2)
 
 
-def test_llama_tiny_mxfp8_matches_fp8_oracle():
+@pytest.mark.parametrize("recipe", ["mxfp8", "blockwise"])
+def test_llama_tiny_fp8_matches_fp8_oracle(recipe):
     z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
-    meta = dict(json.loads(str(z["meta"])), fp8="mxfp8")
-    trace = oracle_trace(meta, torch.bfloat16, fp8="mxfp8")
+    meta = dict(json.loads(str(z["meta"])), fp8=recipe)
+    trace = oracle_trace(meta, torch.bfloat16, fp8=recipe)
     state, gen, _ = run_teacher_forced(meta, trace, enable_cuda_graph=True)
     # Kernel level the FP8 path is exact (bit-exact quantisers, GEMM equal to the fp32 product of the dequantised
     # operands up to the output rounding: tests/test_fp8_gpu.py).  At model level two pipelines that are not
