@@ -189,6 +189,9 @@ int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const v
  *   b200_rope_append for decode steps (one new token per request) inside the same kernel.
  *   num_splits > 1 splits every row's context into that many ranges (flash-decoding) and needs
  *   `workspace` of b200_paged_attention_workspace_bytes.
+ * FP8 pool (kv_cache_fp8; an extension, the reference's pool is always params_dtype): keys and values are
+ *   stored as E4M3 bytes with one fp32 scale per KV head; both kernels quantise what they append
+ *   (RNE-saturate(x / scale)) and the attention kernel converts tiles to f16 on the fly.
  */
 typedef struct {
   const void* qkv;
@@ -216,6 +219,9 @@ typedef struct {
   int32_t num_splits;
   int32_t fuse_rope_append;
   float softmax_scale;    /* 0 = 1/sqrt(d) */
+  int32_t kv_cache_fp8;   /* != 0: k_cache / v_cache hold E4M3 bytes (head_dim 128), value = byte * scale[head] */
+  const float* k_scale;   /* [nkv] fp32, FP8 pool only */
+  const float* v_scale;   /* [nkv] fp32, FP8 pool only */
 } b200_attention_args;
 
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);

@@ -71,6 +71,9 @@ class AttentionArgs(ctypes.Structure):
         ("num_splits", c_int32),
         ("fuse_rope_append", c_int32),
         ("softmax_scale", c_float),
+        ("kv_cache_fp8", c_int32),
+        ("k_scale", c_void_p),
+        ("v_scale", c_void_p),
     ]
 
 

@@ -126,12 +126,16 @@ class DynamicInferenceContext(BaseInferenceContext):
         use_cuda_graphs_for_non_decode_steps: bool = True,
         device: Optional[torch.device] = None,
         allocate_memory_buffer: bool = True,
+        kv_cache_dtype: Optional[torch.dtype] = None,
     ):
         """``num_attention_heads`` is the number of KV heads (query groups), as in the reference.
 
         ``device``: where the KV pool and the kernel-facing index arrays live (default: the current
         CUDA device; pass ``'cpu'`` to exercise the bookkeeping alone).  ``allocate_memory_buffer=False``
-        skips the KV pool for such bookkeeping-only uses.
+        skips the KV pool for such bookkeeping-only uses.  ``kv_cache_dtype=torch.float8_e4m3fn`` (an
+        extension; the reference's pool is always ``params_dtype``) stores keys and values as E4M3 bytes with
+        one fp32 scale per layer and KV head (``kv_scales [L, 2, heads]``, 1.0 until the caller sets them),
+        halving the bytes the attention kernel streams.
         """
         super().__init__(materialize_only_last_token_logits=materialize_only_last_token_logits)
         if cache_mla_latent:
@@ -155,8 +159,12 @@ class DynamicInferenceContext(BaseInferenceContext):
 
         # Chunk geometry (reference :194-217, 285).
         self.chunk_size_tokens = chunk_size_tokens
+        self.kv_cache_dtype = params_dtype if kv_cache_dtype is None else kv_cache_dtype
+        self.kv_cache_fp8 = self.kv_cache_dtype == torch.float8_e4m3fn
+        if self.kv_cache_dtype not in (params_dtype, torch.float8_e4m3fn):
+            raise ValueError("kv_cache_dtype must be params_dtype or torch.float8_e4m3fn")
         self.chunk_size_bytes = (
-            params_dtype.itemsize * 2 * num_layers * chunk_size_tokens * heads_per_partition * kv_channels
+            self.kv_cache_dtype.itemsize * 2 * num_layers * chunk_size_tokens * heads_per_partition * kv_channels
         )
         buffer_size_bytes = int(buffer_size_gb * 1024**3)
         buffer_size_bytes -= buffer_size_bytes % self.chunk_size_bytes
@@ -221,13 +229,15 @@ class DynamicInferenceContext(BaseInferenceContext):
 
         # ---- KV pool ----
         self.memory_buffer = None
+        self.kv_scales = None
         if allocate_memory_buffer:
-            self.memory_buffer = torch.full(
-                (2, num_layers, chunk_count_total, chunk_size_tokens, heads_per_partition, kv_channels),
-                -1,
-                dtype=params_dtype,
-                device=self.device,
-            )
+            shape = (2, num_layers, chunk_count_total, chunk_size_tokens, heads_per_partition, kv_channels)
+            if self.kv_cache_fp8:
+                # raw E4M3 bytes; 0xB8 is -1.0, the fill value of the 16-bit pool
+                self.memory_buffer = torch.full(shape, 0xB8, dtype=torch.uint8, device=self.device)
+                self.kv_scales = torch.ones((num_layers, 2, heads_per_partition), dtype=torch.float32, device=self.device)
+            else:
+                self.memory_buffer = torch.full(shape, -1, dtype=params_dtype, device=self.device)
 
         # ---- CUDA-graph token counts (reference :319-356) ----
         self.cuda_graph_token_counts = None

@@ -72,6 +72,8 @@ class PagedFlashDecodeAttention(torch.nn.Module):
             token_to_local_pos=ctx.token_to_local_position_within_kv_chunk, rope_cos=rotary_pos_cos,
             rope_sin=rotary_pos_sin,
         )
+        if getattr(ctx, "kv_cache_fp8", False):  # E4M3 pool: per-head scales of this layer
+            common.update(k_scale=ctx.kv_scales[self.layer_number - 1, 0], v_scale=ctx.kv_scales[self.layer_number - 1, 1])
         if decode:
             # one new token per request: rows are requests, append fused into the attention kernel
             splits = choose_attention_splits(T, self.num_kv_heads, ctx.max_sequence_length, ctx.chunk_size_tokens)

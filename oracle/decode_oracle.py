@@ -374,11 +374,17 @@ def apply_rope(t: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
     return (t * cos_) + (rot * sin_)
 
 
-def paged_attention(q, k_cache, v_cache, kv_lens, block_table, cu_q=None):
+def quantize_kv_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """E4M3 KV-pool entry (extension, not in the reference): RNE-saturate(x / scale[head]); x [T, heads, d]."""
+    return _to_e4m3(x.float() / scale[None, :, None])
+
+
+def paged_attention(q, k_cache, v_cache, kv_lens, block_table, cu_q=None, k_scale=None, v_scale=None):
     """flash-attn paged contract (attention.py:470-601): q [T,nq,d]; caches [chunks,chunk,nkv,d].
 
     fp32 softmax, scale d^-1/2, head h reads KV head h // g, causal bottom-right aligned,
-    rows with kv_len 0 give zeros; output cast to q.dtype.
+    rows with kv_len 0 give zeros; output cast to q.dtype.  With ``k_scale`` / ``v_scale`` (fp32 [heads]) the
+    caches hold E4M3 values that are multiplied by their head's scale.
     """
     T, H, D = q.shape
     Hkv, cs = k_cache.shape[2], k_cache.shape[1]
@@ -393,8 +399,11 @@ def paged_attention(q, k_cache, v_cache, kv_lens, block_table, cu_q=None):
             continue
         nb = math.ceil(kl / cs)
         ids = torch.as_tensor(block_table[r, :nb]).long()
-        kk = k_cache[ids].reshape(-1, Hkv, D)[:kl].float().repeat_interleave(g, 1)
-        vv = v_cache[ids].reshape(-1, Hkv, D)[:kl].float().repeat_interleave(g, 1)
+        kk = k_cache[ids].reshape(-1, Hkv, D)[:kl].float()
+        vv = v_cache[ids].reshape(-1, Hkv, D)[:kl].float()
+        if k_scale is not None:
+            kk, vv = kk * k_scale[None, :, None], vv * v_scale[None, :, None]
+        kk, vv = kk.repeat_interleave(g, 1), vv.repeat_interleave(g, 1)
         qq = q[off : off + ql].float()
         s = torch.einsum("qhd,khd->hqk", qq, kk) * (D**-0.5)
         m = torch.ones(ql, kl, dtype=torch.bool).tril(kl - ql)
@@ -408,7 +417,7 @@ class GPTOracle:
     """Forward of the local-spec GPT over a ContextOracle (gpt_model.py:279-560, transformer_layer.py:433-660)."""
 
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype,
-                 fp8: Optional[str] = None):
+                 fp8: Optional[str] = None, kv_fp8_scale: Optional[float] = None):
         """``fp8="mxfp8"`` / ``"blockwise"``: every decoder linear multiplies FP8-quantised inputs by FP8-quantised
         weights with fp32 accumulation (the TE recipes of those names under ``fp8_autocast``,
         transformer_block.py:629-643; E8M0 scale per 32 elements, resp. fp32 scale per 128 x 128 / 1 x 128 block);
@@ -416,9 +425,13 @@ class GPTOracle:
         self.s, self.w, self.ctx, self.dtype = spec, weights, ctx, dtype
         self.fp8 = fp8
         self._wdq: Dict[str, torch.Tensor] = {}
+        # E4M3 KV pool (extension): every head uses the same scale here; values are kept dequantised in the
+        # caches (byte * scale is exact in fp32), so the attention restatement itself is unchanged
+        self.kv_fp8_scale = kv_fp8_scale
         nkv = spec.num_query_groups
         self.k_cache = torch.full(
-            (spec.num_layers, ctx.chunk_count_total, ctx.chunk_size_tokens, nkv, spec.kv_channels), -1.0, dtype=dtype
+            (spec.num_layers, ctx.chunk_count_total, ctx.chunk_size_tokens, nkv, spec.kv_channels), -1.0,
+            dtype=torch.float32 if kv_fp8_scale is not None else dtype
         )
         self.v_cache = self.k_cache.clone()
         self.freqs = rope_freqs(spec.max_sequence_length, spec.kv_channels, spec.rotary_base) if spec.llama else None
@@ -469,8 +482,12 @@ class GPTOracle:
             v = qkv[..., (g + 1) * d :]
             if s.llama:
                 k = apply_rope(k, self.freqs[pos_in_req])  # dynamic_context.py:600-631
-            self.k_cache[l][chunk_idx, local] = k  # dynamic_context.py:511-545
-            self.v_cache[l][chunk_idx, local] = v
+            if self.kv_fp8_scale is not None:
+                sc = torch.full((nkv,), self.kv_fp8_scale)
+                k = (quantize_kv_fp8(k, sc).float() * self.kv_fp8_scale).to(torch.float32)
+                v = (quantize_kv_fp8(v, sc).float() * self.kv_fp8_scale).to(torch.float32)
+            self.k_cache[l][chunk_idx, local] = k.to(self.k_cache.dtype)  # dynamic_context.py:511-545
+            self.v_cache[l][chunk_idx, local] = v.to(self.v_cache.dtype)
             if s.llama:
                 q = apply_rope(q, self.freqs[pos])  # dynamic_context.py:566-598
             o = paged_attention(q, self.k_cache[l], self.v_cache[l], c.kv_seq_lengths, c.block_table, cu_q)

@@ -316,3 +316,61 @@ def test_attention_split_invariance_at_long_context(ops):
     assert rel_l2(o16, o1) < 4e-3  # two bf16 roundings of outputs that differ only in summation order
     ref, _, _ = oracle_decode_attention(c)
     assert rel_l2(o16, ref) < 5e-3
+
+
+# ------------------------------------------------------------------------------------------
+# FP8 (E4M3) KV pool with one scale per KV head (an extension beyond the reference)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize(
+    "nkv,G,chunk,kv_lens,splits",
+    [(2, 4, 64, [1, 64, 65, 130, 0, 300, 17, 256], 1), (2, 4, 64, [1, 64, 65, 130, 0, 300, 17, 256], 3),
+     (8, 4, 256, [2304, 128, 700, 1216, 0], 2), (1, 8, 256, [5000, 257], 4)],
+)
+@pytest.mark.parametrize("fused", [True, False])
+def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused):
+    D = 128
+    c = make_paged_case(T=len(kv_lens), nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=kv_lens, seed=21)
+    g = torch.Generator().manual_seed(5)
+    k_scale = 0.01 + 0.02 * torch.rand(nkv, generator=g)
+    v_scale = 0.01 + 0.02 * torch.rand(nkv, generator=g)
+    # the pool as E4M3 bytes
+    kq = O._to_e4m3(c["k_cache"].float() / k_scale[None, None, :, None])
+    vq = O._to_e4m3(c["v_cache"].float() / v_scale[None, None, :, None])
+    T = c["T"]
+    qkv = c["qkv"]
+    q = O.apply_rope(qkv[..., : G * D].reshape(T, nkv * G, D), c["freqs"][c["pos"]])
+    k = O.apply_rope(qkv[..., G * D : (G + 1) * D], c["freqs"][c["pos"]])
+    kq_ref, vq_ref = kq.clone(), vq.clone()
+    kq_ref[c["chunk_idx"], c["local"]] = O.quantize_kv_fp8(k, k_scale)
+    vq_ref[c["chunk_idx"], c["local"]] = O.quantize_kv_fp8(qkv[..., (G + 1) * D :], v_scale)
+    ref = O.paged_attention(q, kq_ref, vq_ref, c["kv_lens"], c["block_table"].numpy(), k_scale=k_scale, v_scale=v_scale)
+
+    dev = "cuda"
+    half = c["freqs"][:, : D // 2]
+    cos, sin = torch.cos(half).to(BF16).to(dev), torch.sin(half).to(BF16).to(dev)
+    kc, vc = kq.view(torch.uint8).to(dev), vq.view(torch.uint8).to(dev)
+    out = torch.full((T, c["nq"] * D), float("nan"), dtype=BF16, device=dev)
+    d = {k_: c[k_].to(dev) for k_ in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
+    ks, vs = k_scale.to(dev), v_scale.to(dev)
+    args = ops.make_attention_args(
+        qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
+        num_q_heads=c["nq"], num_kv_heads=nkv, head_dim=D, chunk_size=chunk, token_to_pos_ids=d["pos"],
+        token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
+        rope_cos=cos, rope_sin=sin, num_splits=splits, fuse_rope_append=fused, k_scale=ks, v_scale=vs)
+    if not fused:
+        ops.rope_append(args)
+    ops.paged_attention(args)
+    torch.cuda.synchronize()
+    live = [r for r, kl in enumerate(kv_lens) if kl > 0]
+    for r in live:  # appended bytes: bit-exact
+        ci, lp = int(c["chunk_idx"][r]), int(c["local"][r])
+        assert torch.equal(kc[ci, lp].cpu(), kq_ref.view(torch.uint8)[ci, lp]), r
+        assert torch.equal(vc[ci, lp].cpu(), vq_ref.view(torch.uint8)[ci, lp]), r
+    if fused:
+        mask = torch.ones(kc.shape[:2], dtype=torch.bool)
+        mask[c["chunk_idx"][live], c["local"][live]] = False
+        assert torch.equal(kc.cpu()[mask], kq.view(torch.uint8)[mask])
+    o = out.cpu().view(T, c["nq"], D)
+    assert not torch.isnan(o.float()).any()
+    # same E4M3 pool on both sides: only summation order and the output rounding differ
+    assert rel_l2(o, ref) < 1.5e-3, rel_l2(o, ref)

@@ -49,7 +49,10 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         buffer_size_gb=meta["buffer_size_gb"], buffer_guaranteed_fraction=0.1,
         chunk_size_tokens=meta["chunk_size_tokens"], max_requests_override=meta["max_requests"],
         max_tokens_override=meta["max_tokens"], tensor_model_parallel_size=meta.get("tp", 1),
-        num_cuda_graphs=num_cuda_graphs)
+        num_cuda_graphs=num_cuda_graphs,
+        kv_cache_dtype=torch.float8_e4m3fn if meta.get("kv_fp8_scale") else None)
+    if meta.get("kv_fp8_scale"):
+        ctx.kv_scales.fill_(meta["kv_fp8_scale"])
     wrapper = GPTInferenceWrapper(model, InferenceWrapperConfig(hidden_size=cfg.hidden_size, params_dtype=torch.bfloat16,
                                                                 padded_vocab_size=meta["vocab_size"]), ctx)
     return model, ctx, wrapper, TextGenerationController
@@ -203,10 +206,10 @@ def test_c0_tiny_gpt_matches_bf16_oracle():
     assert len(fp32_rel) >= 4 and max(fp32_rel) < 2e-2, fp32_rel
 
 
-def oracle_trace(meta, dtype, fp8=None):
+def oracle_trace(meta, dtype, fp8=None, kv_fp8_scale=None):
     """Run the CPU oracle on the fixture's prompts and record what the teacher-forced harness needs."""
     z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
-    model, _ = build_oracle_model(meta, dtype, fp8=fp8)
+    model, _ = build_oracle_model(meta, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale)
     n = len(meta["prompt_lengths"])
     trace = {f"prompt_{i}": z[f"prompt_{i}"] for i in range(n)}
 
@@ -250,6 +253,17 @@ def test_llama_tiny_fp8_matches_fp8_oracle(recipe):
         oracle.append(float((torch.from_numpy(trace[f"s{s}_logits"]) - ref).norm() / ref.norm()))
     assert ours and sum(ours) / len(ours) <= 1.1 * sum(oracle) / len(oracle), (ours, oracle)
     assert max(ours) < 0.15  # MXFP8 of a 512-wide toy model is ~10 % away from its bf16 run, ours and the oracle's alike
+
+
+def test_llama_tiny_fp8_kv_pool_matches_oracle():
+    # E4M3 KV pool with per-head scales (an extension: the reference's pool is always params_dtype)
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = dict(json.loads(str(z["meta"])), kv_fp8_scale=2.0**-7)
+    trace = oracle_trace(meta, torch.bfloat16, kv_fp8_scale=meta["kv_fp8_scale"])
+    state, gen, _ = run_teacher_forced(meta, trace, enable_cuda_graph=True)
+    assert max(state["rel"]) < 3.5e-2 and sum(state["rel"]) / len(state["rel"]) < 1.3 * FP8_LOGIT_TOLERANCE, state["rel"]
+    n_dec = sum(len(v) for k, v in trace.items() if k.endswith("_sample"))
+    assert_flips_are_near_ties(state["flips"], n_dec, resolution=2.0**-4)
 
 
 def test_engine_generate_free_running():

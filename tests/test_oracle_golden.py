@@ -155,7 +155,7 @@ def test_context_oracle_reference_update_requests_golden():
         [481, -1, -1, -1], [488, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1]]
 
 
-def build_oracle_model(meta, dtype, fp8=None):
+def build_oracle_model(meta, dtype, fp8=None, kv_fp8_scale=None):
     from megatron_mixtera_b200.synthetic import canonical_tensor
 
     spec = O.ModelSpec(
@@ -167,12 +167,12 @@ def build_oracle_model(meta, dtype, fp8=None):
     shapes = oracle_weight_shapes(spec)
     w = {k: canonical_tensor(k, s, seed=meta["weight_seed"], dtype=dtype) for k, s in shapes.items()}
     ctx = O.ContextOracle(
-        dtype_bytes=torch.empty(0, dtype=dtype).element_size(), num_layers=spec.num_layers, kv_channels=spec.kv_channels,
+        dtype_bytes=1 if kv_fp8_scale is not None else torch.empty(0, dtype=dtype).element_size(), num_layers=spec.num_layers, kv_channels=spec.kv_channels,
         num_attention_heads=spec.num_query_groups, max_sequence_length=spec.max_sequence_length,
         buffer_size_gb=meta["buffer_size_gb"], buffer_guaranteed_fraction=0.1, chunk_size_tokens=meta["chunk_size_tokens"],
         max_requests_override=meta["max_requests"], max_tokens_override=meta["max_tokens"],
         token_rounder=meta["rounder"], request_rounder=meta["rounder"])
-    return O.GPTOracle(spec, w, ctx, dtype, fp8=fp8), w
+    return O.GPTOracle(spec, w, ctx, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale), w
 
 
 def oracle_weight_shapes(s):
