@@ -222,6 +222,8 @@ typedef struct {
   int32_t kv_cache_fp8;   /* != 0: k_cache / v_cache hold E4M3 bytes (head_dim 128), value = byte * scale[head] */
   const float* k_scale;   /* [nkv] fp32, FP8 pool only */
   const float* v_scale;   /* [nkv] fp32, FP8 pool only */
+  const int32_t* row_order; /* [T] int32 or NULL: a permutation of 0..T-1; the attention kernel starts its work on the
+                               rows in this order (longest context first balances the SMs).  Results do not depend on it. */
 } b200_attention_args;
 
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);

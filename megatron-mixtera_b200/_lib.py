@@ -74,6 +74,7 @@ class AttentionArgs(ctypes.Structure):
         ("kv_cache_fp8", c_int32),
         ("k_scale", c_void_p),
         ("v_scale", c_void_p),
+        ("row_order", c_void_p),
     ]
 
 

@@ -104,6 +104,7 @@ struct Params {
   const int32_t* block_table;
   const int32_t* kv_len;
   const int32_t* row_of_token;
+  const int32_t* row_order;
   const int64_t* pos_q;
   const int64_t* pos_k;
   const int64_t* chunk_idx;
@@ -148,7 +149,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int unit = blockIdx.x;
   const int split = unit % p.num_splits;
   const int h = (unit / p.num_splits) % p.nkv;
-  const int t = unit / (p.num_splits * p.nkv);
+  const int t_slot = unit / (p.num_splits * p.nkv);
+  const int t = p.row_order ? p.row_order[t_slot] : t_slot;
+  if (static_cast<unsigned>(t) >= static_cast<unsigned>(p.T)) return;  // not a permutation: skip, never index with it
   const int G = p.G;
   const int kv_len = p.kv_len[t];
 
@@ -612,6 +615,7 @@ static int fill_params(const b200_attention_args* a, Params& p) {
   p.block_table = a->block_table;
   p.kv_len = a->kv_seq_lengths;
   p.row_of_token = a->row_of_token;
+  p.row_order = a->row_order;
   p.pos_q = a->token_to_pos_ids;
   p.pos_k = a->token_to_pos_in_request;
   p.chunk_idx = a->token_to_chunk_idx;

@@ -269,7 +269,9 @@ class DynamicInferenceContext(BaseInferenceContext):
         self.cu_kv_seq_lengths_cudagraph_only = torch.zeros((R + 1,), dtype=torch.int32, device=dev)
         self.request_to_kv_chunk_ids_cudagraph_only = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, device=dev)
         # host staging: [query lens | cu query | kv lens | cu kv] and the block table
-        self._h_len = torch.zeros((4, R + 1), dtype=torch.int32, pin_memory=pin)
+        # rows processed by the attention kernel in this order (longest context first); decode steps only
+        self.attention_row_order = torch.arange(R, dtype=torch.int32, device=dev)
+        self._h_len = torch.zeros((5, R + 1), dtype=torch.int32, pin_memory=pin)
         self._h_len_np = self._h_len.numpy()
         self._h_bt = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, pin_memory=pin)
         self._h_bt_np = self._h_bt.numpy()
@@ -468,6 +470,11 @@ class DynamicInferenceContext(BaseInferenceContext):
         self.query_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[0, :dev_rows], non_blocking=True)
         self.kv_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[2, :dev_rows], non_blocking=True)
         self.kv_seq_lengths = self.kv_seq_lengths_cudagraph_only[:n_rows]
+        if decode:
+            # One CTA per (row, KV head) runs for a time proportional to the row's context: starting the long rows
+            # first keeps the SMs evenly loaded to the end of the kernel.  Padding rows (length 0) come last.
+            lens[4, :dev_rows] = np.argsort(-lens[2, :dev_rows], kind="stable")
+            self.attention_row_order[:dev_rows].copy_(self._h_len[4, :dev_rows], non_blocking=True)
 
         bt = self._h_bt_np
         bt[:n_req] = self.request_to_kv_chunk_ids.numpy()[p:t]
@@ -475,7 +482,7 @@ class DynamicInferenceContext(BaseInferenceContext):
             bt[n_req:n_rows] = 0
         self.request_to_kv_chunk_ids_cudagraph_only[:dev_rows].copy_(self._h_bt[:dev_rows], non_blocking=True)
         self.block_table = self.request_to_kv_chunk_ids_cudagraph_only[:n_rows]
-        self.h2d_bytes += dev_rows * (8 + 4 * self.max_kv_chunk_count) + (0 if decode else 8 * (n_rows + 1) + 8 * padded)
+        self.h2d_bytes += dev_rows * (8 + 4 * self.max_kv_chunk_count) + (4 * dev_rows if decode else 8 * (n_rows + 1) + 8 * padded)
         self._mark_copies()
 
     def reset(self) -> None:

@@ -289,7 +289,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
                         token_to_pos_in_request=None, token_to_chunk_idx=None, token_to_local_pos=None,
                         row_of_token=None, rope_cos=None, rope_sin=None, num_splits: int = 1,
                         fuse_rope_append: bool = False, softmax_scale: float = 0.0, k_scale=None,
-                        v_scale=None) -> AttentionArgs:
+                        v_scale=None, row_order=None) -> AttentionArgs:
     """Fill the C argument struct.  It holds raw pointers only: the caller keeps the tensors alive until the
     kernels have run.  ``k_scale`` / ``v_scale`` (fp32 [nkv]) select the FP8 (E4M3) KV pool."""
     T = qkv.shape[0]
@@ -320,6 +320,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     a.kv_cache_fp8 = int(k_scale is not None)
     a.k_scale = _p(k_scale)
     a.v_scale = _p(v_scale)
+    a.row_order = _p(row_order)
     ws = attention_workspace(qkv.device, T, num_q_heads, head_dim, num_splits) if out is not None else None
     a.workspace = _p(ws)
     a.workspace_bytes = 0 if ws is None else ws.numel()

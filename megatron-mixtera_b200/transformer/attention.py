@@ -79,7 +79,7 @@ class PagedFlashDecodeAttention(torch.nn.Module):
             splits = choose_attention_splits(T, self.num_kv_heads, ctx.max_sequence_length, ctx.chunk_size_tokens)
             args = ops.make_attention_args(block_table=ctx.request_to_kv_chunk_ids_cudagraph_only,
                                            kv_seq_lengths=ctx.kv_seq_lengths_cudagraph_only, num_splits=splits,
-                                           fuse_rope_append=True, **common)
+                                           fuse_rope_append=True, row_order=ctx.attention_row_order, **common)
             ops.paged_attention(args)
         else:
             # prefill / mixed step: append every token first, then each token is a row that sees its

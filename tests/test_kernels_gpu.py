@@ -221,7 +221,7 @@ def oracle_decode_attention(c):
     return out, kc, vc
 
 
-def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None):
+def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_order=None):
     dev = "cuda"
     D = c["D"]
     cos = sin = None
@@ -233,11 +233,12 @@ def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None):
     # the argument struct holds raw pointers only: keep every device tensor alive in `d`
     d = {k: c[k].to(dev) for k in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
     d["row"] = None if row_of_token is None else row_of_token.to(dev)
+    d["order"] = None if row_order is None else row_order.to(dev)
     args = ops.make_attention_args(
         qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
         num_q_heads=c["nq"], num_kv_heads=c["nkv"], head_dim=D, chunk_size=c["chunk"], token_to_pos_ids=d["pos"],
         token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
-        rope_cos=cos, rope_sin=sin, num_splits=num_splits, fuse_rope_append=fused, row_of_token=d["row"])
+        rope_cos=cos, rope_sin=sin, num_splits=num_splits, fuse_rope_append=fused, row_of_token=d["row"], row_order=d["order"])
     if not fused:
         ops.rope_append(args)
     ops.paged_attention(args)
@@ -305,6 +306,24 @@ def test_paged_attention_prefill_rows_via_row_of_token(ops):
                             cu_q=torch.tensor([0, n]))
     assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
     assert rel_l2(out, ref) < 5e-3
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_row_order_changes_nothing(ops, splits):
+    # the order in which rows are started is a scheduling hint: outputs and pool are bit-identical
+    kv_lens = [5, 700, 64, 1, 1300, 257, 0, 90]
+    c = make_paged_case(T=8, nkv=2, G=4, D=128, chunk=64, kv_lens=kv_lens, seed=11)
+    base = run_cuda_attention(ops, c, num_splits=splits, fused=True)
+    order = torch.argsort(-torch.tensor(kv_lens), stable=True).int()
+    for ro in (order, order.flip(0)):
+        got = run_cuda_attention(ops, c, num_splits=splits, fused=True, row_order=ro)
+        for a, b in zip(got, base):
+            assert torch.equal(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()))
+    # an entry outside 0..T-1 is skipped, never used as an index
+    bad = order.clone()
+    bad[0] = 1000
+    run_cuda_attention(ops, c, num_splits=splits, fused=True, row_order=bad)
+    assert ops.device_status() == 0
 
 
 def test_attention_split_invariance_at_long_context(ops):
