@@ -285,7 +285,7 @@ def run_reference(args, w):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w.name}, "cpu_baseline": best,
             "e2e": {"value": best["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -410,7 +410,7 @@ def run_ours(args, w):
                               "frac": step_bytes(w, ctx, B, tp) / peak / 1e6 / (dev_s / steps * 1e3)},
         "cpu_baseline": cpu, "clocks": clocks, "prefill_s": prefill_s, "device_status": status,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.barrier()
 
@@ -430,6 +430,27 @@ def step_bytes(w, ctx, B, tp):
     return weights + kv
 
 
+_RESULT_FD = None
+
+
+def protect_stdout():
+    """Keep file descriptor 1 for the one JSON line: libraries that write to stdout themselves (NCCL prints its
+    version banner there) are pointed at stderr for the rest of the run."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -439,6 +460,7 @@ def main():
     ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "smoke"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    protect_stdout()
     from megatron_mixtera_b200 import configs
 
     w = {"llama3_8b": configs.LLAMA3_8B_BF16_64REQ, "llama3_8b_mxfp8": configs.LLAMA3_8B_MXFP8_128REQ,
