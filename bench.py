@@ -112,7 +112,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the CUDA stack
 # ---------------------------------------------------------------------------------------------
-def build_stack(w, tp: int, seed: int = 0):
+def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True):
     from megatron_mixtera_b200 import build, parallel_state
     from megatron_mixtera_b200.gpt.gpt_model import GPTModel
     from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext
@@ -128,7 +128,8 @@ def build_stack(w, tp: int, seed: int = 0):
         num_layers=w.num_layers, hidden_size=w.hidden_size, num_attention_heads=w.num_attention_heads,
         num_query_groups=w.num_query_groups, kv_channels=w.kv_channels, ffn_hidden_size=w.ffn_hidden_size,
         normalization="RMSNorm", gated_linear_unit=True, activation="silu", add_bias_linear=False,
-        tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8)
+        tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8,
+        fuse_splitk_reduction_into_norm=fuse_splitk)
     model = GPTModel(cfg, vocab_size=w.vocab_size, max_sequence_length=w.max_sequence_length,
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
@@ -157,7 +158,8 @@ def algorithmic_gemm_bytes(M, N, K, fp8=False):
 
 def kernel_rooflines(model, ctx, T, peak_gbs):
     """Per-kernel algorithmic bytes and CUDA-event time: each kernel is run once per layer on that
-    layer's own weights / KV pool (so nothing is served from L2) and the sweep is timed as a whole."""
+    layer's own weights / KV pool (so nothing is served from L2) and the sweep is timed as a whole
+    (as one CUDA-graph replay, the way the kernels run inside the decode step)."""
     from megatron_mixtera_b200 import ops
 
     layers = list(model.decoder.layers)
@@ -166,13 +168,22 @@ def kernel_rooflines(model, ctx, T, peak_gbs):
     stream_events = lambda: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
 
     def sweep(fn, reps=3):
+        # The sweep (one launch per layer) is captured into a CUDA graph and the replay is timed: issued one by
+        # one from Python, launches shorter than ~15 us would measure the host's launch rate, not the kernel.
         fn()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        graph.replay()
         torch.cuda.synchronize()
         best = None
         for _ in range(reps):
             e0, e1 = stream_events()
             e0.record()
-            fn()
+            graph.replay()
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
@@ -316,7 +327,7 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
-    model, ctx, wrapper, ctl, engine = build_stack(w, tp)
+    model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk)
     prompts = synthetic_prompts(w.num_requests, *w.prompt_len_range, w.vocab_size, seed=0)
     for i, p in enumerate(prompts):
         engine.add_request(i, p, w.num_tokens_to_generate)
@@ -459,6 +470,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "smoke"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused-splitk", action="store_true",
+                    help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
     args = ap.parse_args()
     protect_stdout()
     from megatron_mixtera_b200 import configs

@@ -169,6 +169,38 @@ int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const v
                         size_t workspace_bytes, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Row-parallel linear -> residual add -> norm without the split-K reduction launch.
+ *
+ * At decode sizes the out-projection and fc2 GEMMs (RowParallelLinear.forward, layers.py:1225-1281) are split
+ * along K; their fp32 partial sums are normally reduced by a second kernel, and the residual add + norm that
+ * follows in the layer (transformer_layer.py:433-660: bias-dropout-add, then pre_mlp_layernorm / the next
+ * layer's input_layernorm) is a third.  The *_splitk entry points leave the partial sums
+ * [num_splits][M][N] fp32 in `partials` (b200_gemm_*_splitk_bytes gives the size; *num_splits is written on the
+ * host before the call returns; one split is possible), and b200_add_norm_splitk_* read them in place of `x`:
+ * x = bf16(sum of the splits in split order), then exactly what b200_add_norm_* does (`bias` here is the linear's
+ * bias).  Results are bit-identical to b200_gemm_* followed by b200_add_norm_*.  hidden <= 8192.
+ */
+size_t b200_gemm_bf16_splitk_bytes(int M, int N, int K);
+int b200_gemm_bf16_splitk(const void* x, int64_t ldx, const void* w, int M, int N, int K, float* partials,
+                          size_t partials_bytes, int* num_splits, b200_stream_t stream);
+size_t b200_gemm_mxfp8_splitk_bytes(int M, int N, int K);
+int b200_gemm_mxfp8_splitk(const void* xq, const void* x_sf, const void* wq, const void* w_sf, int M, int N, int K,
+                           float* partials, size_t partials_bytes, int* num_splits, b200_stream_t stream);
+size_t b200_gemm_fp8_block_splitk_bytes(int M, int N, int K);
+int b200_gemm_fp8_block_splitk(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
+                               int M, int N, int K, float* partials, size_t partials_bytes, int* num_splits,
+                               b200_stream_t stream);
+int b200_add_norm_splitk_bf16(const float* partials, int num_splits, const void* bias, const void* residual,
+                              const void* gamma, const void* beta, void* hidden_out, void* normed_out, int rows, int hidden,
+                              float eps, b200_stream_t stream);
+int b200_add_norm_splitk_mxfp8(const float* partials, int num_splits, const void* bias, const void* residual,
+                               const void* gamma, const void* beta, void* hidden_out, void* q_out, void* sf_out, int rows,
+                               int hidden, float eps, b200_stream_t stream);
+int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, const void* bias, const void* residual,
+                                      const void* gamma, const void* beta, void* hidden_out, void* q_out, float* scale_out,
+                                      int m_pad, int rows, int hidden, float eps, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.
  *
  * qkv        [T, nkv, (g+2)*d] bf16: per KV group g query heads, then the key, then the value

@@ -34,6 +34,15 @@ EXPORTED_SYMBOLS = (
     "b200_activation_fp8_rowblock",
     "b200_gemm_fp8_block_workspace_bytes",
     "b200_gemm_fp8_block",
+    "b200_gemm_bf16_splitk_bytes",
+    "b200_gemm_bf16_splitk",
+    "b200_gemm_mxfp8_splitk_bytes",
+    "b200_gemm_mxfp8_splitk",
+    "b200_gemm_fp8_block_splitk_bytes",
+    "b200_gemm_fp8_block_splitk",
+    "b200_add_norm_splitk_bf16",
+    "b200_add_norm_splitk_mxfp8",
+    "b200_add_norm_splitk_fp8_rowblock",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -137,6 +146,21 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_fp8_block_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_fp8_block.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                         c_int, c_int, c_void_p, c_size_t, c_void_p]
+    for name in ("b200_gemm_bf16_splitk_bytes", "b200_gemm_mxfp8_splitk_bytes", "b200_gemm_fp8_block_splitk_bytes"):
+        getattr(lib, name).restype = c_size_t
+        getattr(lib, name).argtypes = [c_int, c_int, c_int]
+    lib.b200_gemm_bf16_splitk.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
+                                          POINTER(c_int), c_void_p]
+    lib.b200_gemm_mxfp8_splitk.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t,
+                                           POINTER(c_int), c_void_p]
+    lib.b200_gemm_fp8_block_splitk.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                               c_size_t, POINTER(c_int), c_void_p]
+    lib.b200_add_norm_splitk_bf16.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_int, c_int, c_float, c_void_p]
+    lib.b200_add_norm_splitk_mxfp8.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_float, c_void_p]
+    lib.b200_add_norm_splitk_fp8_rowblock.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]

@@ -52,13 +52,17 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, cons
 
 // h = x (+bias) (+residual) with a bf16 rounding after each add; normed = norm(h) * gamma (+beta).
 // kMaxVec: vectors of 8 elements cached per thread so that the row is read once.
-template <int kMaxVec>
-__global__ void __launch_bounds__(256)
+// kPartials: x is not read; it is bf16(sum over the `splits` fp32 partial products of a split-K GEMM, in split
+// order) - the reduction the GEMM's own second kernel would have done, so that kernel is not launched.  One
+// vector per thread and up to 1024 threads, so that all partial loads of a row are in flight at once.
+template <int kMaxVec, bool kPartials>
+__global__ void __launch_bounds__(kPartials ? 1024 : 256)
 add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
                 const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
                 __nv_bfloat16* __restrict__ normed_out, int hidden, float eps, uint8_t* __restrict__ q_out,
-                void* __restrict__ sf_out, int q_mode, int m_pad) {
+                void* __restrict__ sf_out, int q_mode, int m_pad, const float* __restrict__ partials, int splits,
+                int64_t split_stride) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -73,12 +77,27 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   for (int it = 0; it < kMaxVec; ++it) {
     const int i = threadIdx.x + it * blockDim.x;
     if (i < nvec) {
-      Vec8 v = xv[i];
       float f[8];
+      if constexpr (kPartials) {
+        const float4* src = reinterpret_cast<const float4*>(partials + off) + 2 * i;
+        const int64_t stride4 = split_stride / 4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+#pragma unroll 8
+        for (int sp = 0; sp < splits; ++sp) {
+          const float4 u = __ldcg(src + sp * stride4);
+          const float4 w = __ldcg(src + sp * stride4 + 1);
+          a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+          b.x += w.x; b.y += w.y; b.z += w.z; b.w += w.w;
+        }
+        f[0] = bf16_round(a.x); f[1] = bf16_round(a.y); f[2] = bf16_round(a.z); f[3] = bf16_round(a.w);
+        f[4] = bf16_round(b.x); f[5] = bf16_round(b.y); f[6] = bf16_round(b.z); f[7] = bf16_round(b.w);
+      } else {
+        const Vec8 v = xv[i];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        f[2 * k] = bf16_lo(v.w[k]);
-        f[2 * k + 1] = bf16_hi(v.w[k]);
+        for (int k = 0; k < 4; ++k) {
+          f[2 * k] = bf16_lo(v.w[k]);
+          f[2 * k + 1] = bf16_hi(v.w[k]);
+        }
       }
       if (bv) {
         const Vec8 b = bv[i];
@@ -242,14 +261,15 @@ int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int 
 
 static int add_norm_impl(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
                          void* hidden_out, void* normed_out, void* q_out, void* sf_out, int q_mode, int m_pad, int rows,
-                         int hidden, float eps, b200_stream_t stream) {
+                         int hidden, float eps, b200_stream_t stream, const float* partials = nullptr, int splits = 0) {
   using namespace b200;
-  if (!x || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if ((!x && !partials) || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (partials && (splits < 1 || hidden > 8192)) return B200_ERR_INVALID_ARGUMENT;
   if ((normed_out || q_out) && !gamma) return B200_ERR_INVALID_ARGUMENT;
   if (!normed_out && !hidden_out && !q_out) return B200_ERR_INVALID_ARGUMENT;
   if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
   if (hidden % 8 != 0 || (q_out && hidden % 128 != 0)) return B200_ERR_ALIGNMENT;
-  const void* ptrs[] = {x, bias, residual, gamma, beta, hidden_out, normed_out, q_out, sf_out};
+  const void* ptrs[] = {x, bias, residual, gamma, beta, hidden_out, normed_out, q_out, sf_out, partials};
   for (const void* q : ptrs)
     if (q && !aligned16(q)) return B200_ERR_ALIGNMENT;
   const int nvec = hidden / 8;
@@ -264,14 +284,21 @@ static int add_norm_impl(const void* x, const void* bias, const void* residual, 
   auto H = static_cast<__nv_bfloat16*>(hidden_out);
   auto Nn = static_cast<__nv_bfloat16*>(normed_out);
   auto Q = static_cast<uint8_t*>(q_out);
+  const float* P = nullptr;
+  const int64_t zero = 0;
+  if (partials) {  // split-K partial sums [splits][rows][hidden] instead of x
+    const int wide = ((nvec + 31) / 32) * 32;  // <= 1024: one vector per thread
+    return launch_pdl(ew::add_norm_kernel<1, true>, dim3(rows), dim3(wide), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q,
+                      sf_out, q_mode, m_pad, partials, splits, static_cast<int64_t>(rows) * hidden);
+  }
   if (per_thread <= 1)
-    return launch_pdl(ew::add_norm_kernel<1>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
+    return launch_pdl(ew::add_norm_kernel<1, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
   else if (per_thread <= 2)
-    return launch_pdl(ew::add_norm_kernel<2>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
+    return launch_pdl(ew::add_norm_kernel<2, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
   else if (per_thread <= 4)
-    return launch_pdl(ew::add_norm_kernel<4>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
+    return launch_pdl(ew::add_norm_kernel<4, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
   else if (per_thread <= 8)
-    return launch_pdl(ew::add_norm_kernel<8>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad);
+    return launch_pdl(ew::add_norm_kernel<8, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
   return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
 }
 
@@ -294,6 +321,30 @@ int b200_add_norm_fp8_rowblock(const void* x, const void* bias, const void* resi
   if (!q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
   return add_norm_impl(x, bias, residual, gamma, beta, hidden_out, nullptr, q_out, scale_out, b200::mx::kQuantBlock128, m_pad,
                        rows, hidden, eps, stream);
+}
+
+int b200_add_norm_splitk_bf16(const float* partials, int num_splits, const void* bias, const void* residual,
+                              const void* gamma, const void* beta, void* hidden_out, void* normed_out, int rows, int hidden,
+                              float eps, b200_stream_t stream) {
+  if (!partials) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, normed_out, nullptr, nullptr, 0, 0, rows, hidden, eps,
+                       stream, partials, num_splits);
+}
+
+int b200_add_norm_splitk_mxfp8(const float* partials, int num_splits, const void* bias, const void* residual,
+                               const void* gamma, const void* beta, void* hidden_out, void* q_out, void* sf_out, int rows,
+                               int hidden, float eps, b200_stream_t stream) {
+  if (!partials || !q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, nullptr, q_out, sf_out, b200::mx::kQuantMx, 0, rows,
+                       hidden, eps, stream, partials, num_splits);
+}
+
+int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, const void* bias, const void* residual,
+                                      const void* gamma, const void* beta, void* hidden_out, void* q_out, float* scale_out,
+                                      int m_pad, int rows, int hidden, float eps, b200_stream_t stream) {
+  if (!partials || !q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, nullptr, q_out, scale_out, b200::mx::kQuantBlock128,
+                       m_pad, rows, hidden, eps, stream, partials, num_splits);
 }
 
 static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int q_mode, int m_pad,

@@ -49,6 +49,7 @@ struct Params {
   int num_k_blocks;     // ceil(K / 64)
   int k_blocks_per_split;
   int num_splits;
+  int keep_partials;    // 1: fp32 partial sums are the result (even for one split); a fused consumer reduces them
 };
 
 // Sum of the split-K partial tiles: y[m, n] = bf16(sum_s partial[s][m][n]) (+ bias), splits added in order
@@ -124,7 +125,7 @@ __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, in
   const bool n_ok = n < p.N;
   const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
-  if (p.num_splits == 1) {
+  if (p.num_splits == 1 && !p.keep_partials) {
     const float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BT; c0 += 32) {
@@ -298,7 +299,8 @@ static int pick_bt(int M) {
 
 template <int BT>
 static int launch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
-                  int K, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool cache_maps = true) {
+                  int K, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool cache_maps = true,
+                  float* partials_out = nullptr, size_t partials_bytes = 0, int* splits_out = nullptr) {
   using C = Config<BT>;
   const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
   const uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -334,7 +336,12 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
   p.num_splits = splits;
   p.partials = nullptr;
   p.counters = nullptr;
-  if (splits > 1) {
+  p.keep_partials = partials_out != nullptr;
+  if (partials_out != nullptr) {
+    if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
+    p.partials = partials_out;
+    *splits_out = splits;
+  } else if (splits > 1) {
     const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
@@ -350,7 +357,7 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
   }
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_bf16_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p);
-  if (rc != B200_OK || splits == 1) return rc;
+  if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
   return launch_splitk_reduce(p, stream);
 }
 
@@ -358,6 +365,29 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
 }  // namespace b200
 
 extern "C" {
+
+size_t b200_gemm_bf16_splitk_bytes(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int bt = pick_bt(M);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
+  return static_cast<size_t>(choose_splits(tiles, (K + kTileK - 1) / kTileK)) * M * N * sizeof(float);
+}
+
+int b200_gemm_bf16_splitk(const void* x, int64_t ldx, const void* w, int M, int N, int K, float* partials,
+                          size_t partials_bytes, int* num_splits, b200_stream_t stream) {
+  using namespace b200;
+  if (!x || !w || !partials || !num_splits || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldx < K) return B200_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch<32>(x, ldx, w, nullptr, nullptr, N, M, N, K, nullptr, 0, s, true, partials, partials_bytes, num_splits);
+    case 64: return gemm::launch<64>(x, ldx, w, nullptr, nullptr, N, M, N, K, nullptr, 0, s, true, partials, partials_bytes, num_splits);
+    case 128: return gemm::launch<128>(x, ldx, w, nullptr, nullptr, N, M, N, K, nullptr, 0, s, true, partials, partials_bytes, num_splits);
+    default: return gemm::launch<256>(x, ldx, w, nullptr, nullptr, N, M, N, K, nullptr, 0, s, true, partials, partials_bytes, num_splits);
+  }
+}
 
 size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K) {
   using namespace b200::gemm;

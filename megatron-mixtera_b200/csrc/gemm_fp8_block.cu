@@ -228,7 +228,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 template <int BT>
 static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
                             const void* bias, void* y, int64_t ldy, int M, int N, int K, void* workspace,
-                            size_t workspace_bytes, cudaStream_t stream) {
+                            size_t workspace_bytes, cudaStream_t stream, float* partials_out = nullptr,
+                            size_t partials_bytes = 0, int* splits_out = nullptr) {
   using C = BlkConfig<BT>;
   const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
   const uint64_t ws[1] = {static_cast<uint64_t>(K)};
@@ -256,7 +257,12 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
   p.num_splits = splits;
   p.partials = nullptr;
   p.counters = nullptr;
-  if (splits > 1) {
+  p.keep_partials = partials_out != nullptr;
+  if (partials_out != nullptr) {
+    if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
+    p.partials = partials_out;
+    *splits_out = splits;
+  } else if (splits > 1) {
     const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
     p.counters = static_cast<int*>(workspace);
@@ -276,7 +282,7 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
   }
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_fp8_block_kernel<BT>, grid, dim3(kBlkThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
-  if (rc != B200_OK || splits == 1) return rc;
+  if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
   return launch_splitk_reduce(p, stream);
 }
 
@@ -286,6 +292,33 @@ static int pick_bt_block(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 }  // namespace b200
 
 extern "C" {
+
+size_t b200_gemm_fp8_block_splitk_bytes(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int bt = pick_bt_block(M);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
+  return static_cast<size_t>(choose_splits(tiles, K / 128)) * M * N * sizeof(float);
+}
+
+int b200_gemm_fp8_block_splitk(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
+                               int M, int N, int K, float* partials, size_t partials_bytes, int* num_splits,
+                               b200_stream_t stream) {
+  using namespace b200;
+  if (!xq || !x_scale || !wq || !w_scale || !partials || !num_splits || M <= 0 || N <= 0 || K <= 0)
+    return B200_ERR_INVALID_ARGUMENT;
+  if (K % 128 != 0 || m_pad < M || m_pad % 4 != 0) return B200_ERR_ALIGNMENT;
+  if (!aligned16(xq) || !aligned16(wq) || !aligned16(x_scale) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt_block(M)) {
+    case 32:
+      return gemm::launch_fp8_block<32>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    case 64:
+      return gemm::launch_fp8_block<64>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    default:
+      return gemm::launch_fp8_block<128>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+  }
+}
 
 size_t b200_gemm_fp8_block_workspace_bytes(int M, int N, int K) {
   using namespace b200::gemm;

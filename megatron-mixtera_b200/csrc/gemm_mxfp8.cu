@@ -177,7 +177,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
 template <int BT>
 static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,
-                        int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                        int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                        float* partials_out = nullptr, size_t partials_bytes = 0, int* splits_out = nullptr) {
   using C = Fp8Config<BT>;
   const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
   const uint64_t ws[1] = {static_cast<uint64_t>(K)};
@@ -205,7 +206,12 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
   p.num_splits = splits;
   p.partials = nullptr;
   p.counters = nullptr;
-  if (splits > 1) {
+  p.keep_partials = partials_out != nullptr;
+  if (partials_out != nullptr) {
+    if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
+    p.partials = partials_out;
+    *splits_out = splits;
+  } else if (splits > 1) {
     const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
     if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
@@ -225,7 +231,7 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
   }
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_mxfp8_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
-  if (rc != B200_OK || splits == 1) return rc;
+  if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
   return launch_splitk_reduce(p, stream);
 }
 
@@ -238,6 +244,31 @@ size_t b200_mxfp8_scale_bytes(int rows, int K) {
   if (rows <= 0 || K <= 0 || K % 128 != 0) return 0;
   // whole 256-row groups, so that a 256-token block of the GEMM can always read two tiles
   return static_cast<size_t>((rows + 255) / 256) * 2 * (K / 128) * b200::gemm::kSfTileBytes;
+}
+
+size_t b200_gemm_mxfp8_splitk_bytes(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int bt = pick_bt(M);
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
+  return static_cast<size_t>(choose_splits(tiles, K / kFp8TileK)) * M * N * sizeof(float);
+}
+
+int b200_gemm_mxfp8_splitk(const void* xq, const void* x_sf, const void* wq, const void* w_sf, int M, int N, int K,
+                           float* partials, size_t partials_bytes, int* num_splits, b200_stream_t stream) {
+  using namespace b200;
+  if (!xq || !x_sf || !wq || !w_sf || !partials || !num_splits || M <= 0 || N <= 0 || K <= 0)
+    return B200_ERR_INVALID_ARGUMENT;
+  if (K % 128 != 0) return B200_ERR_ALIGNMENT;
+  if (!aligned16(xq) || !aligned16(wq) || !aligned16(x_sf) || !aligned16(w_sf) || !aligned16(partials))
+    return B200_ERR_ALIGNMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch_mxfp8<32>(xq, x_sf, wq, w_sf, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    case 64: return gemm::launch_mxfp8<64>(xq, x_sf, wq, w_sf, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    case 128: return gemm::launch_mxfp8<128>(xq, x_sf, wq, w_sf, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    default: return gemm::launch_mxfp8<256>(xq, x_sf, wq, w_sf, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+  }
 }
 
 size_t b200_gemm_mxfp8_workspace_bytes(int M, int N, int K) {

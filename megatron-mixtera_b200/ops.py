@@ -54,8 +54,22 @@ class _Workspace:
 
 _workspace = _Workspace()
 
-# Kernel launches issued through this module since import (attention with splits counts two).
+# Kernel launches issued through this module since import (attention with context splits and GEMMs with a
+# split-K reduction kernel count two).
 launch_count = 0
+# Number of GEMMs that have used the shared split-K workspace: a `GemmPartials` is only valid while this has not moved.
+_gemm_epoch = 0
+
+
+_SPLITK_RESERVED = 64 * 1024  # workspace bytes a GEMM asks for when it is NOT split along K
+
+
+def _gemm_workspace(device, nbytes: int, count_reduction: bool = False) -> torch.Tensor:
+    global _gemm_epoch, launch_count
+    _gemm_epoch += 1
+    if count_reduction and nbytes > _SPLITK_RESERVED:
+        launch_count += 1  # the split-K reduction kernel behind the GEMM kernel
+    return _workspace.get(device, "gemm", nbytes)
 
 
 _NOT_A_LAUNCH = ("b200_device_status",)
@@ -131,7 +145,7 @@ def gemm(x, w, bias=None, out=None):
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.device)
     lib = _lib.load()
     nbytes = lib.b200_gemm_bf16_workspace_bytes(M, N, K)
-    ws = _workspace.get(x.device, "gemm", nbytes)
+    ws = _gemm_workspace(x.device, nbytes, True)
     check("b200_gemm_bf16", lib.b200_gemm_bf16(x.data_ptr(), K, w.data_ptr(), _p(bias), out.data_ptr(), N, M, N, K,
                                                ws.data_ptr(), ws.numel(), _stream()))
     return out
@@ -197,7 +211,7 @@ def gemm_mxfp8(x: Mxfp8Tensor, w: Mxfp8Tensor, bias=None, out=None):
     if out is None:
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
-    ws = _workspace.get(x.q.device, "gemm", lib.b200_gemm_mxfp8_workspace_bytes(M, N, K))
+    ws = _gemm_workspace(x.q.device, lib.b200_gemm_mxfp8_workspace_bytes(M, N, K), True)
     check("b200_gemm_mxfp8", lib.b200_gemm_mxfp8(x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), _p(bias),
                                                  out.data_ptr(), N, M, N, K, ws.data_ptr(), ws.numel(), _stream()))
     return out
@@ -272,11 +286,86 @@ def gemm_fp8_block(x: Fp8BlockTensor, w: Fp8BlockTensor, bias=None, out=None):
     if out is None:
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
-    ws = _workspace.get(x.q.device, "gemm", lib.b200_gemm_fp8_block_workspace_bytes(M, N, K))
+    ws = _gemm_workspace(x.q.device, lib.b200_gemm_fp8_block_workspace_bytes(M, N, K), True)
     check("b200_gemm_fp8_block", lib.b200_gemm_fp8_block(
         x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), _p(bias), out.data_ptr(), N, M, N,
         K, ws.data_ptr(), ws.numel(), _stream()))
     return out
+
+
+class GemmPartials:
+    """fp32 partial sums [num_splits, M, N] of a split-K GEMM, left in the shared GEMM workspace for a fused consumer
+    (`add_norm_splitk`).  Valid until the next GEMM on the same device is enqueued."""
+
+    __slots__ = ("buf", "num_splits", "shape", "epoch")
+
+    def __init__(self, buf: torch.Tensor, num_splits: int, shape):
+        self.buf, self.num_splits, self.shape, self.epoch = buf, num_splits, tuple(shape), _gemm_epoch
+
+    @property
+    def device(self):
+        return self.buf.device
+
+
+def gemm_splitk(x, w) -> GemmPartials:
+    """x @ w.T as split-K partial sums (no reduction launch, no bias); x bf16, `Mxfp8Tensor` or `Fp8BlockTensor`
+    with `w` of the same kind."""
+    lib = _lib.load()
+    n = ctypes.c_int(0)
+    if isinstance(x, Mxfp8Tensor):
+        K, M, N, dev = x.shape[-1], x.q.shape[0], w.q.shape[0], x.q.device
+        ws = _gemm_workspace(dev, lib.b200_gemm_mxfp8_splitk_bytes(M, N, K))
+        check("b200_gemm_mxfp8_splitk", lib.b200_gemm_mxfp8_splitk(
+            x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), M, N, K, ws.data_ptr(), ws.numel(),
+            ctypes.byref(n), _stream()))
+    elif isinstance(x, Fp8BlockTensor):
+        K, M, N, dev = x.shape[-1], x.q.shape[0], w.q.shape[0], x.q.device
+        ws = _gemm_workspace(dev, lib.b200_gemm_fp8_block_splitk_bytes(M, N, K))
+        check("b200_gemm_fp8_block_splitk", lib.b200_gemm_fp8_block_splitk(
+            x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), M, N, K, ws.data_ptr(),
+            ws.numel(), ctypes.byref(n), _stream()))
+    else:
+        _need(x, BF16, "x")
+        _need(w, BF16, "w")
+        K = x.shape[-1]
+        M, N, dev = x.numel() // K, w.shape[0], x.device
+        if w.shape[1] != K:
+            raise B200Error("gemm_splitk", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.shape)}")
+        ws = _gemm_workspace(dev, lib.b200_gemm_bf16_splitk_bytes(M, N, K))
+        check("b200_gemm_bf16_splitk", lib.b200_gemm_bf16_splitk(
+            x.data_ptr(), K, w.data_ptr(), M, N, K, ws.data_ptr(), ws.numel(), ctypes.byref(n), _stream()))
+    return GemmPartials(ws, n.value, (*x.shape[:-1], N))
+
+
+def add_norm_splitk(p: GemmPartials, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5,
+                    want_hidden: bool = False, want_normed: bool = True, quantize=None):
+    """`add_norm` / `add_norm_mxfp8` / `add_norm_fp8_rowblock` (by ``quantize``) with x = the reduced partial sums."""
+    if p.epoch != _gemm_epoch:
+        raise B200Error("add_norm_splitk", -1, "another GEMM has reused the workspace that held these partial sums")
+    hidden = p.shape[-1]
+    rows = 1
+    for d in p.shape[:-1]:
+        rows *= d
+    dev = p.device
+    h = torch.empty(p.shape, dtype=BF16, device=dev) if want_hidden else None
+    lib = _lib.load()
+    if quantize == "mxfp8":
+        q, sf = _mx_buffers(rows, hidden, dev)
+        check("b200_add_norm_splitk_mxfp8", lib.b200_add_norm_splitk_mxfp8(
+            p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(),
+            rows, hidden, eps, _stream()))
+        return h, Mxfp8Tensor(q, sf, p.shape)
+    if quantize == "blockwise":
+        q, scale, m_pad = _rowblock_buffers(rows, hidden, dev)
+        check("b200_add_norm_splitk_fp8_rowblock", lib.b200_add_norm_splitk_fp8_rowblock(
+            p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(),
+            scale.data_ptr(), m_pad, rows, hidden, eps, _stream()))
+        return h, Fp8BlockTensor(q, scale, p.shape, m_pad)
+    y = torch.empty(p.shape, dtype=BF16, device=dev) if want_normed else None
+    check("b200_add_norm_splitk_bf16", lib.b200_add_norm_splitk_bf16(
+        p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps,
+        _stream()))
+    return h, y
 
 
 def attention_workspace(device, num_tokens: int, num_q_heads: int, head_dim: int, num_splits: int):

@@ -45,19 +45,22 @@ class _ParallelLinearBase(torch.nn.Module):
             fn = ops.quantize_mxfp8 if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
             self._wq = fn(self.weight.data)
 
-    def _matmul(self, input_, weight, bias):
+    def _matmul(self, input_, weight, bias, defer_reduction: bool = False):
+        """``defer_reduction``: return the split-K partial sums (`ops.GemmPartials`) for a consumer that reduces
+        them itself, instead of the bf16 product; no bias then."""
+        assert not (defer_reduction and bias is not None)
         quantised_input = isinstance(input_, (ops.Mxfp8Tensor, ops.Fp8BlockTensor))
         if self.fp8 and weight is self.weight:
             if self._wq is None:
                 self.quantize_weights()
             if self.fp8 == "mxfp8":
                 x = input_ if quantised_input else ops.quantize_mxfp8(input_)
-                return ops.gemm_mxfp8(x, self._wq, bias)
+                return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_mxfp8(x, self._wq, bias)
             x = input_ if quantised_input else ops.quantize_fp8_rowblock(input_)
-            return ops.gemm_fp8_block(x, self._wq, bias)
+            return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_fp8_block(x, self._wq, bias)
         if quantised_input:
             raise ops.B200Error("linear", -1, "got an FP8 input but this layer runs in bf16")
-        return ops.gemm(input_, weight, bias)
+        return ops.gemm_splitk(input_, weight) if defer_reduction else ops.gemm(input_, weight, bias)
 
 
 class ColumnParallelLinear(_ParallelLinearBase):
@@ -116,10 +119,16 @@ class RowParallelLinear(_ParallelLinearBase):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, input_):
+    supports_deferred_reduction = True
+
+    def forward(self, input_, defer_reduction: bool = False):
+        """``defer_reduction`` (honoured at TP=1 when no bias has to be added here): the output is the GEMM's
+        split-K partial sums (`ops.GemmPartials`), to be reduced by the residual-add + norm kernel that follows."""
         tp = parallel_state.get_tensor_model_parallel_world_size()
         # The bias must be added once, after the reduction: fuse it into the GEMM only at TP=1.
         fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add and tp == 1) else None
+        if defer_reduction and tp == 1 and fuse_bias is None:
+            return self._matmul(input_, self.weight, None, defer_reduction=True), (self.bias if self.skip_bias_add else None)
         out = self._matmul(input_, self.weight, fuse_bias)
         if tp > 1:
             out = reduce_from_tensor_model_parallel_region(out, self.tp_group)

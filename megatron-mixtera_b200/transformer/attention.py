@@ -109,10 +109,13 @@ class SelfAttention(torch.nn.Module):
             bias=config.add_bias_linear, input_is_parallel=True, skip_bias_add=True, tp_comm_buffer_name="proj")
 
     def forward(self, hidden_states, attention_mask=None, inference_context=None, rotary_pos_cos=None,
-                rotary_pos_sin=None, **_):
-        """``hidden_states`` [T, H] (already normalised) -> (output [T, H], bias or None)."""
+                rotary_pos_sin=None, defer_output_reduction: bool = False, **_):
+        """``hidden_states`` [T, H] (already normalised) -> (output [T, H], bias or None).  With
+        ``defer_output_reduction`` the output may be the out-projection's split-K partial sums."""
         if inference_context is None or inference_context.is_static_batching():
             raise NotImplementedError("only the dynamic-batching inference path is implemented")
         mixed_qkv, _ = self.linear_qkv(hidden_states)
         core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin)
+        if defer_output_reduction and getattr(self.linear_proj, "supports_deferred_reduction", False):
+            return self.linear_proj(core, defer_reduction=True)
         return self.linear_proj(core)

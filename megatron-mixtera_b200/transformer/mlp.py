@@ -29,7 +29,7 @@ class MLP(torch.nn.Module):
                                        bias=config.add_bias_linear, input_is_parallel=True, skip_bias_add=True,
                                        tp_comm_buffer_name="fc2")
 
-    def forward(self, hidden_states):
+    def forward(self, hidden_states, defer_output_reduction: bool = False):
         inter, bias = self.linear_fc1(hidden_states)
         act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[self.config.fp8]
         if self.config.gated_linear_unit:
@@ -38,4 +38,6 @@ class MLP(torch.nn.Module):
             inter = act(inter, "swiglu")
         else:
             inter = act(inter, "gelu", bias)
+        if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
+            return self.linear_fc2(inter, defer_reduction=True)
         return self.linear_fc2(inter)

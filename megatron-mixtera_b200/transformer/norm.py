@@ -22,6 +22,8 @@ class B200Norm(torch.nn.Module):
         else:
             self.register_parameter("bias", None)
 
+    accepts_gemm_partials = True  # add_and_norm takes the split-K partial sums of the linear before it
+
     @staticmethod
     def _op(quantize):
         return {None: ops.add_norm, False: ops.add_norm, "mxfp8": ops.add_norm_mxfp8,
@@ -34,5 +36,9 @@ class B200Norm(torch.nn.Module):
     def add_and_norm(self, x, residual, bias=None, quantize=None):
         """(hidden, normed) with hidden = x (+bias) + residual: the bias-dropout-add of the
         reference (``fused_bias_dropout.py:11-57``, eval mode) fused with the norm that follows it
-        and, with ``quantize``, with the FP8 quantisation of the next linear's input."""
+        and, with ``quantize``, with the FP8 quantisation of the next linear's input.  ``x`` may be the
+        un-reduced split-K partial sums of the linear that produced it (`ops.GemmPartials`)."""
+        if isinstance(x, ops.GemmPartials):
+            return ops.add_norm_splitk(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps,
+                                       want_hidden=True, quantize=quantize or None)
         return self._op(quantize)(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps, want_hidden=True)

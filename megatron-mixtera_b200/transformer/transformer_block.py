@@ -23,8 +23,12 @@ class TransformerBlock(torch.nn.Module):
         hidden = hidden_states.reshape(-1, shape[-1])
         branch = bias = None
         kw = dict(inference_context=inference_context, rotary_pos_cos=rotary_pos_cos, rotary_pos_sin=rotary_pos_sin)
-        for layer in self.layers:
-            hidden, branch, bias = layer.forward_fused(hidden, branch, bias, **kw)
+        consumers = list(self.layers[1:]) + [None]
+        for layer, nxt in zip(self.layers, consumers):
+            # the MLP output of a layer is consumed by the next layer's input norm, or by the final norm
+            norm = nxt.input_layernorm if nxt is not None else self.final_layernorm
+            defer = getattr(norm, "accepts_gemm_partials", False)
+            hidden, branch, bias = layer.forward_fused(hidden, branch, bias, defer_mlp_reduction=defer, **kw)
         if self.final_layernorm is not None:
             _, out = self.final_layernorm.add_and_norm(branch, hidden, bias)
         else:

@@ -26,6 +26,9 @@ class TransformerConfig:
     enable_cuda_graph: bool = False
     inference_sampling_seed: int = 42
     init_method_std: float = 0.02
+    # not in the reference: hand the split-K partial sums of out-proj / fc2 to the residual-add + norm kernel
+    # instead of reducing them in a kernel of their own (bit-identical results, two launches fewer per layer)
+    fuse_splitk_reduction_into_norm: bool = True
     fp8: Optional[str] = None                   # None | "mxfp8" (E8M0 scale per 32) | "blockwise" (fp32, 128x128 / 1x128)
 
     def __post_init__(self):

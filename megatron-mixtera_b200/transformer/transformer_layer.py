@@ -34,17 +34,23 @@ class TransformerLayer(torch.nn.Module):
         self.pre_mlp_layernorm = build_module(submodules.pre_mlp_layernorm, config=config, hidden_size=config.hidden_size, eps=eps)
         self.mlp = build_module(submodules.mlp, config=config)
 
-    def forward_fused(self, hidden, branch, branch_bias, **attn_kwargs):
+    def forward_fused(self, hidden, branch, branch_bias, defer_mlp_reduction: bool = False, **attn_kwargs):
         """``hidden`` [T, H] residual stream; ``branch`` the previous layer's MLP output not yet added
-        (None for the first layer).  Returns (hidden after the attention residual, MLP output, MLP bias)."""
+        (None for the first layer).  Returns (hidden after the attention residual, MLP output, MLP bias).
+
+        The out-projection hands its split-K partial sums straight to the residual-add + norm kernel when that
+        norm can take them; the MLP output does the same when the caller says its consumer can
+        (``defer_mlp_reduction``)."""
         fp8 = self.config.fp8  # with an FP8 recipe the norms emit the quantised input of the linear that follows
+        small = self.config.hidden_size <= 8192 and getattr(self.config, "fuse_splitk_reduction_into_norm", True)
+        defer_attn = small and getattr(self.pre_mlp_layernorm, "accepts_gemm_partials", False)
         if branch is None:
             normed = self.input_layernorm(hidden, quantize=fp8)
         else:
             hidden, normed = self.input_layernorm.add_and_norm(branch, hidden, branch_bias, quantize=fp8)
-        attn_out, attn_bias = self.self_attention(normed, **attn_kwargs)
+        attn_out, attn_bias = self.self_attention(normed, defer_output_reduction=defer_attn, **attn_kwargs)
         hidden, normed = self.pre_mlp_layernorm.add_and_norm(attn_out, hidden, attn_bias, quantize=fp8)
-        mlp_out, mlp_bias = self.mlp(normed)
+        mlp_out, mlp_bias = self.mlp(normed, defer_output_reduction=defer_mlp_reduction and small)
         return hidden, mlp_out, mlp_bias
 
     def forward(self, hidden_states, attention_mask=None, inference_context=None, rotary_pos_cos=None,

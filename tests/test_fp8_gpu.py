@@ -165,3 +165,40 @@ def test_fused_rowblock_quantisers(ops):
     t = ops.activation_fp8_rowblock(y.cuda(), "swiglu")
     q_ref, s_ref = O.quantize_fp8_rowblock(F.silu(a) * b, 128)
     assert (t.q.cpu() != q_ref.view(torch.uint8)).float().mean() < 5e-3
+
+
+# ------------------------------------------------------------------------------------------
+# Split-K partial sums of the FP8 GEMMs consumed by the residual-add + norm (+ quantise) kernel
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("recipe", ["mxfp8", "blockwise"])
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (128, 4096, 14336), (20, 1024, 512)])
+def test_fp8_splitk_partials_into_add_norm_equal_unfused(ops, recipe, M, N, K):
+    x, w = randn((M, K), 1).cuda(), randn((N, K), 2, 0.05).cuda()
+    r = randn((M, N), 3).cuda()
+    g = (1 + randn((N,), 4, 0.02).float()).to(BF16).cuda()
+    if recipe == "mxfp8":
+        xq, wq = ops.quantize_mxfp8(x), ops.quantize_mxfp8(w)
+        y = ops.gemm_mxfp8(xq, wq)
+        h_ref, t_ref = ops.add_norm_mxfp8(y, g, residual=r, want_hidden=True)
+    else:
+        xq, wq = ops.quantize_fp8_rowblock(x), ops.quantize_fp8_weight_block128(w)
+        y = ops.gemm_fp8_block(xq, wq)
+        h_ref, t_ref = ops.add_norm_fp8_rowblock(y, g, residual=r, want_hidden=True)
+    p = ops.gemm_splitk(xq, wq)
+    h, t = ops.add_norm_splitk(p, g, residual=r, want_hidden=True, quantize=recipe)
+    assert torch.equal(h, h_ref) and torch.equal(t.q, t_ref.q)
+    if recipe == "mxfp8":
+        # scale bytes of the rows that exist (the buffers are padded to whole 256-row groups and never cleared)
+        rr = torch.arange(M).view(-1, 1)
+        bb = torch.arange(N // 32).view(1, -1)
+        off = ((rr // 128) * (N // 128) + bb // 4) * 512 + (rr % 32) * 16 + ((rr % 128) // 32) * 4 + bb % 4
+        off = off.flatten().cuda()
+        assert torch.equal(t.sf[off], t_ref.sf[off])
+    else:
+        assert torch.equal(t.scale[:, :M], t_ref.scale[:, :M])
+    # bf16 output of the same partial sums
+    p = ops.gemm_splitk(xq, wq)
+    h2, n2 = ops.add_norm_splitk(p, g, residual=r, want_hidden=True)
+    _, n_ref = ops.add_norm(y, g, residual=r, want_hidden=True)
+    assert torch.equal(h2, h_ref) and torch.equal(n2, n_ref)
+    assert ops.device_status() == 0

@@ -77,6 +77,47 @@ def test_gemm_is_deterministic_and_linear(ops):
     assert torch.equal(y2.float(), y1.float() * 2)
 
 
+@pytest.mark.parametrize(
+    "M,N,K,norm",
+    [
+        (64, 4096, 4096, "rms"),     # Llama-3-8B out-projection at decode: 8 splits
+        (64, 4096, 14336, "rms"),    # fc2: long K
+        (33, 1024, 256, "rms"),      # a single split: the partial sums are the whole product
+        (16, 1024, 512, "layer"),    # LayerNorm with beta and a linear bias
+        (130, 8192, 1024, "rms"),    # two token blocks of 128, widest supported row
+        (5, 264, 640, "layer"),      # row not a multiple of 256 elements
+    ],
+)
+def test_splitk_partials_into_add_norm_equal_unfused(ops, M, N, K, norm):
+    # the fused pair (GEMM leaves fp32 partial sums, residual-add + norm reduces them) is bit-identical to
+    # GEMM -> reduction kernel -> residual-add + norm
+    x, w = randn((M, K), 1).cuda(), randn((N, K), 2, 0.05).cuda()
+    r = randn((M, N), 3).cuda()
+    g = (1 + randn((N,), 4, 0.02).float()).to(BF16).cuda()
+    beta = randn((N,), 5, 0.1).cuda() if norm == "layer" else None
+    bias = randn((N,), 6).cuda() if norm == "layer" else None
+    y = ops.gemm(x, w)
+    h_ref, n_ref = ops.add_norm(y, g, bias=bias, residual=r, beta=beta, want_hidden=True)
+    p = ops.gemm_splitk(x, w)
+    assert p.num_splits >= 1 and p.shape == (M, N)
+    h, n = ops.add_norm_splitk(p, g, bias=bias, residual=r, beta=beta, want_hidden=True)
+    assert torch.equal(h, h_ref) and torch.equal(n, n_ref)
+    # hidden only (the last layer of a model without a final norm)
+    p = ops.gemm_splitk(x, w)
+    h2, none = ops.add_norm_splitk(p, None, bias=bias, residual=r, want_hidden=True, want_normed=False)
+    assert none is None and torch.equal(h2, h_ref)
+    assert ops.device_status() == 0
+
+
+def test_splitk_partials_are_invalidated_by_the_next_gemm(ops):
+    x, w = randn((8, 256), 1).cuda(), randn((256, 256), 2, 0.05).cuda()
+    g = torch.ones(256, dtype=BF16, device="cuda")
+    p = ops.gemm_splitk(x, w)
+    ops.gemm(x, w)  # reuses the workspace that holds p
+    with pytest.raises(ops.B200Error):
+        ops.add_norm_splitk(p, g)
+
+
 def test_gemm_rejects_bad_arguments(ops):
     x = randn((8, 100), 1).cuda()  # K not a multiple of 8
     w = randn((16, 100), 2).cuda()

@@ -36,7 +36,7 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         ffn_hidden_size=meta["ffn_hidden_size"], normalization="RMSNorm" if llama else "LayerNorm",
         gated_linear_unit=llama, activation="silu" if llama else "gelu", add_bias_linear=not llama,
         enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0, tensor_model_parallel_size=meta.get("tp", 1),
-        fp8=meta.get("fp8"))
+        fp8=meta.get("fp8"), fuse_splitk_reduction_into_norm=meta.get("fuse_splitk", True))
     model = GPTModel(cfg, vocab_size=meta["vocab_size"], max_sequence_length=meta["max_sequence_length"],
                      position_embedding_type="rope" if llama else "learned_absolute",
                      rotary_base=meta.get("rotary_base", 10000))
@@ -169,6 +169,19 @@ def test_llama_tiny_cuda_graph_replay_is_bit_identical_to_eager():
     assert s_graph["rel"] == s_eager["rel"] and s_graph["flips"] == s_eager["flips"]
     for step, lg in s_eager["logits"].items():
         assert torch.equal(lg, s_graph["logits"][step])
+
+
+@pytest.mark.parametrize("fp8", [None, "mxfp8"])
+def test_llama_tiny_splitk_fusion_switch_changes_no_bit(fp8):
+    # handing the split-K partial sums of out-proj / fc2 to the norm kernel is a pure launch-count optimisation
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = json.loads(str(z["meta"]))
+    meta["fp8"] = fp8
+    s_fused, _, _ = run_teacher_forced(dict(meta, fuse_splitk=True), z)
+    s_plain, _, _ = run_teacher_forced(dict(meta, fuse_splitk=False), z)
+    assert len(s_fused["logits"]) > 5
+    for step, lg in s_plain["logits"].items():
+        assert torch.equal(lg, s_fused["logits"][step])
 
 
 def test_c0_tiny_gpt_matches_bf16_oracle():
