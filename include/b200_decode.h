@@ -270,9 +270,15 @@ int b200_paged_attention(const b200_attention_args* args, b200_stream_t stream);
  * b200_topk_probs_bf16: temperature, keep logits >= k-th largest, softmax -> fp32 probs [rows, vocab];
  *   replaces modify_logits_for_top_k_filtering + softmax (same file :216-219, 292-305).  The draw itself
  *   (torch.multinomial on the controller's generator) stays with the caller.
+ * b200_topp_probs_bf16: temperature, nucleus filter, softmax over the kept set -> fp32 probs; replaces
+ *   modify_logits_for_top_p_filtering + softmax (same file :221-240, 306-309): with tokens in descending order
+ *   of logit (equal logits by ascending index) a token is kept iff the probability mass strictly ahead of it is
+ *   <= top_p.  Computed in fp32 (the reference's cumulative sum runs in the logits' dtype).
  */
 int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int vocab, b200_stream_t stream);
 int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,
+                         float temperature, b200_stream_t stream);
+int b200_topp_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, float top_p,
                          float temperature, b200_stream_t stream);
 
 #ifdef __cplusplus

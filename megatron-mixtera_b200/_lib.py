@@ -48,6 +48,7 @@ EXPORTED_SYMBOLS = (
     "b200_paged_attention",
     "b200_argmax_bf16",
     "b200_topk_probs_bf16",
+    "b200_topp_probs_bf16",
 )
 
 
@@ -167,6 +168,7 @@ def load() -> ctypes.CDLL:
     lib.b200_paged_attention.argtypes = [POINTER(AttentionArgs), c_void_p]
     lib.b200_argmax_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
     lib.b200_topk_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200_topp_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_float, c_float, c_void_p]
     for name in EXPORTED_SYMBOLS:
         fn = getattr(lib, name)
         if fn.restype is c_int or name.startswith("b200_") and fn.restype not in (c_char_p, c_size_t):

@@ -1,4 +1,4 @@
-// Sampling over vocab-sized bf16 logit rows: greedy argmax and top-k filtered probabilities.
+// Sampling over vocab-sized bf16 logit rows: greedy argmax, top-k and top-p filtered probabilities.
 // One CTA per row; rows are read once with 16-byte loads where the row start allows it.
 #include "common.cuh"
 
@@ -153,6 +153,150 @@ topk_probs_kernel(const uint16_t* __restrict__ logits, int64_t ld, float* __rest
   }
 }
 
+
+// Deterministic block reductions (fixed tree, independent of timing).
+__device__ __forceinline__ float block_sum_1024(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  return warp_sum(red[lane]);
+}
+__device__ __forceinline__ int block_sum_1024_int(int v, int* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int t = red[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// Top-p (nucleus): with the tokens in descending order of logit (equal logits: ascending index), a token is
+// kept iff the probability mass strictly ahead of it is <= top_p (so the token that crosses top_p is kept and
+// the first token always is) - the rule of `modify_logits_for_top_p_filtering`.  Kept tokens get
+// softmax over the kept set, the rest 0.  All tokens with the same bf16 logit have the same probability, so
+// the cut is found by a binary search over the 16-bit key space: A(k) = mass of the tokens with key > k is
+// monotone in k, and the smallest key with A(k) <= top_p is the last (possibly partially) kept value; of its
+// n tied tokens the first floor((top_p - A) / p) + 1 by index are kept.  Everything is computed in fp32 with
+// fixed-order reductions.
+__global__ void __launch_bounds__(kThreads)
+topp_probs_kernel(const uint16_t* __restrict__ logits, int64_t ld, float* __restrict__ probs, int vocab, float top_p,
+                  float temperature) {
+  __shared__ float red[32];
+  __shared__ int redi[32];
+  __shared__ int warp_base[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
+  float* prow = probs + static_cast<int64_t>(blockIdx.x) * vocab;
+  const bool scale = temperature != 1.0f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  auto load_key = [&](int i) -> uint32_t {
+    uint16_t b = row[i];
+    if (scale) {
+      __nv_bfloat16 q = __float2bfloat16_rn(bf16_bits_to_float(b) / temperature);
+      b = *reinterpret_cast<uint16_t*>(&q);
+    }
+    return bf16_key(b);
+  };
+  auto key_to_float = [&](uint32_t key) -> float {
+    const uint16_t b = (key & 0x8000u) ? static_cast<uint16_t>(key & 0x7fffu) : static_cast<uint16_t>(~key & 0xffffu);
+    return bf16_bits_to_float(b);
+  };
+
+  // row maximum (as a key) and the softmax denominator over the whole row
+  uint32_t kmax = 0;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) kmax = max(kmax, load_key(i));
+  kmax = static_cast<uint32_t>(warp_max(static_cast<float>(kmax)));  // keys < 2^16 are exact in fp32
+  if (lane == 0) red[warp] = static_cast<float>(kmax);
+  __syncthreads();
+  kmax = static_cast<uint32_t>(warp_max(red[lane]));
+  const float mx = key_to_float(kmax);
+  float z = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) z += expf(key_to_float(load_key(i)) - mx);
+  z = block_sum_1024(z, red);
+  const float budget = top_p * z;  // un-normalised mass allowed strictly ahead of a kept token
+
+  // mass(k) = sum of exp over tokens with key > k
+  auto mass_above = [&](uint32_t k) -> float {
+    float a = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += kThreads) {
+      const uint32_t ki = load_key(i);
+      if (ki > k) a += expf(key_to_float(ki) - mx);
+    }
+    return block_sum_1024(a, red);
+  };
+  // smallest key in [0, kmax] with mass_above(key) <= budget (kmax always qualifies: mass 0)
+  uint32_t lo = 0, hi = kmax;
+  if (top_p >= 1.0f) hi = 0;  // everything is kept
+  while (lo < hi) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (mass_above(mid) <= budget) {
+      hi = mid;
+    } else {
+      lo = mid + 1;
+    }
+  }
+  // `hi` may be a key no token has; move up to the smallest present key >= hi (same kept set)
+  uint32_t kcut = 0xffffu;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const uint32_t ki = load_key(i);
+    if (ki >= hi) kcut = min(kcut, ki);
+  }
+  kcut = 0xffffu - static_cast<uint32_t>(warp_max(static_cast<float>(0xffffu - kcut)));
+  __syncthreads();
+  if (lane == 0) red[warp] = static_cast<float>(0xffffu - kcut);
+  __syncthreads();
+  kcut = 0xffffu - static_cast<uint32_t>(warp_max(red[lane]));
+
+  const float above = mass_above(kcut);
+  const float e_cut = expf(key_to_float(kcut) - mx);
+  int n_ties = 0;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) n_ties += load_key(i) == kcut ? 1 : 0;
+  n_ties = block_sum_1024_int(n_ties, redi);
+  int keep_ties = n_ties;
+  if (top_p < 1.0f) {
+    const float room = fmaxf(budget - above, 0.f);
+    const float q = floorf(room / e_cut) + 1.f;
+    if (q < static_cast<float>(n_ties)) keep_ties = static_cast<int>(q);
+  }
+  const float inv = 1.f / (above + static_cast<float>(keep_ties) * e_cut);
+
+  // write: key > kcut kept; key == kcut kept for the first keep_ties tokens in index order
+  int base = 0;  // ties seen in earlier chunks
+  for (int c0 = 0; c0 < vocab; c0 += kThreads) {
+    const int i = c0 + threadIdx.x;
+    const uint32_t ki = i < vocab ? load_key(i) : 0u;
+    const bool tie = i < vocab && ki == kcut;
+    const uint32_t ballot = __ballot_sync(0xffffffffu, tie);
+    if (keep_ties < n_ties) {  // uniform branch: rank the ties of this chunk by index
+      __syncthreads();
+      if (lane == 0) warp_base[warp] = __popc(ballot);
+      __syncthreads();
+      int before = 0, total = 0;
+      for (int wI = 0; wI < 32; ++wI) {
+        const int cnt = warp_base[wI];
+        if (wI < warp) before += cnt;
+        total += cnt;
+      }
+      const int rank = base + before + __popc(ballot & ((1u << lane) - 1u));
+      base += total;
+      if (i < vocab) {
+        const bool keep = ki > kcut || (tie && rank < keep_ties);
+        prow[i] = keep ? expf(key_to_float(ki) - mx) * inv : 0.f;
+      }
+    } else if (i < vocab) {
+      prow[i] = ki >= kcut ? expf(key_to_float(ki) - mx) * inv : 0.f;
+    }
+  }
+}
+
 }  // namespace sampling
 }  // namespace b200
 
@@ -173,6 +317,16 @@ int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows,
   return launch_pdl(sampling::topk_probs_kernel, dim3(rows), dim3(sampling::kThreads), 0,
                     reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, probs, vocab,
                     top_k, temperature);
+}
+
+int b200_topp_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, float top_p,
+                         float temperature, b200_stream_t stream) {
+  using namespace b200;
+  if (!logits || !probs || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
+  if (!(top_p > 0.f) || top_p > 1.f || !(temperature > 0.f)) return B200_ERR_INVALID_ARGUMENT;
+  return launch_pdl(sampling::topp_probs_kernel, dim3(rows), dim3(sampling::kThreads), 0,
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, probs, vocab,
+                    top_p, temperature);
 }
 
 }  // extern "C"

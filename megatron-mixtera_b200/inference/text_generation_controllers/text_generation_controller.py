@@ -50,8 +50,8 @@ class TextGenerationController:
         ``top_k == 1``: greedy, the argmax kernel (ties go to the smallest index).  ``top_k > 1``: the
         top-k kernel produces the filtered, temperature-scaled probabilities and ``torch.multinomial``
         draws from them with the controller's generator, as the reference does (:292-309).  ``top_k == 0``
-        with ``top_p == 0`` keeps the whole vocabulary.  top-p (sort-based) sampling is rejected: it is not
-        part of the decode path built here.
+        with ``top_p == 0`` keeps the whole vocabulary.  ``top_p > 0``: the nucleus kernel (the reference's
+        sort + cumulative sum + shift-by-one rule, :221-240, evaluated in fp32 without a sort).
         """
         if kwargs.get("common_inference_params"):
             sampling_params = kwargs["common_inference_params"]
@@ -74,7 +74,11 @@ class TextGenerationController:
             if vocab_size:
                 sampled = torch.clamp(sampled, min=0, max=vocab_size - 1)
             return sampled
-        raise NotImplementedError("top-p sampling is outside the decode path built here")
+        probs = ops.topp_probs(last_token_logits, top_p, temperature)
+        sampled = torch.multinomial(probs, num_samples=1, generator=self.sampling_rng).view(-1)
+        if vocab_size:
+            sampled = torch.clamp(sampled, min=0, max=vocab_size - 1)
+        return sampled
 
     # --------------------------------------------------------------------------------------------
     @torch.inference_mode()

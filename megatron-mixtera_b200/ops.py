@@ -445,3 +445,13 @@ def topk_probs(logits, top_k: int, temperature: float = 1.0):
     check("b200_topk_probs_bf16", _lib.load().b200_topk_probs_bf16(
         logits.data_ptr(), logits.stride(0), probs.data_ptr(), rows, vocab, top_k, float(temperature), _stream()))
     return probs
+
+
+def topp_probs(logits, top_p: float, temperature: float = 1.0):
+    """fp32 probabilities after temperature and top-p (nucleus) filtering, [rows, vocab]."""
+    _need(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    probs = torch.empty((rows, vocab), dtype=torch.float32, device=logits.device)
+    check("b200_topp_probs_bf16", _lib.load().b200_topp_probs_bf16(
+        logits.data_ptr(), logits.stride(0), probs.data_ptr(), rows, vocab, float(top_p), float(temperature), _stream()))
+    return probs

@@ -536,7 +536,7 @@ def filtered_probabilities(logits, top_k: int, top_p: float, temperature: float,
         kth = torch.topk(x, top_k)[0][..., -1, None]
         x.masked_fill_(x < kth, float("-inf"))
     elif top_p > 0.0:
-        sl, si = torch.sort(x, descending=True)
+        sl, si = torch.sort(x, descending=True, stable=True)  # equal logits keep index order
         cp = sl.softmax(dim=-1).cumsum(dim=-1)
         f = cp > top_p
         f[:, 1:] = f[:, :-1].clone()

@@ -212,6 +212,62 @@ def test_topk_probabilities(ops, top_k, temperature):
     assert torch.allclose(probs.sum(-1), torch.ones(5), atol=1e-4)
 
 
+def _nucleus_reference(x_bf16, top_p):
+    """Oracle probabilities (fp32 restatement of the reference's sort / cumsum / shift rule) and, per token, the
+    mass strictly ahead of it in float64 - the quantity the keep decision compares with top_p."""
+    ref = O.filtered_probabilities(x_bf16.float(), 0, top_p, 1.0)
+    sl, si = torch.sort(x_bf16.double(), descending=True, stable=True)
+    excl = sl.softmax(-1).cumsum(-1) - sl.softmax(-1)
+    ahead = torch.empty_like(excl).scatter_(1, si, excl)
+    return ref, ahead
+
+
+@pytest.mark.parametrize("vocab", [1000, 32000, 128256])
+@pytest.mark.parametrize("top_p,temperature", [(0.1, 1.0), (0.5, 0.7), (0.9, 1.0), (0.97, 1.3), (1.0, 1.0)])
+def test_topp_probabilities(ops, vocab, top_p, temperature):
+    g = torch.Generator().manual_seed(2)
+    logits = (torch.randn((6, vocab), generator=g) * 3).to(BF16)
+    logits[5] = (logits[5] * 2).round() / 2  # a row with few distinct values: many ties around the cut
+    probs = ops.topp_probs(logits.cuda(), top_p, temperature).cpu()
+    x = logits.clone()
+    if temperature != 1.0:
+        x.div_(temperature)  # in bf16, like the reference's in-place division
+    ref, ahead = _nucleus_reference(x, top_p)
+    assert torch.allclose(probs.sum(-1), torch.ones(6), atol=1e-4)
+    if top_p == 1.0:
+        # In exact arithmetic nothing is filtered.  (The fp32 restatement drops a tail whose cumulative sum rounds
+        # above 1.0; what it drops carries no mass.)
+        assert float((probs - x.float().softmax(-1)).abs().max()) < 1e-6
+        assert float(probs[ref == 0].sum()) < 1e-4
+        return
+    differ = (probs > 0) != (ref > 0)
+    # a keep/drop decision may only differ where the mass ahead of the token equals top_p to the rounding of an
+    # fp32 sum over the row (ours and the restatement's own): a few 1e-6 at 128 k entries
+    # (in a flat 128 k row that band can hold a hundred tokens of 1e-7 each, so their number is not bounded here)
+    assert bool(((ahead[differ] - top_p).abs() < 5e-5).all()), (int(differ.sum()), ahead[differ])
+    assert bool((probs > 0)[torch.arange(6), x.float().argmax(-1)].all())  # the top token always survives
+    # a token that flips at the cut of a 128 k row carries ~1e-5 of mass, so the vectors agree everywhere to 1e-4;
+    # rows whose support is identical agree to fp32 rounding
+    assert float((probs - ref).abs().max()) < 1e-4
+    same = ~differ.any(-1)
+    if bool(same.any()):
+        assert float((probs[same] - ref[same]).abs().max()) < 1e-5
+
+
+def test_topp_equal_logits_keep_the_lowest_indices(ops):
+    # all tokens tie: the kept ones are the first floor(top_p / p) + 1 by index
+    logits = torch.full((2, 1000), 1.5).to(BF16)
+    probs = ops.topp_probs(logits.cuda(), 0.2995, 1.0).cpu()
+    assert int((probs > 0).sum(-1)[0]) == 300 and bool((probs[:, :300] > 0).all()) and bool((probs[:, 300:] == 0).all())
+    assert torch.allclose(probs[:, :300], torch.full((2, 300), 1 / 300), atol=1e-7)
+    # one dominant token: it alone survives whatever top_p is
+    logits[:, 7] = 40.0
+    probs = ops.topp_probs(logits.cuda(), 0.9, 1.0).cpu()
+    assert bool((probs[:, 7] == 1).all()) and int((probs > 0).sum()) == 2
+    with pytest.raises(ops.B200Error):
+        ops.topp_probs(logits.cuda(), 0.0, 1.0)
+
+
 # ------------------------------------------------------------------------------------------
 # Paged attention
 # ------------------------------------------------------------------------------------------
