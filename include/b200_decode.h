@@ -261,6 +261,14 @@ typedef struct {
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);
 int b200_rope_append(const b200_attention_args* args, b200_stream_t stream);
 int b200_paged_attention(const b200_attention_args* args, b200_stream_t stream);
+/* Prefill / mixed steps (flash_attn_varlen_func with block_table, attention.py:501-558), after b200_rope_append:
+ * `units` [num_units][4] int32 on the device = {block-table row, first token, number of tokens, 0}; the tokens of a
+ * unit are consecutive tokens of ONE request, at most 64 / (nq / nkv) of them; entries with 0 tokens are skipped (so a
+ * fixed-size list can be padded).  kv_seq_lengths[t] is the number of keys token t sees (its position + 1).  Same
+ * result as b200_paged_attention with row_of_token (one CTA per token) up to summation order, but every K/V tile is
+ * read once per unit instead of once per token.  bf16 pool, nq / nkv in {1, 2, 4, 8, 16}. */
+int b200_paged_prefill_attention(const b200_attention_args* args, const int32_t* units, int num_units,
+                                 b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Sampling over [rows, vocab] bf16 logits (row stride ld elements).

@@ -530,6 +530,260 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill / mixed steps: a block of consecutive query tokens of one request shares every K/V tile.
+//
+// One CTA = (unit, KV head); a unit is (block-table row, first token, number of tokens <= 64 / G) from a
+// list the host builds per step.  The 64 MMA rows are (token j, group head g) pairs, row = j * G + g, so
+// each of the four consumer warps owns 16 rows and the whole 64-token tile: S = Q K^T (8 n-tiles), per-row
+// causal limit kv_seq_lengths[token], online softmax, O += P V - no cross-warp merge.  Compared with one
+// CTA per token (the decode kernel used row-wise) a K/V tile is read once per 64 / G tokens instead of
+// once per token.  Keys and values are already in the pool (b200_rope_append ran before); the queries are
+// rotated here, in registers.  bf16 pool only.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads, 2)
+paged_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p,
+                     const int32_t* __restrict__ units) {
+  using C = Cfg<D, false>;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  pdl_launch_dependents();
+  const int h = blockIdx.x % p.nkv;
+  const int32_t* unit = units + 4 * (blockIdx.x / p.nkv);
+  const int row = unit[0];
+  const int t0 = unit[1];
+  const int n_tok = unit[2];
+  const int G = p.G;
+  const int qb = 64 / G;  // tokens per unit
+  if (n_tok <= 0 || n_tok > qb || t0 < 0 || t0 + n_tok > p.T) return;  // padding entry (or a malformed one)
+  int max_kv = 0;
+  for (int j = 0; j < n_tok; ++j) max_kv = max(max_kv, p.kv_len[t0 + j]);
+  const int n_tiles = (max_kv + kTile - 1) / kTile;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kStages);
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      pdl_wait();  // the append kernel before us writes the pool
+      const int32_t* bt_row = p.block_table + static_cast<int64_t>(row) * p.max_chunks;
+      int cur_c = -1, cur_id = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % kStages;
+        const uint32_t phase = (i / kStages) & 1;
+        const int tok0 = i * kTile;
+        const int c = tok0 / p.chunk;
+        if (c != cur_c) {
+          cur_c = c;
+          cur_id = bt_row[c];
+        }
+        const int tok_row = cur_id * p.chunk + (tok0 - c * p.chunk);
+        mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusAttnTimeout);
+        uint8_t* kdst = smem + s * C::kStageBytes;
+        uint8_t* vdst = kdst + C::kTileBytes;
+        mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+#pragma unroll
+        for (int sub = 0; sub < C::kSub; ++sub) {
+          tma_load_3d(kdst + sub * C::kSubBytes, &map_k, &full_bar[s], sub * 64, h, tok_row);
+          tma_load_3d(vdst + sub * C::kSubBytes, &map_v, &full_bar[s], sub * 64, h, tok_row);
+        }
+      }
+    }
+    return;
+  }
+
+  // --------------------------------- consumer warps ---------------------------------
+  const int gid = lane >> 2;
+  const int tig = lane & 3;
+  pdl_wait();  // qkv is an earlier kernel's output
+
+  // This thread's two MMA rows: (token, head) and the keys the token may see.
+  int tok_r[2], head_r[2], kv_r[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int rho = warp * 16 + gid + r * 8;
+    const int j = rho / G;
+    head_r[r] = rho - j * G;
+    tok_r[r] = j < n_tok ? t0 + j : -1;
+    kv_r[r] = j < n_tok ? p.kv_len[t0 + j] : 0;
+  }
+  // Q fragments straight from global memory, rotated in registers: the thread that holds columns
+  // (c, c+1) of a row also holds (c + D/2, c + 1 + D/2), the RoPE partners.
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+  {
+    const bool rope = p.cos != nullptr;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (tok_r[r] < 0) continue;
+      const __nv_bfloat16* q = p.qkv + (static_cast<int64_t>(tok_r[r]) * p.nkv + h) * (G + 2) * D + head_r[r] * D;
+      const int64_t pq = rope ? p.pos_q[tok_r[r]] : 0;
+      const __nv_bfloat16* cs = p.cos + pq * (D / 2);
+      const __nv_bfloat16* sn = p.sin + pq * (D / 2);
+#pragma unroll
+      for (int ks = 0; ks < D / 32; ++ks) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int j = ks * 16 + tig * 2 + half * 8;
+          const uint32_t lo = *reinterpret_cast<const uint32_t*>(q + j);
+          const uint32_t hi = *reinterpret_cast<const uint32_t*>(q + j + D / 2);
+          float a1 = bf16_lo(lo), b1 = bf16_hi(lo), a2 = bf16_lo(hi), b2 = bf16_hi(hi);
+          if (rope) {
+            const uint32_t c2 = *reinterpret_cast<const uint32_t*>(cs + j);
+            const uint32_t s2 = *reinterpret_cast<const uint32_t*>(sn + j);
+            rope_pair(a1, a2, bf16_lo(c2), bf16_lo(s2), a1, a2);
+            rope_pair(b1, b2, bf16_hi(c2), bf16_hi(s2), b1, b2);
+          }
+          qf[ks][r + 2 * half] = pack_bf16x2(a1, b1);
+          qf[ks + D / 32][r + 2 * half] = pack_bf16x2(a2, b2);
+        }
+      }
+    }
+  }
+
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  const float scale_log2 = p.scale_log2;
+  // keys this warp's rows can see at most (warp-uniform): later tiles are skipped
+  int warp_kv = max(kv_r[0], kv_r[1]);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) warp_kv = max(warp_kv, __shfl_xor_sync(0xffffffffu, warp_kv, o));
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int s = i % kStages;
+    const uint32_t phase = (i / kStages) & 1;
+    const int tok0 = i * kTile;
+    mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusAttnTimeout);
+    uint8_t* ktile = smem + s * C::kStageBytes;
+    uint8_t* vtile = ktile + C::kTileBytes;
+    if (tok0 < warp_kv) {
+      // ---- S = Q K^T: 16 rows x 64 tokens ----
+      float sacc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+      const int ld_sub = ((lane >> 4) << 3) + (lane & 7);  // token row inside a 16-token slab
+      const int ld_kh = (lane >> 3) & 1;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int chunk16 = (ks * 2 + ld_kh) & 7;
+        const int sub = (ks * 2) >> 3;
+#pragma unroll
+        for (int slab = 0; slab < 4; ++slab) {
+          const int ld_row = slab * 16 + ld_sub;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(smem_u32(ktile) + sub * C::kSubBytes + ld_row * 128 + ((chunk16 ^ (ld_row & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16_16816(sacc[slab * 2], qf[ks], b0, b1);
+          mma_bf16_16816(sacc[slab * 2 + 1], qf[ks], b2, b3);
+        }
+      }
+      // ---- causal mask + online softmax (log2 domain) ----
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int tok = tok0 + nt * 8 + tig * 2 + (c & 1);
+          float v = sacc[nt][c] * scale_log2;
+          if (tok >= kv_r[c >> 1]) v = -INFINITY;
+          sacc[nt][c] = v;
+          mx[c >> 1] = fmaxf(mx[c >> 1], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int i2 = 0; i2 < D / 8; ++i2) {
+        oacc[i2][0] *= alpha[0];
+        oacc[i2][1] *= alpha[0];
+        oacc[i2][2] *= alpha[1];
+        oacc[i2][3] *= alpha[1];
+      }
+      // ---- O += P V, one 16-token slab at a time (P as hi + lo bf16 terms, like the decode kernel) ----
+      const int v_sub = (((lane >> 3) & 1) << 3) + (lane & 7);
+      const int v_dh = lane >> 4;
+#pragma unroll
+      for (int slab = 0; slab < 4; ++slab) {
+        uint32_t pf[4], pl[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          float pv[4], pr[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            pv[c] = exp2f(sacc[slab * 2 + nt][c] - m_use[c >> 1]);
+            l_run[c >> 1] += pv[c];
+            pr[c] = pv[c] - bf16_round(pv[c]);
+          }
+          pf[nt * 2] = pack_bf16x2(pv[0], pv[1]);
+          pf[nt * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+          pl[nt * 2] = pack_bf16x2(pr[0], pr[1]);
+          pl[nt * 2 + 1] = pack_bf16x2(pr[2], pr[3]);
+        }
+        const int v_row = slab * 16 + v_sub;
+        const uint32_t vbase = smem_u32(vtile) + v_row * 128;
+#pragma unroll
+        for (int dn = 0; dn < D / 16; ++dn) {
+          const int chunk16 = (dn * 2 + v_dh) & 7;
+          const int sub = (dn * 2) >> 3;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(vbase + sub * C::kSubBytes + ((chunk16 ^ (v_row & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16_16816(oacc[dn * 2], pf, b0, b1);
+          mma_bf16_16816(oacc[dn * 2], pl, b0, b1);
+          mma_bf16_16816(oacc[dn * 2 + 1], pf, b2, b3);
+          mma_bf16_16816(oacc[dn * 2 + 1], pl, b2, b3);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+  }
+
+  // ------------------------------ normalise and store ------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    if (tok_r[r] < 0) continue;
+    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;  // a token that sees no key gets zeros, as flash-attn does
+    __nv_bfloat16* o = p.out + (static_cast<int64_t>(tok_r[r]) * p.nq + h * G + head_r[r]) * D;
+#pragma unroll
+    for (int i2 = 0; i2 < D / 8; ++i2) {
+      const int col = i2 * 8 + tig * 2;
+      *reinterpret_cast<uint32_t*>(o + col) = pack_bf16x2(oacc[i2][2 * r] * inv, oacc[i2][2 * r + 1] * inv);
+    }
+  }
+}
+
 // Merge the splits of each (token, query head): out = sum_s 2^(lse_s - max) O_s / sum_s 2^(lse_s - max).
 template <int D>
 __global__ void __launch_bounds__(D) combine_kernel(Params p) {
@@ -675,10 +929,48 @@ static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_
   return rc;
 }
 
+template <int D>
+static int launch_prefill(Params& p, const int32_t* units, int num_units, cudaStream_t stream) {
+  using C = Cfg<D, false>;
+  const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.nkv),
+                            static_cast<uint64_t>(p.num_chunks) * p.chunk};
+  const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(p.nkv) * D * 2};
+  const uint32_t box[3] = {64u, 1, kTile};
+  const CUtensorMap* mk = get_tensor_map(p.k_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (!mk || !mv) return B200_ERR_DRIVER;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+        cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int64_t ctas = static_cast<int64_t>(num_units) * p.nkv;
+  if (ctas > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
+  return launch_pdl(paged_prefill_kernel<D>, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), C::kSmemBytes, stream, *mk,
+                    *mv, p, units);
+}
+
 }  // namespace attn
 }  // namespace b200
 
 extern "C" {
+
+int b200_paged_prefill_attention(const b200_attention_args* a, const int32_t* units, int num_units,
+                                 b200_stream_t stream) {
+  using namespace b200;
+  attn::Params p;
+  int rc = attn::fill_params(a, p);
+  if (rc != B200_OK) return rc;
+  if (!a->out || !units || num_units <= 0 || a->kv_cache_fp8) return B200_ERR_INVALID_ARGUMENT;
+  if (64 % p.G != 0) return B200_ERR_INVALID_ARGUMENT;  // group sizes 1, 2, 4, 8, 16
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return a->head_dim == 128 ? attn::launch_prefill<128>(p, units, num_units, s)
+                            : attn::launch_prefill<64>(p, units, num_units, s);
+}
 
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits) {
   if (num_splits <= 1 || num_tokens <= 0 || num_q_heads <= 0 || head_dim <= 0) return 0;

@@ -275,6 +275,12 @@ class DynamicInferenceContext(BaseInferenceContext):
         self._h_len_np = self._h_len.numpy()
         self._h_bt = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, pin_memory=pin)
         self._h_bt_np = self._h_bt.numpy()
+        # Work list of the prefill attention kernel: (block-table row, first token, token count, 0) per block of
+        # `prefill_q_block` consecutive query tokens of one request; built every non-decode step once
+        # `set_prefill_q_block` has been called (by the model wrapper, which knows the head grouping).
+        self.prefill_q_block = 0
+        self.prefill_units = None
+        self.prefill_unit_count = 0
         self._copy_event = torch.cuda.Event() if pin else None
         self._copies_pending = False
         self.h2d_bytes = 0  # bytes mirrored host -> device so far (benchmark accounting)
@@ -287,6 +293,40 @@ class DynamicInferenceContext(BaseInferenceContext):
         self.dummy_chunk_idx = self.chunk_allocator.dummy_chunk_idx
 
         self.reset_attention_state()
+
+    def set_prefill_q_block(self, q_block: int) -> None:
+        """Tokens per prefill work unit (64 / query heads per KV head); 0 disables the work list."""
+        self.prefill_q_block = int(q_block)
+        if self.prefill_q_block > 0:
+            n = -(-self.max_tokens // self.prefill_q_block) + self.max_requests + 1
+            pin = self.device.type == "cuda"
+            self._h_units = torch.zeros((n, 4), dtype=torch.int32, pin_memory=pin)
+            self._h_units_np = self._h_units.numpy()
+            self.prefill_units = torch.zeros((n, 4), dtype=torch.int32, device=self.device)
+            self.prefill_unit_count = 0
+
+    def _build_prefill_units(self, ql: np.ndarray, n_rows: int, padded: int, graphs: bool) -> None:
+        """Split every request's query tokens into blocks of `prefill_q_block` (host side, vectorised)."""
+        qb = self.prefill_q_block
+        ql = ql.astype(np.int64)
+        nb = -(-ql // qb)
+        total = int(nb.sum())
+        u = self._h_units_np
+        # under a CUDA graph the launch size is fixed by the padded sizes; unused entries have 0 tokens
+        bound = (-(-padded // qb) + n_rows) if graphs else max(total, 1)
+        bound = min(max(bound, total), u.shape[0])
+        if total:
+            first = np.cumsum(nb) - nb
+            within = np.arange(total, dtype=np.int64) - np.repeat(first, nb)
+            tok0 = np.repeat(np.cumsum(ql) - ql, nb) + within * qb
+            u[:total, 0] = np.repeat(np.arange(ql.shape[0], dtype=np.int64), nb)
+            u[:total, 1] = tok0
+            u[:total, 2] = np.minimum(qb, np.repeat(ql, nb) - within * qb)
+            u[:total, 3] = 0
+        u[total:bound] = 0
+        self.prefill_units[:bound].copy_(self._h_units[:bound], non_blocking=True)
+        self.prefill_unit_count = bound
+        self.h2d_bytes += 16 * bound
 
     # ------------------------------------------------------------------ rounding helpers
     @classmethod
@@ -467,6 +507,8 @@ class DynamicInferenceContext(BaseInferenceContext):
                 t32[0, a:padded] = 0
                 t32[1, a:padded] = 0
             self._d_tok32[:, :padded].copy_(self._h_tok32[:, :padded], non_blocking=True)
+            if self.prefill_q_block > 0:
+                self._build_prefill_units(ql, n_rows, padded, graphs)
         self.query_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[0, :dev_rows], non_blocking=True)
         self.kv_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[2, :dev_rows], non_blocking=True)
         self.kv_seq_lengths = self.kv_seq_lengths_cudagraph_only[:n_rows]

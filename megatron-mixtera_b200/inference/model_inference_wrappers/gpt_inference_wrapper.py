@@ -39,6 +39,13 @@ class GPTInferenceWrapper:
         self._graphs: Dict[int, Any] = {}
         self.graph_replays = 0
         model.eval()
+        cfg = getattr(model, "config", None)
+        if inference_context is not None and cfg is not None and hasattr(inference_context, "set_prefill_q_block"):
+            from ... import ops
+
+            groups = cfg.num_query_groups or cfg.num_attention_heads
+            fp8_pool = getattr(inference_context, "kv_cache_fp8", False)  # the prefill kernel reads a bf16 pool
+            inference_context.set_prefill_q_block(0 if fp8_pool else ops.prefill_q_block(cfg.num_attention_heads, groups))
 
     def prep_model_for_inference(self, prompts_tokens=None):
         self.model.eval()

@@ -427,6 +427,19 @@ def paged_attention(args: AttentionArgs) -> None:
         launch_count += 1  # the split-combine kernel
 
 
+def paged_prefill_attention(args: AttentionArgs, units: torch.Tensor, num_units: int) -> None:
+    """Prefill attention over ``units`` int32 [>= num_units, 4] = (block-table row, first token, token count, 0)."""
+    _need(units, torch.int32, "units")
+    check("b200_paged_prefill_attention", _lib.load().b200_paged_prefill_attention(
+        ctypes.byref(args), units.data_ptr(), int(num_units), _stream()))
+
+
+def prefill_q_block(num_q_heads: int, num_kv_heads: int) -> int:
+    """Tokens per prefill unit for this head grouping (0: the prefill kernel does not support it)."""
+    g = num_q_heads // max(num_kv_heads, 1)
+    return 64 // g if g in (1, 2, 4, 8, 16) else 0
+
+
 def argmax(logits):
     """Greedy token per row of bf16 logits [rows, vocab] -> int64 [rows]."""
     _need(logits, BF16, "logits")

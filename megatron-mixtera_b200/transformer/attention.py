@@ -82,13 +82,18 @@ class PagedFlashDecodeAttention(torch.nn.Module):
                                            fuse_rope_append=True, row_order=ctx.attention_row_order, **common)
             ops.paged_attention(args)
         else:
-            # prefill / mixed step: append every token first, then each token is a row that sees its
-            # request's first (position + 1) keys
+            # prefill / mixed step: append every token first; then either blocks of a request's query tokens share
+            # the K/V tiles (work list built by the context), or - FP8 pool, unusual head groupings - each token
+            # is a row that sees its request's first (position + 1) keys
             args = ops.make_attention_args(block_table=ctx.request_to_kv_chunk_ids_cudagraph_only,
                                            kv_seq_lengths=ctx.token_kv_lengths, row_of_token=ctx.token_to_block_table_row,
                                            num_splits=1, fuse_rope_append=False, **common)
             ops.rope_append(args)
-            ops.paged_attention(args)
+            if getattr(ctx, "prefill_q_block", 0) > 0 and ctx.prefill_q_block == ops.prefill_q_block(self.num_q_heads, self.num_kv_heads):
+                out.zero_()  # padding tokens belong to no unit
+                ops.paged_prefill_attention(args, ctx.prefill_units, ctx.prefill_unit_count)
+            else:
+                ops.paged_attention(args)
         return out
 
 

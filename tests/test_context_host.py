@@ -322,3 +322,30 @@ def test_cuda_graph_token_counts():
     assert c.cuda_graph_token_counts == [64]
     c = make_ctx(max_requests_override=60, num_cuda_graphs=16)
     assert c.cuda_graph_token_counts == [60, 56, 48, 40, 32, 24, 16, 8]
+
+
+def test_prefill_work_list_covers_every_token_once():
+    # blocks of `prefill_q_block` consecutive tokens, never across two requests; decode requests are blocks of one
+    set_rounder(1)
+    ctx = make_ctx()
+    ctx.set_prefill_q_block(16)
+    lens = [40, 1, 16, 33]
+    for i, n in enumerate(lens):
+        ctx.add_request(i, torch.arange(n))
+    ctx.initialize_attention_state()
+    assert not ctx.is_decode_only()
+    n_units = ctx.prefill_unit_count
+    units = ctx.prefill_units[:n_units].numpy()
+    assert n_units == 3 + 1 + 1 + 3
+    seen = np.zeros(sum(lens), dtype=int)
+    row_of_token = ctx.token_to_block_table_row[: sum(lens)].numpy()
+    for row, t0, n, pad in units:
+        assert 1 <= n <= 16 and pad == 0
+        seen[t0 : t0 + n] += 1
+        assert (row_of_token[t0 : t0 + n] == row).all()
+    assert (seen == 1).all()
+    assert ctx.token_kv_lengths[: sum(lens)].tolist() == [p + 1 for n in lens for p in range(n)]
+    # the next step is decode only: no list is built, the old one is not used
+    ctx.update_requests(torch.ones(4, dtype=torch.uint8), torch.arange(4))
+    ctx.initialize_attention_state()
+    assert ctx.is_decode_only()

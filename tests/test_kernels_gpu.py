@@ -405,6 +405,57 @@ def test_paged_attention_prefill_rows_via_row_of_token(ops):
     assert rel_l2(out, ref) < 5e-3
 
 
+@pytest.mark.parametrize("nkv,G,D", [(2, 4, 128), (1, 8, 128), (2, 1, 64), (1, 16, 64), (2, 2, 128)])
+def test_paged_prefill_attention_mixed_step(ops, nkv, G, D):
+    # A mixed step: request 0 prefills 70 tokens, request 1 decodes one token on a context of 37, request 2
+    # prefills 150 tokens.  The prefill kernel (blocks of 64 / G query tokens share the K/V tiles) must agree with
+    # the oracle and with the one-CTA-per-token path.
+    chunk = 64
+    q_lens, kv_total = [70, 1, 150], [70, 38, 150]
+    c = make_paged_case(T=3, nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=kv_total, seed=21, max_pos=256)
+    bt = c["block_table"]
+    row_of_token = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(q_lens)])
+    pos = torch.cat([torch.arange(kv - n, kv, dtype=torch.int64) for n, kv in zip(q_lens, kv_total)])
+    T = int(row_of_token.numel())
+    g = torch.Generator().manual_seed(22)
+    c.update(T=T, qkv=torch.randn((T, nkv, (G + 2) * D), generator=g).to(BF16), pos=pos, local=pos % chunk,
+             chunk_idx=bt[row_of_token.long(), (pos // chunk)].long(), kv_lens=(pos + 1).int())
+    ref_rows, kc_ref, vc_ref = run_cuda_attention(ops, c, num_splits=1, fused=False, row_of_token=row_of_token)
+
+    qb = 64 // G
+    units, t0 = [], 0
+    for r, n in enumerate(q_lens):
+        units += [(r, t0 + b, min(qb, n - b), 0) for b in range(0, n, qb)]
+        t0 += n
+    units += [(0, 0, 0, 0)] * 3  # padding entries are skipped
+    dev = "cuda"
+    half = c["freqs"][:, : D // 2]
+    d = {k: c[k].to(dev) for k in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
+    d.update(kc=c["k_cache"].clone().to(dev), vc=c["v_cache"].clone().to(dev), row=row_of_token.to(dev),
+             cos=torch.cos(half).to(BF16).to(dev), sin=torch.sin(half).to(BF16).to(dev),
+             units=torch.tensor(units, dtype=torch.int32, device=dev),
+             out=torch.full((T, c["nq"] * D), float("nan"), dtype=BF16, device=dev))
+    args = ops.make_attention_args(
+        qkv=d["qkv"], k_cache=d["kc"], v_cache=d["vc"], block_table=d["block_table"], kv_seq_lengths=d["kv_lens"],
+        out=d["out"], num_q_heads=c["nq"], num_kv_heads=nkv, head_dim=D, chunk_size=chunk, token_to_pos_ids=d["pos"],
+        token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
+        rope_cos=d["cos"], rope_sin=d["sin"], num_splits=1, fuse_rope_append=False, row_of_token=d["row"])
+    assert ops.prefill_q_block(c["nq"], nkv) == qb
+    ops.rope_append(args)
+    ops.paged_prefill_attention(args, d["units"], len(units))
+    torch.cuda.synchronize()
+    out = d["out"].cpu().view(T, c["nq"], D)
+    assert not torch.isnan(out.float()).any()  # every token belongs to a unit
+    assert torch.equal(d["kc"].cpu(), kc_ref) and torch.equal(d["vc"].cpu(), vc_ref)
+    assert rel_l2(out, ref_rows) < 2e-3  # same arithmetic, different summation order
+
+    q = O.apply_rope(c["qkv"][..., : G * D].reshape(T, nkv * G, D), c["freqs"][pos])
+    cu_q = torch.tensor([0, 70, 71, 221])
+    ref = O.paged_attention(q, kc_ref, vc_ref, torch.tensor(kv_total), bt.numpy(), cu_q=cu_q)
+    assert rel_l2(out, ref) < 5e-3
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("splits", [1, 3])
 def test_attention_row_order_changes_nothing(ops, splits):
     # the order in which rows are started is a scheduling hint: outputs and pool are bit-identical
