@@ -414,7 +414,8 @@ def run_ours(args, w):
         "launches_per_step": {"graph_forward": graph_launches, "eager_outside_graph": eager_launches_per_step},
         "roofline": {"bound": "hbm", "kernel": f"{'gemm_mxfp8_kernel' if w.fp8 else 'gemm_bf16_kernel'} (tcgen05, {len(model.decoder.layers)} layers x qkv/proj/fc1/fc2)",
                      "achieved": g["bytes"] / g["sec"] / 1e9, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": g["bytes"] / g["sec"] / 1e9 / peak, "traffic": GEMM_DRAM_TRAFFIC_PER_LAYER},
+                     "frac": g["bytes"] / g["sec"] / 1e9 / peak,
+                     "algorithmic_bytes": g["bytes"], "traffic": GEMM_DRAM_TRAFFIC_PER_LAYER.get((args.workload, tp))},
         "kernels": kern,
         "kernel_share_of_layer": {"gemm": gemm_us / layer_us, "paged_attention": kern["paged_attention"]["us"] / layer_us},
         "step_vs_hbm_floor": {"bytes_per_step": step_bytes(w, ctx, B, tp), "floor_ms": step_bytes(w, ctx, B, tp) / peak / 1e6,
@@ -426,9 +427,10 @@ def run_ours(args, w):
         dist.barrier()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per layer's four GEMM launches, from the ncu capture
-# summarised in profiles/ (None until a capture exists).
-GEMM_DRAM_TRAFFIC_PER_LAYER = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one layer's four GEMM launches (bytes), from the ncu capture
+# summarised in profiles/gemm_bf16_kernel_dram_traffic_llama3_8b_M64.md; the capture exists for the bf16 8B shapes at
+# 64 tokens on one GPU only.
+GEMM_DRAM_TRAFFIC_PER_LAYER = {("llama3_8b", 1): 441.8e6, ("smoke", 1): 441.8e6}
 
 
 def step_bytes(w, ctx, B, tp):
