@@ -112,7 +112,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the CUDA stack
 # ---------------------------------------------------------------------------------------------
-def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True):
+def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True):
     from megatron_mixtera_b200 import build, parallel_state
     from megatron_mixtera_b200.gpt.gpt_model import GPTModel
     from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext
@@ -129,7 +129,7 @@ def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True):
         num_query_groups=w.num_query_groups, kv_channels=w.kv_channels, ffn_hidden_size=w.ffn_hidden_size,
         normalization="RMSNorm", gated_linear_unit=True, activation="silu", add_bias_linear=False,
         tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8,
-        fuse_splitk_reduction_into_norm=fuse_splitk)
+        fuse_splitk_reduction_into_norm=fuse_splitk, fuse_tp_allreduce_into_norm=fuse_tp)
     model = GPTModel(cfg, vocab_size=w.vocab_size, max_sequence_length=w.max_sequence_length,
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
@@ -327,7 +327,7 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
-    model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk)
+    model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce)
     prompts = synthetic_prompts(w.num_requests, *w.prompt_len_range, w.vocab_size, seed=0)
     for i, p in enumerate(prompts):
         engine.add_request(i, p, w.num_tokens_to_generate)
@@ -472,6 +472,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "smoke"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
     args = ap.parse_args()

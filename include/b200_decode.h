@@ -201,6 +201,41 @@ int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, con
                                       int m_pad, int rows, int hidden, float eps, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Tensor parallelism: the all-reduce after a row-parallel linear (mappings.py:22-33 called from
+ * RowParallelLinear.forward, layers.py:1225-1281) fused into the residual-add + norm kernel that follows it.
+ *
+ * Every rank of the node owns a data buffer of two slots [max_rows][hidden] bf16 and a flag array
+ * [world_size][max_rows] int32 (zero-initialised), both created with b200_peer_buffer_create and mapped by the
+ * other ranks through the 64-byte CUDA IPC handle (b200_peer_buffer_open); `counters` is 2 local int32 (zeroed).
+ * A rank writes the bf16 output of its row-parallel GEMM into its own slot; b200_allreduce_add_norm_* then
+ * (per token row) tells the peers the row is ready, waits - at most 2 s, then B200 device status 4 - until theirs
+ * are, reads all ranks' rows with peer loads and uses x = bf16(sum in rank order, fp32) exactly like
+ * b200_add_norm_*'s x.  All ranks obtain identical bits.  Consecutive calls must alternate the slot (0, 1, 0, ...)
+ * and every rank must issue the same sequence of calls.  hidden <= 8192, world_size 2..8, no multicast.
+ */
+typedef struct {
+  int32_t world_size, rank;
+  int32_t max_rows, hidden;
+  void* data[8];        /* data[r]: rank r's data buffer (two slots); data[rank] is local memory */
+  int32_t* flags[8];    /* flags[r]: rank r's flag array */
+  int32_t* counters;    /* local */
+} b200_tp_comm;
+int b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+int b200_peer_buffer_open(const unsigned char handle[64], void** ptr);
+int b200_peer_buffer_close(void* ptr);
+int b200_peer_buffer_destroy(void* ptr);
+int b200_allreduce_add_norm_bf16(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                 const void* gamma, const void* beta, void* hidden_out, void* normed_out, int rows,
+                                 int hidden, float eps, b200_stream_t stream);
+int b200_allreduce_add_norm_mxfp8(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                  const void* gamma, const void* beta, void* hidden_out, void* q_out, void* sf_out, int rows,
+                                  int hidden, float eps, b200_stream_t stream);
+int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                         const void* gamma, const void* beta, void* hidden_out, void* q_out,
+                                         float* scale_out, int m_pad, int rows, int hidden, float eps,
+                                         b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.
  *
  * qkv        [T, nkv, (g+2)*d] bf16: per KV group g query heads, then the key, then the value

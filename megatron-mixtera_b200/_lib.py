@@ -43,6 +43,13 @@ EXPORTED_SYMBOLS = (
     "b200_add_norm_splitk_bf16",
     "b200_add_norm_splitk_mxfp8",
     "b200_add_norm_splitk_fp8_rowblock",
+    "b200_peer_buffer_create",
+    "b200_peer_buffer_open",
+    "b200_peer_buffer_close",
+    "b200_peer_buffer_destroy",
+    "b200_allreduce_add_norm_bf16",
+    "b200_allreduce_add_norm_mxfp8",
+    "b200_allreduce_add_norm_fp8_rowblock",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -86,6 +93,20 @@ class AttentionArgs(ctypes.Structure):
         ("k_scale", c_void_p),
         ("v_scale", c_void_p),
         ("row_order", c_void_p),
+    ]
+
+
+class TpComm(ctypes.Structure):
+    """Mirror of ``b200_tp_comm``."""
+
+    _fields_ = [
+        ("world_size", c_int32),
+        ("rank", c_int32),
+        ("max_rows", c_int32),
+        ("hidden", c_int32),
+        ("data", c_void_p * 8),
+        ("flags", c_void_p * 8),
+        ("counters", c_void_p),
     ]
 
 
@@ -163,6 +184,16 @@ def load() -> ctypes.CDLL:
                                                c_void_p, c_int, c_int, c_float, c_void_p]
     lib.b200_add_norm_splitk_fp8_rowblock.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200_peer_buffer_create.argtypes = [c_size_t, POINTER(c_void_p), ctypes.c_char_p]
+    lib.b200_peer_buffer_open.argtypes = [ctypes.c_char_p, POINTER(c_void_p)]
+    lib.b200_peer_buffer_close.argtypes = [c_void_p]
+    lib.b200_peer_buffer_destroy.argtypes = [c_void_p]
+    lib.b200_allreduce_add_norm_bf16.argtypes = [POINTER(TpComm), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_void_p, c_int, c_int, c_float, c_void_p]
+    lib.b200_allreduce_add_norm_mxfp8.argtypes = [POINTER(TpComm), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
+    lib.b200_allreduce_add_norm_fp8_rowblock.argtypes = [POINTER(TpComm), c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]

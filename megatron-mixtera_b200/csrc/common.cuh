@@ -20,6 +20,7 @@ __device__ int g_device_status = 0;
 enum : int {
   kStatusGemmTimeout = 1,
   kStatusAttnTimeout = 2,
+  kStatusPeerTimeout = 4,   // a tensor-parallel peer did not signal within the bound
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

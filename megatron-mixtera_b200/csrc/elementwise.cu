@@ -50,22 +50,81 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ table, cons
   }
 }
 
+// Source "peers": x is the sum over the tensor-parallel ranks of each rank's bf16 partial output row (the
+// all-reduce of RowParallelLinear), read straight from the peers' memory.
+struct PeerSrc {
+  const __nv_bfloat16* data[8];  // slot base of every rank's partial output [max_rows][hidden]; data[rank] is local
+  int32_t* flags[8];             // every rank's flag array [world][max_rows]; flags[rank] is local
+  int32_t* counters;             // local: [0] = calls completed, [1] = CTAs that finished the running call
+  int world, rank, max_rows;
+};
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Row handshake of one all-reduce call: tell every peer that this rank's row is complete, then wait (bounded)
+// until every peer has said the same.  Flags carry the call number (monotonic), so nothing is ever reset; a
+// peer can be at most one call ahead, which only makes its flag larger.  Called by one thread per CTA.
+__device__ __forceinline__ void peer_row_handshake(const PeerSrc& ps, int row) {
+  const int32_t call = ld_acquire_sys(ps.counters) + 1;  // every CTA reads the same value: it moves when all are done
+  __threadfence_system();                                 // the producer kernel's row, visible to the peers
+  for (int q = 0; q < ps.world; ++q)
+    if (q != ps.rank) st_release_sys(ps.flags[q] + ps.rank * ps.max_rows + row, call);
+  const uint64_t t0 = global_timer_ns();
+  for (int q = 0; q < ps.world; ++q) {
+    if (q == ps.rank) continue;
+    const int32_t* f = ps.flags[ps.rank] + q * ps.max_rows + row;
+    while (ld_acquire_sys(f) < call) {
+      if (global_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, flag it, carry on with what is there
+        atomicOr(&g_device_status, kStatusPeerTimeout);
+        return;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
 // h = x (+bias) (+residual) with a bf16 rounding after each add; normed = norm(h) * gamma (+beta).
 // kMaxVec: vectors of 8 elements cached per thread so that the row is read once.
 // kPartials: x is not read; it is bf16(sum over the `splits` fp32 partial products of a split-K GEMM, in split
 // order) - the reduction the GEMM's own second kernel would have done, so that kernel is not launched.  One
 // vector per thread and up to 1024 threads, so that all partial loads of a row are in flight at once.
-template <int kMaxVec, bool kPartials>
-__global__ void __launch_bounds__(kPartials ? 1024 : 256)
+// kSrc 2 ("peers"): x = bf16(sum over the tensor-parallel ranks, in rank order, of their bf16 rows), after the
+// row handshake above; every rank computes the same bits.
+template <int kMaxVec, int kSrc>
+__global__ void __launch_bounds__(kSrc != 0 ? 1024 : 256)
 add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias,
                 const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ hidden_out,
                 __nv_bfloat16* __restrict__ normed_out, int hidden, float eps, uint8_t* __restrict__ q_out,
                 void* __restrict__ sf_out, int q_mode, int m_pad, const float* __restrict__ partials, int splits,
-                int64_t split_stride) {
+                int64_t split_stride, PeerSrc ps) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
+  if constexpr (kSrc == 2) {
+    if (threadIdx.x == 0) peer_row_handshake(ps, blockIdx.x);
+    __syncthreads();
+  }
+  // peers: the call counter moves on when the last CTA of this launch is done with the peers' rows
+  auto finish = [&]() {
+    if constexpr (kSrc == 2) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        if (atomicAdd(&ps.counters[1], 1) == static_cast<int>(gridDim.x) - 1) {
+          ps.counters[1] = 0;
+          __threadfence();
+          atomicAdd(&ps.counters[0], 1);
+        }
+      }
+    }
+  };
   const int64_t off = static_cast<int64_t>(blockIdx.x) * hidden;
   const Vec8* xv = reinterpret_cast<const Vec8*>(x + off);
   const Vec8* rv = residual ? reinterpret_cast<const Vec8*>(residual + off) : nullptr;
@@ -78,7 +137,21 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     const int i = threadIdx.x + it * blockDim.x;
     if (i < nvec) {
       float f[8];
-      if constexpr (kPartials) {
+      if constexpr (kSrc == 2) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = 0.f;
+        for (int q = 0; q < ps.world; ++q) {
+          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(ps.data[q] + off) + i);
+          const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            f[2 * k] += bf16_lo(w4[k]);
+            f[2 * k + 1] += bf16_hi(w4[k]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = bf16_round(f[k]);
+      } else if constexpr (kSrc == 1) {
         const float4* src = reinterpret_cast<const float4*>(partials + off) + 2 * i;
         const int64_t stride4 = split_stride / 4;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
@@ -129,7 +202,10 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       }
     }
   }
-  if (normed_out == nullptr && q_out == nullptr) return;
+  if (normed_out == nullptr && q_out == nullptr) {
+    finish();
+    return;
+  }
   float mean = 0.f, rstd;
   if (beta != nullptr) {  // LayerNorm: two-pass variance on the cached values
     mean = block_sum(sum, red) / hidden;
@@ -184,6 +260,7 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       mx::quantize8_any(q_mode, y, valid, blockIdx.x, i * 8, q_out, hidden, sf_out, hidden / 128, m_pad);
     }
   }
+  finish();
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
@@ -261,10 +338,12 @@ int b200_gather_rows_bf16(const void* table, const int64_t* ids, void* out, int 
 
 static int add_norm_impl(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
                          void* hidden_out, void* normed_out, void* q_out, void* sf_out, int q_mode, int m_pad, int rows,
-                         int hidden, float eps, b200_stream_t stream, const float* partials = nullptr, int splits = 0) {
+                         int hidden, float eps, b200_stream_t stream, const float* partials = nullptr, int splits = 0,
+                         const b200::ew::PeerSrc* peers = nullptr) {
   using namespace b200;
-  if ((!x && !partials) || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if ((!x && !partials && !peers) || rows <= 0 || hidden <= 0) return B200_ERR_INVALID_ARGUMENT;
   if (partials && (splits < 1 || hidden > 8192)) return B200_ERR_INVALID_ARGUMENT;
+  if (peers && (hidden > 8192 || rows > peers->max_rows)) return B200_ERR_INVALID_ARGUMENT;
   if ((normed_out || q_out) && !gamma) return B200_ERR_INVALID_ARGUMENT;
   if (!normed_out && !hidden_out && !q_out) return B200_ERR_INVALID_ARGUMENT;
   if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
@@ -286,19 +365,22 @@ static int add_norm_impl(const void* x, const void* bias, const void* residual, 
   auto Q = static_cast<uint8_t*>(q_out);
   const float* P = nullptr;
   const int64_t zero = 0;
-  if (partials) {  // split-K partial sums [splits][rows][hidden] instead of x
-    const int wide = ((nvec + 31) / 32) * 32;  // <= 1024: one vector per thread
-    return launch_pdl(ew::add_norm_kernel<1, true>, dim3(rows), dim3(wide), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q,
-                      sf_out, q_mode, m_pad, partials, splits, static_cast<int64_t>(rows) * hidden);
-  }
+  ew::PeerSrc none = {};
+  const int wide = ((nvec + 31) / 32) * 32;  // <= 1024 for hidden <= 8192: one vector per thread
+  if (peers)  // the tensor-parallel ranks' partial outputs instead of x
+    return launch_pdl(ew::add_norm_kernel<1, 2>, dim3(rows), dim3(wide), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out,
+                      q_mode, m_pad, P, 0, zero, *peers);
+  if (partials)  // split-K partial sums [splits][rows][hidden] instead of x
+    return launch_pdl(ew::add_norm_kernel<1, 1>, dim3(rows), dim3(wide), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out,
+                      q_mode, m_pad, partials, splits, static_cast<int64_t>(rows) * hidden, none);
   if (per_thread <= 1)
-    return launch_pdl(ew::add_norm_kernel<1, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
+    return launch_pdl(ew::add_norm_kernel<1, 0>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero, none);
   else if (per_thread <= 2)
-    return launch_pdl(ew::add_norm_kernel<2, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
+    return launch_pdl(ew::add_norm_kernel<2, 0>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero, none);
   else if (per_thread <= 4)
-    return launch_pdl(ew::add_norm_kernel<4, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
+    return launch_pdl(ew::add_norm_kernel<4, 0>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero, none);
   else if (per_thread <= 8)
-    return launch_pdl(ew::add_norm_kernel<8, false>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero);
+    return launch_pdl(ew::add_norm_kernel<8, 0>, dim3(rows), dim3(threads), 0, s, X, B, R, Gm, Bt, H, Nn, hidden, eps, Q, sf_out, q_mode, m_pad, P, 0, zero, none);
   return B200_ERR_INVALID_ARGUMENT;  // hidden > 16384
 }
 
@@ -345,6 +427,108 @@ int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, con
   if (!partials || !q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
   return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, nullptr, q_out, scale_out, b200::mx::kQuantBlock128,
                        m_pad, rows, hidden, eps, stream, partials, num_splits);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel all-reduce fused into the residual-add + norm kernel (peer loads over NVLink)
+// ---------------------------------------------------------------------------------------------
+static int peer_src(const b200_tp_comm* c, int slot, b200::ew::PeerSrc& ps) {
+  if (!c || c->world_size < 2 || c->world_size > 8 || c->rank < 0 || c->rank >= c->world_size) return B200_ERR_INVALID_ARGUMENT;
+  if (slot < 0 || slot > 1 || c->max_rows <= 0 || c->hidden <= 0 || !c->counters) return B200_ERR_INVALID_ARGUMENT;
+  const size_t slot_elems = static_cast<size_t>(c->max_rows) * c->hidden;
+  for (int q = 0; q < c->world_size; ++q) {
+    if (!c->data[q] || !c->flags[q]) return B200_ERR_INVALID_ARGUMENT;
+    ps.data[q] = static_cast<const __nv_bfloat16*>(c->data[q]) + slot * slot_elems;
+    ps.flags[q] = c->flags[q];
+  }
+  ps.counters = c->counters;
+  ps.world = c->world_size;
+  ps.rank = c->rank;
+  ps.max_rows = c->max_rows;
+  return B200_OK;
+}
+
+int b200_allreduce_add_norm_bf16(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                 const void* gamma, const void* beta, void* hidden_out, void* normed_out, int rows,
+                                 int hidden, float eps, b200_stream_t stream) {
+  b200::ew::PeerSrc ps = {};
+  const int rc = peer_src(comm, slot, ps);
+  if (rc != B200_OK) return rc;
+  if (hidden != comm->hidden) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, normed_out, nullptr, nullptr, 0, 0, rows, hidden, eps,
+                       stream, nullptr, 0, &ps);
+}
+
+int b200_allreduce_add_norm_mxfp8(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                  const void* gamma, const void* beta, void* hidden_out, void* q_out, void* sf_out, int rows,
+                                  int hidden, float eps, b200_stream_t stream) {
+  b200::ew::PeerSrc ps = {};
+  const int rc = peer_src(comm, slot, ps);
+  if (rc != B200_OK) return rc;
+  if (hidden != comm->hidden || !q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, nullptr, q_out, sf_out, b200::mx::kQuantMx, 0, rows,
+                       hidden, eps, stream, nullptr, 0, &ps);
+}
+
+int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, const void* bias, const void* residual,
+                                         const void* gamma, const void* beta, void* hidden_out, void* q_out,
+                                         float* scale_out, int m_pad, int rows, int hidden, float eps,
+                                         b200_stream_t stream) {
+  b200::ew::PeerSrc ps = {};
+  const int rc = peer_src(comm, slot, ps);
+  if (rc != B200_OK) return rc;
+  if (hidden != comm->hidden || !q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+  return add_norm_impl(nullptr, bias, residual, gamma, beta, hidden_out, nullptr, q_out, scale_out, b200::mx::kQuantBlock128,
+                       m_pad, rows, hidden, eps, stream, nullptr, 0, &ps);
+}
+
+// Peer buffers: device memory that the other ranks of the node map through CUDA IPC handles.
+int b200_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]) {
+  if (!ptr || !handle || bytes == 0) return B200_ERR_INVALID_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess || cudaMemset(p, 0, bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_DRIVER;
+  }
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cudaFree(p);
+    return B200_ERR_DRIVER;
+  }
+  memcpy(handle, &h, 64);
+  *ptr = p;
+  return cudaDeviceSynchronize() == cudaSuccess ? B200_OK : B200_ERR_DRIVER;
+}
+
+int b200_peer_buffer_open(const unsigned char handle[64], void** ptr) {
+  if (!ptr || !handle) return B200_ERR_INVALID_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_DRIVER;
+  }
+  return B200_OK;
+}
+
+int b200_peer_buffer_close(void* ptr) {
+  if (!ptr) return B200_ERR_INVALID_ARGUMENT;
+  if (cudaIpcCloseMemHandle(ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_DRIVER;
+  }
+  return B200_OK;
+}
+
+int b200_peer_buffer_destroy(void* ptr) {
+  if (!ptr) return B200_ERR_INVALID_ARGUMENT;
+  if (cudaFree(ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_DRIVER;
+  }
+  return B200_OK;
 }
 
 static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int q_mode, int m_pad,

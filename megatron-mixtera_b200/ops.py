@@ -368,6 +368,37 @@ def add_norm_splitk(p: GemmPartials, gamma, *, bias=None, residual=None, beta=No
     return h, y
 
 
+def allreduce_add_norm(pending, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5,
+                       want_hidden: bool = False, want_normed: bool = True, quantize=None):
+    """`add_norm` (or its FP8-output forms, by ``quantize``) with x = the sum over the tensor-parallel ranks of the
+    partial outputs in ``pending`` (`tensor_parallel.peer_allreduce.TpPending`): collective + add + norm in one kernel."""
+    comm = pending.comm
+    hidden = pending.shape[-1]
+    rows = 1
+    for d in pending.shape[:-1]:
+        rows *= d
+    dev = comm.device
+    h = torch.empty(pending.shape, dtype=BF16, device=dev) if want_hidden else None
+    lib = _lib.load()
+    c = ctypes.byref(comm.comm)
+    if quantize == "mxfp8":
+        q, sf = _mx_buffers(rows, hidden, dev)
+        check("b200_allreduce_add_norm_mxfp8", lib.b200_allreduce_add_norm_mxfp8(
+            c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(), rows, hidden,
+            eps, _stream()))
+        return h, Mxfp8Tensor(q, sf, pending.shape)
+    if quantize == "blockwise":
+        q, scale, m_pad = _rowblock_buffers(rows, hidden, dev)
+        check("b200_allreduce_add_norm_fp8_rowblock", lib.b200_allreduce_add_norm_fp8_rowblock(
+            c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), scale.data_ptr(), m_pad,
+            rows, hidden, eps, _stream()))
+        return h, Fp8BlockTensor(q, scale, pending.shape, m_pad)
+    y = torch.empty(pending.shape, dtype=BF16, device=dev) if want_normed else None
+    check("b200_allreduce_add_norm_bf16", lib.b200_allreduce_add_norm_bf16(
+        c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps, _stream()))
+    return h, y
+
+
 def attention_workspace(device, num_tokens: int, num_q_heads: int, head_dim: int, num_splits: int):
     nbytes = _lib.load().b200_paged_attention_workspace_bytes(num_tokens, num_q_heads, head_dim, num_splits)
     return _workspace.get(device, "attn", nbytes) if nbytes else None

@@ -45,7 +45,7 @@ class _ParallelLinearBase(torch.nn.Module):
             fn = ops.quantize_mxfp8 if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
             self._wq = fn(self.weight.data)
 
-    def _matmul(self, input_, weight, bias, defer_reduction: bool = False):
+    def _matmul(self, input_, weight, bias, defer_reduction: bool = False, out=None):
         """``defer_reduction``: return the split-K partial sums (`ops.GemmPartials`) for a consumer that reduces
         them itself, instead of the bf16 product; no bias then."""
         assert not (defer_reduction and bias is not None)
@@ -55,12 +55,12 @@ class _ParallelLinearBase(torch.nn.Module):
                 self.quantize_weights()
             if self.fp8 == "mxfp8":
                 x = input_ if quantised_input else ops.quantize_mxfp8(input_)
-                return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_mxfp8(x, self._wq, bias)
+                return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_mxfp8(x, self._wq, bias, out=out)
             x = input_ if quantised_input else ops.quantize_fp8_rowblock(input_)
-            return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_fp8_block(x, self._wq, bias)
+            return ops.gemm_splitk(x, self._wq) if defer_reduction else ops.gemm_fp8_block(x, self._wq, bias, out=out)
         if quantised_input:
             raise ops.B200Error("linear", -1, "got an FP8 input but this layer runs in bf16")
-        return ops.gemm_splitk(input_, weight) if defer_reduction else ops.gemm(input_, weight, bias)
+        return ops.gemm_splitk(input_, weight) if defer_reduction else ops.gemm(input_, weight, bias, out=out)
 
 
 class ColumnParallelLinear(_ParallelLinearBase):
@@ -127,8 +127,21 @@ class RowParallelLinear(_ParallelLinearBase):
         tp = parallel_state.get_tensor_model_parallel_world_size()
         # The bias must be added once, after the reduction: fuse it into the GEMM only at TP=1.
         fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add and tp == 1) else None
-        if defer_reduction and tp == 1 and fuse_bias is None:
+        if defer_reduction and tp == 1 and fuse_bias is None and getattr(self.config, "fuse_splitk_reduction_into_norm", True):
             return self._matmul(input_, self.weight, None, defer_reduction=True), (self.bias if self.skip_bias_add else None)
+        if defer_reduction and tp > 1 and (self.bias is None or self.skip_bias_add) \
+                and getattr(self.config, "fuse_tp_allreduce_into_norm", True):
+            # The partial product goes into this rank's peer-visible slot; the norm kernel that follows sums the
+            # ranks' slots itself (collective + residual add + norm in one launch).
+            from .peer_allreduce import TpPending, get_peer_allreduce
+
+            rows = (input_.q.shape[0] if hasattr(input_, "q") else input_.numel() // input_.shape[-1])
+            comm = get_peer_allreduce(self.output_size, rows)
+            if comm is not None:
+                slot, view = comm.output_slot(rows)
+                self._matmul(input_, self.weight, None, out=view)
+                lead = input_.shape[:-1]
+                return TpPending(comm, slot, (*lead, self.output_size)), (self.bias if self.skip_bias_add else None)
         out = self._matmul(input_, self.weight, fuse_bias)
         if tp > 1:
             out = reduce_from_tensor_model_parallel_region(out, self.tp_group)

@@ -38,6 +38,9 @@ class B200Norm(torch.nn.Module):
         reference (``fused_bias_dropout.py:11-57``, eval mode) fused with the norm that follows it
         and, with ``quantize``, with the FP8 quantisation of the next linear's input.  ``x`` may be the
         un-reduced split-K partial sums of the linear that produced it (`ops.GemmPartials`)."""
+        if type(x).__name__ == "TpPending":  # partial outputs of the tensor-parallel ranks, summed by the kernel
+            return ops.allreduce_add_norm(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps,
+                                          want_hidden=True, quantize=quantize or None)
         if isinstance(x, ops.GemmPartials):
             return ops.add_norm_splitk(x, self.weight, bias=bias, residual=residual, beta=self.bias, eps=self.eps,
                                        want_hidden=True, quantize=quantize or None)

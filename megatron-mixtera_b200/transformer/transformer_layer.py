@@ -42,7 +42,7 @@ class TransformerLayer(torch.nn.Module):
         norm can take them; the MLP output does the same when the caller says its consumer can
         (``defer_mlp_reduction``)."""
         fp8 = self.config.fp8  # with an FP8 recipe the norms emit the quantised input of the linear that follows
-        small = self.config.hidden_size <= 8192 and getattr(self.config, "fuse_splitk_reduction_into_norm", True)
+        small = self.config.hidden_size <= 8192  # one 16-byte vector per thread in the fused norm kernels
         defer_attn = small and getattr(self.pre_mlp_layernorm, "accepts_gemm_partials", False)
         if branch is None:
             normed = self.input_layernorm(hidden, quantize=fp8)

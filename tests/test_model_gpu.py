@@ -36,7 +36,8 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         ffn_hidden_size=meta["ffn_hidden_size"], normalization="RMSNorm" if llama else "LayerNorm",
         gated_linear_unit=llama, activation="silu" if llama else "gelu", add_bias_linear=not llama,
         enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0, tensor_model_parallel_size=meta.get("tp", 1),
-        fp8=meta.get("fp8"), fuse_splitk_reduction_into_norm=meta.get("fuse_splitk", True))
+        fp8=meta.get("fp8"), fuse_splitk_reduction_into_norm=meta.get("fuse_splitk", True),
+        fuse_tp_allreduce_into_norm=meta.get("fuse_tp", True))
     model = GPTModel(cfg, vocab_size=meta["vocab_size"], max_sequence_length=meta["max_sequence_length"],
                      position_embedding_type="rope" if llama else "learned_absolute",
                      rotary_base=meta.get("rotary_base", 10000))

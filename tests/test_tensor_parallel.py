@@ -14,8 +14,8 @@ from conftest import GOLDEN, ROOT
 WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 
-def _torchrun(n, mode, out, port, timeout=240):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", TORCHDYNAMO_DISABLE="1")
+def _torchrun(n, mode, out, port, timeout=240, **extra_env):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", TORCHDYNAMO_DISABLE="1", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER, mode, out]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
@@ -32,10 +32,15 @@ def test_tp2_host_logic_on_gloo(tmp_path):
 def test_tp2_cuda_stack_matches_tp1(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    one, two = str(tmp_path / "tp1.npz"), str(tmp_path / "tp2.npz")
+    one, two, two_nccl = str(tmp_path / "tp1.npz"), str(tmp_path / "tp2.npz"), str(tmp_path / "tp2_nccl.npz")
     _torchrun(1, "cuda", one, 29621)
-    _torchrun(2, "cuda", two, 29622)
-    a, b = np.load(one), np.load(two)
+    _torchrun(2, "cuda", two, 29622)  # all-reduce fused into the norm kernel (peer loads)
+    _torchrun(2, "cuda", two_nccl, 29623, TP_WORKER_NCCL_ALLREDUCE="1")
+    a, b, c = np.load(one), np.load(two), np.load(two_nccl)
+    # the fused all-reduce sums in fp32 and rounds once, NCCL adds bf16 values: same function, bf16 noise apart
+    rel_fn = [float((torch.from_numpy(b[k]) - torch.from_numpy(c[k])).norm() / torch.from_numpy(c[k]).norm())
+              for k in b.files if k.endswith("_logits")]
+    assert max(rel_fn) < 8e-3, max(rel_fn)
     z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
     assert int(b["replays"]) > 10
     rel_12, rel_ref, flips = [], [], 0

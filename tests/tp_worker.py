@@ -99,6 +99,7 @@ def cuda_mode(out_path):
     z = np.load(os.path.join(ROOT, "tests", "golden", "llama_tiny_bf16.npz"))
     meta = json.loads(str(z["meta"]))
     meta["tp"] = world
+    meta["fuse_tp"] = os.environ.get("TP_WORKER_NCCL_ALLREDUCE") != "1"  # default: all-reduce inside the norm kernel
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
     out = {}
     state = {"step": 0}
