@@ -112,7 +112,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the CUDA stack
 # ---------------------------------------------------------------------------------------------
-def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True):
+def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True, fuse_swiglu: bool = True):
     from megatron_mixtera_b200 import build, parallel_state
     from megatron_mixtera_b200.gpt.gpt_model import GPTModel
     from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext
@@ -129,7 +129,8 @@ def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bo
         num_query_groups=w.num_query_groups, kv_channels=w.kv_channels, ffn_hidden_size=w.ffn_hidden_size,
         normalization="RMSNorm", gated_linear_unit=True, activation="silu", add_bias_linear=False,
         tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8,
-        fuse_splitk_reduction_into_norm=fuse_splitk, fuse_tp_allreduce_into_norm=fuse_tp)
+        fuse_splitk_reduction_into_norm=fuse_splitk, fuse_tp_allreduce_into_norm=fuse_tp,
+        fuse_swiglu_into_fc1=fuse_swiglu)
     model = GPTModel(cfg, vocab_size=w.vocab_size, max_sequence_length=w.max_sequence_length,
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
@@ -200,9 +201,16 @@ def kernel_rooflines(model, ctx, T, peak_gbs):
         x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
         if fp8:
             x = ops.quantize_mxfp8(x)
-        sec = sweep(lambda: [m._matmul(x, m.weight, None) for m in mods])
-        b = algorithmic_gemm_bytes(T, N, K, fp8)
+        fused_act = name == "linear_fc1" and getattr(mods[0], "_layout_interleaved", False)
+        if fused_act:  # fc1 + SwiGLU in one kernel: the output is [T, N/2]
+            sec = sweep(lambda: [m.forward_swiglu(x) for m in mods])
+            b = 2.0 * (N * K + T * K + T * N / 2)
+        else:
+            sec = sweep(lambda: [m._matmul(x, m.weight, None) for m in mods])
+            b = algorithmic_gemm_bytes(T, N, K, fp8)
         out[name] = {"us": sec * 1e6, "GB/s": b / sec / 1e9, "frac": b / sec / 1e9 / peak_gbs, "shape": [T, N, K]}
+        if fused_act:
+            out[name]["fused"] = "swiglu"
         gemm_bytes += b
         gemm_time += sec
     # attention on the live context (decode state)
@@ -327,7 +335,8 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
-    model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce)
+    model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce,
+                                                     fuse_swiglu=not args.unfused_swiglu)
     prompts = synthetic_prompts(w.num_requests, *w.prompt_len_range, w.vocab_size, seed=0)
     for i, p in enumerate(prompts):
         engine.add_request(i, p, w.num_tokens_to_generate)
@@ -474,6 +483,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
+    ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
     args = ap.parse_args()

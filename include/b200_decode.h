@@ -75,9 +75,20 @@ int b200_add_norm_bf16(const void* x, const void* bias, const void* residual, co
  *                    (megatron/core/fusions/fused_bias_swiglu.py:15-26, eager bf16 rounding points)
  *   kind 1 (GELU):   in [rows, F] (+ bias[F]); out = bf16(gelu_erf(in + bias))
  *                    (megatron/core/transformer/mlp.py:200-213)
+ *   kind 2 (SwiGLU, tile-interleaved input): of every 128 input columns the first 64 are gate features 64j..64j+63
+ *                    and the last 64 the matching up features - the output of an fc1 whose weight rows were
+ *                    arranged for b200_gemm_bf16_swiglu; F a multiple of 64.
  */
 int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind,
                          b200_stream_t stream);
+/* fc1 + SwiGLU in one kernel (mlp.py:140-234 with fused_bias_swiglu.py:15-26): w [N, K] with N = 2F and rows arranged
+ * per 128-row tile j as [gate rows 64j..64j+63 ; up rows 64j..64j+63] of the reference's [gate ; up] weight;
+ * y [M, F] = bf16(bf16(silu(x w_gate^T)) * bf16(x w_up^T)), the same bits as b200_gemm_bf16 + b200_activation_bf16.
+ * Only shapes whose GEMM is not split along K (b200_gemm_bf16_swiglu_supported returns 1); otherwise use
+ * b200_gemm_bf16 and b200_activation_bf16 kind 2. */
+int b200_gemm_bf16_swiglu_supported(int M, int N, int K);
+int b200_gemm_bf16_swiglu(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int M, int N, int K,
+                          b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * y[M, N] = x[M, K] * w[N, K]^T (+ bias[N]), bf16 in, fp32 accumulate in tensor memory (tcgen05),

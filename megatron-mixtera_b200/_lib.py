@@ -34,6 +34,8 @@ EXPORTED_SYMBOLS = (
     "b200_activation_fp8_rowblock",
     "b200_gemm_fp8_block_workspace_bytes",
     "b200_gemm_fp8_block",
+    "b200_gemm_bf16_swiglu_supported",
+    "b200_gemm_bf16_swiglu",
     "b200_gemm_bf16_splitk_bytes",
     "b200_gemm_bf16_splitk",
     "b200_gemm_mxfp8_splitk_bytes",
@@ -145,6 +147,8 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_bf16_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                    c_void_p, c_size_t, c_void_p]
+    lib.b200_gemm_bf16_swiglu_supported.argtypes = [c_int, c_int, c_int]
+    lib.b200_gemm_bf16_swiglu.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
     lib.b200_gemm_bf16_static_scratch_limit.restype = c_size_t
     lib.b200_gemm_bf16_static_scratch_limit.argtypes = []
     lib.b200_gemm_bf16_static_scratch.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,

@@ -267,6 +267,8 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
 // kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
+// kind 2: SwiGLU on the layout of the fused-epilogue weights: of every 128 input columns the first 64 are gate
+// features, the last 64 the matching up features.
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
                                   __nv_bfloat16* __restrict__ out, int F, int kind, uint8_t* __restrict__ q_out,
                                   void* __restrict__ sf_out, int q_mode, int m_pad) {
@@ -279,10 +281,11 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __
   Vec8 o;
   o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0u;
   if (!valid) {
-  } else if (kind == 0) {
+  } else if (kind == 0 || kind == 2) {
     const Vec8* row = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * 2 * F);
-    const Vec8 g = row[i];
-    const Vec8 u = row[nvec + i];
+    const int gi = kind == 0 ? i : ((i >> 3) << 4) + (i & 7);  // 8 vectors = 64 features per half tile
+    const Vec8 g = row[gi];
+    const Vec8 u = row[kind == 0 ? nvec + i : gi + 8];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float a = bf16_round(silu_f(bf16_lo(g.w[k]))) * bf16_lo(u.w[k]);
@@ -534,7 +537,8 @@ int b200_peer_buffer_destroy(void* ptr) {
 static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int q_mode, int m_pad,
                            int rows, int F, int kind, b200_stream_t stream) {
   using namespace b200;
-  if (!in || (!out && !q_out) || rows <= 0 || F <= 0 || (kind != 0 && kind != 1)) return B200_ERR_INVALID_ARGUMENT;
+  if (!in || (!out && !q_out) || rows <= 0 || F <= 0 || kind < 0 || kind > 2) return B200_ERR_INVALID_ARGUMENT;
+  if (kind == 2 && F % 64 != 0) return B200_ERR_ALIGNMENT;
   if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
   if (F % 8 != 0 || (q_out && F % 128 != 0) || !aligned16(in) || (out && !aligned16(out)) || (bias && !aligned16(bias)) ||
       (q_out && (!aligned16(q_out) || !aligned16(sf_out))))

@@ -50,6 +50,8 @@ struct Params {
   int k_blocks_per_split;
   int num_splits;
   int keep_partials;    // 1: fp32 partial sums are the result (even for one split); a fused consumer reduces them
+  int gated;            // 1: rows 0-63 of every 128-row weight tile are gate features, rows 64-127 the matching up
+                        //    features; y[M, N/2] = bf16(bf16(silu(gate)) * up) (whole-K units only)
 };
 
 // Sum of the split-K partial tiles: y[m, n] = bf16(sum_s partial[s][m][n]) (+ bias), splits added in order
@@ -114,7 +116,7 @@ static int launch_splitk_reduce(const Params& p, cudaStream_t stream) {
 // Accumulator -> output.  TMEM lane = output feature, TMEM column = token.  Either rounds to bf16 and
 // stores (whole-K units), or stores the fp32 partial tile for splitk_reduce_kernel.
 template <int BT>
-__device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, int* last_flag, int n_tile, int split,
+__device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, uint8_t* stage_smem, int n_tile, int split,
                                          int m_block) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -125,7 +127,45 @@ __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, in
   const bool n_ok = n < p.N;
   const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
-  if (p.num_splits == 1 && !p.keep_partials) {
+  if (p.gated) {
+    // SwiGLU in the epilogue.  Warps 0-1 hold gate features, warps 2-3 the matching up features (same lane).  Of
+    // every 32 tokens the gate warps finish the first 16 and the up warps the last 16: each side parks the half it
+    // does not finish in shared memory (the pipeline stages are free, every UMMA has completed).  Rounding points as
+    // in the unfused path: GEMM output to bf16, silu to bf16, product to bf16.
+    float* xch = reinterpret_cast<float*>(stage_smem);  // [BT tokens][64 features]
+    const int f = (warp & 1) * 32 + lane;               // feature inside the 64-wide half
+    const int out_col = n_tile * 64 + f;
+    const bool col_ok = out_col < (p.N >> 1);
+    const bool is_gate = warp < 2;
+    const int own0 = is_gate ? 0 : 16;                  // tokens of the chunk this thread finishes
+#pragma unroll 1
+    for (int c0 = 0; c0 < BT; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(lane_addr + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int jj = is_gate ? j + 16 : j;            // the other side's tokens
+        xch[(c0 + jj) * 64 + f] = bf16_round(__uint_as_float(is_gate ? r[j + 16] : r[j]));
+      }
+      __syncthreads();
+      if (col_ok) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c0 + own0 + j;
+          if (m < p.M) {
+            const float mine = bf16_round(__uint_as_float(is_gate ? r[j] : r[j + 16]));
+            const float other = xch[(c0 + own0 + j) * 64 + f];
+            const float g = is_gate ? mine : other;
+            const float u = is_gate ? other : mine;
+            const float a = bf16_round(g / (1.f + expf(-g)));
+            p.y[static_cast<int64_t>(m) * p.ldy + out_col] = __float2bfloat16_rn(a * u);
+          }
+        }
+      }
+      __syncthreads();
+    }
+  } else if (p.num_splits == 1 && !p.keep_partials) {
     const float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BT; c0 += 32) {
@@ -177,7 +217,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   uint64_t* accum_bar = empty_bar + C::kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -198,7 +237,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_x);
@@ -268,7 +306,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
   tcgen05_fence_after_sync();
 
-  epilogue<BT>(p, tmem_base, last_flag, n_tile, split, m_block);
+  epilogue<BT>(p, tmem_base, smem, n_tile, split, m_block);
 
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -300,7 +338,8 @@ static int pick_bt(int M) {
 template <int BT>
 static int launch(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
                   int K, void* workspace, size_t workspace_bytes, cudaStream_t stream, bool cache_maps = true,
-                  float* partials_out = nullptr, size_t partials_bytes = 0, int* splits_out = nullptr) {
+                  float* partials_out = nullptr, size_t partials_bytes = 0, int* splits_out = nullptr,
+                  bool gated = false) {
   using C = Config<BT>;
   const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
   const uint64_t ws[1] = {static_cast<uint64_t>(K) * 2};
@@ -337,6 +376,8 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
   p.partials = nullptr;
   p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
+  p.gated = gated ? 1 : 0;
+  if (gated && (splits != 1 || partials_out != nullptr)) return B200_ERR_INVALID_ARGUMENT;
   if (partials_out != nullptr) {
     if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
     p.partials = partials_out;
@@ -365,6 +406,30 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
 }  // namespace b200
 
 extern "C" {
+
+int b200_gemm_bf16_swiglu_supported(int M, int N, int K) {
+  using namespace b200::gemm;
+  if (M <= 0 || N <= 0 || K <= 0 || N % 128 != 0 || K % 8 != 0) return 0;
+  const int bt = pick_bt(M);
+  const int tiles = (N / kTileN) * ((M + bt - 1) / bt);
+  return choose_splits(tiles, (K + kTileK - 1) / kTileK) == 1 ? 1 : 0;
+}
+
+int b200_gemm_bf16_swiglu(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int M, int N, int K,
+                          b200_stream_t stream) {
+  using namespace b200;
+  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldx < K || N % 128 != 0 || ldy < N / 2) return B200_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(w)) return B200_ERR_ALIGNMENT;
+  if (!b200_gemm_bf16_swiglu_supported(M, N, K)) return B200_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (gemm::pick_bt(M)) {
+    case 32: return gemm::launch<32>(x, ldx, w, nullptr, y, ldy, M, N, K, nullptr, 0, s, true, nullptr, 0, nullptr, true);
+    case 64: return gemm::launch<64>(x, ldx, w, nullptr, y, ldy, M, N, K, nullptr, 0, s, true, nullptr, 0, nullptr, true);
+    case 128: return gemm::launch<128>(x, ldx, w, nullptr, y, ldy, M, N, K, nullptr, 0, s, true, nullptr, 0, nullptr, true);
+    default: return gemm::launch<256>(x, ldx, w, nullptr, y, ldy, M, N, K, nullptr, 0, s, true, nullptr, 0, nullptr, true);
+  }
+}
 
 size_t b200_gemm_bf16_splitk_bytes(int M, int N, int K) {
   using namespace b200::gemm;

@@ -83,7 +83,6 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -110,7 +109,6 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       mbar_init(&acc_empty[b], 4);
     }
     *abort_flag = 0;
-    *last_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_x);
@@ -217,7 +215,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     tmem_st_32x32b_x32(lane_addr + c0, r);
   }
   tmem_st_wait();
-  epilogue<BT>(p, tmem_base, last_flag, n_tile, split, m_block);
+  epilogue<BT>(p, tmem_base, smem, n_tile, split, m_block);
   }
 
   tcgen05_fence_before_sync();
@@ -258,6 +256,7 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
   p.partials = nullptr;
   p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
+  p.gated = 0;
   if (partials_out != nullptr) {
     if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
     p.partials = partials_out;

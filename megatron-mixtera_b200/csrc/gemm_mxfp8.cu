@@ -56,7 +56,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   uint64_t* accum_bar = empty_bar + C::kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -77,7 +76,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_x);
@@ -168,7 +166,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   pdl_wait();
   mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
   tcgen05_fence_after_sync();
-  epilogue<BT>(p, tmem_base, last_flag, n_tile, split, m_block);
+  epilogue<BT>(p, tmem_base, smem, n_tile, split, m_block);
 
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -207,6 +205,7 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
   p.partials = nullptr;
   p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
+  p.gated = 0;
   if (partials_out != nullptr) {
     if (partials_bytes < static_cast<size_t>(splits) * M * N * sizeof(float)) return B200_ERR_WORKSPACE;
     p.partials = partials_out;

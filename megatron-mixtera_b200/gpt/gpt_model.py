@@ -136,10 +136,18 @@ class GPTModel(torch.nn.Module):
             if dst is None or k.endswith("_extra_state"):
                 continue
             dst.copy_(shard_for_rank(k, full[k], rank, tp, gated=self.config.gated_linear_unit))
+        self._weights_are_canonical()
         self.quantize_weights()
 
+    def _weights_are_canonical(self) -> None:
+        """Called after the parameters were overwritten with weights in the reference's layout."""
+        for m in self.modules():
+            if getattr(m, "_layout_interleaved", False):
+                m._layout_interleaved = False
+
     def quantize_weights(self) -> None:
-        """(Re)build the FP8 copies of the linear weights; a no-op for bf16 models."""
+        """After weights were loaded: build the FP8 copies of the linear weights and arrange gated fc1 weights for
+        the fused fc1 + SwiGLU kernel."""
         for m in self.modules():
             if hasattr(m, "quantize_weights") and m is not self:
                 m.quantize_weights()
@@ -155,6 +163,7 @@ class GPTModel(torch.nn.Module):
             full = canonical_tensor(k, shape, seed=seed, std=std, dtype=self.config.params_dtype, device=dev)
             own[k].copy_(shard_for_rank(k, full, rank, tp, gated=self.config.gated_linear_unit))
             del full
+        self._weights_are_canonical()
         self.quantize_weights()
 
 

@@ -121,14 +121,50 @@ def add_norm(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5
     return h, y
 
 
+_ACT_KIND = {"swiglu": 0, "gelu": 1, "swiglu_interleaved": 2}
+
+
 def activation(x, kind: str, bias=None):
-    """kind 'swiglu': x [rows, 2F] -> [rows, F]; kind 'gelu': x [rows, F] (+bias) -> [rows, F]."""
+    """kind 'swiglu': x [rows, 2F] = [gate | up] -> [rows, F]; 'swiglu_interleaved': the same on the column order of
+    an fc1 whose weight went through `interleave_gate_up`; 'gelu': x [rows, F] (+bias) -> [rows, F]."""
     _need(x, BF16, "x")
     rows = x.numel() // x.shape[-1]
-    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    F = x.shape[-1] if kind == "gelu" else x.shape[-1] // 2
     out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.device)
     check("b200_activation_bf16", _lib.load().b200_activation_bf16(
-        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, 0 if kind == "swiglu" else 1, _stream()))
+        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, _ACT_KIND[kind], _stream()))
+    return out
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """[gate ; up] fc1 weight [2F, K] -> the row order `gemm_swiglu` reads: per 128 rows, 64 gate rows then the 64
+    matching up rows.  F must be a multiple of 64.  `deinterleave_gate_up` is the inverse."""
+    F2, K = w.shape
+    F = F2 // 2
+    assert F2 % 2 == 0 and F % 64 == 0, "gated fc1 rows must come in pairs of 64"
+    return torch.stack([w[:F].view(F // 64, 64, K), w[F:].view(F // 64, 64, K)], dim=1).reshape(F2, K)
+
+
+def deinterleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    F2, K = w.shape
+    v = w.view(F2 // 128, 2, 64, K)
+    return torch.cat([v[:, 0].reshape(F2 // 2, K), v[:, 1].reshape(F2 // 2, K)], dim=0)
+
+
+def gemm_swiglu_supported(M: int, N: int, K: int) -> bool:
+    return bool(_lib.load().b200_gemm_bf16_swiglu_supported(M, N, K))
+
+
+def gemm_swiglu(x, w_interleaved, out=None):
+    """[rows, F] = swiglu(x @ w.T) for an interleaved fc1 weight [2F, K], in one kernel (no split-K shapes only)."""
+    _need(x, BF16, "x")
+    _need(w_interleaved, BF16, "w")
+    K = x.shape[-1]
+    M, N = x.numel() // K, w_interleaved.shape[0]
+    if out is None:
+        out = torch.empty((*x.shape[:-1], N // 2), dtype=BF16, device=x.device)
+    check("b200_gemm_bf16_swiglu", _lib.load().b200_gemm_bf16_swiglu(
+        x.data_ptr(), K, w_interleaved.data_ptr(), out.data_ptr(), N // 2, M, N, K, _stream()))
     return out
 
 

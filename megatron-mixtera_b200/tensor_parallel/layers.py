@@ -40,10 +40,23 @@ class _ParallelLinearBase(torch.nn.Module):
     def set_extra_state(self, state):
         pass
 
+    # Gated fc1 only: `gate_up_interleaved` asks for the row order of the fused fc1 + SwiGLU kernel; the weight is
+    # rearranged in place by `quantize_weights` (i.e. after every load of canonical [gate ; up] weights) and
+    # `_layout_interleaved` says that this has happened.  `canonical_weight()` undoes it for export.
+    gate_up_interleaved = False
+    _layout_interleaved = False
+
     def quantize_weights(self) -> None:
+        if self.gate_up_interleaved and not self._layout_interleaved and self.weight is not None:
+            self.weight.data.copy_(ops.interleave_gate_up(self.weight.data))
+            self._layout_interleaved = True
         if self.fp8 and self.weight is not None:
             fn = ops.quantize_mxfp8 if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
             self._wq = fn(self.weight.data)
+
+    def canonical_weight(self) -> torch.Tensor:
+        """The weight in the reference's row order (a copy when the rows are interleaved for the fused kernel)."""
+        return ops.deinterleave_gate_up(self.weight.data) if self._layout_interleaved else self.weight.data
 
     def _matmul(self, input_, weight, bias, defer_reduction: bool = False, out=None):
         """``defer_reduction``: return the split-K partial sums (`ops.GemmPartials`) for a consumer that reduces
@@ -96,6 +109,17 @@ class ColumnParallelLinear(_ParallelLinearBase):
         if gather:
             out = gather_from_tensor_model_parallel_region(out, self.tp_group)
         return out, (self.bias if self.skip_bias_add else None)
+
+
+    def forward_swiglu(self, input_):
+        """fc1 followed by SwiGLU for a weight in the interleaved row order: one kernel when the GEMM is not split
+        along K, else GEMM + the activation kernel on the interleaved columns.  Same bits either way."""
+        assert self._layout_interleaved and self.bias is None and not self.gather_output
+        K = input_.shape[-1]
+        M, N = input_.numel() // K, self.weight.shape[0]
+        if ops.gemm_swiglu_supported(M, N, K):
+            return ops.gemm_swiglu(input_, self.weight)
+        return ops.activation(ops.gemm(input_, self.weight), "swiglu_interleaved")
 
 
 class RowParallelLinear(_ParallelLinearBase):

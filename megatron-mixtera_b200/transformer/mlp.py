@@ -29,7 +29,19 @@ class MLP(torch.nn.Module):
                                        bias=config.add_bias_linear, input_is_parallel=True, skip_bias_add=True,
                                        tp_comm_buffer_name="fc2")
 
+        # bf16 SwiGLU: fc1 and the activation run as one kernel on a weight whose gate / up rows are interleaved
+        # per 64 (arranged in place when the weights are loaded)
+        if (config.gated_linear_unit and config.fp8 is None and getattr(config, "fuse_swiglu_into_fc1", True)
+                and hasattr(self.linear_fc1, "forward_swiglu") and self.linear_fc1.bias is None
+                and (self.linear_fc1.weight.shape[0] // 2) % 64 == 0):
+            self.linear_fc1.gate_up_interleaved = True
+
     def forward(self, hidden_states, defer_output_reduction: bool = False):
+        if getattr(self.linear_fc1, "_layout_interleaved", False):
+            inter = self.linear_fc1.forward_swiglu(hidden_states)
+            if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
+                return self.linear_fc2(inter, defer_reduction=True)
+            return self.linear_fc2(inter)
         inter, bias = self.linear_fc1(hidden_states)
         act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[self.config.fp8]
         if self.config.gated_linear_unit:

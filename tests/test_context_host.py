@@ -349,3 +349,13 @@ def test_prefill_work_list_covers_every_token_once():
     ctx.update_requests(torch.ones(4, dtype=torch.uint8), torch.arange(4))
     ctx.initialize_attention_state()
     assert ctx.is_decode_only()
+
+
+def test_gate_up_interleave_is_a_permutation_with_an_inverse():
+    from megatron_mixtera_b200 import ops
+
+    w = torch.arange(2 * 192 * 3, dtype=torch.float32).view(2 * 192, 3)
+    wi = ops.interleave_gate_up(w)
+    assert torch.equal(ops.deinterleave_gate_up(wi), w)
+    # tile j: gate rows 64j..64j+63, then up rows 64j..64j+63
+    assert torch.equal(wi[128:192], w[64:128]) and torch.equal(wi[192:256], w[192 + 64 : 192 + 128])

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 import torch.nn.functional as F
+from torch.nn.functional import silu as F_silu
 
 from oracle import decode_oracle as O
 
@@ -116,6 +117,31 @@ def test_splitk_partials_are_invalidated_by_the_next_gemm(ops):
     ops.gemm(x, w)  # reuses the workspace that holds p
     with pytest.raises(ops.B200Error):
         ops.add_norm_splitk(p, g)
+
+
+@pytest.mark.parametrize("M,F,K", [(64, 14336, 4096), (8, 10240, 256), (128, 14336, 1024), (200, 19200, 512), (5, 64 * 300, 128)])
+def test_fc1_with_swiglu_epilogue_equals_gemm_then_activation(ops, M, F, K):
+    # fc1 weight [gate ; up] rearranged per 64 rows; fused kernel, unfused kernels on the rearranged columns and the
+    # plain pair on the canonical weight all give the same bits
+    x = randn((M, K), 1).cuda()
+    w = randn((2 * F, K), 2, 0.05).cuda()
+    ref = ops.activation(ops.gemm(x, w), "swiglu")
+    wi = ops.interleave_gate_up(w)
+    assert torch.equal(ops.deinterleave_gate_up(wi), w)
+    assert torch.equal(ops.activation(ops.gemm(x, wi), "swiglu_interleaved"), ref)
+    assert ops.gemm_swiglu_supported(M, 2 * F, K)
+    out = ops.gemm_swiglu(x, wi)
+    assert out.shape == (M, F) and torch.equal(out, ref)
+    g, u = torch.chunk(x.float() @ w.float().t(), 2, dim=-1)
+    assert rel_l2(out, F_silu(g.to(BF16)).float() * u.to(BF16).float()) < 6e-3
+    assert ops.device_status() == 0
+
+
+def test_fc1_with_swiglu_epilogue_is_refused_for_split_k_shapes(ops):
+    M, F, K = 64, 1024, 4096  # 16 output tiles: the GEMM is split along K
+    assert not ops.gemm_swiglu_supported(M, 2 * F, K)
+    with pytest.raises(ops.B200Error):
+        ops.gemm_swiglu(randn((M, K), 1).cuda(), randn((2 * F, K), 2, 0.05).cuda())
 
 
 def test_gemm_rejects_bad_arguments(ops):
