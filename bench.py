@@ -112,7 +112,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the CUDA stack
 # ---------------------------------------------------------------------------------------------
-def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True, fuse_swiglu: bool = True):
+def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True, fuse_swiglu: bool = True, fuse_qkv: bool = False):
     from megatron_mixtera_b200 import build, parallel_state
     from megatron_mixtera_b200.gpt.gpt_model import GPTModel
     from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext
@@ -130,7 +130,7 @@ def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bo
         normalization="RMSNorm", gated_linear_unit=True, activation="silu", add_bias_linear=False,
         tensor_model_parallel_size=tp, enable_cuda_graph=True, inference_sampling_seed=seed, fp8=w.fp8,
         fuse_splitk_reduction_into_norm=fuse_splitk, fuse_tp_allreduce_into_norm=fuse_tp,
-        fuse_swiglu_into_fc1=fuse_swiglu)
+        fuse_swiglu_into_fc1=fuse_swiglu, fuse_qkv_reduction_into_attention=fuse_qkv)
     model = GPTModel(cfg, vocab_size=w.vocab_size, max_sequence_length=w.max_sequence_length,
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
@@ -336,7 +336,7 @@ def run_ours(args, w):
         torch.cuda.synchronize()
 
     model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce,
-                                                     fuse_swiglu=not args.unfused_swiglu)
+                                                     fuse_swiglu=not args.unfused_swiglu, fuse_qkv=args.fused_qkv)
     prompts = synthetic_prompts(w.num_requests, *w.prompt_len_range, w.vocab_size, seed=0)
     for i, p in enumerate(prompts):
         engine.add_request(i, p, w.num_tokens_to_generate)
@@ -483,6 +483,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
+    ap.add_argument("--fused-qkv", action="store_true",
+                    help="ablation: the attention kernel sums the QKV GEMM's split-K partial sums itself")
     ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")

@@ -300,6 +300,11 @@ typedef struct {
   int32_t kv_cache_fp8;   /* != 0: k_cache / v_cache hold E4M3 bytes (head_dim 128), value = byte * scale[head] */
   const float* k_scale;   /* [nkv] fp32, FP8 pool only */
   const float* v_scale;   /* [nkv] fp32, FP8 pool only */
+  const float* qkv_partials; /* NULL, or [qkv_num_splits][T][nkv*(g+2)*d] fp32: the split-K partial sums of the QKV GEMM
+                                (b200_gemm_*_splitk) for b200_paged_attention to use instead of `qkv`: every unit sums its own
+                                head vectors in split order and rounds once to bf16, the bits the GEMM's reduction kernel
+                                would have produced (no QKV bias then).  b200_rope_append and the prefill kernel need `qkv`. */
+  int32_t qkv_num_splits;
   const int32_t* row_order; /* [T] int32 or NULL: a permutation of 0..T-1; the attention kernel starts its work on the
                                rows in this order (longest context first balances the SMs).  Results do not depend on it. */
 } b200_attention_args;

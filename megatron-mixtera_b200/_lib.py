@@ -94,6 +94,8 @@ class AttentionArgs(ctypes.Structure):
         ("kv_cache_fp8", c_int32),
         ("k_scale", c_void_p),
         ("v_scale", c_void_p),
+        ("qkv_partials", c_void_p),
+        ("qkv_num_splits", c_int32),
         ("row_order", c_void_p),
     ]
 

@@ -46,9 +46,11 @@ struct Cfg {
   static constexpr int kConvSubBytes = 16 * 128;      // per-warp converted slice: 16 tokens x 64 dims
   static constexpr int kConvBytes = KV8 ? kConsumerWarps * 2 * kSub * kConvSubBytes : 0;
   static constexpr int kSubStride = KV8 ? kConvSubBytes : kSubBytes;
+  static constexpr int kQkvBytes = 18 * D * 2;        // (G + 2) <= 18 head vectors of this unit, when they are summed
+                                                      // here from the QKV GEMM's split-K partial sums
   static constexpr int kMergeBytes = kConsumerWarps * 16 * (D + 2) * 4;
   static_assert(kMergeBytes <= kStages * kStageBytes, "merge buffers reuse the tile ring");
-  static constexpr int kSmemBytes = kStages * kStageBytes + kQBytes + 256 + kConvBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kQBytes + 256 + kConvBytes + kQkvBytes + 1024;
 };
 
 // 16-bit MMA element type: bf16 for the bf16 pool, f16 for the FP8 pool.
@@ -99,6 +101,8 @@ __device__ __forceinline__ float from_e4m3(uint8_t b) {
 
 struct Params {
   const __nv_bfloat16* qkv;
+  const float* qkv_partials;  // [qkv_splits][T][nkv * (G + 2) * D] fp32: split-K partial sums of the QKV GEMM, used
+  int qkv_splits;             // instead of qkv when non-null (decode kernel only)
   __nv_bfloat16* k_cache;
   __nv_bfloat16* v_cache;
   const int32_t* block_table;
@@ -177,6 +181,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   uint64_t* empty_bar = full_bar + kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kStages);
   uint8_t* conv_smem = smem + kStages * C::kStageBytes + C::kQBytes + 256;  // KV8 only (16-byte aligned)
+  __nv_bfloat16* qkv_smem = reinterpret_cast<__nv_bfloat16*>(conv_smem + C::kConvBytes);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -235,6 +240,27 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const __nv_bfloat16* qkv_t = p.qkv + (static_cast<int64_t>(t) * p.nkv + h) * (G + 2) * D;
 
   pdl_wait();  // qkv is the previous kernel's output
+  if (p.qkv_partials != nullptr) {
+    // The QKV GEMM left fp32 split-K partial sums: reduce this unit's (G + 2) head vectors here (split order, one
+    // bf16 rounding - what the GEMM's own reduction kernel would have written) and read them from shared memory.
+    const int width = (G + 2) * D;
+    const int64_t row_elems = static_cast<int64_t>(p.nkv) * width;
+    const float* src = p.qkv_partials + static_cast<int64_t>(t) * row_elems + static_cast<int64_t>(h) * width;
+    const int64_t split_stride = static_cast<int64_t>(p.T) * row_elems;
+    for (int i = tid * 4; i < width; i += kConsumerThreads * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp = 0; sp < p.qkv_splits; ++sp) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride + i));
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      *reinterpret_cast<uint2*>(qkv_smem + i) = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+    consumer_barrier();
+    qkv_t = qkv_smem;
+  }
   // Stage Q (with RoPE) as a zero-padded [16][D] tile.
   for (int i = tid; i < 16 * C::kQStride / 2; i += kConsumerThreads)
     reinterpret_cast<uint32_t*>(q_smem)[i] = 0u;
@@ -851,8 +877,9 @@ __global__ void __launch_bounds__(128) rope_append_kernel(Params p) {
 }
 
 static int fill_params(const b200_attention_args* a, Params& p) {
-  if (!a || !a->qkv || !a->k_cache || !a->v_cache || !a->kv_seq_lengths || !a->block_table)
+  if (!a || (!a->qkv && !a->qkv_partials) || !a->k_cache || !a->v_cache || !a->kv_seq_lengths || !a->block_table)
     return B200_ERR_INVALID_ARGUMENT;
+  if (a->qkv_partials && (a->qkv_num_splits < 1 || !aligned16(a->qkv_partials))) return B200_ERR_INVALID_ARGUMENT;
   if (a->head_dim != 64 && a->head_dim != 128) return B200_ERR_INVALID_ARGUMENT;
   if (a->num_tokens <= 0 || a->num_kv_heads <= 0 || a->num_q_heads % a->num_kv_heads != 0)
     return B200_ERR_INVALID_ARGUMENT;
@@ -862,8 +889,10 @@ static int fill_params(const b200_attention_args* a, Params& p) {
   if (a->num_splits < 1 || a->num_splits > kMaxSplits) return B200_ERR_INVALID_ARGUMENT;
   if ((a->rope_cos == nullptr) != (a->rope_sin == nullptr)) return B200_ERR_INVALID_ARGUMENT;
   if (a->rope_cos && (!a->token_to_pos_ids || !a->token_to_pos_in_request)) return B200_ERR_INVALID_ARGUMENT;
-  if (!aligned16(a->k_cache) || !aligned16(a->v_cache) || !aligned16(a->qkv)) return B200_ERR_ALIGNMENT;
+  if (!aligned16(a->k_cache) || !aligned16(a->v_cache) || (a->qkv && !aligned16(a->qkv))) return B200_ERR_ALIGNMENT;
   p.qkv = static_cast<const __nv_bfloat16*>(a->qkv);
+  p.qkv_partials = a->qkv_partials;
+  p.qkv_splits = a->qkv_num_splits;
   p.k_cache = static_cast<__nv_bfloat16*>(a->k_cache);
   p.v_cache = static_cast<__nv_bfloat16*>(a->v_cache);
   p.block_table = a->block_table;
@@ -965,7 +994,7 @@ int b200_paged_prefill_attention(const b200_attention_args* a, const int32_t* un
   attn::Params p;
   int rc = attn::fill_params(a, p);
   if (rc != B200_OK) return rc;
-  if (!a->out || !units || num_units <= 0 || a->kv_cache_fp8) return B200_ERR_INVALID_ARGUMENT;
+  if (!a->out || !a->qkv || !units || num_units <= 0 || a->kv_cache_fp8) return B200_ERR_INVALID_ARGUMENT;
   if (64 % p.G != 0) return B200_ERR_INVALID_ARGUMENT;  // group sizes 1, 2, 4, 8, 16
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return a->head_dim == 128 ? attn::launch_prefill<128>(p, units, num_units, s)
@@ -983,7 +1012,7 @@ int b200_rope_append(const b200_attention_args* a, b200_stream_t stream) {
   attn::Params p;
   int rc = attn::fill_params(a, p);
   if (rc != B200_OK) return rc;
-  if (!a->token_to_chunk_idx || !a->token_to_local_pos) return B200_ERR_INVALID_ARGUMENT;
+  if (!a->token_to_chunk_idx || !a->token_to_local_pos || !a->qkv) return B200_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (a->kv_cache_fp8) return launch_pdl(attn::rope_append_kernel<128, true>, dim3(p.T), dim3(128), 0, s, p);
   if (a->head_dim == 128) return launch_pdl(attn::rope_append_kernel<128, false>, dim3(p.T), dim3(128), 0, s, p);
@@ -997,6 +1026,7 @@ int b200_paged_attention(const b200_attention_args* a, b200_stream_t stream) {
   if (rc != B200_OK) return rc;
   if (!a->out) return B200_ERR_INVALID_ARGUMENT;
   if (a->fuse_rope_append && (!a->token_to_chunk_idx || !a->token_to_local_pos)) return B200_ERR_INVALID_ARGUMENT;
+  if (a->qkv_partials && (a->num_q_heads / a->num_kv_heads + 2) * a->head_dim % 4 != 0) return B200_ERR_ALIGNMENT;
   if (a->num_splits > 1) {
     const size_t need =
         b200_paged_attention_workspace_bytes(a->num_tokens, a->num_q_heads, a->head_dim, a->num_splits);

@@ -450,7 +450,14 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     kernels have run.  ``k_scale`` / ``v_scale`` (fp32 [nkv]) select the FP8 (E4M3) KV pool."""
     T = qkv.shape[0]
     a = AttentionArgs()
-    a.qkv = qkv.data_ptr()
+    if isinstance(qkv, GemmPartials):  # un-reduced output of the QKV GEMM (decode kernel only)
+        if qkv.epoch != _gemm_epoch:
+            raise B200Error("attention", -1, "another GEMM has reused the workspace that held the QKV partial sums")
+        a.qkv, a.qkv_partials, a.qkv_num_splits = None, qkv.buf.data_ptr(), qkv.num_splits
+        device = qkv.device
+    else:
+        a.qkv, a.qkv_partials, a.qkv_num_splits = qkv.data_ptr(), None, 0
+        device = qkv.device
     a.k_cache = k_cache.data_ptr()
     a.v_cache = v_cache.data_ptr()
     a.block_table = block_table.data_ptr()
@@ -477,7 +484,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     a.k_scale = _p(k_scale)
     a.v_scale = _p(v_scale)
     a.row_order = _p(row_order)
-    ws = attention_workspace(qkv.device, T, num_q_heads, head_dim, num_splits) if out is not None else None
+    ws = attention_workspace(device, T, num_q_heads, head_dim, num_splits) if out is not None else None
     a.workspace = _p(ws)
     a.workspace_bytes = 0 if ws is None else ws.numel()
     return a

@@ -100,10 +100,18 @@ class ColumnParallelLinear(_ParallelLinearBase):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, input_, weight: Optional[torch.Tensor] = None, runtime_gather_output: Optional[bool] = None):
-        """``input_`` [..., in] -> ([..., out/tp] or gathered [..., out], bias if ``skip_bias_add``)."""
+    supports_deferred_reduction = True
+
+    def forward(self, input_, weight: Optional[torch.Tensor] = None, runtime_gather_output: Optional[bool] = None,
+                defer_reduction: bool = False):
+        """``input_`` [..., in] -> ([..., out/tp] or gathered [..., out], bias if ``skip_bias_add``).  With
+        ``defer_reduction`` (and no bias to add, no gather) the output is the GEMM's split-K partial sums
+        (`ops.GemmPartials`) for a consumer that reduces them itself."""
         w = self.weight if weight is None else weight
         fuse_bias = self.bias if (self.bias is not None and not self.skip_bias_add) else None
+        gather_now = self.gather_output if runtime_gather_output is None else runtime_gather_output
+        if defer_reduction and fuse_bias is None and not gather_now and weight is None:
+            return self._matmul(input_, w, None, defer_reduction=True), (self.bias if self.skip_bias_add else None)
         out = self._matmul(input_, w, fuse_bias)
         gather = self.gather_output if runtime_gather_output is None else runtime_gather_output
         if gather:

@@ -57,15 +57,20 @@ class PagedFlashDecodeAttention(torch.nn.Module):
         self.num_kv_heads = config.num_query_groups // tp
         self.head_dim = config.kv_channels
 
+    accepts_gemm_partials = True  # decode steps: the QKV GEMM's split-K partial sums instead of its bf16 output
+
     def forward(self, mixed_qkv, inference_context, rotary_pos_cos=None, rotary_pos_sin=None):
-        """``mixed_qkv`` [T, (nq + 2 nkv) d / tp] -> [T, nq d / tp]."""
+        """``mixed_qkv`` [T, (nq + 2 nkv) d / tp] (or, in decode steps, the `ops.GemmPartials` of the GEMM that
+        computes it) -> [T, nq d / tp]."""
         ctx = inference_context
         T = mixed_qkv.shape[0]
         k_cache, v_cache, block_table = ctx.key_value_cache(self.layer_number)
-        out = torch.empty((T, self.num_q_heads * self.head_dim), dtype=mixed_qkv.dtype, device=mixed_qkv.device)
+        out = torch.empty((T, self.num_q_heads * self.head_dim), dtype=torch.bfloat16, device=mixed_qkv.device)
         decode = ctx.is_decode_only()
+        partials = isinstance(mixed_qkv, ops.GemmPartials)
+        assert decode or not partials, "only the decode kernel reads un-reduced QKV partial sums"
         common = dict(
-            qkv=mixed_qkv.view(T, self.num_kv_heads, -1), k_cache=k_cache, v_cache=v_cache, out=out,
+            qkv=mixed_qkv if partials else mixed_qkv.view(T, self.num_kv_heads, -1), k_cache=k_cache, v_cache=v_cache, out=out,
             num_q_heads=self.num_q_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
             chunk_size=ctx.chunk_size_tokens, token_to_pos_ids=ctx.token_to_pos_ids,
             token_to_pos_in_request=ctx.token_to_position_in_request, token_to_chunk_idx=ctx.token_to_chunk_idx,
@@ -119,7 +124,13 @@ class SelfAttention(torch.nn.Module):
         ``defer_output_reduction`` the output may be the out-projection's split-K partial sums."""
         if inference_context is None or inference_context.is_static_batching():
             raise NotImplementedError("only the dynamic-batching inference path is implemented")
-        mixed_qkv, _ = self.linear_qkv(hidden_states)
+        defer_qkv = (inference_context.is_decode_only() and getattr(self.config, "fuse_qkv_reduction_into_attention", False)
+                     and getattr(self.linear_qkv, "supports_deferred_reduction", False)
+                     and getattr(self.core_attention, "accepts_gemm_partials", False))
+        if defer_qkv:  # decode: the attention kernel sums the QKV GEMM's split-K partial sums itself
+            mixed_qkv, _ = self.linear_qkv(hidden_states, defer_reduction=True)
+        else:
+            mixed_qkv, _ = self.linear_qkv(hidden_states)
         core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin)
         if defer_output_reduction and getattr(self.linear_proj, "supports_deferred_reduction", False):
             return self.linear_proj(core, defer_reduction=True)

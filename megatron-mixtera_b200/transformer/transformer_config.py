@@ -29,6 +29,9 @@ class TransformerConfig:
     # not in the reference: hand the split-K partial sums of out-proj / fc2 to the residual-add + norm kernel
     # instead of reducing them in a kernel of their own (bit-identical results, two launches fewer per layer)
     fuse_splitk_reduction_into_norm: bool = True
+    # not in the reference: in decode steps the attention kernel sums the QKV GEMM's split-K partial sums itself
+    # (bit-identical, one launch fewer per layer; measured neutral on the step time, hence off by default)
+    fuse_qkv_reduction_into_attention: bool = False
     # not in the reference: bf16 gated MLPs run fc1 + SwiGLU as one kernel; the fc1 weight is kept with its gate / up
     # rows interleaved per 64 (`ColumnParallelLinear.canonical_weight()` gives the reference's order back)
     fuse_swiglu_into_fc1: bool = True

@@ -344,7 +344,7 @@ def oracle_decode_attention(c):
     return out, kc, vc
 
 
-def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_order=None):
+def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_order=None, qkv_from=None):
     dev = "cuda"
     D = c["D"]
     cos = sin = None
@@ -357,6 +357,8 @@ def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_orde
     d = {k: c[k].to(dev) for k in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
     d["row"] = None if row_of_token is None else row_of_token.to(dev)
     d["order"] = None if row_order is None else row_order.to(dev)
+    if qkv_from is not None:  # (x, w): the QKV GEMM's un-reduced split-K partial sums instead of its bf16 output
+        d["qkv"] = ops.gemm_splitk(*qkv_from)
     args = ops.make_attention_args(
         qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
         num_q_heads=c["nq"], num_kv_heads=c["nkv"], head_dim=D, chunk_size=c["chunk"], token_to_pos_ids=d["pos"],
@@ -479,6 +481,23 @@ def test_paged_prefill_attention_mixed_step(ops, nkv, G, D):
     cu_q = torch.tensor([0, 70, 71, 221])
     ref = O.paged_attention(q, kc_ref, vc_ref, torch.tensor(kv_total), bt.numpy(), cu_q=cu_q)
     assert rel_l2(out, ref) < 5e-3
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("nkv,G,D,K", [(8, 4, 128, 4096), (2, 8, 128, 512), (4, 1, 64, 1024)])
+@pytest.mark.parametrize("splits", [1, 2])
+def test_decode_attention_reads_qkv_split_k_partials(ops, nkv, G, D, K, splits):
+    # the decode kernel sums the QKV GEMM's partial sums itself: same output, same pool as with the reduced bf16 qkv
+    kv_lens = [300, 1, 64, 129, 0, 77]
+    T = len(kv_lens)
+    c = make_paged_case(T=T, nkv=nkv, G=G, D=D, chunk=64, kv_lens=kv_lens, seed=31)
+    x = randn((T, K), 32).cuda()
+    w = randn((nkv * (G + 2) * D, K), 33, 0.05).cuda()
+    c["qkv"] = ops.gemm(x, w).view(T, nkv, (G + 2) * D).cpu()
+    base = run_cuda_attention(ops, c, num_splits=splits, fused=True)
+    got = run_cuda_attention(ops, c, num_splits=splits, fused=True, qkv_from=(x, w))
+    for a, b in zip(got, base):
+        assert torch.equal(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()))
     assert ops.device_status() == 0
 
 

@@ -37,7 +37,8 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         gated_linear_unit=llama, activation="silu" if llama else "gelu", add_bias_linear=not llama,
         enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0, tensor_model_parallel_size=meta.get("tp", 1),
         fp8=meta.get("fp8"), fuse_splitk_reduction_into_norm=meta.get("fuse_splitk", True),
-        fuse_tp_allreduce_into_norm=meta.get("fuse_tp", True), fuse_swiglu_into_fc1=meta.get("fuse_swiglu", True))
+        fuse_tp_allreduce_into_norm=meta.get("fuse_tp", True), fuse_swiglu_into_fc1=meta.get("fuse_swiglu", True),
+        fuse_qkv_reduction_into_attention=meta.get("fuse_qkv", True))
     model = GPTModel(cfg, vocab_size=meta["vocab_size"], max_sequence_length=meta["max_sequence_length"],
                      position_embedding_type="rope" if llama else "learned_absolute",
                      rotary_base=meta.get("rotary_base", 10000))
@@ -179,8 +180,8 @@ def test_llama_tiny_fusion_switches_change_no_bit(fp8):
     z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
     meta = json.loads(str(z["meta"]))
     meta["fp8"] = fp8
-    s_fused, _, _ = run_teacher_forced(dict(meta, fuse_splitk=True, fuse_swiglu=True), z)
-    s_plain, _, _ = run_teacher_forced(dict(meta, fuse_splitk=False, fuse_swiglu=False), z)
+    s_fused, _, _ = run_teacher_forced(dict(meta, fuse_splitk=True, fuse_swiglu=True, fuse_qkv=True), z)
+    s_plain, _, _ = run_teacher_forced(dict(meta, fuse_splitk=False, fuse_swiglu=False, fuse_qkv=False), z)
     assert len(s_fused["logits"]) > 5
     for step, lg in s_plain["logits"].items():
         assert torch.equal(lg, s_fused["logits"][step])
