@@ -267,9 +267,12 @@ int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, con
  *   b200_rope_append for decode steps (one new token per request) inside the same kernel.
  *   num_splits > 1 splits every row's context into that many ranges (flash-decoding) and needs
  *   `workspace` of b200_paged_attention_workspace_bytes.
- * FP8 pool (kv_cache_fp8; an extension, the reference's pool is always params_dtype): keys and values are
- *   stored as E4M3 bytes with one fp32 scale per KV head; both kernels quantise what they append
- *   (RNE-saturate(x / scale)) and the attention kernel converts tiles to f16 on the fly.
+ * FP8 pool (kv_cache_fp8; an extension, the reference's pool is always params_dtype; head_dim 128, chunk_size a
+ *   multiple of 128): keys and values are stored as E4M3 bytes with one fp32 scale per KV head; both kernels
+ *   quantise what they append (RNE-saturate(x / scale)) and the attention kernel multiplies E4M3 by E4M3 on the
+ *   tensor cores (queries and probabilities as two E4M3 terms each).  Keys keep the layout
+ *   [chunk][token][head][dim]; the value bytes of a chunk are stored transposed and permuted,
+ *   [chunk][head][dim][b200_fp8_value_position(token)], so that the kernel needs no transposition.
  */
 typedef struct {
   const void* qkv;
@@ -297,7 +300,9 @@ typedef struct {
   int32_t num_splits;
   int32_t fuse_rope_append;
   float softmax_scale;    /* 0 = 1/sqrt(d) */
-  int32_t kv_cache_fp8;   /* != 0: k_cache / v_cache hold E4M3 bytes (head_dim 128), value = byte * scale[head] */
+  int32_t kv_cache_fp8;   /* != 0: k_cache / v_cache hold E4M3 bytes (head_dim 128), value = byte * scale[head];
+                             1: queries and probabilities as two E4M3 terms (adds ~1e-3 to the pool's own ~4e-2 error);
+                             2: one term each (total ~5e-2, 1.6x faster) */
   const float* k_scale;   /* [nkv] fp32, FP8 pool only */
   const float* v_scale;   /* [nkv] fp32, FP8 pool only */
   const float* qkv_partials; /* NULL, or [qkv_num_splits][T][nkv*(g+2)*d] fp32: the split-K partial sums of the QKV GEMM
@@ -310,6 +315,7 @@ typedef struct {
 } b200_attention_args;
 
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);
+int b200_fp8_value_position(int token_in_chunk);
 int b200_rope_append(const b200_attention_args* args, b200_stream_t stream);
 int b200_paged_attention(const b200_attention_args* args, b200_stream_t stream);
 /* Prefill / mixed steps (flash_attn_varlen_func with block_table, attention.py:501-558), after b200_rope_append:

@@ -56,6 +56,7 @@ EXPORTED_SYMBOLS = (
     "b200_rope_append",
     "b200_paged_attention",
     "b200_paged_prefill_attention",
+    "b200_fp8_value_position",
     "b200_argmax_bf16",
     "b200_topk_probs_bf16",
     "b200_topp_probs_bf16",
@@ -204,6 +205,7 @@ def load() -> ctypes.CDLL:
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]
     lib.b200_paged_attention.argtypes = [POINTER(AttentionArgs), c_void_p]
+    lib.b200_fp8_value_position.argtypes = [c_int]
     lib.b200_paged_prefill_attention.argtypes = [POINTER(AttentionArgs), c_void_p, c_int, c_void_p]
     lib.b200_argmax_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
     lib.b200_topk_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_void_p]

@@ -1,4 +1,5 @@
-// Paged-KV attention for the dynamic inference context (GQA, bf16 KV, head dim 64 / 128).
+// Paged-KV attention for the dynamic inference context (GQA, bf16 KV pool, head dim 64 / 128; the E4M3 pool has
+// kernels of its own in attention_fp8.cu).
 //
 // One CTA works on one (token row, KV head, context split) unit:
 //   * a producer warp walks the row's block table and streams 64-token K and V tiles of that KV
@@ -16,9 +17,6 @@
 //
 // The kernel is bound by reading the K/V pool once from HBM: algorithmic bytes per launch are
 // sum_rows kv_len * 2 * nkv * d * 2.
-#include <cuda_fp16.h>
-#include <cuda_fp8.h>
-
 #include "common.cuh"
 
 namespace b200 {
@@ -31,73 +29,20 @@ constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kStages = 3;
 constexpr int kMaxSplits = 64;
 
-// KV8: the pool holds E4M3 bytes (one fp32 scale per KV head for K and for V).  Tiles arrive as fp8
-// (128-byte rows = one head's 128 dims), every consumer warp converts its 16-token slice to f16 into a
-// private buffer with the layout of the 16-bit tiles, and the MMAs run in f16 (exact for E4M3 values).
-template <int D, bool KV8>
+template <int D>
 struct Cfg {
-  static_assert(!KV8 || D == 128, "the FP8 pool path is built for head dim 128");
-  static constexpr int kSub = D / 64;                 // 128-byte swizzle rows hold 64 16-bit values
-  static constexpr int kSubBytes = kTile * 128;       // one [64 tokens x 64 dims] 16-bit sub-tile
-  static constexpr int kTileBytes = KV8 ? kTile * D : kSub * kSubBytes;  // K or V tile in the ring
+  static constexpr int kSub = D / 64;                 // 128-byte swizzle rows hold 64 bf16 values
+  static constexpr int kSubBytes = kTile * 128;       // one [64 tokens x 64 dims] sub-tile
+  static constexpr int kTileBytes = kSub * kSubBytes; // K or V tile in the ring
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kQStride = D + 8;              // 16-bit elements, padded against bank conflicts
+  static constexpr int kQStride = D + 8;              // bf16 elements, padded against bank conflicts
   static constexpr int kQBytes = 16 * kQStride * 2;
-  static constexpr int kConvSubBytes = 16 * 128;      // per-warp converted slice: 16 tokens x 64 dims
-  static constexpr int kConvBytes = KV8 ? kConsumerWarps * 2 * kSub * kConvSubBytes : 0;
-  static constexpr int kSubStride = KV8 ? kConvSubBytes : kSubBytes;
   static constexpr int kQkvBytes = 18 * D * 2;        // (G + 2) <= 18 head vectors of this unit, when they are summed
                                                       // here from the QKV GEMM's split-K partial sums
   static constexpr int kMergeBytes = kConsumerWarps * 16 * (D + 2) * 4;
   static_assert(kMergeBytes <= kStages * kStageBytes, "merge buffers reuse the tile ring");
-  static constexpr int kSmemBytes = kStages * kStageBytes + kQBytes + 256 + kConvBytes + kQkvBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kQBytes + 256 + kQkvBytes + 1024;
 };
-
-// 16-bit MMA element type: bf16 for the bf16 pool, f16 for the FP8 pool.
-template <bool F16>
-__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
-  if constexpr (F16) {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    return pack_bf16x2(lo, hi);
-  }
-}
-template <bool F16>
-__device__ __forceinline__ float round16(float x) {
-  if constexpr (F16) return __half2float(__float2half_rn(x));
-  return bf16_round(x);
-}
-template <bool F16>
-__device__ __forceinline__ uint16_t to16(float x) {
-  if constexpr (F16) {
-    __half v = __float2half_rn(x);
-    return *reinterpret_cast<uint16_t*>(&v);
-  } else {
-    __nv_bfloat16 v = __float2bfloat16_rn(x);
-    return *reinterpret_cast<uint16_t*>(&v);
-  }
-}
-template <bool F16>
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if constexpr (F16) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %2, %3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  } else {
-    mma_bf16_16816(d, a, b0, b1);
-  }
-}
-// E4M3 value nearest to x / scale (saturating), as a byte and as the float it decodes to
-__device__ __forceinline__ uint8_t to_e4m3(float x) {
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-}
-__device__ __forceinline__ float from_e4m3(uint8_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
-  return __half2float(*reinterpret_cast<const __half*>(&h));
-}
 
 struct Params {
   const __nv_bfloat16* qkv;
@@ -116,7 +61,7 @@ struct Params {
   const __nv_bfloat16* cos;
   const __nv_bfloat16* sin;
   __nv_bfloat16* out;
-  const float* k_scale;  // FP8 pool: one scale per KV head (value = byte * scale); nullptr otherwise
+  const float* k_scale;  // E4M3 pool (attention_fp8.cu): one scale per KV head; nullptr otherwise
   const float* v_scale;
   float* ws_o;    // [T][nq][splits][D]
   float* ws_lse;  // [T][nq][splits]   (log2 domain)
@@ -141,10 +86,10 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, 
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int D, bool KV8>
+template <int D>
 __global__ void __launch_bounds__(kThreads, 2)
 paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p) {
-  using C = Cfg<D, KV8>;
+  using C = Cfg<D>;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -180,8 +125,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * C::kStageBytes + C::kQBytes);
   uint64_t* empty_bar = full_bar + kStages;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kStages);
-  uint8_t* conv_smem = smem + kStages * C::kStageBytes + C::kQBytes + 256;  // KV8 only (16-byte aligned)
-  __nv_bfloat16* qkv_smem = reinterpret_cast<__nv_bfloat16*>(conv_smem + C::kConvBytes);
+  __nv_bfloat16* qkv_smem = reinterpret_cast<__nv_bfloat16*>(smem + kStages * C::kStageBytes + C::kQBytes + 256);
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -219,15 +163,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         uint8_t* kdst = smem + s * C::kStageBytes;
         uint8_t* vdst = kdst + C::kTileBytes;
         mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
-        if constexpr (KV8) {
-          tma_load_3d(kdst, &map_k, &full_bar[s], 0, h, tok_row);
-          tma_load_3d(vdst, &map_v, &full_bar[s], 0, h, tok_row);
-        } else {
 #pragma unroll
-          for (int sub = 0; sub < C::kSub; ++sub) {
-            tma_load_3d(kdst + sub * C::kSubBytes, &map_k, &full_bar[s], sub * 64, h, tok_row);
-            tma_load_3d(vdst + sub * C::kSubBytes, &map_v, &full_bar[s], sub * 64, h, tok_row);
-          }
+        for (int sub = 0; sub < C::kSub; ++sub) {
+          tma_load_3d(kdst + sub * C::kSubBytes, &map_k, &full_bar[s], sub * 64, h, tok_row);
+          tma_load_3d(vdst + sub * C::kSubBytes, &map_v, &full_bar[s], sub * 64, h, tok_row);
         }
       }
     }
@@ -276,8 +215,8 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       float x1 = __bfloat162float(qkv_t[g * D + j]);
       float x2 = __bfloat162float(qkv_t[g * D + j + D / 2]);
       if (rope) rope_pair(x1, x2, __bfloat162float(cs[j]), __bfloat162float(sn[j]), x1, x2);
-      reinterpret_cast<uint16_t*>(q_smem)[g * C::kQStride + j] = to16<KV8>(x1);
-      reinterpret_cast<uint16_t*>(q_smem)[g * C::kQStride + j + D / 2] = to16<KV8>(x2);
+      q_smem[g * C::kQStride + j] = __float2bfloat16_rn(x1);
+      q_smem[g * C::kQStride + j + D / 2] = __float2bfloat16_rn(x2);
     }
   }
   consumer_barrier();
@@ -299,8 +238,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   float l_run[2] = {0.f, 0.f};  // per-thread partial row sums (reduced over the quad at the end)
 
   // FP8 pool: K and V are bytes * per-head scale; the scales factor out of both products
-  const float scale_log2 = KV8 ? p.scale_log2 * p.k_scale[h] : p.scale_log2;
-  const float out_scale = KV8 ? p.v_scale[h] : 1.f;
+  const float scale_log2 = p.scale_log2;
   const int new_pos = kv_len - 1;  // position of this step's token (decode)
   const bool owns_new = p.fused && new_pos >= start && new_pos < end;
   const int r0 = warp * 16;        // this warp's token slice inside a tile
@@ -312,45 +250,6 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     mbar_wait_bounded(&full_bar[s], phase, abort_flag, kStatusAttnTimeout);
     uint8_t* ktile = smem + s * C::kStageBytes;
     uint8_t* vtile = ktile + C::kTileBytes;
-
-    // 16-bit tiles the MMAs read: the ring itself, or (FP8 pool) this warp's converted 16-token slice,
-    // addressed as if it were the whole tile.
-    uint8_t* ktile_c = ktile;
-    uint8_t* vtile_c = vtile;
-    if constexpr (KV8) {
-      uint8_t* wk = conv_smem + warp * (2 * C::kSub * C::kConvSubBytes);
-      uint8_t* wv = wk + C::kSub * C::kConvSubBytes;
-      if (tok0 + r0 < end) {
-        // 16 rows x 128 fp8 bytes per matrix = 128 chunks of 16 bytes; each becomes two 16-byte f16 chunks
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int c = lane + 32 * it;
-          const int row = c >> 3, j = c & 7;
-          const int src = (r0 + row) * 128 + ((j ^ ((r0 + row) & 7)) << 4);
-          const int dst = (j >> 2) * C::kConvSubBytes + row * 128;
-          const int ch = (j & 3) * 2;
-#pragma unroll
-          for (int m = 0; m < 2; ++m) {
-            const uint4 u = *reinterpret_cast<const uint4*>((m == 0 ? ktile : vtile) + src);
-            const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-            uint32_t o[8];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w4[k] & 0xffffu), __NV_E4M3);
-              const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w4[k] >> 16), __NV_E4M3);
-              o[2 * k] = static_cast<uint32_t>(lo.x) | (static_cast<uint32_t>(lo.y) << 16);
-              o[2 * k + 1] = static_cast<uint32_t>(hi.x) | (static_cast<uint32_t>(hi.y) << 16);
-            }
-            uint8_t* d = (m == 0 ? wk : wv) + dst;
-            *reinterpret_cast<uint4*>(d + ((ch ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(d + (((ch + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-          }
-        }
-      }
-      ktile_c = wk - r0 * 128;
-      vtile_c = wv - r0 * 128;
-      __syncwarp();
-    }
 
     if (owns_new && new_pos >= tok0 + r0 && new_pos < tok0 + r0 + 16) {
       // This warp's slice contains the new token: rotate k, store k and v to the pool and patch the tile.
@@ -369,35 +268,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           rope_pair(a1, a2, __bfloat162float(cs[j]), __bfloat162float(sn[j]), a1, a2);
           rope_pair(b1, b2, __bfloat162float(cs[j + 1]), __bfloat162float(sn[j + 1]), b1, b2);
         }
-        uint32_t lo, hi, vlo, vhi;  // elements (j, j+1) and (j+D/2, j+1+D/2) in the MMA's 16-bit type
-        if constexpr (KV8) {
-          const float ks = p.k_scale[h], vs = p.v_scale[h];
-          const float v1 = __bfloat162float(vn[j]), v2 = __bfloat162float(vn[j + D / 2]);
-          const float w1 = __bfloat162float(vn[j + 1]), w2 = __bfloat162float(vn[j + 1 + D / 2]);
-          const uint8_t qa1 = to_e4m3(a1 / ks), qb1 = to_e4m3(b1 / ks), qa2 = to_e4m3(a2 / ks), qb2 = to_e4m3(b2 / ks);
-          const uint8_t qv1 = to_e4m3(v1 / vs), qw1 = to_e4m3(w1 / vs), qv2 = to_e4m3(v2 / vs), qw2 = to_e4m3(w2 / vs);
-          uint8_t* kg = reinterpret_cast<uint8_t*>(p.k_cache) + slot * D;
-          uint8_t* vg = reinterpret_cast<uint8_t*>(p.v_cache) + slot * D;
-          *reinterpret_cast<uint16_t*>(kg + j) = static_cast<uint16_t>(qa1 | (qb1 << 8));
-          *reinterpret_cast<uint16_t*>(kg + j + D / 2) = static_cast<uint16_t>(qa2 | (qb2 << 8));
-          *reinterpret_cast<uint16_t*>(vg + j) = static_cast<uint16_t>(qv1 | (qw1 << 8));
-          *reinterpret_cast<uint16_t*>(vg + j + D / 2) = static_cast<uint16_t>(qv2 | (qw2 << 8));
-          lo = pack16x2<true>(from_e4m3(qa1), from_e4m3(qb1));
-          hi = pack16x2<true>(from_e4m3(qa2), from_e4m3(qb2));
-          vlo = pack16x2<true>(from_e4m3(qv1), from_e4m3(qw1));
-          vhi = pack16x2<true>(from_e4m3(qv2), from_e4m3(qw2));
-        } else {
-          __nv_bfloat16* kg = p.k_cache + slot * D;
-          __nv_bfloat16* vg = p.v_cache + slot * D;
-          lo = pack_bf16x2(a1, b1);
-          hi = pack_bf16x2(a2, b2);
-          vlo = *reinterpret_cast<const uint32_t*>(&vn[j]);
-          vhi = *reinterpret_cast<const uint32_t*>(&vn[j + D / 2]);
-          *reinterpret_cast<uint32_t*>(&kg[j]) = lo;
-          *reinterpret_cast<uint32_t*>(&kg[j + D / 2]) = hi;
-          *reinterpret_cast<uint32_t*>(&vg[j]) = vlo;
-          *reinterpret_cast<uint32_t*>(&vg[j + D / 2]) = vhi;
-        }
+        // elements (j, j+1) and (j+D/2, j+1+D/2) of the rotated key and of the value
+        __nv_bfloat16* kg = p.k_cache + slot * D;
+        __nv_bfloat16* vg = p.v_cache + slot * D;
+        const uint32_t lo = pack_bf16x2(a1, b1);
+        const uint32_t hi = pack_bf16x2(a2, b2);
+        const uint32_t vlo = *reinterpret_cast<const uint32_t*>(&vn[j]);
+        const uint32_t vhi = *reinterpret_cast<const uint32_t*>(&vn[j + D / 2]);
+        *reinterpret_cast<uint32_t*>(&kg[j]) = lo;
+        *reinterpret_cast<uint32_t*>(&kg[j + D / 2]) = hi;
+        *reinterpret_cast<uint32_t*>(&vg[j]) = vlo;
+        *reinterpret_cast<uint32_t*>(&vg[j + D / 2]) = vhi;
         const int e[2] = {j, j + D / 2};
         const uint32_t kv[2] = {lo, hi};
         const uint32_t vv[2] = {vlo, vhi};
@@ -405,9 +286,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int q = 0; q < 2; ++q) {
           const int sub = e[q] >> 6;
           const int byte = (e[q] & 63) * 2;
-          const int off = sub * C::kSubStride + rr * 128 + ((((byte >> 4) ^ (rr & 7)) << 4) | (byte & 15));
-          *reinterpret_cast<uint32_t*>(ktile_c + off) = kv[q];
-          *reinterpret_cast<uint32_t*>(vtile_c + off) = vv[q];
+          const int off = sub * C::kSubBytes + rr * 128 + ((((byte >> 4) ^ (rr & 7)) << 4) | (byte & 15));
+          *reinterpret_cast<uint32_t*>(ktile + off) = kv[q];
+          *reinterpret_cast<uint32_t*>(vtile + off) = vv[q];
         }
       }
       __syncwarp();
@@ -418,15 +299,15 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const int ld_row = r0 + ((lane >> 4) << 3) + (lane & 7);  // token row this lane addresses
       const int ld_kh = (lane >> 3) & 1;
-      const uint32_t kbase = smem_u32(ktile_c) + ld_row * 128;
+      const uint32_t kbase = smem_u32(ktile) + ld_row * 128;
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const int chunk16 = (ks * 2 + ld_kh) & 7;
         const int sub = (ks * 2) >> 3;
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(kbase + sub * C::kSubStride + ((chunk16 ^ (ld_row & 7)) << 4), b0, b1, b2, b3);
-        mma_16816<KV8>(sacc[0], qf[ks], b0, b1);
-        mma_16816<KV8>(sacc[1], qf[ks], b2, b3);
+        ldmatrix_x4(kbase + sub * C::kSubBytes + ((chunk16 ^ (ld_row & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(sacc[0], qf[ks], b0, b1);
+        mma_bf16_16816(sacc[1], qf[ks], b2, b3);
       }
       // ---- online softmax (log2 domain) ----
       float mx[2] = {-INFINITY, -INFINITY};
@@ -464,17 +345,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           for (int c = 0; c < 4; ++c) {
             pv[nt][c] = exp2f(sacc[nt][c] - m_use[c >> 1]);
             l_run[c >> 1] += pv[nt][c];
-            pr[nt][c] = pv[nt][c] - round16<KV8>(pv[nt][c]);
+            pr[nt][c] = pv[nt][c] - bf16_round(pv[nt][c]);
           }
         }
-        pf[0] = pack16x2<KV8>(pv[0][0], pv[0][1]);
-        pf[1] = pack16x2<KV8>(pv[0][2], pv[0][3]);
-        pf[2] = pack16x2<KV8>(pv[1][0], pv[1][1]);
-        pf[3] = pack16x2<KV8>(pv[1][2], pv[1][3]);
-        pl[0] = pack16x2<KV8>(pr[0][0], pr[0][1]);
-        pl[1] = pack16x2<KV8>(pr[0][2], pr[0][3]);
-        pl[2] = pack16x2<KV8>(pr[1][0], pr[1][1]);
-        pl[3] = pack16x2<KV8>(pr[1][2], pr[1][3]);
+        pf[0] = pack_bf16x2(pv[0][0], pv[0][1]);
+        pf[1] = pack_bf16x2(pv[0][2], pv[0][3]);
+        pf[2] = pack_bf16x2(pv[1][0], pv[1][1]);
+        pf[3] = pack_bf16x2(pv[1][2], pv[1][3]);
+        pl[0] = pack_bf16x2(pr[0][0], pr[0][1]);
+        pl[1] = pack_bf16x2(pr[0][2], pr[0][3]);
+        pl[2] = pack_bf16x2(pr[1][0], pr[1][1]);
+        pl[3] = pack_bf16x2(pr[1][2], pr[1][3]);
       }
 #pragma unroll
       for (int i2 = 0; i2 < D / 8; ++i2) {
@@ -486,17 +367,17 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       // ---- O += P V ----
       const int v_row = r0 + (((lane >> 3) & 1) << 3) + (lane & 7);
       const int v_dh = lane >> 4;
-      const uint32_t vbase = smem_u32(vtile_c) + v_row * 128;
+      const uint32_t vbase = smem_u32(vtile) + v_row * 128;
 #pragma unroll
       for (int dn = 0; dn < D / 16; ++dn) {
         const int chunk16 = (dn * 2 + v_dh) & 7;
         const int sub = (dn * 2) >> 3;
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(vbase + sub * C::kSubStride + ((chunk16 ^ (v_row & 7)) << 4), b0, b1, b2, b3);
-        mma_16816<KV8>(oacc[dn * 2], pf, b0, b1);
-        mma_16816<KV8>(oacc[dn * 2], pl, b0, b1);
-        mma_16816<KV8>(oacc[dn * 2 + 1], pf, b2, b3);
-        mma_16816<KV8>(oacc[dn * 2 + 1], pl, b2, b3);
+        ldmatrix_x4_trans(vbase + sub * C::kSubBytes + ((chunk16 ^ (v_row & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16_16816(oacc[dn * 2], pf, b0, b1);
+        mma_bf16_16816(oacc[dn * 2], pl, b0, b1);
+        mma_bf16_16816(oacc[dn * 2 + 1], pf, b2, b3);
+        mma_bf16_16816(oacc[dn * 2 + 1], pl, b2, b3);
       }
     }
     __syncwarp();
@@ -545,7 +426,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         lsum += ml[w * 16 + g] * sc;
       }
     }
-    const float o = lsum > 0.f ? acc / lsum * out_scale : 0.f;
+    const float o = lsum > 0.f ? acc / lsum : 0.f;
     const int64_t qh = static_cast<int64_t>(t) * p.nq + h * G + g;
     if (p.num_splits == 1) {
       p.out[qh * D + d] = __float2bfloat16_rn(o);
@@ -571,7 +452,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, 2)
 paged_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p,
                      const int32_t* __restrict__ units) {
-  using C = Cfg<D, false>;
+  using C = Cfg<D>;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -840,7 +721,7 @@ __global__ void __launch_bounds__(D) combine_kernel(Params p) {
 }
 
 // Prefill / mixed steps: rotate k, then scatter k and v of every token into the pool.
-template <int D, bool KV8>
+template <int D>
 __global__ void __launch_bounds__(128) rope_append_kernel(Params p) {
   pdl_launch_dependents();
   pdl_wait();
@@ -859,20 +740,10 @@ __global__ void __launch_bounds__(128) rope_append_kernel(Params p) {
     if (rope)
       rope_pair(x1, x2, __bfloat162float(p.cos[pk * (D / 2) + j]), __bfloat162float(p.sin[pk * (D / 2) + j]), x1, x2);
     const int64_t base = (slot_tok * p.nkv + h) * D;
-    if constexpr (KV8) {
-      const float ks = p.k_scale[h], vs = p.v_scale[h];
-      uint8_t* kc = reinterpret_cast<uint8_t*>(p.k_cache);
-      uint8_t* vc = reinterpret_cast<uint8_t*>(p.v_cache);
-      kc[base + j] = to_e4m3(x1 / ks);
-      kc[base + j + D / 2] = to_e4m3(x2 / ks);
-      vc[base + j] = to_e4m3(__bfloat162float(vn[j]) / vs);
-      vc[base + j + D / 2] = to_e4m3(__bfloat162float(vn[j + D / 2]) / vs);
-    } else {
-      p.k_cache[base + j] = __float2bfloat16_rn(x1);
-      p.k_cache[base + j + D / 2] = __float2bfloat16_rn(x2);
-      p.v_cache[base + j] = vn[j];
-      p.v_cache[base + j + D / 2] = vn[j + D / 2];
-    }
+    p.k_cache[base + j] = __float2bfloat16_rn(x1);
+    p.k_cache[base + j + D / 2] = __float2bfloat16_rn(x2);
+    p.v_cache[base + j] = vn[j];
+    p.v_cache[base + j + D / 2] = vn[j + D / 2];
   }
 }
 
@@ -923,20 +794,20 @@ static int fill_params(const b200_attention_args* a, Params& p) {
   p.k_scale = a->k_scale;
   p.v_scale = a->v_scale;
   if (a->kv_cache_fp8) {
-    if (a->head_dim != 128 || !a->k_scale || !a->v_scale) return B200_ERR_INVALID_ARGUMENT;
+    if (a->head_dim != 128 || !a->k_scale || !a->v_scale || !a->qkv || a->chunk_size % 128 != 0) return B200_ERR_INVALID_ARGUMENT;
   }
   return B200_OK;
 }
 
-template <int D, bool KV8>
+template <int D>
 static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_t stream) {
-  using C = Cfg<D, KV8>;
-  constexpr int kElem = KV8 ? 1 : 2;
+  using C = Cfg<D>;
+  constexpr int kElem = 2;
   const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.nkv),
                             static_cast<uint64_t>(p.num_chunks) * p.chunk};
   const uint64_t strides[2] = {static_cast<uint64_t>(D) * kElem, static_cast<uint64_t>(p.nkv) * D * kElem};
-  const uint32_t box[3] = {KV8 ? 128u : 64u, 1, kTile};
-  const CUtensorMapDataType dt = KV8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint32_t box[3] = {64u, 1, kTile};
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const CUtensorMap* mk = get_tensor_map(p.k_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, dt);
   const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -944,14 +815,14 @@ static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_
   if (!mk || !mv) return B200_ERR_DRIVER;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_attention_kernel<D, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(paged_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::kSmemBytes) != cudaSuccess)
       return B200_ERR_LAUNCH;
     attr_set = true;
   }
   const int64_t units = static_cast<int64_t>(p.T) * p.nkv * p.num_splits;
   if (units > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
-  int rc = launch_pdl(paged_attention_kernel<D, KV8>, dim3(static_cast<unsigned>(units)), dim3(kThreads), C::kSmemBytes,
+  int rc = launch_pdl(paged_attention_kernel<D>, dim3(static_cast<unsigned>(units)), dim3(kThreads), C::kSmemBytes,
                       stream, *mk, *mv, p);
   if (rc != B200_OK) return rc;
   if (p.num_splits > 1) rc = launch_pdl(combine_kernel<D>, dim3(p.T * p.nq), dim3(D), 0, stream, p);
@@ -960,7 +831,7 @@ static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_
 
 template <int D>
 static int launch_prefill(Params& p, const int32_t* units, int num_units, cudaStream_t stream) {
-  using C = Cfg<D, false>;
+  using C = Cfg<D>;
   const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(p.nkv),
                             static_cast<uint64_t>(p.num_chunks) * p.chunk};
   const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(p.nkv) * D * 2};
@@ -984,6 +855,12 @@ static int launch_prefill(Params& p, const int32_t* units, int num_units, cudaSt
 }
 
 }  // namespace attn
+
+// E4M3 pool: kernels of attention_fp8.cu (same translation unit, compiled after this file)
+namespace attn8 {
+static int launch_attention_fp8(attn::Params& p, bool two_terms, cudaStream_t stream);
+__global__ void rope_append_fp8_kernel(attn::Params p);
+}  // namespace attn8
 }  // namespace b200
 
 extern "C" {
@@ -1014,9 +891,9 @@ int b200_rope_append(const b200_attention_args* a, b200_stream_t stream) {
   if (rc != B200_OK) return rc;
   if (!a->token_to_chunk_idx || !a->token_to_local_pos || !a->qkv) return B200_ERR_INVALID_ARGUMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (a->kv_cache_fp8) return launch_pdl(attn::rope_append_kernel<128, true>, dim3(p.T), dim3(128), 0, s, p);
-  if (a->head_dim == 128) return launch_pdl(attn::rope_append_kernel<128, false>, dim3(p.T), dim3(128), 0, s, p);
-  return launch_pdl(attn::rope_append_kernel<64, false>, dim3(p.T), dim3(128), 0, s, p);
+  if (a->kv_cache_fp8) return launch_pdl(attn8::rope_append_fp8_kernel, dim3(p.T), dim3(128), 0, s, p);
+  if (a->head_dim == 128) return launch_pdl(attn::rope_append_kernel<128>, dim3(p.T), dim3(128), 0, s, p);
+  return launch_pdl(attn::rope_append_kernel<64>, dim3(p.T), dim3(128), 0, s, p);
 }
 
 int b200_paged_attention(const b200_attention_args* a, b200_stream_t stream) {
@@ -1035,8 +912,8 @@ int b200_paged_attention(const b200_attention_args* a, b200_stream_t stream) {
     p.ws_lse = p.ws_o + static_cast<size_t>(a->num_tokens) * a->num_q_heads * a->num_splits * a->head_dim;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (a->kv_cache_fp8) return attn::launch_attention<128, true>(a, p, s);
-  return a->head_dim == 128 ? attn::launch_attention<128, false>(a, p, s) : attn::launch_attention<64, false>(a, p, s);
+  if (a->kv_cache_fp8) return attn8::launch_attention_fp8(p, a->kv_cache_fp8 != 2, s);
+  return a->head_dim == 128 ? attn::launch_attention<128>(a, p, s) : attn::launch_attention<64>(a, p, s);
 }
 
 }  // extern "C"

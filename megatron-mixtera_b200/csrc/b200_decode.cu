@@ -6,5 +6,6 @@
 #include "gemm_fp8_block.cu"
 #include "quant.cu"
 #include "attention.cu"
+#include "attention_fp8.cu"
 #include "elementwise.cu"
 #include "sampling.cu"

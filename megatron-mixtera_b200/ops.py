@@ -445,9 +445,10 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
                         token_to_pos_in_request=None, token_to_chunk_idx=None, token_to_local_pos=None,
                         row_of_token=None, rope_cos=None, rope_sin=None, num_splits: int = 1,
                         fuse_rope_append: bool = False, softmax_scale: float = 0.0, k_scale=None,
-                        v_scale=None, row_order=None) -> AttentionArgs:
+                        v_scale=None, row_order=None, fp8_single_term: bool = False) -> AttentionArgs:
     """Fill the C argument struct.  It holds raw pointers only: the caller keeps the tensors alive until the
-    kernels have run.  ``k_scale`` / ``v_scale`` (fp32 [nkv]) select the FP8 (E4M3) KV pool."""
+    kernels have run.  ``k_scale`` / ``v_scale`` (fp32 [nkv]) select the FP8 (E4M3) KV pool; ``fp8_single_term`` its
+    faster, less exact arithmetic (queries and probabilities as one E4M3 term instead of two)."""
     T = qkv.shape[0]
     a = AttentionArgs()
     if isinstance(qkv, GemmPartials):  # un-reduced output of the QKV GEMM (decode kernel only)
@@ -480,7 +481,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     a.num_splits = num_splits
     a.fuse_rope_append = int(fuse_rope_append)
     a.softmax_scale = softmax_scale
-    a.kv_cache_fp8 = int(k_scale is not None)
+    a.kv_cache_fp8 = 0 if k_scale is None else (2 if fp8_single_term else 1)
     a.k_scale = _p(k_scale)
     a.v_scale = _p(v_scale)
     a.row_order = _p(row_order)
@@ -499,6 +500,28 @@ def paged_attention(args: AttentionArgs) -> None:
     check("b200_paged_attention", _lib.load().b200_paged_attention(ctypes.byref(args), _stream()))
     if args.num_splits > 1:
         launch_count += 1  # the split-combine kernel
+
+
+def fp8_value_positions(chunk_size: int) -> torch.Tensor:
+    """positions[t] = where token t of a chunk sits in the FP8 value pool's innermost dimension."""
+    lib = _lib.load()
+    return torch.tensor([lib.b200_fp8_value_position(t) for t in range(chunk_size)], dtype=torch.int64)
+
+
+def fp8_values_to_pool_layout(v: torch.Tensor) -> torch.Tensor:
+    """E4M3 value bytes [chunks, chunk, heads, dim] (the reference's order) -> the byte order of the FP8 pool
+    ([chunks, heads, dim, position], returned with the input's shape so that it drops into the pool tensor)."""
+    pos = fp8_value_positions(v.shape[1]).to(v.device)
+    out = torch.empty((v.shape[0], v.shape[2], v.shape[3], v.shape[1]), dtype=v.dtype, device=v.device)
+    out[..., pos] = v.permute(0, 2, 3, 1)
+    return out.view(v.shape)
+
+
+def fp8_values_from_pool_layout(p: torch.Tensor) -> torch.Tensor:
+    """Inverse of `fp8_values_to_pool_layout`."""
+    chunks, chunk, heads, dim = p.shape
+    pos = fp8_value_positions(chunk).to(p.device)
+    return p.view(chunks, heads, dim, chunk)[..., pos].permute(0, 3, 1, 2).contiguous()
 
 
 def paged_prefill_attention(args: AttentionArgs, units: torch.Tensor, num_units: int) -> None:

@@ -78,7 +78,8 @@ class PagedFlashDecodeAttention(torch.nn.Module):
             rope_sin=rotary_pos_sin,
         )
         if getattr(ctx, "kv_cache_fp8", False):  # E4M3 pool: per-head scales of this layer
-            common.update(k_scale=ctx.kv_scales[self.layer_number - 1, 0], v_scale=ctx.kv_scales[self.layer_number - 1, 1])
+            common.update(k_scale=ctx.kv_scales[self.layer_number - 1, 0], v_scale=ctx.kv_scales[self.layer_number - 1, 1],
+                          fp8_single_term=getattr(ctx, "kv_fp8_single_term", False))
         if decode:
             # one new token per request: rows are requests, append fused into the attention kernel
             splits = choose_attention_splits(T, self.num_kv_heads, ctx.max_sequence_length, ctx.chunk_size_tokens)
@@ -126,7 +127,8 @@ class SelfAttention(torch.nn.Module):
             raise NotImplementedError("only the dynamic-batching inference path is implemented")
         defer_qkv = (inference_context.is_decode_only() and getattr(self.config, "fuse_qkv_reduction_into_attention", False)
                      and getattr(self.linear_qkv, "supports_deferred_reduction", False)
-                     and getattr(self.core_attention, "accepts_gemm_partials", False))
+                     and getattr(self.core_attention, "accepts_gemm_partials", False)
+                     and not getattr(inference_context, "kv_cache_fp8", False))  # the E4M3-pool kernel reads bf16 qkv
         if defer_qkv:  # decode: the attention kernel sums the QKV GEMM's split-K partial sums itself
             mixed_qkv, _ = self.linear_qkv(hidden_states, defer_reduction=True)
         else:

@@ -535,11 +535,11 @@ def test_attention_split_invariance_at_long_context(ops):
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize(
     "nkv,G,chunk,kv_lens,splits",
-    [(2, 4, 64, [1, 64, 65, 130, 0, 300, 17, 256], 1), (2, 4, 64, [1, 64, 65, 130, 0, 300, 17, 256], 3),
-     (8, 4, 256, [2304, 128, 700, 1216, 0], 2), (1, 8, 256, [5000, 257], 4)],
+    [(2, 4, 128, [1, 64, 65, 130, 0, 300, 17, 256, 128, 129], 1), (2, 4, 128, [1, 64, 65, 130, 0, 300, 17, 256], 3),
+     (8, 4, 256, [2304, 128, 700, 1216, 0], 2), (1, 8, 256, [5000, 257], 4), (2, 1, 128, [33, 500], 1)],
 )
-@pytest.mark.parametrize("fused", [True, False])
-def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused):
+@pytest.mark.parametrize("fused,single_term", [(True, False), (False, False), (True, True)])
+def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused, single_term):
     D = 128
     c = make_paged_case(T=len(kv_lens), nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=kv_lens, seed=21)
     g = torch.Generator().manual_seed(5)
@@ -560,7 +560,10 @@ def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused):
     dev = "cuda"
     half = c["freqs"][:, : D // 2]
     cos, sin = torch.cos(half).to(BF16).to(dev), torch.sin(half).to(BF16).to(dev)
-    kc, vc = kq.view(torch.uint8).to(dev), vq.view(torch.uint8).to(dev)
+    # keys as they are; values in the pool's own byte order (transposed inside a chunk, positions permuted)
+    kc = kq.view(torch.uint8).to(dev)
+    vc = ops.fp8_values_to_pool_layout(vq.view(torch.uint8)).to(dev)
+    assert torch.equal(ops.fp8_values_from_pool_layout(vc.cpu()), vq.view(torch.uint8))
     out = torch.full((T, c["nq"] * D), float("nan"), dtype=BF16, device=dev)
     d = {k_: c[k_].to(dev) for k_ in ("qkv", "block_table", "kv_lens", "pos", "chunk_idx", "local")}
     ks, vs = k_scale.to(dev), v_scale.to(dev)
@@ -568,21 +571,26 @@ def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused):
         qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
         num_q_heads=c["nq"], num_kv_heads=nkv, head_dim=D, chunk_size=chunk, token_to_pos_ids=d["pos"],
         token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
-        rope_cos=cos, rope_sin=sin, num_splits=splits, fuse_rope_append=fused, k_scale=ks, v_scale=vs)
+        rope_cos=cos, rope_sin=sin, num_splits=splits, fuse_rope_append=fused, k_scale=ks, v_scale=vs,
+        fp8_single_term=single_term)
     if not fused:
         ops.rope_append(args)
     ops.paged_attention(args)
     torch.cuda.synchronize()
     live = [r for r, kl in enumerate(kv_lens) if kl > 0]
+    v_now = ops.fp8_values_from_pool_layout(vc.cpu())
     for r in live:  # appended bytes: bit-exact
         ci, lp = int(c["chunk_idx"][r]), int(c["local"][r])
         assert torch.equal(kc[ci, lp].cpu(), kq_ref.view(torch.uint8)[ci, lp]), r
-        assert torch.equal(vc[ci, lp].cpu(), vq_ref.view(torch.uint8)[ci, lp]), r
-    if fused:
+        assert torch.equal(v_now[ci, lp], vq_ref.view(torch.uint8)[ci, lp]), r
+    if fused:  # nothing else in the pool was touched
         mask = torch.ones(kc.shape[:2], dtype=torch.bool)
         mask[c["chunk_idx"][live], c["local"][live]] = False
         assert torch.equal(kc.cpu()[mask], kq.view(torch.uint8)[mask])
+        assert torch.equal(v_now[mask], vq.view(torch.uint8)[mask])
     o = out.cpu().view(T, c["nq"], D)
     assert not torch.isnan(o.float()).any()
-    # same E4M3 pool on both sides: only summation order and the output rounding differ
-    assert rel_l2(o, ref) < 1.5e-3, rel_l2(o, ref)
+    # same E4M3 pool on both sides; the kernel feeds queries and probabilities to the fp8 tensor cores as two
+    # E4M3 terms each (~7 significant bits), far inside the 2^-4 resolution of the pool itself
+    # (one term each: E4M3 queries and probabilities, 2^-4 resolution like the pool's own)
+    assert rel_l2(o, ref) < (6e-2 if single_term else 6e-3), rel_l2(o, ref)
