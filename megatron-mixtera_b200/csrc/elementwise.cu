@@ -77,16 +77,16 @@ __device__ __forceinline__ void peer_row_handshake(const PeerSrc& ps, int row) {
   for (int q = 0; q < ps.world; ++q)
     if (q != ps.rank) st_release_sys(ps.flags[q] + ps.rank * ps.max_rows + row, call);
   const uint64_t t0 = global_timer_ns();
-  for (int q = 0; q < ps.world; ++q) {
-    if (q == ps.rank) continue;
-    const int32_t* f = ps.flags[ps.rank] + q * ps.max_rows + row;
-    while (ld_acquire_sys(f) < call) {
-      if (global_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, flag it, carry on with what is there
-        atomicOr(&g_device_status, kStatusPeerTimeout);
-        return;
-      }
-      __nanosleep(64);
+  for (;;) {
+    bool all = true;
+    for (int q = 0; q < ps.world; ++q)
+      if (q != ps.rank && ld_acquire_sys(ps.flags[ps.rank] + q * ps.max_rows + row) < call) all = false;
+    if (all) return;
+    if (global_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, flag it, carry on with what is there
+      atomicOr(&g_device_status, kStatusPeerTimeout);
+      return;
     }
+    __nanosleep(32);
   }
 }
 
@@ -138,15 +138,22 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     if (i < nvec) {
       float f[8];
       if constexpr (kSrc == 2) {
+        // all peers' vectors are requested before any is used: one NVLink round trip, not `world` of them
+        uint4 u[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < ps.world) u[q] = __ldcg(reinterpret_cast<const uint4*>(ps.data[q] + off) + i);
 #pragma unroll
         for (int k = 0; k < 8; ++k) f[k] = 0.f;
-        for (int q = 0; q < ps.world; ++q) {
-          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(ps.data[q] + off) + i);
-          const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            f[2 * k] += bf16_lo(w4[k]);
-            f[2 * k + 1] += bf16_hi(w4[k]);
+        for (int q = 0; q < 8; ++q) {
+          if (q < ps.world) {  // rank order: every rank adds in the same order
+            const uint32_t w4[4] = {u[q].x, u[q].y, u[q].z, u[q].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              f[2 * k] += bf16_lo(w4[k]);
+              f[2 * k + 1] += bf16_hi(w4[k]);
+            }
           }
         }
 #pragma unroll
