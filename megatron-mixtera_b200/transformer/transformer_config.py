@@ -36,7 +36,7 @@ class TransformerConfig:
     # rows interleaved per 64 (`ColumnParallelLinear.canonical_weight()` gives the reference's order back)
     fuse_swiglu_into_fc1: bool = True
     # not in the reference: at TP > 1 the all-reduce after out-proj / fc2 is done by the residual-add + norm kernel
-    # itself with peer loads over NVLink (one node, <= 8 ranks, <= 512 token rows; NCCL otherwise)
+    # itself with peer loads over NVLink (one node, <= 4 ranks, <= 512 token rows; NCCL otherwise)
     fuse_tp_allreduce_into_norm: bool = True
     fp8: Optional[str] = None                   # None | "mxfp8" (E8M0 scale per 32) | "blockwise" (fp32, 128x128 / 1x128)
 
