@@ -2,7 +2,7 @@
 
 Run from the repository root, in a container that has the reference checkout:
 
-    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py [--ref /path/to/reference]
+    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py --ref /path/to/reference
 
 Nothing here is needed at test time; the tests only read the ``*.npz`` files this
 script wrote.  The reference needs three shims to run without a GPU:
@@ -377,7 +377,7 @@ LLAMA_TINY = dict(
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of the reference (the directory that holds megatron/)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     _shim_and_import(args.ref)
