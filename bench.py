@@ -429,7 +429,11 @@ def run_ours(args, w):
         "kernel_share_of_layer": {"gemm": gemm_us / layer_us, "paged_attention": kern["paged_attention"]["us"] / layer_us},
         "step_vs_hbm_floor": {"bytes_per_step": step_bytes(w, ctx, B, tp), "floor_ms": step_bytes(w, ctx, B, tp) / peak / 1e6,
                               "frac": step_bytes(w, ctx, B, tp) / peak / 1e6 / (dev_s / steps * 1e3)},
-        "cpu_baseline": cpu, "clocks": clocks, "prefill_s": prefill_s, "device_status": status,
+        "cpu_baseline": cpu, "clocks": clocks, "prefill_s": prefill_s,
+        # outside the timed region, wall clock, includes the first-use set-up of every kernel: an indication only
+        "prefill": {"prompt_tokens": int(sum(len(p) for p in prompts)), "seconds": prefill_s,
+                    "tokens_per_s": sum(len(p) for p in prompts) / prefill_s},
+        "device_status": status,
     }
     emit(line)
     if world > 1:
