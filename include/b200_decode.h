@@ -222,7 +222,7 @@ int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, con
  * (per token row) tells the peers the row is ready, waits - at most 2 s, then B200 device status 4 - until theirs
  * are, reads all ranks' rows with peer loads and uses x = bf16(sum in rank order, fp32) exactly like
  * b200_add_norm_*'s x.  All ranks obtain identical bits.  Consecutive calls must alternate the slot (0, 1, 0, ...)
- * and every rank must issue the same sequence of calls.  hidden <= 8192, world_size 2..8, no multicast.
+ * and every rank must issue the same sequence of calls.  hidden <= 8192, world_size 2..8; plain peer loads and stores only.
  */
 typedef struct {
   int32_t world_size, rank;

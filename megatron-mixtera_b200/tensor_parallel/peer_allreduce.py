@@ -5,7 +5,7 @@ The reference reduces the partial outputs of ``RowParallelLinear`` with an NCCL 
 kernels.  Here every tensor-parallel rank of the node writes its bf16 partial output into a buffer that the other
 ranks map through CUDA IPC, and the norm kernel itself synchronises per token row (flags in peer memory, bounded
 waits) and sums the ranks' rows with plain peer loads over NVLink - one kernel for collective + add + norm, no
-NCCL launch, no multicast.  All ranks compute the same bits (fixed rank order, fp32 sum, one bf16 rounding).
+NCCL launch.  All ranks compute the same bits (fixed rank order, fp32 sum, one bf16 rounding).
 """
 from __future__ import annotations
 
