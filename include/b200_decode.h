@@ -42,6 +42,11 @@ const char* b200_error_string(int code);
  * 0 = no kernel has given up since the last reset.
  */
 int b200_device_status(int reset, int* status_out);
+/* `rows` rows of `width_bytes` from (pinned) host memory to the device in ONE asynchronous copy: the per-step index
+ * arrays of the context (token -> position / chunk / slot, lengths; dynamic_context.py:656-825, 1284-1296) are rows
+ * of one staging matrix, and a step updates the first n entries of each. */
+int b200_copy_rows_h2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                       b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Embedding / row gather.  out[i, :] = table[ids[i] - vocab_start, :] if vocab_start <= ids[i]

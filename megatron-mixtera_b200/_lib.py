@@ -15,6 +15,7 @@ EXPORTED_SYMBOLS = (
     "b200_version",
     "b200_error_string",
     "b200_device_status",
+    "b200_copy_rows_h2d",
     "b200_gather_rows_bf16",
     "b200_add_norm_bf16",
     "b200_activation_bf16",
@@ -141,6 +142,7 @@ def load() -> ctypes.CDLL:
     lib.b200_error_string.restype = c_char_p
     lib.b200_error_string.argtypes = [c_int]
     lib.b200_device_status.argtypes = [c_int, POINTER(c_int)]
+    lib.b200_copy_rows_h2d.argtypes = [c_void_p, c_size_t, c_void_p, c_size_t, c_size_t, c_size_t, c_void_p]
     lib.b200_gather_rows_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_void_p,
                                           c_void_p, c_void_p]
     lib.b200_add_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

@@ -143,4 +143,16 @@ int b200_device_status(int reset, int* status_out) {
   return B200_OK;
 }
 
+int b200_copy_rows_h2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                       b200_stream_t stream) {
+  if (!dst || !src || width_bytes == 0 || rows == 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
+    return B200_ERR_INVALID_ARGUMENT;
+  if (cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyHostToDevice,
+                        reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_DRIVER;
+  }
+  return B200_OK;
+}
+
 }  // extern "C"

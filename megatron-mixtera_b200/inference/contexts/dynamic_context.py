@@ -97,6 +97,7 @@ class BaseInferenceContext:
 
 # rows of the token-level arena
 _TOK_INPUT, _TOK_POS, _TOK_REQ, _TOK_CHUNK, _TOK_POS_IN_REQ, _TOK_LOCAL = range(6)
+_LEN_Q, _LEN_KV, _LEN_ORDER, _LEN_CUQ, _LEN_CUKV = range(5)  # rows of the per-request length matrix
 
 
 class DynamicInferenceContext(BaseInferenceContext):
@@ -269,14 +270,17 @@ class DynamicInferenceContext(BaseInferenceContext):
 
         # ---- attention state with stable device addresses (reference :358-382) ----
         dev = self.device
-        self.query_seq_lengths_cudagraph_only = torch.zeros((R,), dtype=torch.int32, device=dev)
-        self.cu_query_seq_lengths_cudagraph_only = torch.zeros((R + 1,), dtype=torch.int32, device=dev)
-        self.kv_seq_lengths_cudagraph_only = torch.zeros((R,), dtype=torch.int32, device=dev)
-        self.cu_kv_seq_lengths_cudagraph_only = torch.zeros((R + 1,), dtype=torch.int32, device=dev)
-        self.request_to_kv_chunk_ids_cudagraph_only = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, device=dev)
-        # host staging: [query lens | cu query | kv lens | cu kv] and the block table
+        # [query lens | kv lens | attention row order | cu query | cu kv]: rows of ONE device matrix mirrored from one
+        # pinned staging matrix, so that a step publishes them with a single 2-D copy
+        self._d_len = torch.zeros((5, R + 1), dtype=torch.int32, device=dev)
+        self._d_len[_LEN_ORDER, :R] = torch.arange(R, dtype=torch.int32, device=dev)
+        self.query_seq_lengths_cudagraph_only = self._d_len[_LEN_Q, :R]
+        self.kv_seq_lengths_cudagraph_only = self._d_len[_LEN_KV, :R]
         # rows processed by the attention kernel in this order (longest context first); decode steps only
-        self.attention_row_order = torch.arange(R, dtype=torch.int32, device=dev)
+        self.attention_row_order = self._d_len[_LEN_ORDER, :R]
+        self.cu_query_seq_lengths_cudagraph_only = self._d_len[_LEN_CUQ]
+        self.cu_kv_seq_lengths_cudagraph_only = self._d_len[_LEN_CUKV]
+        self.request_to_kv_chunk_ids_cudagraph_only = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, device=dev)
         self._h_len = torch.zeros((5, R + 1), dtype=torch.int32, pin_memory=pin)
         self._h_len_np = self._h_len.numpy()
         self._h_bt = torch.zeros((R, self.max_kv_chunk_count), dtype=torch.int32, pin_memory=pin)
@@ -407,13 +411,29 @@ class DynamicInferenceContext(BaseInferenceContext):
             self._copy_event.record()
             self._copies_pending = True
 
-    def _push_token_rows(self, rows, lo: int, hi: int) -> None:
-        if hi <= lo:
+    def _push_rows(self, dst: Tensor, src: Tensor, rows: int, lo: int, hi: int, first_row: int = 0) -> None:
+        """dst[first_row : first_row + rows, lo:hi] = src[same] (pinned host -> device), one 2-D copy on a GPU."""
+        if hi <= lo or rows <= 0:
             return
-        for r in rows:
-            self._d_tok[r, lo:hi].copy_(self._h_tok[r, lo:hi], non_blocking=True)
-            self.h2d_bytes += (hi - lo) * 8
+        d, s_ = dst[first_row : first_row + rows], src[first_row : first_row + rows]
+        if dst.is_cuda:
+            from ... import ops
+
+            ops.copy_rows_h2d(d, s_, rows, lo, hi)
+        else:
+            d[:, lo:hi].copy_(s_[:, lo:hi])
+        self.h2d_bytes += rows * (hi - lo) * src.element_size()
         self._mark_copies()
+
+    def _push_token_rows(self, rows, lo: int, hi: int) -> None:
+        rows = sorted(rows)
+        start = 0
+        while start < len(rows):  # runs of consecutive rows go out together
+            end = start
+            while end + 1 < len(rows) and rows[end + 1] == rows[end] + 1:
+                end += 1
+            self._push_rows(self._d_tok, self._h_tok, end - start + 1, lo, hi, first_row=rows[start])
+            start = end + 1
 
     # ------------------------------------------------------------------ attention state
     def reset_attention_state(self) -> None:
@@ -481,8 +501,8 @@ class DynamicInferenceContext(BaseInferenceContext):
         n_rows = self.padded_active_request_count
         lens = self._h_len_np
         lens[:, : n_rows + 1] = 0
-        lens[0, :n_req] = ql
-        lens[2, :n_req] = kv
+        lens[_LEN_Q, :n_req] = ql
+        lens[_LEN_KV, :n_req] = kv
         dev_rows = max(n_rows, 1)
         if decode:
             self.cu_query_seq_lengths = None
@@ -490,13 +510,11 @@ class DynamicInferenceContext(BaseInferenceContext):
             self.max_seqlen_q = 1
             self.max_seqlen_k = self.max_sequence_length
         else:
-            lens[1, 1 : n_req + 1] = np.cumsum(ql)
-            lens[3, 1 : n_req + 1] = np.cumsum(kv)
+            lens[_LEN_CUQ, 1 : n_req + 1] = np.cumsum(ql)
+            lens[_LEN_CUKV, 1 : n_req + 1] = np.cumsum(kv)
             if n_rows > n_req:
-                lens[1, n_req + 1 : n_rows + 1] = lens[1, n_req]
-                lens[3, n_req + 1 : n_rows + 1] = lens[3, n_req]
-            self.cu_query_seq_lengths_cudagraph_only[: n_rows + 1].copy_(self._h_len[1, : n_rows + 1], non_blocking=True)
-            self.cu_kv_seq_lengths_cudagraph_only[: n_rows + 1].copy_(self._h_len[3, : n_rows + 1], non_blocking=True)
+                lens[_LEN_CUQ, n_req + 1 : n_rows + 1] = lens[_LEN_CUQ, n_req]
+                lens[_LEN_CUKV, n_req + 1 : n_rows + 1] = lens[_LEN_CUKV, n_req]
             self.cu_query_seq_lengths = self.cu_query_seq_lengths_cudagraph_only[: n_rows + 1]
             self.cu_kv_seq_lengths = self.cu_kv_seq_lengths_cudagraph_only[: n_rows + 1]
             if graphs:
@@ -512,17 +530,18 @@ class DynamicInferenceContext(BaseInferenceContext):
             if padded > a:
                 t32[0, a:padded] = 0
                 t32[1, a:padded] = 0
-            self._d_tok32[:, :padded].copy_(self._h_tok32[:, :padded], non_blocking=True)
+            self._push_rows(self._d_tok32, self._h_tok32, 2, 0, padded)
             if self.prefill_q_block > 0:
                 self._build_prefill_units(ql, n_rows, padded, graphs)
-        self.query_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[0, :dev_rows], non_blocking=True)
-        self.kv_seq_lengths_cudagraph_only[:dev_rows].copy_(self._h_len[2, :dev_rows], non_blocking=True)
-        self.kv_seq_lengths = self.kv_seq_lengths_cudagraph_only[:n_rows]
         if decode:
             # One CTA per (row, KV head) runs for a time proportional to the row's context: starting the long rows
             # first keeps the SMs evenly loaded to the end of the kernel.  Padding rows (length 0) come last.
-            lens[4, :dev_rows] = np.argsort(-lens[2, :dev_rows], kind="stable")
-            self.attention_row_order[:dev_rows].copy_(self._h_len[4, :dev_rows], non_blocking=True)
+            lens[_LEN_ORDER, :dev_rows] = np.argsort(-lens[_LEN_KV, :dev_rows], kind="stable")
+            self._push_rows(self._d_len, self._h_len, 3, 0, dev_rows)           # query lens, kv lens, row order
+        else:
+            lens[_LEN_ORDER, : n_rows + 1] = np.arange(n_rows + 1)
+            self._push_rows(self._d_len, self._h_len, 5, 0, n_rows + 1)         # ... and the cumulative lengths
+        self.kv_seq_lengths = self.kv_seq_lengths_cudagraph_only[:n_rows]
 
         bt = self._h_bt_np
         bt[:n_req] = self.request_to_kv_chunk_ids.numpy()[p:t]
@@ -530,7 +549,7 @@ class DynamicInferenceContext(BaseInferenceContext):
             bt[n_req:n_rows] = 0
         self.request_to_kv_chunk_ids_cudagraph_only[:dev_rows].copy_(self._h_bt[:dev_rows], non_blocking=True)
         self.block_table = self.request_to_kv_chunk_ids_cudagraph_only[:n_rows]
-        self.h2d_bytes += dev_rows * (8 + 4 * self.max_kv_chunk_count) + (4 * dev_rows if decode else 8 * (n_rows + 1) + 8 * padded)
+        self.h2d_bytes += dev_rows * 4 * self.max_kv_chunk_count  # the block table; the rest is counted in _push_rows
         self._mark_copies()
 
     def reset(self) -> None:

@@ -109,19 +109,20 @@ class TextGenerationController:
         new_sample_dev = self.sample_from_logits(last_token_logits.contiguous(), sampling_params, vocab_size=vocab_size)
         new_sample = new_sample_dev.cpu()  # the step's one synchronising read
 
+        # finished mask on the host (the request-level state lives there): numpy views, no tensor ops
         p, t = context.paused_request_count, context.total_request_count
-        active_request_ids = context.request_ids[p:t].long().clone()
-        active_sequence_lengths = context.get_active_sequence_lengths() + 1
-        max_sequence_lengths = context.get_max_sequence_lengths()
-        active_request_mask = (new_sample != termination_id).byte() & torch.less(active_sequence_lengths, max_sequence_lengths).byte()
-        finished_idxs = torch.nonzero(active_request_mask == 0, as_tuple=True)[0] + p
-        finished_request_ids = context.request_ids[finished_idxs].clone()
+        ids_np = context.request_ids.numpy()[p:t]
+        seq_np = context.request_kv_length_offsets.numpy()[p:t] + context.request_query_lengths.numpy()[p:t] + 1
+        mask_np = ((new_sample.numpy() != termination_id) & (seq_np < context.request_output_lengths.numpy()[p:t])).astype(np.uint8)
+        active_request_ids = torch.from_numpy(ids_np.astype(np.int64))
+        finished_request_ids = torch.from_numpy(ids_np[mask_np == 0].copy())
+        active_request_mask = torch.from_numpy(mask_np)
 
         log_probs = None
         if sampling_params.return_log_probs:
             log_probs = context.calculate_log_probs(logits, new_sample_dev, only_last_token_logits=materialize_last)
 
-        newly_paused_request_ids = context.update_requests(active_request_mask, new_sample.clone())
+        newly_paused_request_ids = context.update_requests(active_request_mask, new_sample)
         return {
             "active_request_ids": active_request_ids,
             "newly_paused_request_ids": newly_paused_request_ids,

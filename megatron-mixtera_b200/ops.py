@@ -72,7 +72,7 @@ def _gemm_workspace(device, nbytes: int, count_reduction: bool = False) -> torch
     return _workspace.get(device, "gemm", nbytes)
 
 
-_NOT_A_LAUNCH = ("b200_device_status",)
+_NOT_A_LAUNCH = ("b200_device_status", "b200_copy_rows_h2d")
 
 
 def check(fn_name: str, code: int) -> None:
@@ -88,6 +88,16 @@ def device_status(reset: bool = False) -> int:
     out = ctypes.c_int(0)
     check("b200_device_status", _lib.load().b200_device_status(int(reset), ctypes.byref(out)))
     return out.value
+
+
+def copy_rows_h2d(dst: torch.Tensor, src: torch.Tensor, rows: int, lo: int, hi: int) -> None:
+    """dst[:rows, lo:hi] = src[:rows, lo:hi] for two 2-D tensors of the same dtype (src pinned host memory, dst on the
+    device, unit stride along the last dimension) as one asynchronous 2-D copy on the current stream."""
+    es = src.element_size()
+    assert dst.dtype == src.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and not src.is_cuda and dst.is_cuda
+    check("b200_copy_rows_h2d", _lib.load().b200_copy_rows_h2d(
+        dst.data_ptr() + lo * es, dst.stride(0) * es, src.data_ptr() + lo * es, src.stride(0) * es, (hi - lo) * es, rows,
+        _stream()))
 
 
 def gather_rows(table, ids, *, vocab_start: int = 0, vocab_end: Optional[int] = None, add_table=None, add_ids=None,
