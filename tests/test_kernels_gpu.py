@@ -50,6 +50,8 @@ def randn(shape, seed, scale=1.0):
         (64, 6144, 4096, False),   # Llama-3-8B QKV projection at decode
         (64, 4096, 14336, False),  # Llama-3-8B fc2 at decode (long K, deep split)
         (16, 20000, 512, False),   # many tiles: no split
+        (1, 130, 72, True),        # a single token; K tail inside the first 64-wide block; ragged N
+        (256, 128, 4096, False),   # the largest token block, one weight tile, deep split
     ],
 )
 def test_gemm_matches_fp32_matmul(ops, M, N, K, bias):
@@ -380,6 +382,8 @@ def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_orde
         (8, 4, 128, 256, [2304, 128, 700, 1216, 0, 0], 4),     # Llama-3-8B head geometry
         (4, 1, 64, 64, [33, 200, 64], 2),                       # MHA, head dim 64
         (2, 2, 64, 128, [129, 5], 1),
+        (1, 16, 128, 64, [70, 1, 640], 2),                      # the widest group the kernel takes (16 query heads)
+        (3, 3, 64, 64, [5, 0, 191, 64], 1),                     # odd group size, three KV heads
     ],
 )
 @pytest.mark.parametrize("fused", [True, False])
