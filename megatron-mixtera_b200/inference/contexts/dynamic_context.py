@@ -294,6 +294,9 @@ class DynamicInferenceContext(BaseInferenceContext):
         self._copy_event = torch.cuda.Event() if pin else None
         self._copies_pending = False
         self.h2d_bytes = 0  # bytes mirrored host -> device so far (benchmark accounting)
+        # The device copy of the block table is refreshed only when rows or the set of active requests changed.
+        self._bt_version = 0
+        self._bt_pushed = None
 
         # ---- guaranteed-request reserve (reference :384-401) ----
         gtd_chunk_count = min(int(buffer_guaranteed_fraction * chunk_count_total), chunk_count_total)
@@ -543,14 +546,17 @@ class DynamicInferenceContext(BaseInferenceContext):
             self._push_rows(self._d_len, self._h_len, 5, 0, n_rows + 1)         # ... and the cumulative lengths
         self.kv_seq_lengths = self.kv_seq_lengths_cudagraph_only[:n_rows]
 
-        bt = self._h_bt_np
-        bt[:n_req] = self.request_to_kv_chunk_ids.numpy()[p:t]
-        if n_rows > n_req:
-            bt[n_req:n_rows] = 0
-        self.request_to_kv_chunk_ids_cudagraph_only[:dev_rows].copy_(self._h_bt[:dev_rows], non_blocking=True)
+        state = (self._bt_version, p, t, n_rows)
+        if state != self._bt_pushed or num_warmup_tokens is not None:  # unchanged since the last step: already there
+            bt = self._h_bt_np
+            bt[:n_req] = self.request_to_kv_chunk_ids.numpy()[p:t]
+            if n_rows > n_req:
+                bt[n_req:n_rows] = 0
+            self.request_to_kv_chunk_ids_cudagraph_only[:dev_rows].copy_(self._h_bt[:dev_rows], non_blocking=True)
+            self.h2d_bytes += dev_rows * 4 * self.max_kv_chunk_count
+            self._bt_pushed = None if num_warmup_tokens is not None else state
+            self._mark_copies()
         self.block_table = self.request_to_kv_chunk_ids_cudagraph_only[:n_rows]
-        self.h2d_bytes += dev_rows * 4 * self.max_kv_chunk_count  # the block table; the rest is counted in _push_rows
-        self._mark_copies()
 
     def reset(self) -> None:
         """Drop every request and return all chunks (reference :827-869)."""
@@ -576,6 +582,7 @@ class DynamicInferenceContext(BaseInferenceContext):
         self._mark_copies()
         self.reset_attention_state()
         self.chunk_allocator.reset()
+        self._bt_version += 1
 
     def current_input_and_position_ids(self, *, num_warmup_tokens: Optional[int] = None) -> Tuple[Tensor, Tensor]:
         """Flattened ``[1, T]`` input and position ids of the padded step (device views)."""
@@ -601,6 +608,7 @@ class DynamicInferenceContext(BaseInferenceContext):
         """Admit a request: pop ``ceil(len / chunk)`` chunks, fill its row and its token entries
         (reference :920-1015).  Unlike the reference, the sequence-length check runs before chunks
         are popped, so a rejected request does not leak chunks."""
+        self._bt_version += 1
         if isinstance(tokens, Tensor):
             context_length = tokens.numel()
         else:
@@ -668,6 +676,8 @@ class DynamicInferenceContext(BaseInferenceContext):
             a[dst_idxs] = a[src_idxs]
         next_tokens[dst_idxs] = next_tokens[src_idxs]
 
+    FAST_DECODE_UPDATE = True  # shortcut for the steady state of decoding (tests switch it off to compare)
+
     def update_requests(self, active_requests_mask, new_tokens) -> Optional[Tensor]:
         """Advance the context after a step (reference :1033-1298).
 
@@ -684,8 +694,32 @@ class DynamicInferenceContext(BaseInferenceContext):
         finished_request_count = int((mask == 0).sum())
         assert active_request_count + finished_request_count + self.paused_request_count == self.total_request_count
         self.reset_attention_state()
-        chunk_ids = self.request_to_kv_chunk_ids.numpy()
         P = self.paused_request_count
+        if self.FAST_DECODE_UPDATE and finished_request_count == 0 and P == 0 and active_request_count > 0:
+            n = active_request_count
+            last_off = self.request_last_kv_chunk_offset.numpy()
+            if not (last_off[:n] == self.chunk_size_tokens - 1).any():
+                # Steady state of decoding - every request continues inside its current chunk: nothing moves, no
+                # chunk is popped or pushed, the block table stays as it is.  (The general path below computes
+                # exactly this in that case.)
+                self.active_token_count = n
+                offs = self.request_kv_length_offsets.numpy()
+                qlen = self.request_query_lengths.numpy()
+                offs[:n] += qlen[:n]
+                qlen[:n] = 1
+                last_off[:n] += 1
+                self._wait_copies()
+                tok = self._h_tok_np
+                tok[_TOK_INPUT, :n] = new_tokens
+                tok[_TOK_POS, :n] = offs[:n]
+                tok[_TOK_REQ, :n] = np.arange(n)
+                tok[_TOK_POS_IN_REQ, :n] = offs[:n]
+                tok[_TOK_CHUNK, :n] = self.request_last_kv_chunk_id.numpy()[:n]
+                tok[_TOK_LOCAL, :n] = last_off[:n]
+                self._push_token_rows(range(6), 0, n)
+                return None
+        self._bt_version += 1
+        chunk_ids = self.request_to_kv_chunk_ids.numpy()
 
         if active_request_count + P == 0:
             if finished_request_count > 0:

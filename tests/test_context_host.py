@@ -359,3 +359,33 @@ def test_gate_up_interleave_is_a_permutation_with_an_inverse():
     assert torch.equal(ops.deinterleave_gate_up(wi), w)
     # tile j: gate rows 64j..64j+63, then up rows 64j..64j+63
     assert torch.equal(wi[128:192], w[64:128]) and torch.equal(wi[192:256], w[192 + 64 : 192 + 128])
+
+
+def test_steady_state_shortcut_of_update_requests_equals_the_general_path():
+    # two contexts driven identically, one with the decode shortcut switched off: every host array stays equal
+    set_rounder(1)
+    a, b = make_ctx(chunk_size_tokens=16, max_sequence_length=96), make_ctx(chunk_size_tokens=16, max_sequence_length=96)
+    b.FAST_DECODE_UPDATE = False
+    rng = np.random.RandomState(7)
+    lens = [5, 17, 30, 9]
+    for c in (a, b):
+        for i, n in enumerate(lens):
+            c.add_request(i, torch.arange(n), 40)
+    for step in range(45):
+        n = a.total_request_count - a.paused_request_count
+        if n == 0:
+            break
+        toks = rng.randint(0, 100, size=n)
+        seq = a.get_active_sequence_lengths() + 1
+        mask = torch.less(seq, a.get_max_sequence_lengths()).byte()
+        if step == 20:
+            mask[0] = 0  # an early finish in the middle
+        for c in (a, b):
+            c.initialize_attention_state()
+            c.update_requests(mask.clone(), torch.from_numpy(toks.copy()))
+        for name in ("request_ids", "request_query_lengths", "request_kv_length_offsets", "request_kv_chunk_counts",
+                     "request_last_kv_chunk_id", "request_last_kv_chunk_offset", "request_to_kv_chunk_ids", "_h_tok"):
+            assert torch.equal(getattr(a, name), getattr(b, name)), (step, name)
+        assert (a.total_request_count, a.paused_request_count, a.active_token_count) == (
+            b.total_request_count, b.paused_request_count, b.active_token_count)
+        assert torch.equal(a.chunk_allocator.chunk_bag, b.chunk_allocator.chunk_bag)
