@@ -100,6 +100,8 @@ def cuda_mode(out_path):
     meta = json.loads(str(z["meta"]))
     meta["tp"] = world
     meta["fuse_tp"] = os.environ.get("TP_WORKER_NCCL_ALLREDUCE") != "1"  # default: all-reduce inside the norm kernel
+    if os.environ.get("TP_WORKER_FP8"):
+        meta["fp8"] = os.environ["TP_WORKER_FP8"]  # "mxfp8" | "blockwise": FP8 linears, sharded per rank
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
     out = {}
     state = {"step": 0}
