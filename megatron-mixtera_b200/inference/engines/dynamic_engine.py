@@ -151,16 +151,12 @@ class DynamicInferenceEngine:
 
     async def async_step(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False) -> Dict:
         prev_decode = self.context.is_decode_only()
-        if self._cuda:
-            self.step_start_event.record()
+        # The controller returns after reading the sampled tokens back, i.e. after the step's device work is done:
+        # the host clock around the call measures the step (the reference brackets it with CUDA events and then
+        # synchronises on the second one, dynamic_engine.py:560-575 - two more driver calls with the GPU idle).
         t0 = time.perf_counter()
         result = await self.controller.async_generate_output_tokens_dynamic_batch(sampling_params, self.termination_id)
-        if self._cuda:
-            self.step_end_event.record()
-            self.step_end_event.synchronize()
-            step_time = self.step_start_event.elapsed_time(self.step_end_event) / 1e3
-        else:
-            step_time = time.perf_counter() - t0
+        step_time = time.perf_counter() - t0
         cuda_graph_request_count = None
         active_requests: List[DynamicInferenceRequest] = []
         finished_requests: List[DynamicInferenceRequest] = []
