@@ -112,7 +112,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # the CUDA stack
 # ---------------------------------------------------------------------------------------------
-def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True, fuse_swiglu: bool = True, fuse_qkv: bool = False):
+def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bool = True, fuse_swiglu: bool = True, fuse_qkv: bool = False, overlap: bool = True):
     from megatron_mixtera_b200 import build, parallel_state
     from megatron_mixtera_b200.gpt.gpt_model import GPTModel
     from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext
@@ -147,7 +147,7 @@ def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bo
         model, InferenceWrapperConfig(hidden_size=w.hidden_size, params_dtype=torch.bfloat16,
                                       padded_vocab_size=w.vocab_size), ctx)
     ctl = TextGenerationController(wrapper, types.SimpleNamespace(vocab_size=w.vocab_size, detokenize=lambda t: ""))
-    engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=seed)
+    engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=seed, overlap_host_and_device=overlap)
     return model, ctx, wrapper, ctl, engine
 
 
@@ -336,7 +336,7 @@ def run_ours(args, w):
         torch.cuda.synchronize()
 
     model, ctx, wrapper, ctl, engine = build_stack(w, tp, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce,
-                                                     fuse_swiglu=not args.unfused_swiglu, fuse_qkv=args.fused_qkv)
+                                                     fuse_swiglu=not args.unfused_swiglu, fuse_qkv=args.fused_qkv, overlap=not args.no_overlap)
     prompts = synthetic_prompts(w.num_requests, *w.prompt_len_range, w.vocab_size, seed=0)
     for i, p in enumerate(prompts):
         engine.add_request(i, p, w.num_tokens_to_generate)
@@ -489,6 +489,8 @@ def main():
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
     ap.add_argument("--fused-qkv", action="store_true",
                     help="ablation: the attention kernel sums the QKV GEMM's split-K partial sums itself")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="ablation (e2e): do not enqueue the next decode forward before post-processing the step")
     ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")

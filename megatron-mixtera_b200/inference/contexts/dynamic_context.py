@@ -676,6 +676,11 @@ class DynamicInferenceContext(BaseInferenceContext):
             a[dst_idxs] = a[src_idxs]
         next_tokens[dst_idxs] = next_tokens[src_idxs]
 
+    @property
+    def state_version(self) -> int:
+        """Changes whenever requests are admitted, finish, are paused / resumed, get a new chunk, or on reset."""
+        return self._bt_version
+
     FAST_DECODE_UPDATE = True  # shortcut for the steady state of decoding (tests switch it off to compare)
 
     def update_requests(self, active_requests_mask, new_tokens) -> Optional[Tensor]:

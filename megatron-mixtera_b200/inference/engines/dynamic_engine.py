@@ -21,7 +21,7 @@ from ..text_generation_controllers.text_generation_controller import TextGenerat
 class DynamicInferenceEngine:
     def __init__(self, controller: TextGenerationController, context: DynamicInferenceContext, termination_id: int,
                  enable_cuda_graph: Optional[bool] = None, random_seed: Optional[int] = None, *,
-                 track_paused_request_events: bool = False):
+                 track_paused_request_events: bool = False, overlap_host_and_device: bool = False):
         assert isinstance(controller, TextGenerationController)
         assert isinstance(context, DynamicInferenceContext)
         assert isinstance(termination_id, int)
@@ -29,6 +29,9 @@ class DynamicInferenceEngine:
         self.controller, self.context = controller, context
         self.termination_id, self.random_seed = termination_id, random_seed
         self.track_paused_request_events = track_paused_request_events
+        # Not in the reference: in decode steps the controller enqueues the NEXT forward before it returns, so the
+        # GPU runs while this engine post-processes the step (same tokens; see the controller).
+        controller.enqueue_next_forward_early = bool(overlap_host_and_device)
         self.step_count = 0
         self.finished_request_count = 0
         self.waiting_request_ids = deque()

@@ -37,6 +37,10 @@ class TextGenerationController:
         self.sampling_rng = torch.Generator(device=dev)
         self.sampling_rng.manual_seed(cfg.inference_sampling_seed)
 
+    # Off by default (the reference's step is strictly forward -> sample -> update); the engine may switch it on.
+    enqueue_next_forward_early = False
+    _early_forward = None
+
     # --------------------------------------------------------------------------------------------
     def tokenize_prompt(self, prompt: str, add_BOS: bool = False):
         tokens = self.tokenizer.tokenize(prompt)
@@ -94,14 +98,18 @@ class TextGenerationController:
         if sampling_params.return_log_probs:
             skip = getattr(sampling_params, "skip_prompt_log_probs_for_dynamic_inference", False)
             assert skip or materialize_last is False, "Materialize only last token logits must be false for returning log probs"
+        early, self._early_forward = getattr(self, "_early_forward", None), None
         if context.active_token_count == 0:
             return None
 
-        context.initialize_attention_state()
+        if early is not None and early[0] == context.state_version and context.is_decode_only():
+            logits = early[1]  # this step's forward was enqueued at the end of the previous call (see below)
+        else:
+            context.initialize_attention_state()
+            input_ids, position_ids = context.current_input_and_position_ids()
+            logits = self.inference_wrapped_model.run_one_forward_step(
+                {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None})
         cuda_graph_request_count = context.padded_active_request_count if context.is_decode_only() else None
-        input_ids, position_ids = context.current_input_and_position_ids()
-        logits = self.inference_wrapped_model.run_one_forward_step(
-            {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None})
         await asyncio.sleep(0)  # the forward is enqueued; let other coroutines run
 
         last_token_logits = logits.squeeze(0) if materialize_last else context.last_token_logits(logits)
@@ -123,6 +131,17 @@ class TextGenerationController:
             log_probs = context.calculate_log_probs(logits, new_sample_dev, only_last_token_logits=materialize_last)
 
         newly_paused_request_ids = context.update_requests(active_request_mask, new_sample)
+        if (self.enqueue_next_forward_early and not sampling_params.return_log_probs and materialize_last
+                and context.active_token_count > 0 and context.is_decode_only()):
+            # The next decode step depends on nothing the caller still has to do with this step's result (request
+            # records, detokenisation, scheduling): enqueue its forward now, so that the GPU works while the host
+            # does that.  If the set of requests changes before the next call (add_request / reset bump the
+            # context's state version), the early forward is simply not used: it wrote the same keys / values the
+            # repeated step writes again.
+            context.initialize_attention_state()
+            input_ids, position_ids = context.current_input_and_position_ids()
+            self._early_forward = (context.state_version, self.inference_wrapped_model.run_one_forward_step(
+                {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None}))
         return {
             "active_request_ids": active_request_ids,
             "newly_paused_request_ids": newly_paused_request_ids,

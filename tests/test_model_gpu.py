@@ -282,8 +282,13 @@ def test_llama_tiny_fp8_kv_pool_matches_oracle():
     assert_flips_are_near_ties(state["flips"], n_dec, resolution=2.0**-4)
 
 
-def test_engine_generate_free_running():
-    # the public API end to end, no teacher forcing: engine.generate on the tiny Llama
+_FREE_RUNS = {}
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_engine_generate_free_running(overlap):
+    # the public API end to end, no teacher forcing: engine.generate on the tiny Llama; with `overlap` the next
+    # decode forward is enqueued before the engine post-processes a step (same tokens either way)
     from megatron_mixtera_b200.inference.engines.dynamic_engine import DynamicInferenceEngine
     from megatron_mixtera_b200.inference.sampling_params import SamplingParams
 
@@ -291,7 +296,7 @@ def test_engine_generate_free_running():
     meta = json.loads(str(z["meta"]))
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
     ctl = Controller(wrapper, types.SimpleNamespace(vocab_size=meta["vocab_size"], detokenize=lambda t: " ".join(map(str, t))))
-    engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=0)
+    engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=0, overlap_host_and_device=overlap)
     n = len(meta["prompt_lengths"])
     prompts = [torch.from_numpy(z[f"prompt_{i}"]).cuda() for i in range(n)]
     done = engine.generate(prompts, SamplingParams(top_k=1, num_tokens_to_generate=meta["num_tokens_to_generate"]))
@@ -306,3 +311,7 @@ def test_engine_generate_free_running():
     # free-running sequences agree with the reference until a near-tie flips; most tokens must agree
     assert agree / total > 0.7, (agree, total)
     assert ctx.chunk_allocator.chunk_count_avail == ctx.chunk_allocator.chunk_count_total - 1
+    tokens = {req.request_id: list(req.generated_tokens) for req in done}
+    for other in _FREE_RUNS.values():  # the early enqueue of the next forward changes no token
+        assert tokens == other
+    _FREE_RUNS[overlap] = tokens
