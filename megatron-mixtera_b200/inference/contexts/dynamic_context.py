@@ -695,8 +695,9 @@ class DynamicInferenceContext(BaseInferenceContext):
         """
         mask = _to_host(active_requests_mask).astype(np.int64)
         new_tokens = _to_host(new_tokens).astype(np.int64)
-        active_request_count = int((mask == 1).sum())
-        finished_request_count = int((mask == 0).sum())
+        active_request_count = int(np.count_nonzero(mask == 1))
+        finished_request_count = mask.size - active_request_count
+        assert finished_request_count == int(np.count_nonzero(mask == 0)), "the mask holds 0 / 1 only"
         assert active_request_count + finished_request_count + self.paused_request_count == self.total_request_count
         self.reset_attention_state()
         P = self.paused_request_count

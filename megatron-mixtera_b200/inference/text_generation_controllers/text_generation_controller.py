@@ -124,13 +124,12 @@ class TextGenerationController:
         mask_np = ((new_sample.numpy() != termination_id) & (seq_np < context.request_output_lengths.numpy()[p:t])).astype(np.uint8)
         active_request_ids = torch.from_numpy(ids_np.astype(np.int64))
         finished_request_ids = torch.from_numpy(ids_np[mask_np == 0].copy())
-        active_request_mask = torch.from_numpy(mask_np)
 
         log_probs = None
         if sampling_params.return_log_probs:
             log_probs = context.calculate_log_probs(logits, new_sample_dev, only_last_token_logits=materialize_last)
 
-        newly_paused_request_ids = context.update_requests(active_request_mask, new_sample)
+        newly_paused_request_ids = context.update_requests(mask_np, new_sample.numpy())
         if (self.enqueue_next_forward_early and not sampling_params.return_log_probs and materialize_last
                 and context.active_token_count > 0 and context.is_decode_only()):
             # The next decode step depends on nothing the caller still has to do with this step's result (request
