@@ -103,6 +103,8 @@ def cuda_mode(out_path):
     if os.environ.get("TP_WORKER_FP8"):
         meta["fp8"] = os.environ["TP_WORKER_FP8"]  # "mxfp8" | "blockwise": FP8 linears, sharded per rank
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
+    # tokens fed back every step: the reference's bf16 trace, or a trace made by the caller (e.g. the FP8 oracle's)
+    forced = np.load(os.environ["TP_WORKER_TRACE"]) if os.environ.get("TP_WORKER_TRACE") else z
     out = {}
     state = {"step": 0}
 
@@ -111,7 +113,7 @@ def cuda_mode(out_path):
             own = super().sample_from_logits(last_token_logits, sampling_params, vocab_size, **kw)
             out[f"s{state['step']}_logits"] = last_token_logits.float().cpu().numpy()
             out[f"s{state['step']}_own"] = own.cpu().numpy()
-            return torch.from_numpy(z[f"s{state['step']}_sample"]).to(last_token_logits.device)
+            return torch.from_numpy(forced[f"s{state['step']}_sample"]).to(last_token_logits.device)
 
     ctl = Forced(wrapper, types.SimpleNamespace(vocab_size=meta["vocab_size"]))
     sp = SamplingParams(top_k=1, num_tokens_to_generate=meta["num_tokens_to_generate"])
