@@ -417,13 +417,18 @@ class GPTOracle:
     """Forward of the local-spec GPT over a ContextOracle (gpt_model.py:279-560, transformer_layer.py:433-660)."""
 
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype,
-                 fp8: Optional[str] = None, kv_fp8_scale: Optional[float] = None):
+                 fp8: Optional[str] = None, kv_fp8_scale: Optional[float] = None, tp: int = 1):
         """``fp8="mxfp8"`` / ``"blockwise"``: every decoder linear multiplies FP8-quantised inputs by FP8-quantised
         weights with fp32 accumulation (the TE recipes of those names under ``fp8_autocast``,
         transformer_block.py:629-643; E8M0 scale per 32 elements, resp. fp32 scale per 128 x 128 / 1 x 128 block);
         embedding, norms, attention and the output layer stay in ``dtype``."""
         self.s, self.w, self.ctx, self.dtype = spec, weights, ctx, dtype
         self.fp8 = fp8
+        # tp > 1 restates the arithmetic of the reference's tensor-parallel run: a row-parallel linear (out-proj,
+        # fc2; layers.py:1225-1281) multiplies its K shard on every rank, each partial product is rounded to the
+        # parameter dtype, and the all-reduce adds the rounded partials (mappings.py:22-33).  Column-parallel
+        # linears and attention heads are exact under sharding, so nothing else changes.
+        self.tp = tp
         self._wdq: Dict[str, torch.Tensor] = {}
         # E4M3 KV pool (extension): every head uses the same scale here; values are kept dequantised in the
         # caches (byte * scale is exact in fp32), so the attention restatement itself is unchanged
@@ -443,6 +448,18 @@ class GPTOracle:
         return F.layer_norm(x, (s.hidden_size,), self.w[prefix + ".weight"], self.w[prefix + ".bias"], s.eps)
 
     def _linear(self, x, prefix, add_bias=True):
+        if self.tp > 1 and prefix.endswith(("linear_proj", "linear_fc2")):
+            K = x.shape[-1]
+            assert K % self.tp == 0
+            ks = K // self.tp
+            w_full = self.w[prefix + ".weight"]
+            y = None
+            for r in range(self.tp):
+                part = self._matmul_shard(x[..., r * ks : (r + 1) * ks], w_full[:, r * ks : (r + 1) * ks], f"{prefix}@{r}")
+                y = part.float() if y is None else y + part.float()
+            y = y.to(x.dtype)
+            b = self.w.get(prefix + ".bias")
+            return y + b if (add_bias and b is not None) else y
         if self.fp8 == "mxfp8":
             if prefix not in self._wdq:
                 self._wdq[prefix] = dequantize_mxfp8(*quantize_mxfp8(self.w[prefix + ".weight"]))
@@ -457,6 +474,18 @@ class GPTOracle:
         if add_bias and b is not None:
             y = y + b
         return y
+
+    def _matmul_shard(self, x, w, key):
+        """x @ w.T for one K shard, rounded to x.dtype (FP8 recipes quantise the shard like a whole operand)."""
+        if self.fp8 == "mxfp8":
+            if key not in self._wdq:
+                self._wdq[key] = dequantize_mxfp8(*quantize_mxfp8(w.contiguous()))
+            return torch.matmul(dequantize_mxfp8(*quantize_mxfp8(x.contiguous())), self._wdq[key].t()).to(x.dtype)
+        if self.fp8 == "blockwise":
+            if key not in self._wdq:
+                self._wdq[key] = dequantize_fp8_block_weight(*quantize_fp8_block_weight(w.contiguous()))
+            return torch.matmul(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x.contiguous())), self._wdq[key].t()).to(x.dtype)
+        return torch.matmul(x, w.t())
 
     def forward(self) -> torch.Tensor:
         """Returns last-token logits [active requests, vocab] in the parameter dtype."""

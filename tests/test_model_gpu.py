@@ -222,10 +222,10 @@ def test_c0_tiny_gpt_matches_bf16_oracle():
     assert len(fp32_rel) >= 4 and max(fp32_rel) < 2e-2, fp32_rel
 
 
-def oracle_trace(meta, dtype, fp8=None, kv_fp8_scale=None):
+def oracle_trace(meta, dtype, fp8=None, kv_fp8_scale=None, tp=1):
     """Run the CPU oracle on the fixture's prompts and record what the teacher-forced harness needs."""
     z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
-    model, _ = build_oracle_model(meta, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale)
+    model, _ = build_oracle_model(meta, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale, tp=tp)
     n = len(meta["prompt_lengths"])
     trace = {f"prompt_{i}": z[f"prompt_{i}"] for i in range(n)}
 

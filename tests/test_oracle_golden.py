@@ -155,7 +155,7 @@ def test_context_oracle_reference_update_requests_golden():
         [481, -1, -1, -1], [488, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1], [-1, -1, -1, -1]]
 
 
-def build_oracle_model(meta, dtype, fp8=None, kv_fp8_scale=None):
+def build_oracle_model(meta, dtype, fp8=None, kv_fp8_scale=None, tp=1):
     from megatron_mixtera_b200.synthetic import canonical_tensor
 
     spec = O.ModelSpec(
@@ -172,7 +172,7 @@ def build_oracle_model(meta, dtype, fp8=None, kv_fp8_scale=None):
         buffer_size_gb=meta["buffer_size_gb"], buffer_guaranteed_fraction=0.1, chunk_size_tokens=meta["chunk_size_tokens"],
         max_requests_override=meta["max_requests"], max_tokens_override=meta["max_tokens"],
         token_rounder=meta["rounder"], request_rounder=meta["rounder"])
-    return O.GPTOracle(spec, w, ctx, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale), w
+    return O.GPTOracle(spec, w, ctx, dtype, fp8=fp8, kv_fp8_scale=kv_fp8_scale, tp=tp), w
 
 
 def oracle_weight_shapes(s):
