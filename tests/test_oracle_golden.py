@@ -245,3 +245,23 @@ def test_quantisers_roundtrip():
     assert float((O.dequantize_fp8_block_weight(qw, s) - x).norm() / x.norm()) < 0.04
     qa, sa = O.quantize_fp8_rowblock(x, 128)
     assert float((O.dequantize_fp8_rowblock(qa, sa) - x).norm() / x.norm()) < 0.04
+
+
+def test_oracle_tensor_parallel_arithmetic_is_a_small_perturbation():
+    # tp=2 rounds the two partial products of every row-parallel linear to bf16 before adding them - the reference's
+    # own TP arithmetic.  In fp32 that is exact up to summation order; in bf16 it moves the logits by < 1e-2.
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = json.loads(str(z["meta"]))
+    for dtype, bound in ((torch.float32, 1e-5), (torch.bfloat16, 1.2e-2)):
+        logits = {}
+        for tp in (1, 2):
+            model, _ = build_oracle_model(meta, dtype, tp=tp)
+            c = model.ctx
+            for i in range(2):
+                c.add_request(i, z[f"prompt_{i}"], 4)
+            c.initialize_attention_state()
+            with torch.inference_mode():
+                logits[tp] = model.forward().float()
+        rel = float((logits[1] - logits[2]).norm() / logits[1].norm())
+        assert rel < bound, (dtype, rel)
+        assert dtype == torch.float32 or rel > 0  # bf16: the partial roundings are really there
