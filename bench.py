@@ -135,14 +135,18 @@ def build_stack(w, tp: int, seed: int = 0, fuse_splitk: bool = True, fuse_tp: bo
                      position_embedding_type="rope", rotary_base=w.rotary_base)
     model.init_synthetic_weights(seed=seed)  # N(0, 0.02), generated on the device
     chunks_per_req = -(-w.max_sequence_length // w.chunk_size_tokens)
-    chunk_bytes = 2 * 2 * w.num_layers * w.chunk_size_tokens * (w.num_query_groups // tp) * w.kv_channels
+    kv_elem = 1 if w.kv_fp8 else 2
+    chunk_bytes = 2 * kv_elem * w.num_layers * w.chunk_size_tokens * (w.num_query_groups // tp) * w.kv_channels
     n_chunks = int(w.num_requests * chunks_per_req * 1.15) + chunks_per_req + 2
     ctx = DynamicInferenceContext(
         params_dtype=torch.bfloat16, num_layers=w.num_layers, kv_channels=w.kv_channels,
         num_attention_heads=w.num_query_groups, max_sequence_length=w.max_sequence_length,
         buffer_size_gb=n_chunks * chunk_bytes / 1024**3, buffer_guaranteed_fraction=0.05,
         chunk_size_tokens=w.chunk_size_tokens, max_requests_override=w.num_requests,
-        max_tokens_override=w.num_requests * w.prompt_len_range[1], tensor_model_parallel_size=tp)
+        max_tokens_override=w.num_requests * w.prompt_len_range[1], tensor_model_parallel_size=tp,
+        kv_cache_dtype=torch.float8_e4m3fn if w.kv_fp8 else None, kv_fp8_single_term=w.kv_fp8 == "one_term")
+    if w.kv_fp8:
+        ctx.kv_scales.fill_(2.0**-6)  # keys / values of the synthetic model stay below 448 * 2^-6 = 7
     wrapper = GPTInferenceWrapper(
         model, InferenceWrapperConfig(hidden_size=w.hidden_size, params_dtype=torch.bfloat16,
                                       padded_vocab_size=w.vocab_size), ctx)
@@ -217,7 +221,8 @@ def kernel_rooflines(model, ctx, T, peak_gbs):
     attn = layers[0].self_attention.core_attention
     qkv = torch.randn(T, (attn.num_q_heads + 2 * attn.num_kv_heads) * attn.head_dim, device=dev, dtype=torch.bfloat16)
     kv_lens = ctx.kv_seq_lengths_cudagraph_only[:T].cpu()
-    kv_bytes = float(kv_lens.sum()) * 2 * attn.num_kv_heads * attn.head_dim * 2 + 2.0 * T * qkv.shape[1] * 2
+    kv_elem = 1 if getattr(ctx, "kv_cache_fp8", False) else 2
+    kv_bytes = float(kv_lens.sum()) * 2 * attn.num_kv_heads * attn.head_dim * kv_elem + 2.0 * T * qkv.shape[1] * 2
     sec = sweep(lambda: [l.self_attention.core_attention(qkv, ctx, model.rotary_pos_cos, model.rotary_pos_sin) for l in layers])
     out["paged_attention"] = {"us": sec * 1e6, "GB/s": kv_bytes / sec / 1e9, "frac": kv_bytes / sec / 1e9 / peak_gbs,
                               "kv_tokens": int(kv_lens.sum())}
@@ -452,7 +457,7 @@ def step_bytes(w, ctx, B, tp):
     per_layer = ((w.num_attention_heads + 2 * w.num_query_groups) * d * H + w.num_attention_heads * d * H + 3 * F * H) // tp
     bytes_per_weight = (1.0 + 1.0 / 32.0) if w.fp8 else 2.0
     weights = bytes_per_weight * w.num_layers * per_layer + 2.0 * (w.vocab_size * H // tp)
-    kv = float(ctx.kv_seq_lengths_cudagraph_only[:B].sum()) * 2 * (w.num_query_groups // tp) * d * 2 * w.num_layers
+    kv = float(ctx.kv_seq_lengths_cudagraph_only[:B].sum()) * 2 * (w.num_query_groups // tp) * d * (1 if w.kv_fp8 else 2) * w.num_layers
     return weights + kv
 
 
@@ -483,7 +488,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "smoke", "smoke_mxfp8"])
+    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "llama3_8b_mxfp8_fp8kv", "smoke", "smoke_mxfp8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
@@ -499,7 +504,7 @@ def main():
     from megatron_mixtera_b200 import configs
 
     w = {"llama3_8b": configs.LLAMA3_8B_BF16_64REQ, "llama3_8b_mxfp8": configs.LLAMA3_8B_MXFP8_128REQ,
-         "smoke": configs.LLAMA3_8B_SHAPE_2LAYER, "smoke_mxfp8": configs.LLAMA3_8B_MXFP8_SHAPE_2LAYER}[args.workload]
+         "llama3_8b_mxfp8_fp8kv": configs.LLAMA3_8B_MXFP8_FP8KV_128REQ, "smoke": configs.LLAMA3_8B_SHAPE_2LAYER, "smoke_mxfp8": configs.LLAMA3_8B_MXFP8_SHAPE_2LAYER}[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
     else:

@@ -22,6 +22,7 @@ class Workload:
     rotary_base: float = 500000.0
     log_uniform_lengths: bool = False
     fp8: str = None  # None (bf16 linears) or "mxfp8"
+    kv_fp8: str = None  # None (bf16 KV pool), "two_term" or "one_term": E4M3 KV pool and the arithmetic of its kernel
 
     @property
     def max_sequence_length(self) -> int:
@@ -54,3 +55,11 @@ LLAMA3_8B_MXFP8_SHAPE_2LAYER = Workload(
     name="llama3-8b-shape MXFP8 cut to 2 layers, 128 requests, prompt U[256,4096]", num_layers=2, hidden_size=4096,
     num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256,
     num_requests=128, prompt_len_range=(256, 4096), num_tokens_to_generate=24, fp8="mxfp8")
+
+# MXFP8 linears and an E4M3 KV pool (per-head scales; one-term attention arithmetic), 128 requests: the single-GPU form of
+# the "FP8 weights + FP8 KV" configuration.
+LLAMA3_8B_MXFP8_FP8KV_128REQ = Workload(
+    name="llama3-8b-shape MXFP8 linears + E4M3 KV (one-term attention) decode, 128 requests, prompt U[256,4096], 256 greedy tokens, KV chunk 256",
+    num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
+    ffn_hidden_size=14336, vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096),
+    num_tokens_to_generate=256, fp8="mxfp8", kv_fp8="one_term")
