@@ -488,7 +488,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "llama3_8b_mxfp8_fp8kv", "smoke", "smoke_mxfp8"])
+    ap.add_argument("--workload", default="llama3_8b", choices=["llama3_8b", "llama3_8b_mxfp8", "llama3_8b_mxfp8_fp8kv", "smoke", "smoke_mxfp8", "smoke_mxfp8_fp8kv"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-load kernel")
@@ -504,7 +504,8 @@ def main():
     from megatron_mixtera_b200 import configs
 
     w = {"llama3_8b": configs.LLAMA3_8B_BF16_64REQ, "llama3_8b_mxfp8": configs.LLAMA3_8B_MXFP8_128REQ,
-         "llama3_8b_mxfp8_fp8kv": configs.LLAMA3_8B_MXFP8_FP8KV_128REQ, "smoke": configs.LLAMA3_8B_SHAPE_2LAYER, "smoke_mxfp8": configs.LLAMA3_8B_MXFP8_SHAPE_2LAYER}[args.workload]
+         "llama3_8b_mxfp8_fp8kv": configs.LLAMA3_8B_MXFP8_FP8KV_128REQ, "smoke": configs.LLAMA3_8B_SHAPE_2LAYER, "smoke_mxfp8": configs.LLAMA3_8B_MXFP8_SHAPE_2LAYER,
+         "smoke_mxfp8_fp8kv": configs.LLAMA3_8B_MXFP8_FP8KV_SHAPE_2LAYER}[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
     else:

@@ -63,3 +63,10 @@ LLAMA3_8B_MXFP8_FP8KV_128REQ = Workload(
     num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
     ffn_hidden_size=14336, vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096),
     num_tokens_to_generate=256, fp8="mxfp8", kv_fp8="one_term")
+
+# Two-layer cut of it for profiler captures.
+LLAMA3_8B_MXFP8_FP8KV_SHAPE_2LAYER = Workload(
+    name="llama3-8b-shape MXFP8 + E4M3 KV (one-term attention) cut to 2 layers, 128 requests, prompt U[256,4096]",
+    num_layers=2, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336,
+    vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096), num_tokens_to_generate=24, fp8="mxfp8",
+    kv_fp8="one_term")
