@@ -9,9 +9,10 @@
 //               (v_position below) to the order in which the S accumulators of a thread hold the tokens:
 //               the P fragment is then built from the thread's own registers, without shuffles.
 // One CTA = (row, KV head, context split) as in the 16-bit kernel; a tile is 128 tokens (K 16 KB + V^T 16 KB),
-// every consumer warp takes 32 of them.  The kernel is bound by the mma.sync issue rate, not by HBM: with two terms
-// it reads E4M3 bytes at ~4 TB/s (1.16x the tokens per second of the 16-bit kernel), with one term at ~6.5 TB/s
-// (1.8x).
+// every consumer warp takes 32 of them.  Neither HBM nor the tensor pipe is saturated (profiler: 61 % / 29 % with one
+// term): the per-tile chain ldmatrix -> mma -> softmax -> pack -> ldmatrix -> mma of the eight consumer warps an SM holds
+// is latency bound.  With two terms the kernel reads E4M3 bytes at ~4 TB/s (1.16x the tokens per second of the 16-bit
+// kernel), with one term at ~6.5 TB/s (1.8x).  (Two stages and three CTAs per SM were tried: registers spill, no gain.)
 #include <cuda_fp8.h>
 
 #include "common.cuh"
