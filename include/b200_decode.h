@@ -102,7 +102,7 @@ int b200_gemm_bf16_swiglu(const void* x, int64_t ldx, const void* w, void* y, in
  * (megatron/core/tensor_parallel/layers.py:317-336, 946-1043, 1225-1281; torch.matmul(x, W.t())).
  * The all-reduce of the row-parallel variant stays with the caller.
  * `workspace`: split-K partial sums (fp32), see b200_gemm_bf16_workspace_bytes; its contents need no
- * initialisation (the first 64 KiB are reserved).  When K is split a second kernel on the same stream sums the
+ * initialisation and it must be 16-byte aligned (0 bytes are needed when K is not split).  When K is split a second kernel on the same stream sums the
  * partials in a fixed order, so results are deterministic.
  */
 size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K);
@@ -115,7 +115,7 @@ int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, 
  * Who needs it: code that runs where cudaMalloc is not an option - a latency-critical serving loop that must
  * not take the allocator's locks or its implicit synchronisation, a server that has given the whole device to
  * its own memory pool, or a plugin that is handed nothing but input and output pointers.  The split-K scratch that b200_gemm_bf16 takes as `workspace` is here a fixed array inside
- * the library (b200_gemm_bf16_static_scratch_limit() bytes: 64 KiB reserved + 16 MiB of partial sums,
+ * the library (b200_gemm_bf16_static_scratch_limit() bytes: 16 MiB of partial sums,
  * resident on every GPU that loads the library until the process exits).  The call performs no device or host
  * allocation; the caller still owns x, w, bias and y.
  *

@@ -100,13 +100,19 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int h = (unit / p.num_splits) % p.nkv;
   const int t_slot = unit / (p.num_splits * p.nkv);
   const int t = p.row_order ? p.row_order[t_slot] : t_slot;
-  if (static_cast<unsigned>(t) >= static_cast<unsigned>(p.T)) return;  // not a permutation: skip, never index with it
+  // Every CTA waits for the preceding grid before it exits, also on the early exits below: programmatic
+  // launch ordering is only transitive (this grid's successors may assume that its predecessors are done)
+  // if no grid can complete before the one in front of it.
+  if (static_cast<unsigned>(t) >= static_cast<unsigned>(p.T)) {  // not a permutation: skip, never index with it
+    pdl_wait();
+    return;
+  }
   const int G = p.G;
   const int kv_len = p.kv_len[t];
 
   if (kv_len <= 0) {  // padding row: flash-attn returns zeros for it
+    pdl_wait();
     if (p.num_splits == 1) {
-      pdl_wait();
       __nv_bfloat16* o = p.out + (static_cast<int64_t>(t) * p.nq + h * G) * D;
       for (int i = tid; i < G * D; i += kThreads) o[i] = __float2bfloat16_rn(0.f);
     }
@@ -114,7 +120,10 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
   const int L = split_length(kv_len, p.num_splits, p.min_split);
   const int start = split * L;
-  if (start >= kv_len) return;
+  if (start >= kv_len) {
+    pdl_wait();
+    return;
+  }
   const int end = min(kv_len, start + L);
   const int n_tiles = (end - start + kTile - 1) / kTile;
   const int row = p.row_of_token ? p.row_of_token[t] : t;
@@ -465,7 +474,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   const int n_tok = unit[2];
   const int G = p.G;
   const int qb = 64 / G;  // tokens per unit
-  if (n_tok <= 0 || n_tok > qb || t0 < 0 || t0 + n_tok > p.T) return;  // padding entry (or a malformed one)
+  if (n_tok <= 0 || n_tok > qb || t0 < 0 || t0 + n_tok > p.T) {  // padding entry (or a malformed one)
+    pdl_wait();
+    return;
+  }
   int max_kv = 0;
   for (int j = 0; j < n_tok; ++j) max_kv = max(max_kv, p.kv_len[t0 + j]);
   const int n_tiles = (max_kv + kTile - 1) / kTile;
@@ -813,13 +825,8 @@ static int launch_attention(const b200_attention_args* a, Params& p, cudaStream_
   const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, dt);
   if (!mk || !mv) return B200_ERR_DRIVER;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::kSmemBytes) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  if (ensure_dynamic_smem(paged_attention_kernel<D>, C::kSmemBytes, smem_attr_done) != B200_OK) return B200_ERR_LAUNCH;
   const int64_t units = static_cast<int64_t>(p.T) * p.nkv * p.num_splits;
   if (units > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
   int rc = launch_pdl(paged_attention_kernel<D>, dim3(static_cast<unsigned>(units)), dim3(kThreads), C::kSmemBytes,
@@ -841,13 +848,8 @@ static int launch_prefill(Params& p, const int32_t* units, int num_units, cudaSt
   const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   if (!mk || !mv) return B200_ERR_DRIVER;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
-        cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  if (ensure_dynamic_smem(paged_prefill_kernel<D>, C::kSmemBytes, smem_attr_done) != B200_OK) return B200_ERR_LAUNCH;
   const int64_t ctas = static_cast<int64_t>(num_units) * p.nkv;
   if (ctas > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
   return launch_pdl(paged_prefill_kernel<D>, dim3(static_cast<unsigned>(ctas)), dim3(kThreads), C::kSmemBytes, stream, *mk,

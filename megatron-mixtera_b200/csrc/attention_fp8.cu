@@ -100,12 +100,16 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int h = (unit / p.num_splits) % p.nkv;
   const int t_slot = unit / (p.num_splits * p.nkv);
   const int t = p.row_order ? p.row_order[t_slot] : t_slot;
-  if (static_cast<unsigned>(t) >= static_cast<unsigned>(p.T)) return;
+  // (every CTA waits for the preceding grid before it exits, early exits included: see attention.cu)
+  if (static_cast<unsigned>(t) >= static_cast<unsigned>(p.T)) {
+    pdl_wait();
+    return;
+  }
   const int G = p.G;
   const int kv_len = p.kv_len[t];
   if (kv_len <= 0) {  // padding row: zeros
+    pdl_wait();
     if (p.num_splits == 1) {
-      pdl_wait();
       __nv_bfloat16* o = p.out + (static_cast<int64_t>(t) * p.nq + h * G) * D;
       for (int i = tid; i < G * D; i += kThreads) o[i] = __float2bfloat16_rn(0.f);
     }
@@ -113,7 +117,10 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   }
   const int L = split_length(kv_len, p.num_splits, p.min_split);
   const int start = split * L;
-  if (start >= kv_len) return;
+  if (start >= kv_len) {
+    pdl_wait();
+    return;
+  }
   const int end = min(kv_len, start + L);
   const int n_tiles = (end - start + kTile - 1) / kTile;
   const int row = p.row_of_token ? p.row_of_token[t] : t;
@@ -513,15 +520,10 @@ static int launch_attention_fp8(Params& p, bool two_terms, cudaStream_t stream) 
   const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, vdims, vstr, vbox, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_DATA_TYPE_UINT8);
   if (!mk || !mv) return B200_ERR_DRIVER;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_attention_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(paged_attention_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-            cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done2{0}, smem_attr_done1{0};
+  if (ensure_dynamic_smem(paged_attention_fp8_kernel<true>, kSmemBytes, smem_attr_done2) != B200_OK ||
+      ensure_dynamic_smem(paged_attention_fp8_kernel<false>, kSmemBytes, smem_attr_done1) != B200_OK)
+    return B200_ERR_LAUNCH;
   const int64_t units = static_cast<int64_t>(p.T) * p.nkv * p.num_splits;
   if (units > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
   int rc = two_terms ? launch_pdl(paged_attention_fp8_kernel<true>, dim3(static_cast<unsigned>(units)), dim3(kThreads),

@@ -1,5 +1,6 @@
 // Host-side plumbing shared by the kernels: error strings, the device status word,
 // tensor-map (TMA descriptor) encoding with a small cache, device properties.
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -46,6 +47,8 @@ struct MapKeyHash {
 
 std::mutex g_map_mutex;
 std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
+constexpr size_t kMaxCachedMaps = 16384;  // 2 MiB of descriptors at most
+constexpr unsigned kScratchMaps = 8;
 
 }  // namespace
 
@@ -88,7 +91,16 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
   std::lock_guard<std::mutex> lock(g_map_mutex);
   auto it = g_maps.find(key);
   if (it != g_maps.end()) return it->second;
-  // The descriptor is a 128-byte host object passed to kernels by value; it is kept for the process lifetime.
+  if (g_maps.size() >= kMaxCachedMaps) {
+    // The cache is keyed by base address, and eager steps hand in fresh activation addresses all the time: once it
+    // is full, further descriptors are encoded into a small per-thread ring instead of being kept (a launch copies
+    // the descriptor into its kernel parameters, and no launch uses more than kScratchMaps of them).
+    alignas(64) static thread_local CUtensorMap scratch[kScratchMaps];
+    static thread_local unsigned next = 0;
+    CUtensorMap* m = &scratch[next++ % kScratchMaps];
+    return encode_tensor_map(m, base, rank, dims, strides_bytes, box, swizzle, l2, dtype) ? m : nullptr;
+  }
+  // The descriptor is a 128-byte host object passed to kernels by value; cached ones are kept for the process lifetime.
   CUtensorMap* m = static_cast<CUtensorMap*>(aligned_alloc(64, sizeof(CUtensorMap)));
   if (!m) return nullptr;
   if (!encode_tensor_map(m, base, rank, dims, strides_bytes, box, swizzle, l2, dtype)) {
@@ -100,16 +112,16 @@ const CUtensorMap* get_tensor_map(const void* base, int rank, const uint64_t* di
 }
 
 int sm_count() {
-  static int cached[16] = {0};
+  static std::atomic<int> cached[64];
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 16) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+  const bool slot = dev >= 0 && dev < 64;
+  int n = slot ? cached[dev].load(std::memory_order_relaxed) : 0;
+  if (n == 0) {
+    if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (slot) cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 }  // namespace b200

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/b200_decode.h"
 
 namespace b200 {
@@ -314,6 +316,23 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     (void)cudaGetLastError();
     return B200_ERR_LAUNCH;
   }
+  return B200_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is a per-device setting.  `done` remembers, one bit per
+// device ordinal, where it has been made for one kernel; ordinals >= 64 simply set it on every launch.  Two
+// host threads that race on the first launch both set the same value, which is harmless.
+template <typename K>
+inline int ensure_dynamic_smem(K kernel, int bytes, std::atomic<uint64_t>& done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B200_ERR_LAUNCH;
+  const uint64_t bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0ull;
+  if (bit != 0 && (done.load(std::memory_order_acquire) & bit) != 0) return B200_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  if (bit != 0) done.fetch_or(bit, std::memory_order_release);
   return B200_OK;
 }
 

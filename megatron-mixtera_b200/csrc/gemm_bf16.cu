@@ -25,7 +25,6 @@ constexpr int kTileN = 128;   // weight rows per CTA (UMMA M)
 constexpr int kTileK = 64;    // bf16 elements per stage along K = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 128;
-constexpr int kCounterBytes = 64 * 1024;
 constexpr int kMaxSplits = 32;
 
 template <int BT>
@@ -43,7 +42,6 @@ struct Params {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y;
   float* partials;      // [splits][M][N] fp32 (split-K only)
-  int* counters;        // one per (n tile, m block)
   int64_t ldy;
   int M, N, K;
   int num_k_blocks;     // ceil(K / 64)
@@ -302,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 
   // ---------------- epilogue: all four warps ----------------
-  pdl_wait();  // outputs, partials and counters may still be in use by the previous kernel until here
+  pdl_wait();  // outputs and partial sums may still be in use by the previous kernel until here
   mbar_wait_bounded(accum_bar, 0, abort_flag, kStatusGemmTimeout);
   tcgen05_fence_after_sync();
 
@@ -374,7 +372,6 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
   p.k_blocks_per_split = (num_kb + splits - 1) / splits;
   p.num_splits = splits;
   p.partials = nullptr;
-  p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
   p.gated = gated ? 1 : 0;
   if (gated && (splits != 1 || partials_out != nullptr)) return B200_ERR_INVALID_ARGUMENT;
@@ -383,19 +380,12 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
     p.partials = partials_out;
     *splits_out = splits;
   } else if (splits > 1) {
-    const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
-    if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
-    if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
-    p.counters = static_cast<int*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+    const size_t need = static_cast<size_t>(splits) * M * N * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200_ERR_WORKSPACE;
+    p.partials = static_cast<float*>(workspace);
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
-        cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  if (ensure_dynamic_smem(gemm_bf16_kernel<BT>, C::kSmemBytes, smem_attr_done) != B200_OK) return B200_ERR_LAUNCH;
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_bf16_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p);
   if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
@@ -460,8 +450,8 @@ size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K) {
   const int bt = pick_bt(M);
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
   const int splits = choose_splits(tiles, (K + kTileK - 1) / kTileK);
-  if (splits == 1) return static_cast<size_t>(kCounterBytes);
-  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
+  if (splits == 1) return 0;
+  return static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
 }
 
 int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M, int N,
@@ -487,31 +477,33 @@ int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, 
 // Some hosts of this library cannot call cudaMalloc at the point where they need a GEMM: a
 // latency-critical serving loop that must not take the allocator's locks or its implicit
 // synchronisation, a server that has handed the whole device to a memory pool of its own, or a
-// plugin that only receives input and output pointers from its framework.  For them the split-K scratch (tile counters + fp32 partial sums)
+// plugin that only receives input and output pointers from its framework.  For them the split-K scratch (the fp32 partial sums)
 // lives in the fixed array below instead of a caller workspace.  Every GPU that loads the library
 // pays for the array once, until the process exits.
 // =============================================================================================
 namespace b200 {
 namespace gemm {
 
-constexpr size_t kStaticScratchBytes = static_cast<size_t>(kCounterBytes) + (16u << 20);  // 64 KiB + 16 MiB
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB of partial sums
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // `g_static_scratch` is a device symbol: in host code its name is only a handle, so the device
 // address is looked up once per device (with that device current) and cached.
+// Two host threads that make the first call on a device at the same time both look the address up and
+// store the same value (the slots are atomic), so no ordering is needed between them.
 static void* static_scratch_address() {
-  static void* addr[64] = {nullptr};
+  static std::atomic<void*> addr[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (addr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess) {
       (void)cudaGetLastError();
       return nullptr;
     }
-    addr[dev] = p;
+    addr[dev].store(p, std::memory_order_release);
   }
-  return addr[dev];
+  return p;
 }
 
 }  // namespace gemm
@@ -533,7 +525,7 @@ int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, con
   if (scratch == nullptr) return B200_ERR_LAUNCH;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // Nothing in the array has to start at zero: the partial sums of a call are completely written by the
-  // GEMM kernel before the reduction kernel of the same call reads them (the first 64 KiB are reserved).
+  // GEMM kernel before the reduction kernel of the same call reads them.
   const size_t bytes = gemm::kStaticScratchBytes;
   switch (gemm::pick_bt(M)) {
     case 32: return gemm::launch<32>(x, ldx, w, bias, y, ldy, M, N, K, scratch, bytes, s, false);

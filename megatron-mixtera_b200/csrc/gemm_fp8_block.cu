@@ -254,7 +254,6 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
   p.k_blocks_per_split = (num_kb + splits - 1) / splits;
   p.num_splits = splits;
   p.partials = nullptr;
-  p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
   p.gated = 0;
   if (partials_out != nullptr) {
@@ -262,23 +261,17 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
     p.partials = partials_out;
     *splits_out = splits;
   } else if (splits > 1) {
-    const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
-    if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
-    p.counters = static_cast<int*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+    const size_t need = static_cast<size_t>(splits) * M * N * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200_ERR_WORKSPACE;
+    p.partials = static_cast<float*>(workspace);
   }
   BlkOperands q;
   q.w_scale = w_scale;
   q.x_scale = x_scale;
   q.k_tiles = num_kb;
   q.m_pad = m_pad;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_fp8_block_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
-        cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  if (ensure_dynamic_smem(gemm_fp8_block_kernel<BT>, C::kSmemBytes, smem_attr_done) != B200_OK) return B200_ERR_LAUNCH;
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_fp8_block_kernel<BT>, grid, dim3(kBlkThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
   if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
@@ -325,8 +318,8 @@ size_t b200_gemm_fp8_block_workspace_bytes(int M, int N, int K) {
   const int bt = pick_bt_block(M);
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
   const int splits = choose_splits(tiles, K / 128);
-  if (splits == 1) return static_cast<size_t>(kCounterBytes);
-  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
+  if (splits == 1) return 0;
+  return static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
 }
 
 int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,

@@ -2,7 +2,7 @@
 //
 // Both operands are E4M3 with one E8M0 (power-of-two) scale per 32 elements along K.  The kernel has
 // the structure of the bf16 weight-streaming GEMM (128-row weight tile = UMMA M side, tokens = UMMA
-// N side, TMA ring, split-K with last-arriver reduction, shared epilogue) with two differences:
+// N side, TMA ring, split-K partial sums reduced by a second kernel or by the consumer, shared epilogue) with two differences:
 //   * one stage is 128 bytes of K per row (128 elements = four 32-wide scale blocks), and
 //   * the MMA is tcgen05.mma kind::mxf8f6f4.block_scale: the scales of a stage (a 512-byte tile per
 //     128 rows) arrive by a 1-D bulk copy, are moved to tensor memory with tcgen05.cp and applied by
@@ -203,7 +203,6 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
   p.k_blocks_per_split = (num_kb + splits - 1) / splits;
   p.num_splits = splits;
   p.partials = nullptr;
-  p.counters = nullptr;
   p.keep_partials = partials_out != nullptr;
   p.gated = 0;
   if (partials_out != nullptr) {
@@ -211,23 +210,16 @@ static int launch_mxfp8(const void* xq, const void* x_sf, const void* wq, const 
     p.partials = partials_out;
     *splits_out = splits;
   } else if (splits > 1) {
-    const size_t need = kCounterBytes + static_cast<size_t>(splits) * M * N * sizeof(float);
-    if (workspace == nullptr || workspace_bytes < need) return B200_ERR_WORKSPACE;
-    if (static_cast<size_t>(n_tiles) * m_blocks * sizeof(int) > kCounterBytes) return B200_ERR_WORKSPACE;
-    p.counters = static_cast<int*>(workspace);
-    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
+    const size_t need = static_cast<size_t>(splits) * M * N * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return B200_ERR_WORKSPACE;
+    p.partials = static_cast<float*>(workspace);
   }
   Fp8Operands q;
   q.w_sf = static_cast<const uint8_t*>(w_sf);
   q.x_sf = static_cast<const uint8_t*>(x_sf);
   q.k_tiles = num_kb;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_mxfp8_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
-        cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static std::atomic<uint64_t> smem_attr_done{0};
+  if (ensure_dynamic_smem(gemm_mxfp8_kernel<BT>, C::kSmemBytes, smem_attr_done) != B200_OK) return B200_ERR_LAUNCH;
   dim3 grid(n_tiles, splits, m_blocks);
   const int rc = launch_pdl(gemm_mxfp8_kernel<BT>, grid, dim3(kThreads), C::kSmemBytes, stream, *mw, *mx, p, q);
   if (rc != B200_OK || splits == 1 || p.keep_partials) return rc;
@@ -276,8 +268,8 @@ size_t b200_gemm_mxfp8_workspace_bytes(int M, int N, int K) {
   const int bt = pick_bt(M);
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
   const int splits = choose_splits(tiles, K / kFp8TileK);
-  if (splits == 1) return static_cast<size_t>(kCounterBytes);
-  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
+  if (splits == 1) return 0;
+  return static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
 }
 
 int b200_gemm_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,

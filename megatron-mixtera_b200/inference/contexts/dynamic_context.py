@@ -608,7 +608,6 @@ class DynamicInferenceContext(BaseInferenceContext):
         """Admit a request: pop ``ceil(len / chunk)`` chunks, fill its row and its token entries
         (reference :920-1015).  Unlike the reference, the sequence-length check runs before chunks
         are popped, so a rejected request does not leak chunks."""
-        self._bt_version += 1
         if isinstance(tokens, Tensor):
             context_length = tokens.numel()
         else:
@@ -628,6 +627,10 @@ class DynamicInferenceContext(BaseInferenceContext):
             raise ChunkOverflowError(request_id)
         if num_tokens_to_generate is None:
             num_tokens_to_generate = self.max_sequence_length - context_length
+        # Admission succeeded: only now does the state change.  (A request that is rejected - e.g. one that waits in
+        # the engine's queue and is retried after every step - must leave the version alone, or every step would
+        # invalidate the block table on the device and the forward the controller enqueued early.)
+        self._bt_version += 1
 
         r = self.total_request_count
         self.request_ids[r] = request_id

@@ -35,10 +35,17 @@ def _need(t: torch.Tensor, dtype, name: str) -> None:
 
 
 class _Workspace:
-    """Grow-only device scratch per (device, tag) (split-K partial sums, attention split partials)."""
+    """Grow-only device scratch per (device, tag) (split-K partial sums, attention split partials).
+
+    A captured CUDA graph has the address of the buffer it was captured with baked in, so a buffer that is
+    superseded by a larger one is never released: it stays in `_retired` for the life of the process and
+    graph replays keep writing to memory that is still theirs.  `reserve` sizes a buffer up front (before any
+    capture) so that the common case never grows at all.
+    """
 
     def __init__(self):
         self._buf = {}
+        self._retired = []
 
     def get(self, device: torch.device, tag: str, nbytes: int) -> torch.Tensor:
         key = (device.index, tag)
@@ -47,9 +54,14 @@ class _Workspace:
             if torch.cuda.is_current_stream_capturing():
                 raise B200Error("workspace", -3, "workspace would have to grow during CUDA graph capture; "
                                 "run one eager warm-up step of the same shapes first")
+            if buf is not None:
+                self._retired.append(buf)  # a graph may still replay into it
             buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
             self._buf[key] = buf
         return buf
+
+    def reserve(self, device: torch.device, tag: str, nbytes: int) -> None:
+        self.get(device, tag, nbytes)
 
 
 _workspace = _Workspace()
@@ -61,13 +73,10 @@ launch_count = 0
 _gemm_epoch = 0
 
 
-_SPLITK_RESERVED = 64 * 1024  # workspace bytes a GEMM asks for when it is NOT split along K
-
-
 def _gemm_workspace(device, nbytes: int, count_reduction: bool = False) -> torch.Tensor:
     global _gemm_epoch, launch_count
     _gemm_epoch += 1
-    if count_reduction and nbytes > _SPLITK_RESERVED:
+    if count_reduction and nbytes > 0:
         launch_count += 1  # the split-K reduction kernel behind the GEMM kernel
     return _workspace.get(device, "gemm", nbytes)
 
@@ -134,15 +143,21 @@ def add_norm(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5
 _ACT_KIND = {"swiglu": 0, "gelu": 1, "swiglu_interleaved": 2}
 
 
+def _act_kind(kind: str) -> int:
+    if kind not in _ACT_KIND:
+        raise B200Error("activation", -1, f"unknown activation kind {kind!r} (one of {sorted(_ACT_KIND)})")
+    return _ACT_KIND[kind]
+
+
 def activation(x, kind: str, bias=None):
     """kind 'swiglu': x [rows, 2F] = [gate | up] -> [rows, F]; 'swiglu_interleaved': the same on the column order of
     an fc1 whose weight went through `interleave_gate_up`; 'gelu': x [rows, F] (+bias) -> [rows, F]."""
     _need(x, BF16, "x")
     rows = x.numel() // x.shape[-1]
-    F = x.shape[-1] if kind == "gelu" else x.shape[-1] // 2
+    F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.device)
     check("b200_activation_bf16", _lib.load().b200_activation_bf16(
-        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, _ACT_KIND[kind], _stream()))
+        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, _act_kind(kind), _stream()))
     return out
 
 
@@ -240,10 +255,10 @@ def activation_mxfp8(x, kind: str, bias=None) -> Mxfp8Tensor:
     """`activation` with MXFP8 output."""
     _need(x, BF16, "x")
     rows = x.numel() // x.shape[-1]
-    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     q, sf = _mx_buffers(rows, F, x.device)
     check("b200_activation_mxfp8", _lib.load().b200_activation_mxfp8(
-        x.data_ptr(), _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, 0 if kind == "swiglu" else 1, _stream()))
+        x.data_ptr(), _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, _act_kind(kind), _stream()))
     return Mxfp8Tensor(q, sf, (*x.shape[:-1], F))
 
 
@@ -316,10 +331,10 @@ def add_norm_fp8_rowblock(x, gamma, *, bias=None, residual=None, beta=None, eps:
 def activation_fp8_rowblock(x, kind: str, bias=None) -> Fp8BlockTensor:
     _need(x, BF16, "x")
     rows = x.numel() // x.shape[-1]
-    F = x.shape[-1] // 2 if kind == "swiglu" else x.shape[-1]
+    F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     q, scale, m_pad = _rowblock_buffers(rows, F, x.device)
     check("b200_activation_fp8_rowblock", _lib.load().b200_activation_fp8_rowblock(
-        x.data_ptr(), _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, 0 if kind == "swiglu" else 1, _stream()))
+        x.data_ptr(), _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, _act_kind(kind), _stream()))
     return Fp8BlockTensor(q, scale, (*x.shape[:-1], F), m_pad)
 
 

@@ -37,7 +37,7 @@ def test_host_only_entry_points():
     assert lib.b200_version() >= 1
     assert lib.b200_error_string(0) and b"scratch" in lib.b200_error_string(-7)
     assert lib.b200_error_string(-12345)  # unknown codes still give a string
-    assert lib.b200_gemm_bf16_static_scratch_limit() == 64 * 1024 + 16 * 1024 * 1024
+    assert lib.b200_gemm_bf16_static_scratch_limit() == 16 * 1024 * 1024
     assert lib.b200_mxfp8_scale_bytes(64, 4096) == 2 * 32 * 512 and lib.b200_mxfp8_scale_bytes(64, 100) == 0
     # FP8 value-pool positions: a permutation inside every 32 tokens
     pos = [lib.b200_fp8_value_position(t) for t in range(256)]
