@@ -102,9 +102,16 @@ int b200_gemm_bf16_swiglu(const void* x, int64_t ldx, const void* w, void* y, in
  * (megatron/core/tensor_parallel/layers.py:317-336, 946-1043, 1225-1281; torch.matmul(x, W.t())).
  * The all-reduce of the row-parallel variant stays with the caller.
  * `workspace`: split-K partial sums (fp32), see b200_gemm_bf16_workspace_bytes; its contents need no
- * initialisation and it must be 16-byte aligned (0 bytes are needed when K is not split).  When K is split a second kernel on the same stream sums the
- * partials in a fixed order, so results are deterministic.
+ * initialisation and it must be 16-byte aligned (0 bytes are needed when K is not split).  When K is split a
+ * second kernel on the same stream sums the partials in a fixed order, so results are deterministic.
+ *
+ * b200_set_gemm_split_policy: tuning of the K split shared by all GEMM entry points (no counterpart in the
+ * reference; cuBLAS picks its own).  A shape with fewer output tiles than `ctas_per_sm` CTAs per SM is split along K
+ * until it has that many CTAs, keeping at least `min_k_blocks_per_split` K blocks (64 bf16 / 128 FP8 elements
+ * each) per split and at most `max_splits` (<= 32) splits.  Defaults 2, 4, 32.  Process-wide; change it only
+ * between, not inside, a *_workspace_bytes / *_splitk_bytes query and the launch it sizes.
  */
+int b200_set_gemm_split_policy(int ctas_per_sm, int min_k_blocks_per_split, int max_splits);
 size_t b200_gemm_bf16_workspace_bytes(int M, int N, int K);
 int b200_gemm_bf16(const void* x, int64_t ldx, const void* w, const void* bias, void* y, int64_t ldy, int M,
                    int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
@@ -144,27 +151,48 @@ int b200_gemm_bf16_static_scratch(const void* x, int64_t ldx, const void* w, con
  * (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4).  Scale byte e means 2^(e - 127); a block's scale is the smallest
  * power of two >= amax / 448.  K must be a multiple of 128.
  *
- * b200_quantize_mxfp8    bf16 [rows, K] (row stride ldx) -> q [rows, K] + scales (weights at load; activations
- *                        whose producer is not fused).
+ * Weight bytes are stored TILE-MAJOR by both FP8 recipes: [ceil(N/128)][K/128] tiles of 128 rows x 128 bytes, 16 KiB of
+ * consecutive memory each (byte (n, k) at ((n/128) * (K/128) + k/128) * 16384 + (n%128) * 128 + k%128;
+ * b200_fp8_weight_bytes(N, K) bytes; rows past N are padding), so that a GEMM CTA's 128-row x 128-byte operand
+ * box is one contiguous DRAM read.  Activations stay row-major [rows, K].
+ *
+ * b200_quantize_mxfp8    bf16 activations [rows, K] (row stride ldx) -> q [rows, K] + scales (activations whose
+ *                        producer is not fused).
+ * b200_quantize_mxfp8_weight  bf16 weight [N, K] (dense) -> tile-major q + scales (once, at load).
  * b200_add_norm_mxfp8    b200_add_norm_bf16 whose normalised output is written as MXFP8 instead of bf16
  *                        (the quantisation of the next linear's input fused into its producer).
  * b200_activation_mxfp8  b200_activation_bf16 with MXFP8 output (input of fc2).
  * b200_gemm_mxfp8        y[M, N] = dq(xq)[M, K] * dq(wq)[N, K]^T (+ bias); workspace as for b200_gemm_bf16.
+ * (b200_gemm_mxfp8_swiglu is declared below, after the plain entry points.)
  */
 size_t b200_mxfp8_scale_bytes(int rows, int K);
+size_t b200_fp8_weight_bytes(int N, int K);
+int b200_quantize_mxfp8_weight(const void* w, void* q, void* sf, int N, int K, b200_stream_t stream);
 int b200_quantize_mxfp8(const void* x, int64_t ldx, void* q, void* sf, int rows, int K, b200_stream_t stream);
 int b200_add_norm_mxfp8(const void* x, const void* bias, const void* residual, const void* gamma, const void* beta,
                         void* hidden_out, void* q_out, void* sf_out, int rows, int hidden, float eps,
                         b200_stream_t stream);
 int b200_activation_mxfp8(const void* in, const void* bias, void* q_out, void* sf_out, int rows, int F, int kind,
                           b200_stream_t stream);
+/*
+ * b200_gemm_mxfp8_swiglu fc1 + SwiGLU (+ MXFP8 quantisation) in one kernel for the gated MLP (MLP.forward, mlp.py:140-213;
+ *                        TE's fused fc1 path, extensions/transformer_engine.py:561-583): wq is the fc1 weight [2F, K] in
+ *                        the reference's [gate ; up] row order.  One CTA multiplies 128 gate rows and the 128 matching
+ *                        up rows by the same token tile; the epilogue writes bf16(bf16(silu(gate)) * up) either as
+ *                        MXFP8 (q_out [M, F] + sf_out, the fc2 input) or as bf16 (y_out, row stride ldy) - exactly
+ *                        one of the two.  Bit-identical to b200_gemm_mxfp8 + b200_activation_mxfp8 / _bf16 when that GEMM is not split
+ *                        along K either (split-K sums its partial sums in another order).  K is not
+ *                        split: meant for shapes with F / 128 CTAs enough to fill the GPU.  F % 128 == 0.
+ */
+int b200_gemm_mxfp8_swiglu(const void* xq, const void* x_sf, const void* wq, const void* w_sf, void* q_out, void* sf_out,
+                           void* y_out, int64_t ldy, int M, int F, int K, b200_stream_t stream);
 size_t b200_gemm_mxfp8_workspace_bytes(int M, int N, int K);
 int b200_gemm_mxfp8(const void* xq, const void* x_sf, const void* wq, const void* w_sf, const void* bias, void* y,
                     int64_t ldy, int M, int N, int K, void* workspace, size_t workspace_bytes, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
- * Block-scaled FP8 linears with fp32 scales: E4M3 weights with one scale per 128 x 128 block
- * (w_scale [ceil(N/128)][K/128]) and E4M3 activations with one scale per token per 128 elements of K
+ * Block-scaled FP8 linears with fp32 scales: E4M3 weights (tile-major bytes, see above) with one scale per
+ * 128 x 128 block (w_scale [ceil(N/128)][K/128]) and E4M3 activations with one scale per token per 128 elements of K
  * (x_scale [K/128][m_pad], m_pad >= M a multiple of 4); scale = amax / 448, value = RNE-saturate(x / scale).
  * Replaces the FP8 path of the TE linears under the `blockwise` recipe (Float8BlockScaling,
  * megatron/core/fp8_utils.py:451-468; arithmetic in Transformer Engine 2.7, absent from the reference tree).
@@ -195,6 +223,10 @@ int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const v
  * host before the call returns; one split is possible), and b200_add_norm_splitk_* read them in place of `x`:
  * x = bf16(sum of the splits in split order), then exactly what b200_add_norm_* does (`bias` here is the linear's
  * bias).  Results are bit-identical to b200_gemm_* followed by b200_add_norm_*.  hidden <= 8192.
+ *
+ * b200_activation_splitk_* do the same for the column-parallel fc1 -> activation pair (MLP.forward,
+ * megatron/core/transformer/mlp.py:140-213): `partials` [num_splits][rows][2F] (gated kinds) or [num_splits][rows][F]
+ * replace the bf16 input of b200_activation_*; bit-identical to GEMM + reduction + b200_activation_*.
  */
 size_t b200_gemm_bf16_splitk_bytes(int M, int N, int K);
 int b200_gemm_bf16_splitk(const void* x, int64_t ldx, const void* w, int M, int N, int K, float* partials,
@@ -215,6 +247,12 @@ int b200_add_norm_splitk_mxfp8(const float* partials, int num_splits, const void
 int b200_add_norm_splitk_fp8_rowblock(const float* partials, int num_splits, const void* bias, const void* residual,
                                       const void* gamma, const void* beta, void* hidden_out, void* q_out, float* scale_out,
                                       int m_pad, int rows, int hidden, float eps, b200_stream_t stream);
+int b200_activation_splitk_bf16(const float* partials, int num_splits, const void* bias, void* out, int rows, int F, int kind,
+                                b200_stream_t stream);
+int b200_activation_splitk_mxfp8(const float* partials, int num_splits, const void* bias, void* q_out, void* sf_out, int rows,
+                                 int F, int kind, b200_stream_t stream);
+int b200_activation_splitk_fp8_rowblock(const float* partials, int num_splits, const void* bias, void* q_out, float* scale_out,
+                                        int m_pad, int rows, int F, int kind, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Tensor parallelism: the all-reduce after a row-parallel linear (mappings.py:22-33 called from
@@ -317,6 +355,15 @@ typedef struct {
   int32_t qkv_num_splits;
   const int32_t* row_order; /* [T] int32 or NULL: a permutation of 0..T-1; the attention kernel starts its work on the
                                rows in this order (longest context first balances the SMs).  Results do not depend on it. */
+  void* out_q;              /* NULL, or E4M3 bytes [T][nq * d]: b200_paged_attention writes its output quantised as the
+                               FP8 input of the out-projection instead of bf16 `out` (which is then not written): the
+                               bits b200_quantize_mxfp8 / b200_quantize_fp8_rowblock would produce from the bf16 output
+                               (TE quantises the attention output inside its row-parallel linear,
+                               megatron/core/extensions/transformer_engine.py:736-828).  Decode kernels only. */
+  void* out_scales;         /* out_q_mode 1: E8M0 scales in the MXFP8 tile layout (b200_mxfp8_scale_bytes(T, nq * d));
+                               out_q_mode 2: fp32 [nq][out_m_pad], one scale per token per head (head_dim 128 only) */
+  int32_t out_q_mode;       /* 1: MXFP8, 2: 128-block recipe */
+  int32_t out_m_pad;        /* out_q_mode 2: row stride of out_scales (>= T, multiple of 4) */
 } b200_attention_args;
 
 size_t b200_paged_attention_workspace_bytes(int num_tokens, int num_q_heads, int head_dim, int num_splits);

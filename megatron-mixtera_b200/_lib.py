@@ -19,16 +19,20 @@ EXPORTED_SYMBOLS = (
     "b200_gather_rows_bf16",
     "b200_add_norm_bf16",
     "b200_activation_bf16",
+    "b200_set_gemm_split_policy",
     "b200_gemm_bf16_workspace_bytes",
     "b200_gemm_bf16",
     "b200_gemm_bf16_static_scratch_limit",
     "b200_gemm_bf16_static_scratch",
     "b200_mxfp8_scale_bytes",
     "b200_quantize_mxfp8",
+    "b200_quantize_mxfp8_weight",
+    "b200_fp8_weight_bytes",
     "b200_add_norm_mxfp8",
     "b200_activation_mxfp8",
     "b200_gemm_mxfp8_workspace_bytes",
     "b200_gemm_mxfp8",
+    "b200_gemm_mxfp8_swiglu",
     "b200_quantize_fp8_weight_block128",
     "b200_quantize_fp8_rowblock",
     "b200_add_norm_fp8_rowblock",
@@ -46,6 +50,9 @@ EXPORTED_SYMBOLS = (
     "b200_add_norm_splitk_bf16",
     "b200_add_norm_splitk_mxfp8",
     "b200_add_norm_splitk_fp8_rowblock",
+    "b200_activation_splitk_bf16",
+    "b200_activation_splitk_mxfp8",
+    "b200_activation_splitk_fp8_rowblock",
     "b200_peer_buffer_create",
     "b200_peer_buffer_open",
     "b200_peer_buffer_close",
@@ -99,6 +106,10 @@ class AttentionArgs(ctypes.Structure):
         ("qkv_partials", c_void_p),
         ("qkv_num_splits", c_int32),
         ("row_order", c_void_p),
+        ("out_q", c_void_p),
+        ("out_scales", c_void_p),
+        ("out_q_mode", c_int32),
+        ("out_m_pad", c_int32),
     ]
 
 
@@ -148,6 +159,7 @@ def load() -> ctypes.CDLL:
     lib.b200_add_norm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                        c_int, c_float, c_void_p]
     lib.b200_activation_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_set_gemm_split_policy.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_bf16_workspace_bytes.restype = c_size_t
     lib.b200_gemm_bf16_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
@@ -161,6 +173,9 @@ def load() -> ctypes.CDLL:
     lib.b200_mxfp8_scale_bytes.restype = c_size_t
     lib.b200_mxfp8_scale_bytes.argtypes = [c_int, c_int]
     lib.b200_quantize_mxfp8.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_quantize_mxfp8_weight.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_fp8_weight_bytes.restype = c_size_t
+    lib.b200_fp8_weight_bytes.argtypes = [c_int, c_int]
     lib.b200_add_norm_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_float, c_void_p]
     lib.b200_activation_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
@@ -168,6 +183,12 @@ def load() -> ctypes.CDLL:
     lib.b200_gemm_mxfp8_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_mxfp8.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                     c_int, c_void_p, c_size_t, c_void_p]
+    lib.b200_gemm_mxfp8_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                           c_int, c_int, c_int, c_void_p]
+    lib.b200_activation_splitk_bf16.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_activation_splitk_mxfp8.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.b200_activation_splitk_fp8_rowblock.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                        c_int, c_void_p]
     lib.b200_quantize_fp8_weight_block128.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.b200_quantize_fp8_rowblock.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.b200_add_norm_fp8_rowblock.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -18,6 +18,7 @@
 // The kernel is bound by reading the K/V pool once from HBM: algorithmic bytes per launch are
 // sum_rows kv_len * 2 * nkv * d * 2.
 #include "common.cuh"
+#include "quant.cuh"
 
 namespace b200 {
 namespace attn {
@@ -61,6 +62,12 @@ struct Params {
   const __nv_bfloat16* cos;
   const __nv_bfloat16* sin;
   __nv_bfloat16* out;
+  // Quantised output (the out-projection's FP8 input) instead of `out`: E4M3 bytes [T][nq * D] + scales, written by the
+  // kernel that finishes an output row (decode kernels only).  out_q_mode: mx::kQuantMx (E8M0 per 32, tile layout) or
+  // mx::kQuantBlock128 (fp32 per token per 128 = per head, scale[nq][out_m_pad]; head_dim 128 only).
+  uint8_t* out_q;
+  void* out_sf;
+  int out_q_mode, out_m_pad;
   const float* k_scale;  // E4M3 pool (attention_fp8.cu): one scale per KV head; nullptr otherwise
   const float* v_scale;
   float* ws_o;    // [T][nq][splits][D]
@@ -85,6 +92,39 @@ __device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, 
 }
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// One finished output element o of (token t, query head `head`, dim d).  Plain mode: bf16 store.  Quantised mode: the
+// bf16-rounded value (what a stand-alone quantiser would read) goes out as E4M3 with the scale of its block.  The 32
+// lanes of a warp hold 32 consecutive dims of one head (all call sites), which is one MXFP8 scale block; the 128-block
+// recipe needs the maximum over the whole head (D == 128 = four warps): `red` is a 4-float shared array and
+// `block_sync` the barrier over exactly the threads that take part.  Every thread of the warp / block must call it.
+template <int D, typename Sync>
+__device__ __forceinline__ void store_output(const Params& p, int t, int head, int d, float o, float* red, Sync block_sync) {
+  if (p.out_q == nullptr) {
+    p.out[(static_cast<int64_t>(t) * p.nq + head) * D + d] = __float2bfloat16_rn(o);
+    return;
+  }
+  const float ob = bf16_round(o);
+  const int64_t ldq = static_cast<int64_t>(p.nq) * D;
+  const int col = head * D + d;
+  float amax = warp_max(fabsf(ob));
+  if (p.out_q_mode == mx::kQuantMx) {
+    const uint32_t e = mx::e8m0_scale_byte(amax);
+    const float inv = scalbnf(1.0f, 127 - static_cast<int>(e));
+    p.out_q[t * ldq + col] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(ob * inv, __NV_SATFINITE, __NV_E4M3));
+    if ((threadIdx.x & 31) == 0)
+      static_cast<uint8_t*>(p.out_sf)[mx::sf_offset(t, col >> 5, static_cast<int>(ldq >> 7))] = static_cast<uint8_t>(e);
+  } else {
+    const int w = (d >> 5) & 3;
+    if ((threadIdx.x & 31) == 0) red[w] = amax;
+    block_sync();
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    block_sync();  // `red` may be rewritten by the next call
+    const float sc = fmaxf(amax / 448.0f, 1e-30f);
+    p.out_q[t * ldq + col] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(ob / sc, __NV_SATFINITE, __NV_E4M3));
+    if (d == 0) static_cast<float*>(p.out_sf)[static_cast<int64_t>(head) * p.out_m_pad + t] = sc;
+  }
+}
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -113,8 +153,9 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   if (kv_len <= 0) {  // padding row: flash-attn returns zeros for it
     pdl_wait();
     if (p.num_splits == 1) {
-      __nv_bfloat16* o = p.out + (static_cast<int64_t>(t) * p.nq + h * G) * D;
-      for (int i = tid; i < G * D; i += kThreads) o[i] = __float2bfloat16_rn(0.f);
+      __shared__ float red0[4];
+      if (tid < kConsumerThreads)
+        for (int i = tid; i < G * D; i += kConsumerThreads) store_output<D>(p, t, h * G + i / D, i % D, 0.f, red0, consumer_barrier);
     }
     return;
   }
@@ -438,7 +479,7 @@ paged_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const float o = lsum > 0.f ? acc / lsum : 0.f;
     const int64_t qh = static_cast<int64_t>(t) * p.nq + h * G + g;
     if (p.num_splits == 1) {
-      p.out[qh * D + d] = __float2bfloat16_rn(o);
+      store_output<D>(p, t, h * G + g, d, o, ml + kConsumerWarps * 16, consumer_barrier);
     } else {
       p.ws_o[(qh * p.num_splits + split) * D + d] = o;
       if (d == 0) p.ws_lse[qh * p.num_splits + split] = lsum > 0.f ? m + log2f(lsum) : -INFINITY;
@@ -729,7 +770,8 @@ __global__ void __launch_bounds__(D) combine_kernel(Params p) {
       o = acc / wsum;
     }
   }
-  p.out[static_cast<int64_t>(qh) * D + d] = __float2bfloat16_rn(o);
+  __shared__ float red[4];
+  store_output<D>(p, t, qh - t * p.nq, d, o, red, [] { __syncthreads(); });
 }
 
 // Prefill / mixed steps: rotate k, then scatter k and v of every token into the pool.
@@ -789,6 +831,20 @@ static int fill_params(const b200_attention_args* a, Params& p) {
   p.cos = static_cast<const __nv_bfloat16*>(a->rope_cos);
   p.sin = static_cast<const __nv_bfloat16*>(a->rope_sin);
   p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out_q = static_cast<uint8_t*>(a->out_q);
+  p.out_sf = a->out_scales;
+  p.out_q_mode = a->out_q_mode;
+  p.out_m_pad = a->out_m_pad;
+  if (a->out_q != nullptr) {
+    const int64_t width = static_cast<int64_t>(a->num_q_heads) * a->head_dim;
+    if (!a->out_scales || !aligned16(a->out_q) || !aligned16(a->out_scales) || width % 128 != 0)
+      return B200_ERR_INVALID_ARGUMENT;
+    if (a->out_q_mode == mx::kQuantBlock128) {
+      if (a->head_dim != 128 || a->out_m_pad < a->num_tokens || a->out_m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+    } else if (a->out_q_mode != mx::kQuantMx) {
+      return B200_ERR_INVALID_ARGUMENT;
+    }
+  }
   p.T = a->num_tokens;
   p.nq = a->num_q_heads;
   p.nkv = a->num_kv_heads;
@@ -873,7 +929,7 @@ int b200_paged_prefill_attention(const b200_attention_args* a, const int32_t* un
   attn::Params p;
   int rc = attn::fill_params(a, p);
   if (rc != B200_OK) return rc;
-  if (!a->out || !a->qkv || !units || num_units <= 0 || a->kv_cache_fp8) return B200_ERR_INVALID_ARGUMENT;
+  if (!a->out || a->out_q || !a->qkv || !units || num_units <= 0 || a->kv_cache_fp8) return B200_ERR_INVALID_ARGUMENT;
   if (64 % p.G != 0) return B200_ERR_INVALID_ARGUMENT;  // group sizes 1, 2, 4, 8, 16
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return a->head_dim == 128 ? attn::launch_prefill<128>(p, units, num_units, s)
@@ -903,7 +959,7 @@ int b200_paged_attention(const b200_attention_args* a, b200_stream_t stream) {
   attn::Params p;
   int rc = attn::fill_params(a, p);
   if (rc != B200_OK) return rc;
-  if (!a->out) return B200_ERR_INVALID_ARGUMENT;
+  if (!a->out && !a->out_q) return B200_ERR_INVALID_ARGUMENT;
   if (a->fuse_rope_append && (!a->token_to_chunk_idx || !a->token_to_local_pos)) return B200_ERR_INVALID_ARGUMENT;
   if (a->qkv_partials && (a->num_q_heads / a->num_kv_heads + 2) * a->head_dim % 4 != 0) return B200_ERR_ALIGNMENT;
   if (a->num_splits > 1) {

@@ -110,8 +110,10 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   if (kv_len <= 0) {  // padding row: zeros
     pdl_wait();
     if (p.num_splits == 1) {
-      __nv_bfloat16* o = p.out + (static_cast<int64_t>(t) * p.nq + h * G) * D;
-      for (int i = tid; i < G * D; i += kThreads) o[i] = __float2bfloat16_rn(0.f);
+      __shared__ float red0[4];
+      if (tid < kConsumerThreads)
+        for (int i = tid; i < G * D; i += kConsumerThreads)
+          attn::store_output<D>(p, t, h * G + i / D, i % D, 0.f, red0, attn::consumer_barrier);
     }
     return;
   }
@@ -439,7 +441,7 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const float o = lsum > 0.f ? acc / lsum * out_scale : 0.f;
     const int64_t qh_idx = static_cast<int64_t>(t) * p.nq + h * G + g;
     if (p.num_splits == 1) {
-      p.out[qh_idx * D + d] = __float2bfloat16_rn(o);
+      attn::store_output<D>(p, t, h * G + g, d, o, ml + kConsumerWarps * 16, attn::consumer_barrier);
     } else {
       p.ws_o[(qh_idx * p.num_splits + split) * D + d] = o;
       if (d == 0) p.ws_lse[qh_idx * p.num_splits + split] = lsum > 0.f ? m + log2f(lsum) : -INFINITY;
@@ -472,7 +474,8 @@ __global__ void __launch_bounds__(D) combine_fp8_kernel(Params p) {
       o = acc / wsum;
     }
   }
-  p.out[static_cast<int64_t>(qh) * D + d] = __float2bfloat16_rn(o);
+  __shared__ float red[4];
+  attn::store_output<D>(p, t, qh - t * p.nq, d, o, red, [] { __syncthreads(); });
 }
 
 // Prefill / mixed steps: rotate k, quantise, scatter k (row layout) and v (transposed, permuted layout).

@@ -276,9 +276,29 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 // kind 0: out = bf16(bf16(silu(gate)) * up); kind 1: out = bf16(gelu(bf16(in + bias)))
 // kind 2: SwiGLU on the layout of the fused-epilogue weights: of every 128 input columns the first 64 are gate
 // features, the last 64 the matching up features.
+// x = bf16(sum over the splits, in split order, of 8 consecutive fp32 partial sums): what the GEMM's own reduction
+// kernel would have written.
+__device__ __forceinline__ Vec8 sum_partials8(const float* __restrict__ src, int splits, int64_t split_stride) {
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+#pragma unroll 4
+  for (int sp = 0; sp < splits; ++sp) {
+    const float4 u = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride));
+    const float4 w = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride) + 1);
+    a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+    b.x += w.x; b.y += w.y; b.z += w.z; b.w += w.w;
+  }
+  Vec8 o;
+  o.w[0] = pack_bf16x2(a.x, a.y);
+  o.w[1] = pack_bf16x2(a.z, a.w);
+  o.w[2] = pack_bf16x2(b.x, b.y);
+  o.w[3] = pack_bf16x2(b.z, b.w);
+  return o;
+}
+
 __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ bias,
                                   __nv_bfloat16* __restrict__ out, int F, int kind, uint8_t* __restrict__ q_out,
-                                  void* __restrict__ sf_out, int q_mode, int m_pad) {
+                                  void* __restrict__ sf_out, int q_mode, int m_pad, const float* __restrict__ partials,
+                                  int splits, int64_t split_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x;
@@ -289,10 +309,18 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __
   o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0u;
   if (!valid) {
   } else if (kind == 0 || kind == 2) {
-    const Vec8* row = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * 2 * F);
     const int gi = kind == 0 ? i : ((i >> 3) << 4) + (i & 7);  // 8 vectors = 64 features per half tile
-    const Vec8 g = row[gi];
-    const Vec8 u = row[kind == 0 ? nvec + i : gi + 8];
+    const int ui = kind == 0 ? nvec + i : gi + 8;
+    Vec8 g, u;
+    if (partials != nullptr) {  // the fc1 GEMM left its split-K partial sums: reduce them here
+      const float* row = partials + static_cast<int64_t>(r) * 2 * F;
+      g = sum_partials8(row + gi * 8, splits, split_stride);
+      u = sum_partials8(row + ui * 8, splits, split_stride);
+    } else {
+      const Vec8* row = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * 2 * F);
+      g = row[gi];
+      u = row[ui];
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float a = bf16_round(silu_f(bf16_lo(g.w[k]))) * bf16_lo(u.w[k]);
@@ -300,7 +328,8 @@ __global__ void activation_kernel(const __nv_bfloat16* __restrict__ in, const __
       o.w[k] = pack_bf16x2(a, b);
     }
   } else {
-    const Vec8 v = reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * F)[i];
+    const Vec8 v = partials != nullptr ? sum_partials8(partials + static_cast<int64_t>(r) * F + i * 8, splits, split_stride)
+                                       : reinterpret_cast<const Vec8*>(in + static_cast<int64_t>(r) * F)[i];
     Vec8 b;
     b.w[0] = b.w[1] = b.w[2] = b.w[3] = 0u;
     if (bias) b = reinterpret_cast<const Vec8*>(bias)[i];
@@ -542,19 +571,22 @@ int b200_peer_buffer_destroy(void* ptr) {
 }
 
 static int activation_impl(const void* in, const void* bias, void* out, void* q_out, void* sf_out, int q_mode, int m_pad,
-                           int rows, int F, int kind, b200_stream_t stream) {
+                           int rows, int F, int kind, b200_stream_t stream, const float* partials = nullptr, int splits = 0) {
   using namespace b200;
-  if (!in || (!out && !q_out) || rows <= 0 || F <= 0 || kind < 0 || kind > 2) return B200_ERR_INVALID_ARGUMENT;
+  if ((!in && !partials) || (!out && !q_out) || rows <= 0 || F <= 0 || kind < 0 || kind > 2) return B200_ERR_INVALID_ARGUMENT;
+  if (partials && splits < 1) return B200_ERR_INVALID_ARGUMENT;
   if (kind == 2 && F % 64 != 0) return B200_ERR_ALIGNMENT;
   if ((q_out == nullptr) != (sf_out == nullptr)) return B200_ERR_INVALID_ARGUMENT;
-  if (F % 8 != 0 || (q_out && F % 128 != 0) || !aligned16(in) || (out && !aligned16(out)) || (bias && !aligned16(bias)) ||
-      (q_out && (!aligned16(q_out) || !aligned16(sf_out))))
+  if (F % 8 != 0 || (q_out && F % 128 != 0) || (in && !aligned16(in)) || (partials && !aligned16(partials)) ||
+      (out && !aligned16(out)) || (bias && !aligned16(bias)) || (q_out && (!aligned16(q_out) || !aligned16(sf_out))))
     return B200_ERR_ALIGNMENT;
   const int nvec = F / 8;
   dim3 grid(rows, (nvec + 255) / 256);
+  const int64_t split_stride = static_cast<int64_t>(rows) * (kind == 1 ? F : 2 * F);
   return launch_pdl(ew::activation_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(in), static_cast<const __nv_bfloat16*>(bias),
-                    static_cast<__nv_bfloat16*>(out), F, kind, static_cast<uint8_t*>(q_out), sf_out, q_mode, m_pad);
+                    static_cast<__nv_bfloat16*>(out), F, kind, static_cast<uint8_t*>(q_out), sf_out, q_mode, m_pad, partials,
+                    splits, split_stride);
 }
 
 int b200_activation_bf16(const void* in, const void* bias, void* out, int rows, int F, int kind, b200_stream_t stream) {
@@ -571,6 +603,26 @@ int b200_activation_fp8_rowblock(const void* in, const void* bias, void* q_out, 
                                  int kind, b200_stream_t stream) {
   if (!q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
   return activation_impl(in, bias, nullptr, q_out, scale_out, b200::mx::kQuantBlock128, m_pad, rows, F, kind, stream);
+}
+
+int b200_activation_splitk_bf16(const float* partials, int num_splits, const void* bias, void* out, int rows, int F, int kind,
+                                b200_stream_t stream) {
+  if (!partials) return B200_ERR_INVALID_ARGUMENT;
+  return activation_impl(nullptr, bias, out, nullptr, nullptr, 0, 0, rows, F, kind, stream, partials, num_splits);
+}
+
+int b200_activation_splitk_mxfp8(const float* partials, int num_splits, const void* bias, void* q_out, void* sf_out, int rows,
+                                 int F, int kind, b200_stream_t stream) {
+  if (!partials || !q_out || !sf_out) return B200_ERR_INVALID_ARGUMENT;
+  return activation_impl(nullptr, bias, nullptr, q_out, sf_out, b200::mx::kQuantMx, 0, rows, F, kind, stream, partials,
+                         num_splits);
+}
+
+int b200_activation_splitk_fp8_rowblock(const float* partials, int num_splits, const void* bias, void* q_out, float* scale_out,
+                                        int m_pad, int rows, int F, int kind, b200_stream_t stream) {
+  if (!partials || !q_out || !scale_out || m_pad < rows || m_pad % 4 != 0) return B200_ERR_INVALID_ARGUMENT;
+  return activation_impl(nullptr, bias, nullptr, q_out, scale_out, b200::mx::kQuantBlock128, m_pad, rows, F, kind, stream,
+                         partials, num_splits);
 }
 
 }  // extern "C"

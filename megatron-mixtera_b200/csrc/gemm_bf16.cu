@@ -111,6 +111,9 @@ static int launch_splitk_reduce(const Params& p, cudaStream_t stream) {
                     p.num_splits, p.M, p.N, p.bias, p.y, p.ldy);
 }
 
+// Barrier over the 128 threads that run the epilogue (warps 0-3 in every GEMM kernel; some kernels have more warps).
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
 // Accumulator -> output.  TMEM lane = output feature, TMEM column = token.  Either rounds to bf16 and
 // stores (whole-K units), or stores the fp32 partial tile for splitk_reduce_kernel.
 template <int BT>
@@ -165,43 +168,98 @@ __device__ __forceinline__ void epilogue(const Params& p, uint32_t tmem_base, ui
     }
   } else if (p.num_splits == 1 && !p.keep_partials) {
     const float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.f;
+    if (n0 + kTileN <= p.N && (p.ldy & 7) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0) {
+      // Whole tile, 16-byte aligned rows: transpose through shared memory (the pipeline stages are free, every UMMA
+      // has completed) so that the tile leaves as 16-byte vectors along the features - one store instruction per 8
+      // outputs instead of one per output.
+      __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(stage_smem);  // [<= 128 tokens][128 features]
+      constexpr int kRows = BT < 128 ? BT : 128;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BT; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(lane_addr + c0, r);
-      tmem_ld_wait();
-      if (n_ok) {
+      for (int h0 = 0; h0 < BT; h0 += kRows) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kRows; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(lane_addr + h0 + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int m = m0 + c0 + j;
-          if (m < p.M) {
+          for (int j = 0; j < 32; ++j) {
             float v = __uint_as_float(r[j]);
-            // bias is added to the bf16-rounded product, as `matmul(x, w.t()) + bias` does
-            if (p.bias != nullptr) v = bf16_round(v) + b;
-            p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            if (p.bias != nullptr) v = bf16_round(v) + b;  // bias is added to the bf16-rounded product
+            tile[(c0 + j) * kTileN + warp * 32 + lane] = __float2bfloat16_rn(v);
+          }
+        }
+        epilogue_barrier();
+        const uint4* tile_v = reinterpret_cast<const uint4*>(tile);
+#pragma unroll 1
+        for (int v = tid; v < kRows * 16; v += kThreads) {
+          const int m = m0 + h0 + (v >> 4);
+          if (m < p.M) *reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(m) * p.ldy + n0 + (v & 15) * 8) = tile_v[v];
+        }
+        if (h0 + kRows < BT) epilogue_barrier();
+      }
+    } else {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + c0, r);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < p.M) {
+              float v = __uint_as_float(r[j]);
+              // bias is added to the bf16-rounded product, as `matmul(x, w.t()) + bias` does
+              if (p.bias != nullptr) v = bf16_round(v) + b;
+              p.y[static_cast<int64_t>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            }
           }
         }
       }
     }
   } else {
     float* part = p.partials + static_cast<int64_t>(split) * p.M * p.N;
+    if (n0 + kTileN <= p.N && (p.N & 3) == 0) {
+      // the same transposition for the fp32 partial tile: float4 stores along the features
+      float* tile = reinterpret_cast<float*>(stage_smem);  // [<= 64 tokens][128 features]
+      constexpr int kRows = BT < 64 ? BT : 64;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BT; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(lane_addr + c0, r);
-      tmem_ld_wait();
-      if (n_ok) {
+      for (int h0 = 0; h0 < BT; h0 += kRows) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kRows; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(lane_addr + h0 + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int m = m0 + c0 + j;
-          if (m < p.M) __stcg(&part[static_cast<int64_t>(m) * p.N + n], __uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j) tile[(c0 + j) * kTileN + warp * 32 + lane] = __uint_as_float(r[j]);
+        }
+        epilogue_barrier();
+        const float4* tile_v = reinterpret_cast<const float4*>(tile);
+#pragma unroll 1
+        for (int v = tid; v < kRows * 32; v += kThreads) {
+          const int m = m0 + h0 + (v >> 5);
+          if (m < p.M) __stcg(reinterpret_cast<float4*>(part + static_cast<int64_t>(m) * p.N + n0) + (v & 31), tile_v[v]);
+        }
+        if (h0 + kRows < BT) epilogue_barrier();
+      }
+    } else {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + c0, r);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < p.M) __stcg(&part[static_cast<int64_t>(m) * p.N + n], __uint_as_float(r[j]));
+          }
         }
       }
     }
-    // The partial tile is complete once this kernel ends; splitk_reduce_kernel (launched right behind) sums
-    // the splits of every output element in split order.
+    // The partial tile is complete once this kernel ends; a second kernel (splitk_reduce_kernel, or the fused consumer)
+    // sums the splits of every output element in split order.
   }
-
 }
 
 template <int BT>
@@ -311,14 +369,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
-// Number of K splits: fill ~2 CTAs per SM when there are too few output tiles, keep >= 4 K blocks
-// per split.
+// Number of K splits: fill `ctas_per_sm` CTAs per SM when there are too few output tiles, keep at least
+// `min_k_blocks` K blocks per split, never more than `max_splits`.  The three numbers are a tuning policy that
+// the host may change (b200_set_gemm_split_policy); it must not change between a b200_gemm_*_bytes query and the
+// launch it sizes.
+static std::atomic<int> g_split_ctas_per_sm{2}, g_split_min_k_blocks{4}, g_split_max{kMaxSplits};
+
 static int choose_splits(int tiles, int num_k_blocks) {
-  const int slots = 2 * sm_count();
+  const int slots = g_split_ctas_per_sm.load(std::memory_order_relaxed) * sm_count();
+  const int min_kb = g_split_min_k_blocks.load(std::memory_order_relaxed);
   if (tiles * 2 > slots) return 1;
   int s = slots / tiles;
-  if (s > kMaxSplits) s = kMaxSplits;
-  if (s > num_k_blocks / 4) s = num_k_blocks / 4;
+  const int cap = g_split_max.load(std::memory_order_relaxed);
+  if (s > cap) s = cap;
+  if (s > num_k_blocks / min_kb) s = num_k_blocks / min_kb;
   if (s < 1) s = 1;
   // drop empty trailing splits
   const int per = (num_k_blocks + s - 1) / s;
@@ -396,6 +460,16 @@ static int launch(const void* x, int64_t ldx, const void* w, const void* bias, v
 }  // namespace b200
 
 extern "C" {
+
+int b200_set_gemm_split_policy(int ctas_per_sm, int min_k_blocks_per_split, int max_splits) {
+  using namespace b200::gemm;
+  if (ctas_per_sm < 1 || ctas_per_sm > 4 || min_k_blocks_per_split < 1 || max_splits < 1 || max_splits > kMaxSplits)
+    return B200_ERR_INVALID_ARGUMENT;
+  g_split_ctas_per_sm.store(ctas_per_sm, std::memory_order_relaxed);
+  g_split_min_k_blocks.store(min_k_blocks_per_split, std::memory_order_relaxed);
+  g_split_max.store(max_splits, std::memory_order_relaxed);
+  return B200_OK;
+}
 
 int b200_gemm_bf16_swiglu_supported(int M, int N, int K) {
   using namespace b200::gemm;

@@ -135,7 +135,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int pre = num_kb < C::kStages ? num_kb : C::kStages;
     for (int i = 0; i < pre; ++i) {  // weights are written by no kernel: request them before the wait
       mbar_arrive_expect_tx(&full_bar[i], tx_bytes);
-      tma_load_2d(smem + i * C::kStageBytes, &map_w, &full_bar[i], (kb_begin + i) * 128, n0);
+      tma_load_2d(smem + i * C::kStageBytes, &map_w, &full_bar[i], 0, (n_tile * q.k_tiles + kb_begin + i) * kTileN);
     }
     pdl_wait();
     for (int i = 0; i < pre; ++i) load_x(i, i);
@@ -144,7 +144,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       const uint32_t phase = (i / C::kStages) & 1;
       mbar_wait_bounded(&empty_bar[s], phase ^ 1, abort_flag, kStatusGemmTimeout);
       mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
-      tma_load_2d(smem + s * C::kStageBytes, &map_w, &full_bar[s], (kb_begin + i) * 128, n0);
+      tma_load_2d(smem + s * C::kStageBytes, &map_w, &full_bar[s], 0, (n_tile * q.k_tiles + kb_begin + i) * kTileN);
       load_x(i, s);
     }
    }
@@ -229,12 +229,14 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
                             size_t workspace_bytes, cudaStream_t stream, float* partials_out = nullptr,
                             size_t partials_bytes = 0, int* splits_out = nullptr) {
   using C = BlkConfig<BT>;
-  const uint64_t wd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+  // weights: tile-major (see weight_tile_offset in quant.cuh) = a [tiles * 128 rows][128 bytes] matrix
+  const uint64_t wd[2] = {128, static_cast<uint64_t>((N + kTileN - 1) / kTileN) * (K / 128) * kTileN};
+  const uint64_t wst[1] = {128};
   const uint64_t ws[1] = {static_cast<uint64_t>(K)};
   const uint32_t wb[2] = {128, kTileN};
   const uint64_t xd[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
   const uint32_t xb[2] = {128, BT};
-  const CUtensorMap* mw = get_tensor_map(wq, 2, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  const CUtensorMap* mw = get_tensor_map(wq, 2, wd, wst, wb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                          CU_TENSOR_MAP_DATA_TYPE_UINT8);
   const CUtensorMap* mx = get_tensor_map(xq, 2, xd, ws, xb, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                          CU_TENSOR_MAP_DATA_TYPE_UINT8);

@@ -7,7 +7,7 @@ namespace mx {
 
 __global__ void __launch_bounds__(256)
 quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q, void* __restrict__ sf,
-                int K, int k_tiles, int mode, int m_pad) {
+                int K, int k_tiles, int mode, int m_pad, int packed) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
@@ -26,7 +26,7 @@ quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, uint8_t* __res
         v[2 * k + 1] = bf16_hi(w[k]);
       }
     }
-    quantize8_any(mode, v, valid, row, i * 8, q, K, sf, k_tiles, m_pad);
+    quantize8_any(mode, v, valid, row, i * 8, q, K, sf, k_tiles, m_pad, packed != 0);
   }
 }
 
@@ -81,7 +81,7 @@ quantize_weight_block128_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __
         const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[i][4 * h + 2] / sc, v[i][4 * h + 3] / sc), __NV_SATFINITE, __NV_E4M3);
         o[h] = lo | (hi << 16);
       }
-      *reinterpret_cast<uint2*>(q + static_cast<int64_t>(r) * K + c0) = make_uint2(o[0], o[1]);
+      *reinterpret_cast<uint2*>(q + weight_tile_offset(r, c0, k_tiles)) = make_uint2(o[0], o[1]);  // tile-major
     }
   }
 }
@@ -100,7 +100,24 @@ int b200_quantize_mxfp8(const void* x, int64_t ldx, void* q, void* sf, int rows,
   if (chunks > 8) chunks = 8;
   return launch_pdl(mx::quantize_kernel, dim3(rows, chunks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), sf, K, K / 128,
-                    static_cast<int>(mx::kQuantMx), 0);
+                    static_cast<int>(mx::kQuantMx), 0, 0);
+}
+
+size_t b200_fp8_weight_bytes(int N, int K) {
+  if (N <= 0 || K <= 0 || K % 128 != 0) return 0;
+  return static_cast<size_t>((N + 127) / 128) * 128 * static_cast<size_t>(K);
+}
+
+int b200_quantize_mxfp8_weight(const void* w, void* q, void* sf, int N, int K, b200_stream_t stream) {
+  using namespace b200;
+  if (!w || !q || !sf || N <= 0 || K <= 0) return B200_ERR_INVALID_ARGUMENT;
+  if (K % 128 != 0 || !aligned16(w) || !aligned16(q) || !aligned16(sf)) return B200_ERR_ALIGNMENT;
+  const int nvec = K / 8;
+  int chunks = (nvec + 255) / 256;
+  if (chunks > 8) chunks = 8;
+  return launch_pdl(mx::quantize_kernel, dim3(N, chunks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(w), static_cast<int64_t>(K), static_cast<uint8_t*>(q), sf, K, K / 128,
+                    static_cast<int>(mx::kQuantMx), 0, 1);
 }
 
 int b200_quantize_fp8_rowblock(const void* x, int64_t ldx, void* q, float* scale, int rows, int K, int m_pad,
@@ -115,7 +132,7 @@ int b200_quantize_fp8_rowblock(const void* x, int64_t ldx, void* q, float* scale
   if (chunks > 8) chunks = 8;
   return launch_pdl(mx::quantize_kernel, dim3(rows, chunks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                     static_cast<const __nv_bfloat16*>(x), ldx, static_cast<uint8_t*>(q), static_cast<void*>(scale), K,
-                    K / 128, static_cast<int>(mx::kQuantBlock128), m_pad);
+                    K / 128, static_cast<int>(mx::kQuantBlock128), m_pad, 0);
 }
 
 int b200_quantize_fp8_weight_block128(const void* w, void* q, float* scale, int N, int K, b200_stream_t stream) {

@@ -26,10 +26,17 @@ __device__ __forceinline__ int64_t sf_offset(int row, int kb, int k_tiles) {
   return (static_cast<int64_t>(tile) * k_tiles + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3);
 }
 
+// FP8 WEIGHTS are stored tile-major ("packed"): [ceil(N/128)][K/128] tiles of 128 rows x 128 bytes, each tile 16 KiB
+// of consecutive memory, so that the GEMM's TMA box (128 rows x 128 bytes of K) is one contiguous DRAM read instead
+// of 128 reads of 128 bytes that lie a whole weight row apart.  Offset of byte (row, col) of an [N, K] matrix:
+__host__ __device__ __forceinline__ int64_t weight_tile_offset(int row, int col, int k_tiles) {
+  return (static_cast<int64_t>(row >> 7) * k_tiles + (col >> 7)) * 16384 + (row & 127) * 128 + (col & 127);
+}
+
 // Quantise 8 consecutive values held by this lane; lanes 4j .. 4j+3 of the warp hold one 32-element block.
 // Every lane of the warp must call this (inactive lanes pass valid = false and zeros).
 __device__ __forceinline__ void quantize8(const float (&v)[8], bool valid, int row, int col0, uint8_t* q, int64_t ldq,
-                                          uint8_t* sf, int k_tiles) {
+                                          uint8_t* sf, int k_tiles, bool packed = false) {
   float amax = 0.f;
 #pragma unroll
   for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
@@ -45,7 +52,8 @@ __device__ __forceinline__ void quantize8(const float (&v)[8], bool valid, int r
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h + 2] * inv, v[4 * h + 3] * inv), __NV_SATFINITE, __NV_E4M3);
     w[h] = lo | (hi << 16);
   }
-  *reinterpret_cast<uint2*>(q + static_cast<int64_t>(row) * ldq + col0) = make_uint2(w[0], w[1]);
+  uint8_t* dst = packed ? q + weight_tile_offset(row, col0, k_tiles) : q + static_cast<int64_t>(row) * ldq + col0;
+  *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
   if ((col0 & 31) == 0) sf[sf_offset(row, col0 >> 5, k_tiles)] = static_cast<uint8_t>(e);
 }
 
@@ -76,9 +84,9 @@ enum : int { kQuantMx = 1, kQuantBlock128 = 2 };
 
 // Dispatch used by the fused producers: `sf` is the E8M0 tile buffer (mode 1) or the fp32 scale matrix (mode 2).
 __device__ __forceinline__ void quantize8_any(int mode, const float (&v)[8], bool valid, int row, int col0, uint8_t* q,
-                                              int64_t ldq, void* sf, int k_tiles, int m_pad) {
+                                              int64_t ldq, void* sf, int k_tiles, int m_pad, bool packed = false) {
   if (mode == kQuantMx)
-    quantize8(v, valid, row, col0, q, ldq, static_cast<uint8_t*>(sf), k_tiles);
+    quantize8(v, valid, row, col0, q, ldq, static_cast<uint8_t*>(sf), k_tiles, packed);
   else
     quantize8_block128(v, valid, row, col0, q, ldq, static_cast<float*>(sf), m_pad);
 }

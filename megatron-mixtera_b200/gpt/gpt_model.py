@@ -152,6 +152,11 @@ class GPTModel(torch.nn.Module):
             if hasattr(m, "quantize_weights") and m is not self:
                 m.quantize_weights()
 
+    def release_checkpoint_weights(self) -> int:
+        """Serve from the FP8 weight copies only: free the bf16 tensors of every FP8 linear (2 bytes per weight).
+        Returns the number of layers released; loading or exporting a state dict is not possible afterwards."""
+        return sum(1 for m in self.modules() if hasattr(m, "release_checkpoint_weight") and m.release_checkpoint_weight())
+
     def init_synthetic_weights(self, seed: int = 0, std: float = 0.02, device=None) -> None:
         """Seeded N(0, std) weights (norm scales 1 + N(0, std)), identical across TP sizes."""
         from ..synthetic import canonical_tensor

@@ -213,12 +213,31 @@ def gemm(x, w, bias=None, out=None):
 
 
 class Mxfp8Tensor:
-    """An MXFP8-quantised [rows, K] matrix: E4M3 bytes + E8M0 scales in the GEMM's tile layout."""
+    """An MXFP8-quantised [rows, K] matrix: E4M3 bytes + E8M0 scales in the GEMM's tile layout.  Activations keep
+    their bytes row-major (``q [rows, K]``); weights (``packed``) keep them tile-major, see `weight_tiles_to_rows`."""
 
-    __slots__ = ("q", "sf", "shape")
+    __slots__ = ("q", "sf", "shape", "packed")
 
-    def __init__(self, q: torch.Tensor, sf: torch.Tensor, shape):
-        self.q, self.sf, self.shape = q, sf, tuple(shape)
+    def __init__(self, q: torch.Tensor, sf: torch.Tensor, shape, packed: bool = False):
+        self.q, self.sf, self.shape, self.packed = q, sf, tuple(shape), packed
+
+
+def weight_tiles_to_rows(q: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Tile-major FP8 weight bytes ([ceil(N/128)][K/128] tiles of 128 rows x 128 bytes) -> row-major [N, K]."""
+    nt = (N + 127) // 128
+    return q.view(nt, K // 128, 128, 128).permute(0, 2, 1, 3).reshape(nt * 128, K)[:N]
+
+
+def quantize_mxfp8_weight(w) -> Mxfp8Tensor:
+    """bf16 weight [N, K] -> MXFP8 with tile-major bytes (what the MXFP8 GEMMs stream)."""
+    _need(w, BF16, "w")
+    N, K = w.shape
+    lib = _lib.load()
+    q = torch.zeros((lib.b200_fp8_weight_bytes(N, K),), dtype=torch.uint8, device=w.device)
+    sf = torch.empty((lib.b200_mxfp8_scale_bytes(N, K),), dtype=torch.uint8, device=w.device)
+    check("b200_quantize_mxfp8_weight", lib.b200_quantize_mxfp8_weight(w.data_ptr(), q.data_ptr(), sf.data_ptr(), N, K,
+                                                                       _stream()))
+    return Mxfp8Tensor(q, sf, w.shape, packed=True)
 
 
 def _mx_buffers(rows: int, K: int, device):
@@ -266,15 +285,72 @@ def gemm_mxfp8(x: Mxfp8Tensor, w: Mxfp8Tensor, bias=None, out=None):
     """y = dq(x) @ dq(w).T (+ bias) on the block-scaled FP8 tensor cores; bf16 output."""
     K = x.shape[-1]
     M = x.q.shape[0]
-    N = w.q.shape[0]
-    if w.q.shape[1] != K:
-        raise B200Error("gemm_mxfp8", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.q.shape)}")
+    N = w.shape[0]
+    if w.shape[1] != K or not w.packed or x.packed:
+        raise B200Error("gemm_mxfp8", -1, f"x[..., {K}] (row-major) vs w{tuple(w.shape)} (tile-major, `quantize_mxfp8_weight`)")
     if out is None:
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
     ws = _gemm_workspace(x.q.device, lib.b200_gemm_mxfp8_workspace_bytes(M, N, K), True)
     check("b200_gemm_mxfp8", lib.b200_gemm_mxfp8(x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), _p(bias),
                                                  out.data_ptr(), N, M, N, K, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
+def gemm_mxfp8_swiglu(x: Mxfp8Tensor, w: Mxfp8Tensor, quantize: bool = True):
+    """swiglu(dq(x) @ dq(w).T) for a gated fc1 weight [2F, K] in [gate ; up] row order, one kernel: returns the fc2 input
+    as `Mxfp8Tensor` [rows, F] (or bf16 with ``quantize=False``).  K is not split: see `gemm_mxfp8_swiglu_preferred`."""
+    K = x.shape[-1]
+    M, F = x.q.shape[0], w.shape[0] // 2
+    if w.shape[1] != K or not w.packed:
+        raise B200Error("gemm_mxfp8_swiglu", -1, f"x[..., {K}] vs w{tuple(w.shape)} (tile-major, `quantize_mxfp8_weight`)")
+    lib = _lib.load()
+    if quantize:
+        q, sf = _mx_buffers(M, F, x.q.device)
+        check("b200_gemm_mxfp8_swiglu", lib.b200_gemm_mxfp8_swiglu(
+            x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), q.data_ptr(), sf.data_ptr(), None, 0, M, F, K,
+            _stream()))
+        return Mxfp8Tensor(q, sf, (*x.shape[:-1], F))
+    out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.q.device)
+    check("b200_gemm_mxfp8_swiglu", lib.b200_gemm_mxfp8_swiglu(
+        x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), None, None, out.data_ptr(), F, M, F, K, _stream()))
+    return out
+
+
+def gemm_mxfp8_swiglu_preferred(M: int, F: int, K: int) -> bool:
+    """Whether the one-kernel fc1 + SwiGLU (F / 128 CTAs, each streaming its rows over the whole of K) is the better
+    choice: enough CTAs to keep most SMs streaming.  Below that the fc1 GEMM is split along K and the activation
+    kernel reduces its partial sums."""
+    return F % 128 == 0 and K % 128 == 0 and F // 128 >= 96
+
+
+def activation_splitk(p: "GemmPartials", kind: str, bias=None, quantize=None):
+    """`activation` / `activation_mxfp8` / `activation_fp8_rowblock` (by ``quantize``) with x = the reduced split-K
+    partial sums of the fc1 GEMM."""
+    if p.epoch != _gemm_epoch:
+        raise B200Error("activation_splitk", -1, "another GEMM has reused the workspace that held these partial sums")
+    k = _act_kind(kind)
+    width = p.shape[-1]
+    F = width if k == 1 else width // 2
+    rows = 1
+    for d in p.shape[:-1]:
+        rows *= d
+    dev = p.device
+    lib = _lib.load()
+    shape = (*p.shape[:-1], F)
+    if quantize == "mxfp8":
+        q, sf = _mx_buffers(rows, F, dev)
+        check("b200_activation_splitk_mxfp8", lib.b200_activation_splitk_mxfp8(
+            p.buf.data_ptr(), p.num_splits, _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, k, _stream()))
+        return Mxfp8Tensor(q, sf, shape)
+    if quantize == "blockwise":
+        q, scale, m_pad = _rowblock_buffers(rows, F, dev)
+        check("b200_activation_splitk_fp8_rowblock", lib.b200_activation_splitk_fp8_rowblock(
+            p.buf.data_ptr(), p.num_splits, _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, k, _stream()))
+        return Fp8BlockTensor(q, scale, shape, m_pad)
+    out = torch.empty(shape, dtype=BF16, device=dev)
+    check("b200_activation_splitk_bf16", lib.b200_activation_splitk_bf16(
+        p.buf.data_ptr(), p.num_splits, _p(bias), out.data_ptr(), rows, F, k, _stream()))
     return out
 
 
@@ -298,7 +374,7 @@ def _rowblock_buffers(rows: int, K: int, device):
 def quantize_fp8_weight_block128(w) -> Fp8BlockTensor:
     _need(w, BF16, "w")
     N, K = w.shape
-    q = torch.empty((N, K), dtype=torch.uint8, device=w.device)
+    q = torch.zeros((_lib.load().b200_fp8_weight_bytes(N, K),), dtype=torch.uint8, device=w.device)  # tile-major
     scale = torch.empty(((N + 127) // 128, K // 128), dtype=torch.float32, device=w.device)
     check("b200_quantize_fp8_weight_block128", _lib.load().b200_quantize_fp8_weight_block128(
         w.data_ptr(), q.data_ptr(), scale.data_ptr(), N, K, _stream()))
@@ -341,9 +417,9 @@ def activation_fp8_rowblock(x, kind: str, bias=None) -> Fp8BlockTensor:
 def gemm_fp8_block(x: Fp8BlockTensor, w: Fp8BlockTensor, bias=None, out=None):
     """y = dq(x) @ dq(w).T (+ bias) for the 128-block recipe (fp32 scales promoted per K block)."""
     K = x.shape[-1]
-    M, N = x.q.shape[0], w.q.shape[0]
-    if w.q.shape[1] != K:
-        raise B200Error("gemm_fp8_block", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.q.shape)}")
+    M, N = x.q.shape[0], w.shape[0]
+    if w.shape[1] != K:
+        raise B200Error("gemm_fp8_block", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.shape)}")
     if out is None:
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
@@ -352,6 +428,14 @@ def gemm_fp8_block(x: Fp8BlockTensor, w: Fp8BlockTensor, bias=None, out=None):
         x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), _p(bias), out.data_ptr(), N, M, N,
         K, ws.data_ptr(), ws.numel(), _stream()))
     return out
+
+
+def gemm_num_splits(fp8, M: int, N: int, K: int) -> int:
+    """How many K splits the GEMM of this recipe (None / "mxfp8" / "blockwise") uses for the shape."""
+    lib = _lib.load()
+    fn = {None: lib.b200_gemm_bf16_splitk_bytes, "mxfp8": lib.b200_gemm_mxfp8_splitk_bytes,
+          "blockwise": lib.b200_gemm_fp8_block_splitk_bytes}[fp8]
+    return int(fn(M, N, K) // (4 * M * N))
 
 
 class GemmPartials:
@@ -374,13 +458,15 @@ def gemm_splitk(x, w) -> GemmPartials:
     lib = _lib.load()
     n = ctypes.c_int(0)
     if isinstance(x, Mxfp8Tensor):
-        K, M, N, dev = x.shape[-1], x.q.shape[0], w.q.shape[0], x.q.device
+        K, M, N, dev = x.shape[-1], x.q.shape[0], w.shape[0], x.q.device
+        if not w.packed:
+            raise B200Error("gemm_splitk", -1, "MXFP8 weights must be tile-major (`quantize_mxfp8_weight`)")
         ws = _gemm_workspace(dev, lib.b200_gemm_mxfp8_splitk_bytes(M, N, K))
         check("b200_gemm_mxfp8_splitk", lib.b200_gemm_mxfp8_splitk(
             x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), M, N, K, ws.data_ptr(), ws.numel(),
             ctypes.byref(n), _stream()))
     elif isinstance(x, Fp8BlockTensor):
-        K, M, N, dev = x.shape[-1], x.q.shape[0], w.q.shape[0], x.q.device
+        K, M, N, dev = x.shape[-1], x.q.shape[0], w.shape[0], x.q.device
         ws = _gemm_workspace(dev, lib.b200_gemm_fp8_block_splitk_bytes(M, N, K))
         check("b200_gemm_fp8_block_splitk", lib.b200_gemm_fp8_block_splitk(
             x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), M, N, K, ws.data_ptr(),
@@ -470,7 +556,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
                         token_to_pos_in_request=None, token_to_chunk_idx=None, token_to_local_pos=None,
                         row_of_token=None, rope_cos=None, rope_sin=None, num_splits: int = 1,
                         fuse_rope_append: bool = False, softmax_scale: float = 0.0, k_scale=None,
-                        v_scale=None, row_order=None, fp8_single_term: bool = False) -> AttentionArgs:
+                        v_scale=None, row_order=None, fp8_single_term: bool = False, out_quantized=None) -> AttentionArgs:
     """Fill the C argument struct.  It holds raw pointers only: the caller keeps the tensors alive until the
     kernels have run.  ``k_scale`` / ``v_scale`` (fp32 [nkv]) select the FP8 (E4M3) KV pool; ``fp8_single_term`` its
     faster, less exact arithmetic (queries and probabilities as one E4M3 term instead of two)."""
@@ -510,10 +596,28 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     a.k_scale = _p(k_scale)
     a.v_scale = _p(v_scale)
     a.row_order = _p(row_order)
-    ws = attention_workspace(device, T, num_q_heads, head_dim, num_splits) if out is not None else None
+    if isinstance(out_quantized, Mxfp8Tensor):      # the decode kernel writes the out-projection's FP8 input itself
+        a.out_q, a.out_scales, a.out_q_mode, a.out_m_pad = out_quantized.q.data_ptr(), out_quantized.sf.data_ptr(), 1, 0
+    elif isinstance(out_quantized, Fp8BlockTensor):
+        a.out_q, a.out_scales, a.out_q_mode, a.out_m_pad = (out_quantized.q.data_ptr(), out_quantized.scale.data_ptr(), 2,
+                                                            out_quantized.m_pad)
+    else:
+        a.out_q, a.out_scales, a.out_q_mode, a.out_m_pad = None, None, 0, 0
+    ws = attention_workspace(device, T, num_q_heads, head_dim, num_splits) if (out is not None or out_quantized is not None) else None
     a.workspace = _p(ws)
     a.workspace_bytes = 0 if ws is None else ws.numel()
     return a
+
+
+def quantized_like(kind: str, rows: int, K: int, device, lead_shape=None):
+    """Empty `Mxfp8Tensor` (kind "mxfp8") or `Fp8BlockTensor` ("blockwise") for a [rows, K] activation that a producer
+    kernel will fill."""
+    shape = (*(lead_shape if lead_shape is not None else (rows,)), K)
+    if kind == "mxfp8":
+        q, sf = _mx_buffers(rows, K, device)
+        return Mxfp8Tensor(q, sf, shape)
+    q, scale, m_pad = _rowblock_buffers(rows, K, device)
+    return Fp8BlockTensor(q, scale, shape, m_pad)
 
 
 def rope_append(args: AttentionArgs) -> None:

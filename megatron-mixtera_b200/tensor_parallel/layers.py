@@ -50,9 +50,28 @@ class _ParallelLinearBase(torch.nn.Module):
         if self.gate_up_interleaved and not self._layout_interleaved and self.weight is not None:
             self.weight.data.copy_(ops.interleave_gate_up(self.weight.data))
             self._layout_interleaved = True
-        if self.fp8 and self.weight is not None:
-            fn = ops.quantize_mxfp8 if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
+        if self.fp8 and self.weight is not None and self._weight_shape is None:
+            fn = ops.quantize_mxfp8_weight if self.fp8 == "mxfp8" else ops.quantize_fp8_weight_block128
             self._wq = fn(self.weight.data)
+
+    @property
+    def weight_shape(self):
+        """(out, in) of this rank's shard, also after `release_checkpoint_weight`."""
+        return self._weight_shape if self._weight_shape is not None else tuple(self.weight.shape)
+
+    _weight_shape = None
+
+    def release_checkpoint_weight(self) -> bool:
+        """Free the bf16 ``weight`` once its FP8 copy exists (serving from the quantised weights only: the bf16
+        tensor is the checkpoint format and is not read by any FP8 GEMM).  The parameter object stays, empty;
+        `state_dict` can then no longer export this layer.  Returns True if memory was released."""
+        if not self.fp8 or self.weight is None:
+            return False
+        if self._wq is None:
+            self.quantize_weights()
+        self._weight_shape = tuple(self.weight.shape)
+        self.weight.data = torch.empty(0, dtype=self.weight.dtype, device=self.weight.device)
+        return True
 
     def canonical_weight(self) -> torch.Tensor:
         """The weight in the reference's row order (a copy when the rows are interleaved for the fused kernel)."""
@@ -118,6 +137,27 @@ class ColumnParallelLinear(_ParallelLinearBase):
             out = gather_from_tensor_model_parallel_region(out, self.tp_group)
         return out, (self.bias if self.skip_bias_add else None)
 
+
+    def forward_gated(self, input_):
+        """Gated fc1 in the reference's [gate ; up] row order followed by SwiGLU: the fc2 input, quantised under an
+        FP8 recipe.  One of three forms, all with the same bits: the one-kernel gate / up pair GEMM with the
+        activation and quantisation in its epilogue (MXFP8, enough output features to fill the GPU without
+        splitting K); the split-K GEMM whose partial sums the activation kernel reduces itself (no reduction
+        launch); or GEMM followed by the activation kernel."""
+        assert self.bias is None and not self.gather_output
+        fp8, cfg = self.fp8, self.config
+        quantised_input = isinstance(input_, (ops.Mxfp8Tensor, ops.Fp8BlockTensor))
+        M = input_.q.shape[0] if quantised_input else input_.numel() // input_.shape[-1]
+        N, K = self.weight_shape
+        if fp8 == "mxfp8" and getattr(cfg, "fuse_swiglu_into_fc1", True) and ops.gemm_mxfp8_swiglu_preferred(M, N // 2, K):
+            if self._wq is None:
+                self.quantize_weights()
+            x = input_ if quantised_input else ops.quantize_mxfp8(input_)
+            return ops.gemm_mxfp8_swiglu(x, self._wq)
+        if getattr(cfg, "fuse_splitk_reduction_into_norm", True) and ops.gemm_num_splits(fp8, M, N, K) > 1:
+            return ops.activation_splitk(self._matmul(input_, self.weight, None, defer_reduction=True), "swiglu", quantize=fp8)
+        act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[fp8]
+        return act(self._matmul(input_, self.weight, None), "swiglu")
 
     def forward_swiglu(self, input_):
         """fc1 followed by SwiGLU for a weight in the interleaved row order: one kernel when the GEMM is not split

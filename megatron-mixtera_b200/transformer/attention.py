@@ -58,18 +58,25 @@ class PagedFlashDecodeAttention(torch.nn.Module):
         self.head_dim = config.kv_channels
 
     accepts_gemm_partials = True  # decode steps: the QKV GEMM's split-K partial sums instead of its bf16 output
+    quantizes_output = True       # decode steps: FP8 output for an FP8 out-projection
 
-    def forward(self, mixed_qkv, inference_context, rotary_pos_cos=None, rotary_pos_sin=None):
+    def forward(self, mixed_qkv, inference_context, rotary_pos_cos=None, rotary_pos_sin=None, quantize_output=None):
         """``mixed_qkv`` [T, (nq + 2 nkv) d / tp] (or, in decode steps, the `ops.GemmPartials` of the GEMM that
-        computes it) -> [T, nq d / tp]."""
+        computes it) -> [T, nq d / tp].  ``quantize_output`` ("mxfp8" | "blockwise"; honoured in decode steps): the
+        kernel that finishes an output row writes it as the FP8 input of the out-projection (`ops.Mxfp8Tensor` /
+        `ops.Fp8BlockTensor`) instead of bf16 - no stand-alone quantisation kernel between attention and out-proj."""
         ctx = inference_context
         T = mixed_qkv.shape[0]
         k_cache, v_cache, block_table = ctx.key_value_cache(self.layer_number)
-        out = torch.empty((T, self.num_q_heads * self.head_dim), dtype=torch.bfloat16, device=mixed_qkv.device)
         decode = ctx.is_decode_only()
+        width = self.num_q_heads * self.head_dim
+        out_q = None
+        if (decode and quantize_output and width % 128 == 0 and (quantize_output == "mxfp8" or self.head_dim == 128)):
+            out_q = ops.quantized_like(quantize_output, T, width, mixed_qkv.device)
+        out = None if out_q is not None else torch.empty((T, width), dtype=torch.bfloat16, device=mixed_qkv.device)
         partials = isinstance(mixed_qkv, ops.GemmPartials)
         assert decode or not partials, "only the decode kernel reads un-reduced QKV partial sums"
-        common = dict(
+        common = dict(out_quantized=out_q,
             qkv=mixed_qkv if partials else mixed_qkv.view(T, self.num_kv_heads, -1), k_cache=k_cache, v_cache=v_cache, out=out,
             num_q_heads=self.num_q_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
             chunk_size=ctx.chunk_size_tokens, token_to_pos_ids=ctx.token_to_pos_ids,
@@ -87,6 +94,8 @@ class PagedFlashDecodeAttention(torch.nn.Module):
                                            kv_seq_lengths=ctx.kv_seq_lengths_cudagraph_only, num_splits=splits,
                                            fuse_rope_append=True, row_order=ctx.attention_row_order, **common)
             ops.paged_attention(args)
+            if out_q is not None:
+                return out_q
         else:
             # prefill / mixed step: append every token first; then either blocks of a request's query tokens share
             # the K/V tiles (work list built by the context), or - FP8 pool, unusual head groupings - each token
@@ -133,7 +142,12 @@ class SelfAttention(torch.nn.Module):
             mixed_qkv, _ = self.linear_qkv(hidden_states, defer_reduction=True)
         else:
             mixed_qkv, _ = self.linear_qkv(hidden_states)
-        core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin)
+        fp8 = getattr(self.linear_proj, "fp8", None)
+        if fp8 and getattr(self.config, "fuse_attention_output_quantization", True) \
+                and getattr(self.core_attention, "quantizes_output", False):
+            core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin, quantize_output=fp8)
+        else:
+            core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin)
         if defer_output_reduction and getattr(self.linear_proj, "supports_deferred_reduction", False):
             return self.linear_proj(core, defer_reduction=True)
         return self.linear_proj(core)

@@ -42,6 +42,11 @@ class MLP(torch.nn.Module):
             if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
                 return self.linear_fc2(inter, defer_reduction=True)
             return self.linear_fc2(inter)
+        if self.config.gated_linear_unit and self.linear_fc1.bias is None and hasattr(self.linear_fc1, "forward_gated"):
+            inter = self.linear_fc1.forward_gated(hidden_states)
+            if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
+                return self.linear_fc2(inter, defer_reduction=True)
+            return self.linear_fc2(inter)
         inter, bias = self.linear_fc1(hidden_states)
         act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[self.config.fp8]
         if self.config.gated_linear_unit:

@@ -38,6 +38,9 @@ class TransformerConfig:
     # not in the reference: at TP > 1 the all-reduce after out-proj / fc2 is done by the residual-add + norm kernel
     # itself with peer loads over NVLink (one node, <= 4 ranks, <= 512 token rows; NCCL otherwise)
     fuse_tp_allreduce_into_norm: bool = True
+    # not in the reference: under an FP8 recipe the decode attention kernel writes its output already quantised for the
+    # out-projection (same bits as the stand-alone quantiser, one launch fewer per layer)
+    fuse_attention_output_quantization: bool = True
     fp8: Optional[str] = None                   # None | "mxfp8" (E8M0 scale per 32) | "blockwise" (fp32, 128x128 / 1x128)
 
     def __post_init__(self):

@@ -417,13 +417,17 @@ class GPTOracle:
     """Forward of the local-spec GPT over a ContextOracle (gpt_model.py:279-560, transformer_layer.py:433-660)."""
 
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], ctx: ContextOracle, dtype: torch.dtype,
-                 fp8: Optional[str] = None, kv_fp8_scale: Optional[float] = None, tp: int = 1):
+                 fp8: Optional[str] = None, kv_fp8_scale: Optional[float] = None, tp: int = 1, reverse_k: bool = False):
         """``fp8="mxfp8"`` / ``"blockwise"``: every decoder linear multiplies FP8-quantised inputs by FP8-quantised
         weights with fp32 accumulation (the TE recipes of those names under ``fp8_autocast``,
         transformer_block.py:629-643; E8M0 scale per 32 elements, resp. fp32 scale per 128 x 128 / 1 x 128 block);
         embedding, norms, attention and the output layer stay in ``dtype``."""
         self.s, self.w, self.ctx, self.dtype = spec, weights, ctx, dtype
         self.fp8 = fp8
+        # reverse_k: every linear accumulates its K dimension in the opposite order.  Same arithmetic, same rounding
+        # points, another (equally valid) summation order: the distance between a run with and a run without it is
+        # the noise floor that separates ANY two correct implementations of this model in this dtype.
+        self.reverse_k = reverse_k
         # tp > 1 restates the arithmetic of the reference's tensor-parallel run: a row-parallel linear (out-proj,
         # fc2; layers.py:1225-1281) multiplies its K shard on every rank, each partial product is rounded to the
         # parameter dtype, and the all-reduce adds the rounded partials (mappings.py:22-33).  Column-parallel
@@ -447,6 +451,15 @@ class GPTOracle:
             return F.rms_norm(x, (s.hidden_size,), self.w[prefix + ".weight"], s.eps)
         return F.layer_norm(x, (s.hidden_size,), self.w[prefix + ".weight"], self.w[prefix + ".bias"], s.eps)
 
+    def _mm(self, x, w):
+        """x @ w.T (layers.py:333), optionally with the K dimension accumulated in reverse order."""
+        if self.reverse_k:
+            key = ("flip", w.data_ptr(), tuple(w.shape))
+            if key not in self._wdq:
+                self._wdq[key] = w.flip(-1).contiguous()
+            return torch.matmul(x.flip(-1).contiguous(), self._wdq[key].t())
+        return torch.matmul(x, w.t())
+
     def _linear(self, x, prefix, add_bias=True):
         if self.tp > 1 and prefix.endswith(("linear_proj", "linear_fc2")):
             K = x.shape[-1]
@@ -463,13 +476,13 @@ class GPTOracle:
         if self.fp8 == "mxfp8":
             if prefix not in self._wdq:
                 self._wdq[prefix] = dequantize_mxfp8(*quantize_mxfp8(self.w[prefix + ".weight"]))
-            y = torch.matmul(dequantize_mxfp8(*quantize_mxfp8(x)), self._wdq[prefix].t()).to(x.dtype)
+            y = self._mm(dequantize_mxfp8(*quantize_mxfp8(x)), self._wdq[prefix]).to(x.dtype)
         elif self.fp8 == "blockwise":
             if prefix not in self._wdq:
                 self._wdq[prefix] = dequantize_fp8_block_weight(*quantize_fp8_block_weight(self.w[prefix + ".weight"]))
-            y = torch.matmul(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x)), self._wdq[prefix].t()).to(x.dtype)
+            y = self._mm(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x)), self._wdq[prefix]).to(x.dtype)
         else:
-            y = torch.matmul(x, self.w[prefix + ".weight"].t())  # layers.py:333
+            y = self._mm(x, self.w[prefix + ".weight"])  # layers.py:333
         b = self.w.get(prefix + ".bias")
         if add_bias and b is not None:
             y = y + b
@@ -480,12 +493,12 @@ class GPTOracle:
         if self.fp8 == "mxfp8":
             if key not in self._wdq:
                 self._wdq[key] = dequantize_mxfp8(*quantize_mxfp8(w.contiguous()))
-            return torch.matmul(dequantize_mxfp8(*quantize_mxfp8(x.contiguous())), self._wdq[key].t()).to(x.dtype)
+            return self._mm(dequantize_mxfp8(*quantize_mxfp8(x.contiguous())), self._wdq[key]).to(x.dtype)
         if self.fp8 == "blockwise":
             if key not in self._wdq:
                 self._wdq[key] = dequantize_fp8_block_weight(*quantize_fp8_block_weight(w.contiguous()))
-            return torch.matmul(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x.contiguous())), self._wdq[key].t()).to(x.dtype)
-        return torch.matmul(x, w.t())
+            return self._mm(dequantize_fp8_rowblock(*quantize_fp8_rowblock(x.contiguous())), self._wdq[key]).to(x.dtype)
+        return self._mm(x, w)
 
     def forward(self) -> torch.Tensor:
         """Returns last-token logits [active requests, vocab] in the parameter dtype."""
@@ -540,7 +553,7 @@ class GPTOracle:
         x = self._norm(x, "decoder.final_layernorm")
         P, Tt = c.paused_request_count, c.total_request_count
         last = torch.from_numpy(np.cumsum(c.request_query_lengths[P:Tt]) - 1).long()  # dynamic_context.py:890-918
-        return torch.matmul(x[last], w["output_layer.weight"].t())
+        return self._mm(x[last], w["output_layer.weight"])
 
 
 # ======================================================================================

@@ -389,3 +389,25 @@ def test_steady_state_shortcut_of_update_requests_equals_the_general_path():
         assert (a.total_request_count, a.paused_request_count, a.active_token_count) == (
             b.total_request_count, b.paused_request_count, b.active_token_count)
         assert torch.equal(a.chunk_allocator.chunk_bag, b.chunk_allocator.chunk_bag)
+
+
+def test_rejected_admission_leaves_the_state_version_alone():
+    # A request that does not fit (and is retried by the engine after every step) must not look like a change of the
+    # set of requests: the version guards the block table on the device and the forward that is enqueued early.
+    set_rounder(1)
+    c = make_ctx(num_layers=2, kv_channels=64, num_attention_heads=8, max_sequence_length=128, buffer_size_gb=0.01,
+                 chunk_size_tokens=32, max_requests_override=2)
+    c.add_request(0, torch.zeros(10, dtype=torch.int64))
+    c.add_request(1, torch.zeros(10, dtype=torch.int64))
+    v = c.state_version
+    for _ in range(3):
+        with pytest.raises(RequestOverflowError):
+            c.add_request(2, torch.zeros(10, dtype=torch.int64))
+        assert c.state_version == v
+    c.update_requests(np.array([1, 0], dtype=np.uint8), np.array([7, 8]))  # request 1 finishes: a row is free again
+    v = c.state_version
+    with pytest.raises(MaxSequenceLengthOverflowError):
+        c.add_request(3, torch.zeros(10, dtype=torch.int64), 1000)
+    assert c.state_version == v
+    c.add_request(2, torch.zeros(10, dtype=torch.int64))
+    assert c.state_version == v + 1

@@ -79,7 +79,7 @@ def test_quantize_mxfp8_bit_exact(ops, rows, K):
 def test_gemm_mxfp8_matches_dequantised_product(ops, M, N, K, bias):
     x, w = randn((M, K), 1), randn((N, K), 2, 0.05)
     b = randn((N,), 3) if bias else None
-    xq, wq = ops.quantize_mxfp8(x.cuda()), ops.quantize_mxfp8(w.cuda())
+    xq, wq = ops.quantize_mxfp8(x.cuda()), ops.quantize_mxfp8_weight(w.cuda())
     y = ops.gemm_mxfp8(xq, wq, None if b is None else b.cuda())
     xd = O.dequantize_mxfp8(*O.quantize_mxfp8(x))
     wd = O.dequantize_mxfp8(*O.quantize_mxfp8(w))
@@ -93,6 +93,18 @@ def test_gemm_mxfp8_matches_dequantised_product(ops, M, N, K, bias):
     # and the FP8 format itself stays within the stated 2e-2 of the bf16 product
     assert rel_l2(y, x.float() @ w.float().t() + (0 if b is None else b.float())) < 4e-2
     assert torch.equal(ops.gemm_mxfp8(xq, wq, None if b is None else b.cuda()), y)
+
+
+@pytest.mark.parametrize("N,K", [(128, 128), (300, 512), (1024, 4096)])
+def test_mxfp8_weight_quantiser_is_the_row_quantiser_with_tile_major_bytes(ops, N, K):
+    w = randn((N, K), 4, 0.05).cuda()
+    rows, tiles = ops.quantize_mxfp8(w), ops.quantize_mxfp8_weight(w)
+    assert tiles.packed and not rows.packed
+    assert torch.equal(ops.weight_tiles_to_rows(tiles.q, N, K), rows.q)
+    idx = _sf_indices(N, K).to(rows.sf.device)
+    assert torch.equal(tiles.sf[idx], rows.sf[idx])
+    with pytest.raises(ops.B200Error):
+        ops.gemm_mxfp8(ops.quantize_mxfp8(randn((8, K), 5).cuda()), rows)  # row-major bytes are not a weight
 
 
 def test_fused_norm_and_activation_quantisers(ops):
@@ -128,7 +140,7 @@ def test_weight_block_quantiser_bit_exact(ops, N, K):
     t = ops.quantize_fp8_weight_block128(w.cuda())
     q_ref, s_ref = O.quantize_fp8_block_weight(w, 128)
     assert torch.equal(t.scale.cpu(), s_ref)
-    assert torch.equal(t.q.cpu(), q_ref.view(torch.uint8))
+    assert torch.equal(ops.weight_tiles_to_rows(t.q, N, K).cpu(), q_ref.view(torch.uint8))  # bytes are tile-major
 
 
 @pytest.mark.parametrize(
@@ -177,7 +189,7 @@ def test_fp8_splitk_partials_into_add_norm_equal_unfused(ops, recipe, M, N, K):
     r = randn((M, N), 3).cuda()
     g = (1 + randn((N,), 4, 0.02).float()).to(BF16).cuda()
     if recipe == "mxfp8":
-        xq, wq = ops.quantize_mxfp8(x), ops.quantize_mxfp8(w)
+        xq, wq = ops.quantize_mxfp8(x), ops.quantize_mxfp8_weight(w)
         y = ops.gemm_mxfp8(xq, wq)
         h_ref, t_ref = ops.add_norm_mxfp8(y, g, residual=r, want_hidden=True)
     else:
@@ -201,4 +213,79 @@ def test_fp8_splitk_partials_into_add_norm_equal_unfused(ops, recipe, M, N, K):
     h2, n2 = ops.add_norm_splitk(p, g, residual=r, want_hidden=True)
     _, n_ref = ops.add_norm(y, g, residual=r, want_hidden=True)
     assert torch.equal(h2, h_ref) and torch.equal(n2, n_ref)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(128, 512, 1024), (64, 256, 512), (17, 128, 256), (200, 384, 640), (128, 14336 // 8, 4096)])
+@pytest.mark.parametrize("quantize", [True, False])
+def test_mxfp8_gate_up_pair_gemm_equals_gemm_then_activation(M, F, K, quantize):
+    # fc1 + SwiGLU (+ quantisation) in one kernel against the unfused pair: the same bits whenever the unfused GEMM
+    # accumulates K in one piece too (a split-K GEMM adds its partial sums in another order: fp32 rounding noise)
+    from megatron_mixtera_b200 import ops
+
+    exact = ops.gemm_num_splits("mxfp8", M, 2 * F, K) == 1
+
+    x = ops.quantize_mxfp8(randn((M, K), 5).cuda())
+    w = ops.quantize_mxfp8_weight(randn((2 * F, K), 6, 0.05).cuda())
+    y = ops.gemm_mxfp8(x, w)
+    if quantize:
+        ref = ops.activation_mxfp8(y, "swiglu")
+        got = ops.gemm_mxfp8_swiglu(x, w)
+        torch.cuda.synchronize()
+        # scale bytes of the rows that exist (the tile layout pads rows to 256)
+        assert got.sf.numel() == ref.sf.numel()
+        idx = _sf_indices(M, F).to(got.sf.device)
+        if exact:
+            assert torch.equal(got.q[:M], ref.q[:M])
+            assert torch.equal(got.sf[idx], ref.sf[idx])
+        else:
+            assert float((got.q[:M] != ref.q[:M]).float().mean()) < 2e-3
+            assert float((got.sf[idx] != ref.sf[idx]).float().mean()) < 2e-3
+    else:
+        ref = ops.activation(y, "swiglu")
+        got = ops.gemm_mxfp8_swiglu(x, w, quantize=False)
+        torch.cuda.synchronize()
+        if exact:
+            assert torch.equal(got, ref)
+        else:
+            assert float((got != ref).float().mean()) < 2e-3 and rel_l2(got, ref) < 1e-3
+    assert ops.device_status() == 0
+
+
+def _sf_indices(rows, K):
+    """Flat positions, in the tile layout, of the scale bytes of rows [0, rows) x K / 32 blocks."""
+    r = torch.arange(rows)[:, None]
+    b = torch.arange(K // 32)[None, :]
+    off = (r // 128) * (K // 128) * 512 + (b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (b % 4)
+    return off.reshape(-1)
+
+
+@pytest.mark.parametrize("recipe", [None, "mxfp8", "blockwise"])
+@pytest.mark.parametrize("M,F,K", [(64, 256, 4096), (128, 512, 2048)])
+def test_activation_reduces_fc1_split_k_partials(recipe, M, F, K):
+    # fc1 split along K: the activation kernel sums the partial sums itself (no reduction launch); same bits
+    from megatron_mixtera_b200 import ops
+
+    xb, wb = randn((M, K), 7).cuda(), randn((2 * F, K), 8, 0.05).cuda()
+    if recipe == "mxfp8":
+        x, w = ops.quantize_mxfp8(xb), ops.quantize_mxfp8_weight(wb)
+        ref = ops.activation_mxfp8(ops.gemm_mxfp8(x, w), "swiglu")
+    elif recipe == "blockwise":
+        x, w = ops.quantize_fp8_rowblock(xb), ops.quantize_fp8_weight_block128(wb)
+        ref = ops.activation_fp8_rowblock(ops.gemm_fp8_block(x, w), "swiglu")
+    else:
+        x, w = xb, wb
+        ref = ops.activation(ops.gemm(x, w), "swiglu")
+    assert ops.gemm_num_splits(recipe, M, 2 * F, K) > 1
+    got = ops.activation_splitk(ops.gemm_splitk(x, w), "swiglu", quantize=recipe)
+    torch.cuda.synchronize()
+    if recipe is None:
+        assert torch.equal(got, ref)
+    else:
+        assert torch.equal(got.q[:M], ref.q[:M])
+        if recipe == "blockwise":
+            assert torch.equal(got.scale[:, :M], ref.scale[:, :M])
+        else:
+            idx = _sf_indices(M, F).to(got.sf.device)
+            assert torch.equal(got.sf[idx], ref.sf[idx])
     assert ops.device_status() == 0

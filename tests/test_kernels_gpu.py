@@ -112,6 +112,35 @@ def test_splitk_partials_into_add_norm_equal_unfused(ops, M, N, K, norm):
     assert ops.device_status() == 0
 
 
+def test_workspace_growth_after_graph_capture_leaves_the_captured_buffer_alive(ops):
+    # A captured graph has the split-K workspace address baked in.  A later, larger eager GEMM makes the workspace
+    # grow; the old buffer must stay allocated, or replays would write partial sums into memory that the caching
+    # allocator has handed to someone else.
+    x, w = randn((64, 4096), 1).cuda(), randn((4096, 4096), 2, 0.05).cuda()
+    ref = ops.gemm(x, w)  # eager warm-up sizes the workspace for this shape
+    torch.cuda.synchronize()
+    small = ops._workspace._buf[(x.device.index, "gemm")]
+    out = torch.empty_like(ref)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.gemm(x, w, out=out)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    big_bytes = small.numel() * 4 + (8 << 20)
+    ops._workspace.reserve(x.device, "gemm", big_bytes)  # what an eager prefill GEMM of many rows does
+    assert ops._workspace._buf[(x.device.index, "gemm")].numel() >= big_bytes
+    assert any(b is small for b in ops._workspace._retired)
+    # whatever is allocated now must not land on the old buffer: fill fresh tensors of that size with a pattern
+    canaries = [torch.full((small.numel(),), 0x5A, dtype=torch.uint8, device="cuda") for _ in range(4)]
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    for c in canaries:
+        assert bool((c == 0x5A).all())
+
+
 def test_splitk_partials_are_invalidated_by_the_next_gemm(ops):
     x, w = randn((8, 256), 1).cuda(), randn((256, 256), 2, 0.05).cuda()
     g = torch.ones(256, dtype=BF16, device="cuda")
@@ -346,7 +375,7 @@ def oracle_decode_attention(c):
     return out, kc, vc
 
 
-def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_order=None, qkv_from=None):
+def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_order=None, qkv_from=None, out_quantized=None):
     dev = "cuda"
     D = c["D"]
     cos = sin = None
@@ -365,12 +394,46 @@ def run_cuda_attention(ops, c, *, num_splits, fused, row_of_token=None, row_orde
         qkv=d["qkv"], k_cache=kc, v_cache=vc, block_table=d["block_table"], kv_seq_lengths=d["kv_lens"], out=out,
         num_q_heads=c["nq"], num_kv_heads=c["nkv"], head_dim=D, chunk_size=c["chunk"], token_to_pos_ids=d["pos"],
         token_to_pos_in_request=d["pos"], token_to_chunk_idx=d["chunk_idx"], token_to_local_pos=d["local"],
-        rope_cos=cos, rope_sin=sin, num_splits=num_splits, fuse_rope_append=fused, row_of_token=d["row"], row_order=d["order"])
+        rope_cos=cos, rope_sin=sin, num_splits=num_splits, fuse_rope_append=fused, row_of_token=d["row"], row_order=d["order"],
+        out_quantized=out_quantized)
     if not fused:
         ops.rope_append(args)
     ops.paged_attention(args)
     torch.cuda.synchronize()
     return out.cpu().view(c["T"], c["nq"], D), kc.cpu(), vc.cpu()
+
+
+@pytest.mark.parametrize("nkv,G,D,chunk,kv_lens,splits", [
+    (2, 4, 128, 64, [1, 64, 65, 130, 0, 300, 17, 256], 1),
+    (2, 4, 128, 64, [1, 64, 65, 130, 0, 300, 17, 256], 4),
+    (8, 4, 128, 256, [2304, 128, 700, 1216, 0, 0], 4),
+    (4, 2, 64, 64, [33, 200, 64, 0], 1),
+    (4, 2, 64, 64, [33, 200, 64, 0], 2),
+])
+@pytest.mark.parametrize("recipe", ["mxfp8", "blockwise"])
+def test_decode_attention_writes_quantised_output(ops, nkv, G, D, chunk, kv_lens, splits, recipe):
+    # the kernel that finishes an output row quantises it for the out-projection: same bytes and scales as the
+    # stand-alone quantiser applied to the kernel's bf16 output
+    if recipe == "blockwise" and D != 128:
+        pytest.skip("the 128-block recipe takes one scale per head of 128 dims")
+    T = len(kv_lens)
+    c = make_paged_case(T=T, nkv=nkv, G=G, D=D, chunk=chunk, kv_lens=kv_lens, seed=21)
+    out, _, _ = run_cuda_attention(ops, c, num_splits=splits, fused=True)
+    width = c["nq"] * D
+    ref_in = out.reshape(T, width).cuda()
+    ref = ops.quantize_mxfp8(ref_in) if recipe == "mxfp8" else ops.quantize_fp8_rowblock(ref_in)
+    got = ops.quantized_like(recipe, T, width, "cuda")
+    got.q.fill_(0x7F)
+    nan_out, _, _ = run_cuda_attention(ops, c, num_splits=splits, fused=True, out_quantized=got)
+    assert torch.isnan(nan_out.float()).all()  # the bf16 output was not written
+    assert torch.equal(got.q[:T].cpu(), ref.q[:T].cpu())
+    if recipe == "mxfp8":
+        r = torch.arange(T)[:, None]
+        b = torch.arange(width // 32)[None, :]
+        idx = ((r // 128) * (width // 128) * 512 + (b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (b % 4)).reshape(-1)
+        assert torch.equal(got.sf.cpu()[idx], ref.sf.cpu()[idx])
+    else:
+        assert torch.equal(got.scale[:, :T].cpu(), ref.scale[:, :T].cpu())
 
 
 @pytest.mark.parametrize(

@@ -38,7 +38,8 @@ def build_cuda_stack(meta, enable_cuda_graph=False, num_cuda_graphs=None):
         enable_cuda_graph=enable_cuda_graph, inference_sampling_seed=0, tensor_model_parallel_size=meta.get("tp", 1),
         fp8=meta.get("fp8"), fuse_splitk_reduction_into_norm=meta.get("fuse_splitk", True),
         fuse_tp_allreduce_into_norm=meta.get("fuse_tp", True), fuse_swiglu_into_fc1=meta.get("fuse_swiglu", True),
-        fuse_qkv_reduction_into_attention=meta.get("fuse_qkv", True))
+        fuse_qkv_reduction_into_attention=meta.get("fuse_qkv", True),
+        fuse_attention_output_quantization=meta.get("fuse_attn_quant", True))
     model = GPTModel(cfg, vocab_size=meta["vocab_size"], max_sequence_length=meta["max_sequence_length"],
                      position_embedding_type="rope" if llama else "learned_absolute",
                      rotary_base=meta.get("rotary_base", 10000))
@@ -173,7 +174,7 @@ def test_llama_tiny_cuda_graph_replay_is_bit_identical_to_eager():
         assert torch.equal(lg, s_graph["logits"][step])
 
 
-@pytest.mark.parametrize("fp8", [None, "mxfp8"])
+@pytest.mark.parametrize("fp8", [None, "mxfp8", "blockwise"])
 def test_llama_tiny_fusion_switches_change_no_bit(fp8):
     # handing the split-K partial sums of out-proj / fc2 to the norm kernel, and running fc1 + SwiGLU on the
     # interleaved weight layout, are pure launch-count optimisations
@@ -181,7 +182,7 @@ def test_llama_tiny_fusion_switches_change_no_bit(fp8):
     meta = json.loads(str(z["meta"]))
     meta["fp8"] = fp8
     s_fused, _, _ = run_teacher_forced(dict(meta, fuse_splitk=True, fuse_swiglu=True, fuse_qkv=True), z)
-    s_plain, _, _ = run_teacher_forced(dict(meta, fuse_splitk=False, fuse_swiglu=False, fuse_qkv=False), z)
+    s_plain, _, _ = run_teacher_forced(dict(meta, fuse_splitk=False, fuse_swiglu=False, fuse_qkv=False, fuse_attn_quant=False), z)
     assert len(s_fused["logits"]) > 5
     for step, lg in s_plain["logits"].items():
         assert torch.equal(lg, s_fused["logits"][step])
@@ -315,3 +316,47 @@ def test_engine_generate_free_running(overlap):
     for other in _FREE_RUNS.values():  # the early enqueue of the next forward changes no token
         assert tokens == other
     _FREE_RUNS[overlap] = tokens
+
+
+def test_waiting_request_does_not_cost_a_second_forward_per_step():
+    # One request waits in the engine's queue for the whole run (the context has no free row for it) and is retried
+    # after every step.  The retries must not invalidate the forward that the controller enqueued early: one graph
+    # replay per decode step, same tokens as without the queued request.
+    from megatron_mixtera_b200.inference.engines.dynamic_engine import DynamicInferenceEngine
+    from megatron_mixtera_b200.inference.sampling_params import SamplingParams
+
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = json.loads(str(z["meta"]))
+    n = len(meta["prompt_lengths"])
+    runs = {}
+    for extra in (0, 1):
+        model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
+        ctl = Controller(wrapper, types.SimpleNamespace(vocab_size=meta["vocab_size"], detokenize=lambda t: ""))
+        engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=0, overlap_host_and_device=True)
+        sp = SamplingParams(top_k=1, num_tokens_to_generate=meta["num_tokens_to_generate"])
+        cap = ctx.max_requests
+        assert cap >= n
+        for i in range(cap):  # fill every row of the context (the fixture's prompts, then copies of the shortest)
+            prompt = z[f"prompt_{i}"] if i < n else z[f"prompt_{int(np.argmin(meta['prompt_lengths']))}"]
+            engine.add_request(i, torch.from_numpy(prompt), meta["num_tokens_to_generate"])
+        assert not engine.waiting_request_ids and ctx.total_request_count == cap
+        if extra:
+            engine.add_request(cap, torch.from_numpy(z["prompt_0"]), meta["num_tokens_to_generate"])
+            assert list(engine.waiting_request_ids) == [cap]
+        tokens = {i: [] for i in range(n)}
+        decode_steps = 0
+        engine.step_modern(sp)  # prefill
+        replays0 = wrapper.graph_replays
+        for _ in range(6):
+            assert ctx.is_decode_only()
+            r = engine.step_modern(sp)
+            decode_steps += 1
+            for req in r["active_requests"]:
+                if req.request_id < n:
+                    tokens[req.request_id] = list(req.generated_tokens)
+            if extra:
+                assert list(engine.waiting_request_ids) == [cap]
+        # the early forward of step k+1 is enqueued inside step k: one replay per step (+ the one in flight)
+        runs[extra] = (tokens, wrapper.graph_replays - replays0, decode_steps)
+    assert runs[0][0] == runs[1][0]
+    assert runs[1][1] == runs[0][1] <= runs[0][2] + 1, runs
