@@ -42,6 +42,11 @@ const char* b200_error_string(int code);
  * 0 = no kernel has given up since the last reset.
  */
 int b200_device_status(int reset, int* status_out);
+/* Bound, in nanoseconds, of every device-side wait of the library on the current device (mbarrier waits inside a
+ * CTA, waits for a tensor-parallel peer's flag).  Default 2 s.  When a wait runs out the kernel records a code in the
+ * status word (1 GEMM pipeline, 2 attention pipeline, 4 tensor-parallel peer), carries on without the missing data
+ * and ends normally, so the context stays usable.  Not to be changed while kernels are in flight. */
+int b200_set_wait_limit_ns(uint64_t limit_ns);
 /* `rows` rows of `width_bytes` from (pinned) host memory to the device in ONE asynchronous copy: the per-step index
  * arrays of the context (token -> position / chunk / slot, lengths; dynamic_context.py:656-825, 1284-1296) are rows
  * of one staging matrix, and a step updates the first n entries of each. */
@@ -289,6 +294,34 @@ int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, con
                                          float* scale_out, int m_pad, int rows, int hidden, float eps,
                                          b200_stream_t stream);
 
+/*
+ * Two-shot form of the same fusion, for larger groups (the reference's symmetric-memory all-reduce has the same
+ * choice: `two_shot` / `one_shot`, megatron/training/arguments.py:1437-1442).  The token rows are divided among the
+ * ranks (rank r owns rows [r * ceil(rows / w), ...)); a rank sums ITS rows from all ranks' `in` buffers (peer loads),
+ * adds bias + residual, normalises (+ quantises: q_mode 0 bf16, 1 MXFP8, 2 the 128-block recipe) and stores the
+ * finished rows into EVERY rank's output buffers (peer stores): `hidden_out` [max_rows][hidden] bf16, `normed_out`
+ * ([max_rows][hidden] bf16, or E4M3 bytes) and `scales_out` (MXFP8 tile-layout scale bytes of a [max_rows, hidden]
+ * matrix, or fp32 [hidden / 128][m_pad]).  Each row is computed exactly once, so all ranks hold identical bits.
+ * `flags[r]`: 16 int32 of rank r (zero-initialised, peer-mapped); `counters`: 2 local int32 (zeroed).  Two flag
+ * exchanges per call (inputs complete / outputs stored), each wait bounded by b200_set_wait_limit_ns (device status
+ * 4 on expiry); the kernel completes only after every rank's rows have arrived, so later kernels on the stream may
+ * read the local output buffers.  `residual` is local memory and may be this rank's `hidden_out` buffer itself.
+ * One buffer of each kind is enough (no slot alternation); every rank must issue the same sequence of calls.
+ */
+typedef struct {
+  int32_t world_size, rank;
+  int32_t max_rows, hidden;
+  int32_t m_pad;           /* row stride of the fp32 scale matrix (q_mode 2): >= max_rows, multiple of 4 */
+  void* in[8];             /* in[r]: rank r's partial GEMM output [max_rows][hidden] bf16; in[rank] is local */
+  void* hidden_out[8];
+  void* normed_out[8];
+  void* scales_out[8];     /* may be NULL when q_mode 0 is the only mode used */
+  int32_t* flags[8];
+  int32_t* counters;
+} b200_tp_exchange;
+int b200_allreduce2_add_norm(const b200_tp_exchange* comm, const void* bias, const void* residual, const void* gamma,
+                             const void* beta, int q_mode, int rows, int hidden, float eps, b200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.
  *
@@ -393,6 +426,15 @@ int b200_paged_prefill_attention(const b200_attention_args* args, const int32_t*
  *   <= top_p.  Computed in fp32 (the reference's cumulative sum runs in the logits' dtype).
  */
 int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int vocab, b200_stream_t stream);
+/* Greedy sampling over VOCAB-PARALLEL logits without gathering them (the reference all-gathers [B, V/tp] logits on
+ * every step, megatron/core/tensor_parallel/layers.py:1037-1039 -> mappings.py:80-96, and then takes the argmax of the
+ * full row).  b200_argmax_shard_bf16: per row of this rank's shard [rows, vocab_shard] one 64-bit key =
+ * (order-preserving code of the largest value << 32) | (2^32 - 1 - (index_offset + its smallest index)).  The keys of
+ * all ranks ([shards][rows], 8 bytes per row and rank - an all-gather of a few KB) go to b200_argmax_merge, whose
+ * maximum per row is the token torch.argmax would pick on the gathered row (ties: smallest index). */
+int b200_argmax_shard_bf16(const void* logits, int64_t ld, uint64_t* keys, int rows, int vocab, int64_t index_offset,
+                           b200_stream_t stream);
+int b200_argmax_merge(const uint64_t* keys, int shards, int rows, int64_t* out, b200_stream_t stream);
 int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,
                          float temperature, b200_stream_t stream);
 int b200_topp_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, float top_p,

@@ -15,6 +15,7 @@ EXPORTED_SYMBOLS = (
     "b200_version",
     "b200_error_string",
     "b200_device_status",
+    "b200_set_wait_limit_ns",
     "b200_copy_rows_h2d",
     "b200_gather_rows_bf16",
     "b200_add_norm_bf16",
@@ -60,12 +61,15 @@ EXPORTED_SYMBOLS = (
     "b200_allreduce_add_norm_bf16",
     "b200_allreduce_add_norm_mxfp8",
     "b200_allreduce_add_norm_fp8_rowblock",
+    "b200_allreduce2_add_norm",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
     "b200_paged_prefill_attention",
     "b200_fp8_value_position",
     "b200_argmax_bf16",
+    "b200_argmax_shard_bf16",
+    "b200_argmax_merge",
     "b200_topk_probs_bf16",
     "b200_topp_probs_bf16",
 )
@@ -122,6 +126,24 @@ class TpComm(ctypes.Structure):
         ("max_rows", c_int32),
         ("hidden", c_int32),
         ("data", c_void_p * 8),
+        ("flags", c_void_p * 8),
+        ("counters", c_void_p),
+    ]
+
+
+class TpExchange(ctypes.Structure):
+    """Mirror of ``b200_tp_exchange``."""
+
+    _fields_ = [
+        ("world_size", c_int32),
+        ("rank", c_int32),
+        ("max_rows", c_int32),
+        ("hidden", c_int32),
+        ("m_pad", c_int32),
+        ("in_", c_void_p * 8),
+        ("hidden_out", c_void_p * 8),
+        ("normed_out", c_void_p * 8),
+        ("scales_out", c_void_p * 8),
         ("flags", c_void_p * 8),
         ("counters", c_void_p),
     ]
@@ -224,6 +246,9 @@ def load() -> ctypes.CDLL:
                                                   c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
     lib.b200_allreduce_add_norm_fp8_rowblock.argtypes = [POINTER(TpComm), c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    lib.b200_allreduce2_add_norm.argtypes = [POINTER(TpExchange), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_float, c_void_p]
+    lib.b200_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.b200_rope_append.argtypes = [POINTER(AttentionArgs), c_void_p]
@@ -231,6 +256,8 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_value_position.argtypes = [c_int]
     lib.b200_paged_prefill_attention.argtypes = [POINTER(AttentionArgs), c_void_p, c_int, c_void_p]
     lib.b200_argmax_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]
+    lib.b200_argmax_shard_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int64, c_void_p]
+    lib.b200_argmax_merge.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.b200_topk_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200_topp_probs_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_float, c_float, c_void_p]
     for name in EXPORTED_SYMBOLS:

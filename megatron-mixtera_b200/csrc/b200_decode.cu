@@ -8,4 +8,5 @@
 #include "attention.cu"
 #include "attention_fp8.cu"
 #include "elementwise.cu"
+#include "tp_exchange.cu"
 #include "sampling.cu"

@@ -155,6 +155,16 @@ int b200_device_status(int reset, int* status_out) {
   return B200_OK;
 }
 
+int b200_set_wait_limit_ns(uint64_t limit_ns) {
+  if (limit_ns == 0) return B200_ERR_INVALID_ARGUMENT;
+  const unsigned long long v = limit_ns;
+  if (cudaMemcpyToSymbol(b200::g_wait_limit_ns, &v, sizeof(v)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_ERR_LAUNCH;
+  }
+  return B200_OK;
+}
+
 int b200_copy_rows_h2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
                        b200_stream_t stream) {
   if (!dst || !src || width_bytes == 0 || rows == 0 || dst_pitch < width_bytes || src_pitch < width_bytes)

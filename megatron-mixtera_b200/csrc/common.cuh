@@ -18,6 +18,10 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------------
 // (The library is one translation unit, see b200_decode.cu, so the definition lives here.)
 __device__ int g_device_status = 0;
+// Bound of every device-side wait (mbarrier waits inside a CTA, waits for a tensor-parallel peer's flag), in
+// nanoseconds of %globaltimer.  2 s by default: far beyond any legitimate wait; b200_set_wait_limit_ns changes it
+// (per device), e.g. to a few milliseconds for a test that lets a wait run out.
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
 
 enum : int {
   kStatusGemmTimeout = 1,
@@ -84,8 +88,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` lives in shared memory; once any thread of the CTA has given up,
 // every later wait in that CTA returns at once, so a broken pipeline drains in bounded time
 // instead of hanging the device.  Returns false if the wait was abandoned.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait here
-
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int status_code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -97,7 +99,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     if ((++spins & 0x3ff) == 0) {
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > g_wait_limit_ns) {
         *abort_flag = 1;
         atomicExch(&g_device_status, status_code);
         return false;

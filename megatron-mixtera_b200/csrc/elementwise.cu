@@ -82,7 +82,7 @@ __device__ __forceinline__ void peer_row_handshake(const PeerSrc& ps, int row) {
     for (int q = 0; q < ps.world; ++q)
       if (q != ps.rank && ld_acquire_sys(ps.flags[ps.rank] + q * ps.max_rows + row) < call) all = false;
     if (all) return;
-    if (global_timer_ns() - t0 > 2000000000ull) {  // 2 s: give up, flag it, carry on with what is there
+    if (global_timer_ns() - t0 > g_wait_limit_ns) {  // give up, flag it, carry on with what is there
       atomicOr(&g_device_status, kStatusPeerTimeout);
       return;
     }

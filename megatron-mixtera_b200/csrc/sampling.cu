@@ -13,7 +13,8 @@ __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_
 
 // Greedy: largest value, smallest index among equal values (NaN never wins).
 __global__ void __launch_bounds__(kThreads)
-argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int64_t* __restrict__ out, int vocab) {
+argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int64_t* __restrict__ out, int vocab,
+              uint64_t* __restrict__ keys, int64_t index_offset) {
   pdl_launch_dependents();
   pdl_wait();
   const uint16_t* row = logits + static_cast<int64_t>(blockIdx.x) * ld;
@@ -55,8 +56,35 @@ argmax_kernel(const uint16_t* __restrict__ logits, int64_t ld, int64_t* __restri
         best_i = oi;
       }
     }
-    if (lane == 0) out[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+    if (lane == 0) {
+      const int idx = best_i == 0x7fffffff ? 0 : best_i;
+      if (keys == nullptr) {
+        out[blockIdx.x] = idx;
+      } else {
+        // Vocabulary shard: a 64-bit key whose maximum over the shards is the global greedy choice - the value's
+        // order-preserving 16-bit code (-0 counts as +0, as a float comparison does) above the complement of the global
+        // index, so that among equal values the smallest index wins.
+        uint16_t bits = best_i == 0x7fffffff ? 0xff80u : row[idx];  // a shard without a comparable value counts as -inf
+        if (bits == 0x8000u) bits = 0;
+        keys[blockIdx.x] = (static_cast<uint64_t>(bf16_key(bits)) << 32) |
+                           (0xffffffffull - static_cast<uint64_t>(index_offset + idx));
+      }
+    }
   }
+}
+
+// Greedy token per row from the per-shard keys [shards][rows] written by argmax_kernel.
+__global__ void argmax_merge_kernel(const uint64_t* __restrict__ keys, int shards, int rows, int64_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  uint64_t best = 0;
+  for (int s = 0; s < shards; ++s) {
+    const uint64_t k = keys[static_cast<int64_t>(s) * rows + r];
+    best = k > best ? k : best;
+  }
+  out[r] = static_cast<int64_t>(0xffffffffull - (best & 0xffffffffull));
 }
 
 // Top-k: the k-th largest value is found exactly by a two-pass radix select on the 16-bit keys
@@ -306,7 +334,25 @@ int b200_argmax_bf16(const void* logits, int64_t ld, int64_t* out, int rows, int
   using namespace b200;
   if (!logits || !out || rows <= 0 || vocab <= 0 || ld < vocab) return B200_ERR_INVALID_ARGUMENT;
   return launch_pdl(sampling::argmax_kernel, dim3(rows), dim3(sampling::kThreads), 0,
-                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, out, vocab);
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld, out, vocab,
+                    static_cast<uint64_t*>(nullptr), static_cast<int64_t>(0));
+}
+
+int b200_argmax_shard_bf16(const void* logits, int64_t ld, uint64_t* keys, int rows, int vocab, int64_t index_offset,
+                           b200_stream_t stream) {
+  using namespace b200;
+  if (!logits || !keys || rows <= 0 || vocab <= 0 || ld < vocab || index_offset < 0 || index_offset + vocab > 0xffffffffll)
+    return B200_ERR_INVALID_ARGUMENT;
+  return launch_pdl(sampling::argmax_kernel, dim3(rows), dim3(sampling::kThreads), 0,
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(logits), ld,
+                    static_cast<int64_t*>(nullptr), vocab, keys, index_offset);
+}
+
+int b200_argmax_merge(const uint64_t* keys, int shards, int rows, int64_t* out, b200_stream_t stream) {
+  using namespace b200;
+  if (!keys || !out || shards <= 0 || rows <= 0) return B200_ERR_INVALID_ARGUMENT;
+  return launch_pdl(sampling::argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0,
+                    reinterpret_cast<cudaStream_t>(stream), keys, shards, rows, out);
 }
 
 int b200_topk_probs_bf16(const void* logits, int64_t ld, float* probs, int rows, int vocab, int top_k,

@@ -50,13 +50,19 @@ class GPTInferenceWrapper:
     def prep_model_for_inference(self, prompts_tokens=None):
         self.model.eval()
 
+    def _gather_mode(self):
+        """``True`` = all-gather the vocabulary-parallel logits inside the forward, as the reference does
+        (``abstract_model_inference_wrapper.py:166``); ``"deferred"`` = hand the controller this rank's shard, which
+        greedy sampling reduces with 8 bytes per row and rank instead (config ``defer_logits_gather``)."""
+        return "deferred" if getattr(self.model.config, "defer_logits_gather", True) else True
+
     def _forward(self, inference_input):
         return self.model(inference_input["tokens"], inference_input["position_ids"], inference_input["attention_mask"],
-                          inference_context=self.inference_context, runtime_gather_output=True)
+                          inference_context=self.inference_context, runtime_gather_output=self._gather_mode())
 
     def _decode_rows(self, T: int):
         ctx = self.inference_context
-        return self.model.forward_rows(ctx.token_to_input_ids[:T], ctx.token_to_pos_ids[:T], ctx, None, True)
+        return self.model.forward_rows(ctx.token_to_input_ids[:T], ctx.token_to_pos_ids[:T], ctx, None, self._gather_mode())
 
     @torch.inference_mode()
     def run_one_forward_step(self, inference_input: Dict[str, Any]) -> torch.Tensor:

@@ -65,6 +65,10 @@ class TextGenerationController:
         assert top_p <= 1.0, "top-p should be in (0,1]"
         if sampling_params.top_n_logprobs > 0:
             raise NotImplementedError("top-n log-probabilities are outside the decode path built here")
+        if hasattr(last_token_logits, "greedy_tokens"):  # this rank's vocabulary shard (tensor parallel)
+            if top_k == 1:
+                return last_token_logits.greedy_tokens()
+            last_token_logits = last_token_logits.gather()  # everything else samples from the full rows
         if top_k == 1:
             return ops.argmax(last_token_logits)
         if top_k > 1 or (top_k == 0 and top_p == 0.0):
@@ -109,6 +113,8 @@ class TextGenerationController:
             input_ids, position_ids = context.current_input_and_position_ids()
             logits = self.inference_wrapped_model.run_one_forward_step(
                 {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None})
+        if hasattr(logits, "gather") and (not materialize_last or sampling_params.return_log_probs):
+            logits = logits.gather().unsqueeze(0)  # every token's logits / log-probs are wanted: the full rows
         cuda_graph_request_count = context.padded_active_request_count if context.is_decode_only() else None
         await asyncio.sleep(0)  # the forward is enqueued; let other coroutines run
 

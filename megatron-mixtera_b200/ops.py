@@ -81,7 +81,7 @@ def _gemm_workspace(device, nbytes: int, count_reduction: bool = False) -> torch
     return _workspace.get(device, "gemm", nbytes)
 
 
-_NOT_A_LAUNCH = ("b200_device_status", "b200_copy_rows_h2d")
+_NOT_A_LAUNCH = ("b200_device_status", "b200_copy_rows_h2d", "b200_set_wait_limit_ns")
 
 
 def check(fn_name: str, code: int) -> None:
@@ -90,6 +90,11 @@ def check(fn_name: str, code: int) -> None:
     _lib.check(fn_name, code)
     if fn_name not in _NOT_A_LAUNCH:
         launch_count += 1
+
+
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """Bound of the library's device-side waits on the current device (default 2 s)."""
+    check("b200_set_wait_limit_ns", _lib.load().b200_set_wait_limit_ns(int(limit_ns)))
 
 
 def device_status(reset: bool = False) -> int:
@@ -525,6 +530,13 @@ def allreduce_add_norm(pending, gamma, *, bias=None, residual=None, beta=None, e
     for d in pending.shape[:-1]:
         rows *= d
     dev = comm.device
+    if getattr(comm, "two_shot", False):
+        # every rank finishes its share of the rows and stores them into all ranks' buffers: the results are views of
+        # this rank's buffers (valid until the next call through the same communicator)
+        q_mode = {None: 0, "mxfp8": 1, "blockwise": 2}[quantize]
+        check("b200_allreduce2_add_norm", _lib.load().b200_allreduce2_add_norm(
+            ctypes.byref(comm.comm), _p(bias), _p(residual), _p(gamma), _p(beta), q_mode, rows, hidden, eps, _stream()))
+        return comm.hidden_view(pending.shape), comm.normed_view(rows, quantize, pending.shape)
     h = torch.empty(pending.shape, dtype=BF16, device=dev) if want_hidden else None
     lib = _lib.load()
     c = ctypes.byref(comm.comm)
@@ -673,6 +685,27 @@ def argmax(logits):
     out = torch.empty((rows,), dtype=torch.int64, device=logits.device)
     check("b200_argmax_bf16", _lib.load().b200_argmax_bf16(logits.data_ptr(), logits.stride(0), out.data_ptr(), rows,
                                                             vocab, _stream()))
+    return out
+
+
+def argmax_shard(logits, index_offset: int, keys=None):
+    """Per-row key of the largest logit of a vocabulary shard [rows, vocab_shard] (int64 bit patterns, see
+    `argmax_merge`); ``index_offset`` = first vocabulary id of the shard."""
+    _need(logits, BF16, "logits")
+    rows, vocab = logits.shape
+    if keys is None:
+        keys = torch.empty((rows,), dtype=torch.int64, device=logits.device)
+    check("b200_argmax_shard_bf16", _lib.load().b200_argmax_shard_bf16(
+        logits.data_ptr(), logits.stride(0), keys.data_ptr(), rows, vocab, int(index_offset), _stream()))
+    return keys
+
+
+def argmax_merge(keys):
+    """Greedy token per row from the shards' keys [shards, rows] -> int64 [rows]."""
+    _need(keys, torch.int64, "keys")
+    shards, rows = keys.shape
+    out = torch.empty((rows,), dtype=torch.int64, device=keys.device)
+    check("b200_argmax_merge", _lib.load().b200_argmax_merge(keys.data_ptr(), shards, rows, out.data_ptr(), _stream()))
     return out
 
 

@@ -20,6 +20,57 @@ def _device():
     return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
 
 
+class VocabParallelLogits:
+    """This rank's shard ``[rows, V / tp]`` of the output layer's logits, standing in for the gathered ``[rows, V]``
+    tensor that the reference materialises on every step (``layers.py:1037-1039``).  Greedy sampling needs 8 bytes per
+    row and rank (`TextGenerationController.sample_from_logits`); everything else calls `gather()` (or `float()`),
+    which is the reference's all-gather.  Implements the few tensor methods the wrapper / controller path uses."""
+
+    def __init__(self, local: torch.Tensor, vocab_start: int, vocab_size: int, group=None):
+        self.local, self.vocab_start, self.vocab_size, self.group = local, int(vocab_start), int(vocab_size), group
+
+    @property
+    def shape(self):
+        return (self.local.shape[0], self.vocab_size)
+
+    @property
+    def device(self):
+        return self.local.device
+
+    def size(self, dim=None):
+        return self.shape if dim is None else self.shape[dim]
+
+    def __getitem__(self, rows):
+        if not isinstance(rows, slice):
+            raise TypeError("vocabulary-parallel logits can be sliced along the rows only")
+        return VocabParallelLogits(self.local[rows], self.vocab_start, self.vocab_size, self.group)
+
+    def unsqueeze(self, dim):
+        return self
+
+    squeeze = unsqueeze
+
+    def contiguous(self):
+        return self
+
+    def gather(self) -> torch.Tensor:
+        """The full ``[rows, V]`` logits (all-gather over the tensor-parallel group)."""
+        return gather_from_tensor_model_parallel_region(self.local, self.group)
+
+    def float(self) -> torch.Tensor:
+        return self.gather().float()
+
+    def greedy_tokens(self) -> torch.Tensor:
+        """argmax over the whole vocabulary (ties: smallest id) without gathering the logits: per-shard
+        (value, index) keys, an all-gather of 8 bytes per row and rank, then the maximum key."""
+        tp = parallel_state.get_tensor_model_parallel_world_size()
+        local = self.local if self.local.is_contiguous() else self.local.contiguous()
+        keys = ops.argmax_shard(local, self.vocab_start)
+        allk = torch.empty((tp, keys.shape[0]), dtype=torch.int64, device=keys.device)
+        torch.distributed.all_gather_into_tensor(allk, keys, group=self.group or parallel_state.get_tensor_model_parallel_group())
+        return ops.argmax_merge(allk)
+
+
 class _ParallelLinearBase(torch.nn.Module):
     """Shared by the column- and row-parallel linears: optional MXFP8 execution.
 
@@ -133,7 +184,12 @@ class ColumnParallelLinear(_ParallelLinearBase):
             return self._matmul(input_, w, None, defer_reduction=True), (self.bias if self.skip_bias_add else None)
         out = self._matmul(input_, w, fuse_bias)
         gather = self.gather_output if runtime_gather_output is None else runtime_gather_output
-        if gather:
+        if gather == "deferred":  # hand out the shard; the consumer gathers only if it needs the full rows
+            if parallel_state.get_tensor_model_parallel_world_size() > 1:
+                per = self.output_size_per_partition
+                out = VocabParallelLogits(out.view(-1, per), parallel_state.get_tensor_model_parallel_rank() * per,
+                                          self.output_size, self.tp_group)
+        elif gather:
             out = gather_from_tensor_model_parallel_region(out, self.tp_group)
         return out, (self.bias if self.skip_bias_add else None)
 

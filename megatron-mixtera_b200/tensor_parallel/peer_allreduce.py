@@ -77,6 +77,20 @@ class PeerAllReduce:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every rank has mapped every buffer before anyone uses them
 
+    two_shot = False
+
+    def begin_forward(self) -> None:
+        """Called where a forward pass starts (and its CUDA graph, if any): see `end_forward`."""
+        self._slot_at_entry = self._next_slot
+
+    def end_forward(self) -> None:
+        """The handshake only fences the call after next, so consecutive calls must use different slots - also across
+        replays of one captured forward, whose slots are baked in.  That holds iff a forward makes an even number of
+        calls (it then ends on the slot it did not start with): two per decoder layer.  Anything else is refused."""
+        if self._next_slot != getattr(self, "_slot_at_entry", self._next_slot):
+            raise RuntimeError("a forward pass made an odd number of fused all-reduce calls: replays of its CUDA graph "
+                               "would use the same peer slot twice in a row; use the two-shot exchange or NCCL")
+
     def output_slot(self, rows: int):
         """(slot index, [rows, hidden] bf16 view of this rank's slot) for the next call; slots alternate."""
         assert rows <= self.max_rows
@@ -94,28 +108,126 @@ class PeerAllReduce:
         self._opened, self._own = [], []
 
 
-_COMM: Optional[PeerAllReduce] = None
+class PeerExchange:
+    """Two-shot form: peer buffers for the ranks' partial outputs AND for the finished rows.  Every rank reduces,
+    normalises and (for an FP8 recipe) quantises only its share of the token rows and stores them into all ranks'
+    output buffers (`b200_allreduce2_add_norm`).  The results of a call live in this object's buffers until the next
+    call overwrites them: `hidden` (the residual stream) is rewritten in place row by row, the normalised rows are
+    consumed by the linear that follows.  Creation is a collective."""
+
+    two_shot = True
+
+    def begin_forward(self) -> None:  # one buffer, two flag exchanges per call: any number of calls per forward is safe
+        pass
+
+    end_forward = begin_forward
+
+    def __init__(self, group, rank: int, world_size: int, max_rows: int, hidden: int, device: torch.device):
+        import torch.distributed as dist
+
+        if not 2 <= world_size <= 8:
+            raise ValueError("peer exchange supports 2..8 ranks")
+        self.group, self.rank, self.world_size = group, rank, world_size
+        self.max_rows, self.hidden, self.device = int(max_rows), int(hidden), device
+        lib = _lib.load()
+        self._lib = lib
+        self.m_pad = (self.max_rows + 3) // 4 * 4
+        row_bytes = self.max_rows * self.hidden
+        sf_bytes = max(lib.b200_mxfp8_scale_bytes(self.max_rows, self.hidden) if self.hidden % 128 == 0 else 0,
+                       (self.hidden // 128) * self.m_pad * 4, 16)
+        # in (bf16), hidden_out (bf16), normed_out (bf16 or E4M3 bytes), scales_out, flags (2 x 8 int32, one 128-byte line each way)
+        self._sizes = (2 * row_bytes, 2 * row_bytes, 2 * row_bytes, sf_bytes, 256)
+        self._own, handles = [], []
+        for nbytes in self._sizes:
+            ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            _lib.check("b200_peer_buffer_create", lib.b200_peer_buffer_create(nbytes, ctypes.byref(ptr), handle))
+            self._own.append(ptr.value)
+            handles.append(handle.raw)
+        gathered = [None] * world_size
+        dist.all_gather_object(gathered, tuple(handles), group=group)
+        self._opened = []
+        comm = _lib.TpExchange()
+        comm.world_size, comm.rank, comm.max_rows, comm.hidden, comm.m_pad = world_size, rank, self.max_rows, self.hidden, self.m_pad
+        for r in range(world_size):
+            if r == rank:
+                ptrs = list(self._own)
+            else:
+                ptrs = []
+                for h in gathered[r]:
+                    ptr = ctypes.c_void_p()
+                    _lib.check("b200_peer_buffer_open", lib.b200_peer_buffer_open(h, ctypes.byref(ptr)))
+                    ptrs.append(ptr.value)
+                    self._opened.append(ptr.value)
+            comm.in_[r], comm.hidden_out[r], comm.normed_out[r], comm.scales_out[r], comm.flags[r] = ptrs
+        self._counters = torch.zeros(2, dtype=torch.int32, device=device)
+        comm.counters = self._counters.data_ptr()
+        self.comm = comm
+        wrap = lambda i: torch.as_tensor(_DeviceBytes(self._own[i], self._sizes[i]), device=device)
+        self._in = wrap(0).view(torch.bfloat16)
+        self._hidden = wrap(1).view(torch.bfloat16)
+        self._normed = wrap(2)
+        self._scales = wrap(3)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone uses them
+
+    def output_slot(self, rows: int):
+        """(0, [rows, hidden] bf16 view of this rank's input buffer): where the row-parallel GEMM writes."""
+        assert rows <= self.max_rows
+        return 0, self._in[: rows * self.hidden].view(rows, self.hidden)
+
+    def hidden_view(self, shape):
+        n = 1
+        for d in shape:
+            n *= d
+        return self._hidden[:n].view(shape)
+
+    def normed_view(self, rows: int, quantize, shape):
+        """The local copy of the finished normalised rows: bf16 tensor, `ops.Mxfp8Tensor` or `ops.Fp8BlockTensor`."""
+        from .. import ops
+
+        H = self.hidden
+        if quantize == "mxfp8":
+            nbytes = self._lib.b200_mxfp8_scale_bytes(rows, H)
+            return ops.Mxfp8Tensor(self._normed[: rows * H].view(rows, H), self._scales[:nbytes], shape)
+        if quantize == "blockwise":
+            scale = self._scales[: (H // 128) * self.m_pad * 4].view(torch.float32).view(H // 128, self.m_pad)
+            return ops.Fp8BlockTensor(self._normed[: rows * H].view(rows, H), scale, shape, self.m_pad)
+        return self._normed[: rows * H * 2].view(torch.bfloat16).view(shape)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            self._lib.b200_peer_buffer_close(p)
+        for p in self._own:
+            self._lib.b200_peer_buffer_destroy(p)
+        self._opened, self._own = [], []
 
 
-def get_peer_allreduce(hidden: int, rows: int, max_rows: int = 512, max_world: int = 4) -> Optional[PeerAllReduce]:
+_COMM = None
+
+
+# Groups of up to this many ranks use the one-shot form (every rank pulls every peer's rows: one flag exchange, w - 1
+# times the data per rank), larger ones the two-shot form (two exchanges, 2 (w - 1) / w of the data per rank).
+ONE_SHOT_MAX_WORLD = 2
+
+
+def get_peer_allreduce(hidden: int, rows: int, max_rows: int = 512):
     """The group's communicator (created on first use: a collective, so every rank must get here together), or None
-    when this output cannot go through it (more rows than a slot holds, a different width, capture in progress
+    when this output cannot go through it (more rows than a buffer holds, a different width, capture in progress
     before the first eager use)."""
     from .. import parallel_state
 
     global _COMM
     tp = parallel_state.get_tensor_model_parallel_world_size()
-    # Every rank pulls every peer's row: measured on config 1 the fused kernel wins at 2 ranks (4.44 vs 4.71 ms per
-    # step), ties at 4 (4.00 vs 4.02) and loses at 8 (5.61 vs 4.17, where NCCL reduces inside the switch), so larger
-    # groups stay on NCCL unless asked (`max_world`).
-    if tp < 2 or tp > max_world or rows > max_rows or hidden > 8192 or hidden % 8 != 0 or not torch.cuda.is_available():
+    if tp < 2 or tp > 8 or rows > max_rows or hidden > 8192 or hidden % 8 != 0 or not torch.cuda.is_available():
         return None
     if _COMM is None:
         if torch.cuda.is_current_stream_capturing():
             return None
         dev = torch.device("cuda", torch.cuda.current_device())
-        _COMM = PeerAllReduce(parallel_state.get_tensor_model_parallel_group(),
-                              parallel_state.get_tensor_model_parallel_rank(), tp, max_rows, hidden, dev)
+        cls = PeerAllReduce if tp <= ONE_SHOT_MAX_WORLD else PeerExchange
+        _COMM = cls(parallel_state.get_tensor_model_parallel_group(), parallel_state.get_tensor_model_parallel_rank(), tp,
+                    max_rows, hidden, dev)
     return _COMM if _COMM.hidden == hidden else None
 
 

@@ -41,6 +41,9 @@ class TransformerConfig:
     # not in the reference: under an FP8 recipe the decode attention kernel writes its output already quantised for the
     # out-projection (same bits as the stand-alone quantiser, one launch fewer per layer)
     fuse_attention_output_quantization: bool = True
+    # not in the reference: at TP > 1 the output layer hands the controller its vocabulary shard; greedy sampling then
+    # exchanges one (value, index) key per row and rank instead of all-gathering the logits (False: the reference's way)
+    defer_logits_gather: bool = True
     fp8: Optional[str] = None                   # None | "mxfp8" (E8M0 scale per 32) | "blockwise" (fp32, 128x128 / 1x128)
 
     def __post_init__(self):

@@ -661,3 +661,24 @@ def test_paged_attention_fp8_pool(ops, nkv, G, chunk, kv_lens, splits, fused, si
     # E4M3 terms each (~7 significant bits), far inside the 2^-4 resolution of the pool itself
     # (one term each: E4M3 queries and probabilities, 2^-4 resolution like the pool's own)
     assert rel_l2(o, ref) < (6e-2 if single_term else 6e-3), rel_l2(o, ref)
+
+
+@pytest.mark.parametrize("shards,vocab", [(2, 1000), (8, 128256), (4, 4096)])
+def test_shardwise_argmax_equals_argmax_of_the_gathered_rows(ops, shards, vocab):
+    rows = 37
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn((rows, vocab), generator=g).to(BF16)
+    per = vocab // shards
+    logits[0, :] = 1.5                      # all equal: index 0
+    logits[1, per - 1] = 9.0                # the maximum twice, in two shards: the smaller index wins
+    logits[1, per + 3] = 9.0
+    logits[2, :] = -0.0                     # signed zeros compare equal
+    logits[2, vocab - 1] = 0.0
+    logits[3, :] = float("-inf")
+    logits[4, vocab - 1] = 50.0             # last element of the last shard
+    ref = ops.argmax(logits.cuda())
+    keys = torch.stack([ops.argmax_shard(logits[:, s * per:(s + 1) * per].contiguous().cuda(), s * per) for s in range(shards)])
+    got = ops.argmax_merge(keys)
+    assert torch.equal(got, ref)
+    assert got[0] == 0 and got[1] == per - 1 and got[2] == 0 and got[3] == 0 and got[4] == vocab - 1
+    assert torch.equal(got.cpu(), torch.argmax(logits.float(), dim=-1))

@@ -84,3 +84,102 @@ def test_a_single_slot_is_not_enough():
         except AssertionError:
             failures += 1
     assert failures > 0
+
+
+def test_same_slot_twice_in_a_row_can_read_stale_data():
+    # What an odd number of calls per captured forward would do to the one-shot form: replays end and start on the
+    # same slot, the handshake only fences the call after next, and a fast rank overwrites what a slow peer still reads.
+    def program(rank, world, slot_of_call, slots, flags):
+        for k, s in enumerate(slot_of_call, start=1):
+            slots[rank][s] = (rank, k)
+            yield
+            for q in range(world):
+                if q != rank:
+                    flags[q][rank] = k
+                    yield
+            while any(flags[rank][q] < k for q in range(world) if q != rank):
+                yield
+            for q in range(world):
+                if slots[q][s] != (q, k):
+                    raise AssertionError("stale read")
+                yield
+
+    rng = random.Random(1)
+    failures = 0
+    for trial in range(300):
+        slots, flags = [[None, None], [None, None]], [[0, 0], [0, 0]]
+        progs = [program(r, 2, [0, 1, 0, 0, 1, 0], slots, flags) for r in range(2)]  # a 3-call forward replayed twice
+        live = [0, 1]
+        try:
+            while live:
+                r = 0 if (0 in live and rng.random() < 0.8) else rng.choice(live)
+                try:
+                    next(progs[r])
+                except StopIteration:
+                    live.remove(r)
+        except AssertionError:
+            failures += 1
+    assert failures > 0
+
+
+def two_shot_program(rank, world, calls, rows, inp, hidden, normed, flags_a, flags_b, log):
+    """csrc/tp_exchange.cu: ONE input buffer and ONE output buffer per rank, two flag exchanges per call."""
+    per = -(-rows // world)
+    mine = range(rank * per, min(rows, (rank + 1) * per))
+    for k in range(1, calls + 1):
+        for r in range(rows):                      # the GEMM writes this rank's partial output
+            inp[rank][r] = (rank, k, r)
+            yield
+        for q in range(world):                     # exchange A: announce, then wait
+            if q != rank:
+                flags_a[q][rank] = k
+                yield
+        while any(flags_a[rank][q] < k for q in range(world) if q != rank):
+            yield
+        for r in mine:                             # reduce my rows from every rank, add my residual, store everywhere
+            for q in range(world):
+                got = inp[q][r]
+                assert got == (q, k, r), f"rank {rank} call {k}: input row {r} of rank {q} holds {got}"
+                yield
+            res = hidden[rank][r]                  # the residual: the previous call's hidden row (in place)
+            assert res == (k - 1, r), f"rank {rank} call {k}: residual row {r} is {res}"
+            for q in range(world):
+                hidden[q][r] = (k, r)
+                normed[q][r] = (k, r)
+                yield
+        for q in range(world):                     # exchange B
+            if q != rank:
+                flags_b[q][rank] = k
+                yield
+        while any(flags_b[rank][q] < k for q in range(world) if q != rank):
+            yield
+        for r in range(rows):                      # the next GEMM reads all normalised rows of this call
+            assert normed[rank][r] == (k, r), f"rank {rank} after call {k}: normed row {r} is {normed[rank][r]}"
+            log.append((rank, k, r))
+            yield
+
+
+@pytest.mark.parametrize("world,rows", [(2, 5), (3, 7), (4, 8), (8, 16), (8, 3)])
+def test_two_shot_exchange_needs_one_buffer_only(world, rows):
+    rng = random.Random(10 * world + rows)
+    for trial in range(100):
+        calls = rng.randint(1, 6)
+        inp = [[None] * rows for _ in range(world)]
+        hidden = [[(0, r) for r in range(rows)] for _ in range(world)]
+        normed = [[None] * rows for _ in range(world)]
+        fa = [[0] * world for _ in range(world)]
+        fb = [[0] * world for _ in range(world)]
+        log = []
+        progs = [two_shot_program(r, world, calls, rows, inp, hidden, normed, fa, fb, log) for r in range(world)]
+        live = list(range(world))
+        favourite = rng.randrange(world)
+        steps = 0
+        while live:
+            r = favourite if (favourite in live and rng.random() < 0.7) else rng.choice(live)
+            try:
+                next(progs[r])
+            except StopIteration:
+                live.remove(r)
+            steps += 1
+            assert steps < 2000000, "deadlock"
+        assert len(log) == world * rows * calls

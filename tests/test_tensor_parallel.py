@@ -33,10 +33,16 @@ def test_tp2_cuda_stack_matches_tp1(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     one, two, two_nccl = str(tmp_path / "tp1.npz"), str(tmp_path / "tp2.npz"), str(tmp_path / "tp2_nccl.npz")
+    two_shot = str(tmp_path / "tp2_two_shot.npz")
     _torchrun(1, "cuda", one, 29621)
     _torchrun(2, "cuda", two, 29622)  # all-reduce fused into the norm kernel (peer loads)
     _torchrun(2, "cuda", two_nccl, 29623, TP_WORKER_NCCL_ALLREDUCE="1")
-    a, b, c = np.load(one), np.load(two), np.load(two_nccl)
+    _torchrun(2, "cuda", two_shot, 29624, TP_WORKER_TWO_SHOT="1")  # rows divided among the ranks, results stored to all
+    a, b, c, d = np.load(one), np.load(two), np.load(two_nccl), np.load(two_shot)
+    # one-shot and two-shot sum the ranks' rows in the same order with one rounding: identical bits
+    for k in b.files:
+        if k.endswith("_logits"):
+            assert np.array_equal(b[k], d[k]), k
     # the fused all-reduce sums in fp32 and rounds once, NCCL adds bf16 values: same function, bf16 noise apart
     rel_fn = [float((torch.from_numpy(b[k]) - torch.from_numpy(c[k])).norm() / torch.from_numpy(c[k]).norm())
               for k in b.files if k.endswith("_logits")]
@@ -76,6 +82,13 @@ def test_tp2_mxfp8_matches_the_fp8_oracle_at_tp2(tmp_path):
         np.savez(trace_path, **trace)
         _torchrun(tp, "cuda", out, port, TP_WORKER_FP8="mxfp8", TP_WORKER_TRACE=trace_path)
         got = np.load(out)
+        if tp == 2:  # the two-shot exchange emits the same quantised rows
+            out2 = str(tmp_path / "tp2_two_shot.npz")
+            _torchrun(tp, "cuda", out2, port + 10, TP_WORKER_FP8="mxfp8", TP_WORKER_TRACE=trace_path, TP_WORKER_TWO_SHOT="1")
+            got2 = np.load(out2)
+            for k in got.files:
+                if k.endswith("_logits"):
+                    assert np.array_equal(got[k], got2[k]), k
         rel = [float((torch.from_numpy(got[k]) - torch.from_numpy(trace[k]).float()).norm() / torch.from_numpy(trace[k]).float().norm())
                for k in got.files if k.endswith("_logits")]
         dist_to_oracle[tp] = (max(rel), sum(rel) / len(rel))

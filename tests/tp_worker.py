@@ -100,6 +100,10 @@ def cuda_mode(out_path):
     meta = json.loads(str(z["meta"]))
     meta["tp"] = world
     meta["fuse_tp"] = os.environ.get("TP_WORKER_NCCL_ALLREDUCE") != "1"  # default: all-reduce inside the norm kernel
+    if os.environ.get("TP_WORKER_TWO_SHOT") == "1":  # the two-shot exchange also for small groups
+        from megatron_mixtera_b200.tensor_parallel import peer_allreduce
+
+        peer_allreduce.ONE_SHOT_MAX_WORLD = 1
     if os.environ.get("TP_WORKER_FP8"):
         meta["fp8"] = os.environ["TP_WORKER_FP8"]  # "mxfp8" | "blockwise": FP8 linears, sharded per rank
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
@@ -111,6 +115,10 @@ def cuda_mode(out_path):
     class Forced(Controller):
         def sample_from_logits(self, last_token_logits, sampling_params=None, vocab_size=None, **kw):
             own = super().sample_from_logits(last_token_logits, sampling_params, vocab_size, **kw)
+            if hasattr(last_token_logits, "gather"):  # vocabulary-parallel greedy sampling against the gathered rows
+                full = last_token_logits.gather()
+                assert torch.equal(own, ops.argmax(full.contiguous())), "shard-wise greedy sampling differs from argmax"
+                state["vp_checked"] = state.get("vp_checked", 0) + 1
             out[f"s{state['step']}_logits"] = last_token_logits.float().cpu().numpy()
             out[f"s{state['step']}_own"] = own.cpu().numpy()
             return torch.from_numpy(forced[f"s{state['step']}_sample"]).to(last_token_logits.device)
@@ -134,6 +142,7 @@ def cuda_mode(out_path):
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     if world > 1:
+        assert state.get("vp_checked", 0) > 5, "the vocabulary-parallel sampling path did not run"
         # every rank must have produced identical logits and tokens (SPMD sampling)
         for k in sorted(out):
             t = torch.from_numpy(out[k]).cuda().double()
