@@ -113,7 +113,7 @@ class TextGenerationController:
             input_ids, position_ids = context.current_input_and_position_ids()
             logits = self.inference_wrapped_model.run_one_forward_step(
                 {"tokens": input_ids, "position_ids": position_ids, "attention_mask": None})
-        if hasattr(logits, "gather") and (not materialize_last or sampling_params.return_log_probs):
+        if hasattr(logits, "greedy_tokens") and (not materialize_last or sampling_params.return_log_probs):
             logits = logits.gather().unsqueeze(0)  # every token's logits / log-probs are wanted: the full rows
         cuda_graph_request_count = context.padded_active_request_count if context.is_decode_only() else None
         await asyncio.sleep(0)  # the forward is enqueued; let other coroutines run

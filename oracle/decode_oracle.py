@@ -428,6 +428,9 @@ class GPTOracle:
         # points, another (equally valid) summation order: the distance between a run with and a run without it is
         # the noise floor that separates ANY two correct implementations of this model in this dtype.
         self.reverse_k = reverse_k
+        # split_k = n > 1: every linear adds up n partial products over consecutive K ranges (fp32), the way a split-K
+        # GEMM does.  Another equally valid summation order; combined with reverse_k it gives further "twins".
+        self.split_k = 1
         # tp > 1 restates the arithmetic of the reference's tensor-parallel run: a row-parallel linear (out-proj,
         # fc2; layers.py:1225-1281) multiplies its K shard on every rank, each partial product is rounded to the
         # parameter dtype, and the all-reduce adds the rounded partials (mappings.py:22-33).  Column-parallel
@@ -452,7 +455,15 @@ class GPTOracle:
         return F.layer_norm(x, (s.hidden_size,), self.w[prefix + ".weight"], self.w[prefix + ".bias"], s.eps)
 
     def _mm(self, x, w):
-        """x @ w.T (layers.py:333), optionally with the K dimension accumulated in reverse order."""
+        """x @ w.T (layers.py:333), optionally with the K dimension accumulated in another order."""
+        if self.split_k > 1 and x.shape[-1] % self.split_k == 0:
+            ks = x.shape[-1] // self.split_k
+            parts = [torch.matmul(x[..., i * ks:(i + 1) * ks].float(), w[:, i * ks:(i + 1) * ks].float().t())
+                     for i in (range(self.split_k - 1, -1, -1) if self.reverse_k else range(self.split_k))]
+            acc = parts[0]
+            for p in parts[1:]:
+                acc = acc + p
+            return acc.to(x.dtype)
         if self.reverse_k:
             key = ("flip", w.data_ptr(), tuple(w.shape))
             if key not in self._wdq:

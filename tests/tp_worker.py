@@ -115,7 +115,7 @@ def cuda_mode(out_path):
     class Forced(Controller):
         def sample_from_logits(self, last_token_logits, sampling_params=None, vocab_size=None, **kw):
             own = super().sample_from_logits(last_token_logits, sampling_params, vocab_size, **kw)
-            if hasattr(last_token_logits, "gather"):  # vocabulary-parallel greedy sampling against the gathered rows
+            if hasattr(last_token_logits, "greedy_tokens"):  # vocabulary-parallel greedy sampling against the gathered rows
                 full = last_token_logits.gather()
                 assert torch.equal(own, ops.argmax(full.contiguous())), "shard-wise greedy sampling differs from argmax"
                 state["vp_checked"] = state.get("vp_checked", 0) + 1

@@ -35,6 +35,13 @@ def bar_for(meta) -> float:
     return FP8_BAR if (meta.get("fp8") or meta.get("kv_fp8_scale")) else BF16_BAR
 
 
+def floor_factor(meta) -> float:
+    """Allowed multiple of the oracle-twin floor (what each is made of: tests/test_width_parity_gpu.py)."""
+    if meta.get("kv_fp8_scale"):
+        return 2.75
+    return 1.75 if meta.get("fp8") == "mxfp8" else 1.2
+
+
 def cut_prompts(meta):
     g = torch.Generator().manual_seed(1234)
     return [torch.randint(0, meta["vocab_size"], (n,), generator=g, dtype=torch.int64).numpy() for n in meta["prompt_lengths"]]
@@ -45,7 +52,7 @@ def _oracle_meta(meta):
     return meta
 
 
-def oracle_trace_for(meta, reverse_k: bool = False, forced=None):
+def oracle_trace_for(meta, reverse_k: bool = False, forced=None, split_k: int = 1):
     """Trace of the CPU oracle on the cut (`forced`: teacher-force the tokens of an earlier trace)."""
     from oracle import decode_oracle as O
     from test_oracle_golden import build_oracle_model
@@ -53,6 +60,7 @@ def oracle_trace_for(meta, reverse_k: bool = False, forced=None):
     model, _ = build_oracle_model(_oracle_meta(meta), torch.bfloat16, fp8=meta.get("fp8"), kv_fp8_scale=meta.get("kv_fp8_scale"),
                                   tp=meta.get("tp", 1))
     model.reverse_k = reverse_k
+    model.split_k = split_k
     prompts = cut_prompts(meta)
     trace = {f"prompt_{i}": p for i, p in enumerate(prompts)}
 
@@ -71,15 +79,25 @@ def oracle_trace_for(meta, reverse_k: bool = False, forced=None):
     return trace
 
 
-def oracle_floor(meta, trace):
-    """Relative L2 per step between the oracle and the same oracle with reversed accumulation order, on the same
-    token trajectory: the distance that separates two correct evaluations of this model in this arithmetic."""
-    other = oracle_trace_for(meta, reverse_k=True, forced=trace)
-    rel = []
-    for s in range(trace["num_steps"]):
-        a, b = torch.from_numpy(trace[f"s{s}_logits"]), torch.from_numpy(other[f"s{s}_logits"])
-        rel.append(float((a - b).norm() / a.norm()))
+def oracle_floor(meta, trace, twins=((True, 1),)):
+    """Relative L2 per step between the oracle and "twins" of it - the same model, the same rounding points, every dot
+    product accumulated in another order (reversed; in split-K fashion) - on the same token trajectory: the distance
+    that separates two correct evaluations of this model in this arithmetic.  Per step the largest over the twins."""
+    rel = [0.0] * trace["num_steps"]
+    for reverse_k, split_k in twins:
+        other = oracle_trace_for(meta, reverse_k=reverse_k, forced=trace, split_k=split_k)
+        for s in range(trace["num_steps"]):
+            a, b = torch.from_numpy(trace[f"s{s}_logits"]), torch.from_numpy(other[f"s{s}_logits"])
+            rel[s] = max(rel[s], float((a - b).norm() / a.norm()))
     return rel
+
+
+def unquantised_reference(meta, trace):
+    """Logits of the same model WITHOUT any FP8 (bf16 oracle), teacher-forced on `trace`'s tokens: the ground truth that
+    an FP8 evaluation approximates.  Returns {step: logits}."""
+    plain = dict(meta, fp8=None, kv_fp8_scale=None)
+    ref = oracle_trace_for(plain, forced=trace)
+    return {s: torch.from_numpy(ref[f"s{s}_logits"]) for s in range(trace["num_steps"])}
 
 
 def run_cuda_cut(meta, trace, enable_cuda_graph: bool = True):
@@ -97,4 +115,4 @@ def run_cuda_cut(meta, trace, enable_cuda_graph: bool = True):
         flips_ok = False
     checksum = float(sum(v.double().sum() for v in state["logits"].values()))
     return {"rel": state["rel"], "flips": state["flips"], "flips_ok": flips_ok, "decisions": n_dec, "checksum": checksum,
-            "graph_replays": wrapper.graph_replays}
+            "graph_replays": wrapper.graph_replays, "logits": state["logits"]}
