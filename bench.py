@@ -167,7 +167,7 @@ def build_stack(w, tp: int, prompts, seed: int = 0, fuse_splitk: bool = True, fu
     torch.cuda.synchronize()
     free, _total = torch.cuda.mem_get_info()
     # headroom: activations of the largest prefill step, logits, workspaces, CUDA graphs
-    prefill_tokens = w.max_prefill_tokens or sum(len(p) for p in prompts)
+    prefill_tokens = w.num_requests if w.synthesize_kv else (w.max_prefill_tokens or sum(len(p) for p in prompts))
     act_bytes = prefill_tokens * (2 * w.hidden_size + 3 * (w.ffn_hidden_size // tp) + 2 * (w.num_attention_heads + 2 * w.num_query_groups) * w.kv_channels // tp) * 2
     headroom = int(act_bytes * 1.5) + (6 << 30)
     cap = max(chunks_per_req + 2, (free - headroom) // chunk_bytes)
@@ -486,6 +486,10 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.one_shot_max_world is not None:
+        from megatron_mixtera_b200.tensor_parallel import peer_allreduce
+
+        peer_allreduce.ONE_SHOT_MAX_WORLD = args.one_shot_max_world
     prompts = request_lengths(w, seed=0)
     model, ctx, wrapper, ctl, engine, pool = build_stack(
         w, tp, prompts, fuse_splitk=not args.unfused_splitk, fuse_tp=not args.nccl_allreduce,
@@ -705,6 +709,8 @@ def main():
                     help="N > 1: skip the 2-layer cut against the CPU oracle (the token comparison across ranks stays)")
     ap.add_argument("--no-tp-floor", action="store_true",
                     help="N > 1: skip the oracle-against-its-twin run that puts the cut's distance into context")
+    ap.add_argument("--one-shot-max-world", type=int, default=None,
+                    help="ablation (TP > 1): largest group that uses the one-shot fused all-reduce (larger ones: two-shot)")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="ablation (TP > 1): NCCL all-reduce + separate norm kernel instead of the fused peer-memory kernel")
     ap.add_argument("--fused-qkv", action="store_true",

@@ -244,10 +244,13 @@ allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, c
   }
 
   // ---- exchange B: this rank's rows are stored everywhere; wait for everybody else's ----
-  __threadfence_system();  // every thread: its peer stores are performed before the CTA reports in
+  // The CTA barrier orders every thread's peer stores before thread 0's system-scope fence (fences are cumulative), and
+  // that fence before the counter update: whoever sees the counter (the last CTA, which then releases the B flags)
+  // also sees the stores.  One fence per CTA instead of one per thread: a system-scope fence waits for the SM's
+  // outstanding remote writes and costs microseconds.
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    __threadfence_system();
     s_last = atomicAdd(&x.counters[1], 1) == static_cast<int>(gridDim.x) - 1;
     __threadfence();
   }

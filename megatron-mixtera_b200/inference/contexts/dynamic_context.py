@@ -95,6 +95,10 @@ class BaseInferenceContext:
         pass
 
 
+class AttentionStateError(RuntimeError):
+    """`DynamicInferenceContext.validate_attention_state` found an index the kernels must not be given."""
+
+
 # rows of the token-level arena
 _TOK_INPUT, _TOK_POS, _TOK_REQ, _TOK_CHUNK, _TOK_POS_IN_REQ, _TOK_LOCAL = range(6)
 _LEN_Q, _LEN_KV, _LEN_ORDER, _LEN_CUQ, _LEN_CUKV = range(5)  # rows of the per-request length matrix
@@ -129,6 +133,7 @@ class DynamicInferenceContext(BaseInferenceContext):
         allocate_memory_buffer: bool = True,
         kv_cache_dtype: Optional[torch.dtype] = None,
         kv_fp8_single_term: bool = False,
+        debug_validate: bool = False,
     ):
         """``num_attention_heads`` is the number of KV heads (query groups), as in the reference.
 
@@ -140,6 +145,9 @@ class DynamicInferenceContext(BaseInferenceContext):
         halving the bytes the attention kernel streams.
         """
         super().__init__(materialize_only_last_token_logits=materialize_only_last_token_logits)
+        # Debug mode: every `initialize_attention_state` checks on the host what the kernels are about to index with
+        # (`validate_attention_state`): the stand-in for a memory checker on machines where none can be run.
+        self.debug_validate = bool(debug_validate)
         if cache_mla_latent:
             raise NotImplementedError("multi-latent attention caches are outside this decode path")
         if device is None:
@@ -557,6 +565,51 @@ class DynamicInferenceContext(BaseInferenceContext):
             self._bt_pushed = None if num_warmup_tokens is not None else state
             self._mark_copies()
         self.block_table = self.request_to_kv_chunk_ids_cudagraph_only[:n_rows]
+        if self.debug_validate:
+            self.validate_attention_state()
+
+    def validate_attention_state(self) -> None:
+        """Host-side check of every index array the attention kernels consume for the step just published (the
+        staging copies are what the device receives).  Raises `AttentionStateError` naming the first violation:
+        block-table ids outside ``[0, chunk_count_total)`` in a column a row's length reaches, a length that exceeds
+        the row's chunks, a row order that is not a permutation, a token slot outside its chunk or the pool."""
+        n_rows = self.padded_active_request_count
+        padded = self.padded_active_token_count
+        p, t = self.paused_request_count, self.total_request_count
+        n_req = t - p
+        total = self.chunk_allocator.chunk_count_total
+        chunk = self.chunk_size_tokens
+        lens = self._h_len_np
+        bt = self._h_bt_np
+        kv = lens[_LEN_KV, :n_rows].astype(np.int64)
+        if (kv < 0).any() or (kv > self.max_sequence_length).any():
+            raise AttentionStateError(f"kv_seq_lengths outside [0, {self.max_sequence_length}]: {kv[(kv < 0) | (kv > self.max_sequence_length)][:4]}")
+        if (kv[n_req:] != 0).any():
+            raise AttentionStateError("a padding row has a non-zero length")
+        need = -(-kv // chunk)
+        if (need > self.max_kv_chunk_count).any():
+            raise AttentionStateError("a length needs more chunks than a block-table row holds")
+        cols = np.arange(self.max_kv_chunk_count)[None, :]
+        used = cols < need[:, None]
+        ids = bt[:n_rows]
+        bad = used & ((ids < 0) | (ids >= total))
+        if bad.any():
+            r, c = np.argwhere(bad)[0]
+            raise AttentionStateError(f"block table row {r} column {c} holds chunk id {ids[r, c]} (pool has {total}) inside its length {kv[r]}")
+        if self.is_decode_only():
+            rows = max(n_rows, 1)
+            order = np.sort(lens[_LEN_ORDER, :rows])
+            if not np.array_equal(order, np.arange(rows)):
+                raise AttentionStateError("attention_row_order is not a permutation of the rows")
+        tok = self._h_tok_np
+        ci, lp = tok[_TOK_CHUNK, :padded], tok[_TOK_LOCAL, :padded]
+        if ((ci < 0) | (ci >= total)).any() or ((lp < 0) | (lp >= chunk)).any():
+            raise AttentionStateError("a token's KV slot (chunk id, position in chunk) lies outside the pool")
+        a = self.active_token_count
+        if (ci[a:] != self.dummy_chunk_idx).any():
+            raise AttentionStateError("a padding token does not point at the dummy chunk")
+        if (ci[:a] == self.dummy_chunk_idx).any():
+            raise AttentionStateError("an active token points at the dummy chunk")
 
     def reset(self) -> None:
         """Drop every request and return all chunks (reference :827-869)."""

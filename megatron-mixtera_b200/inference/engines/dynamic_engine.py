@@ -16,6 +16,7 @@ from ..contexts.dynamic_context import ContextOverflowError, DynamicInferenceCon
 from ..inference_request import DynamicInferenceRequest, Status
 from ..sampling_params import SamplingParams
 from ..text_generation_controllers.text_generation_controller import TextGenerationController, get_asyncio_loop
+from ...utils import nvtx_range_pop, nvtx_range_push
 
 
 class DynamicInferenceEngine:
@@ -154,6 +155,7 @@ class DynamicInferenceEngine:
 
     async def async_step(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False) -> Dict:
         prev_decode = self.context.is_decode_only()
+        nvtx_range_push("Decode" if prev_decode else "Prefill")  # reference :562
         # The controller returns after reading the sampled tokens back, i.e. after the step's device work is done:
         # the host clock around the call measures the step (the reference brackets it with CUDA events and then
         # synchronises on the second one, dynamic_engine.py:560-575 - two more driver calls with the GPU idle).
@@ -189,6 +191,7 @@ class DynamicInferenceEngine:
                 self.step_count, "decode" if prev_decode else "non-decode", step_time, c.total_request_count,
                 c.gtd_request_count, c.paused_request_count, self.finished_request_count))
         self.step_count += 1
+        nvtx_range_pop()  # reference :658
         return {"active_requests": active_requests, "finished_requests": finished_requests, "step_time": step_time,
                 "cuda_graph_request_count": cuda_graph_request_count}
 

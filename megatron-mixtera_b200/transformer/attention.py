@@ -13,6 +13,7 @@ from typing import Optional, Union
 import torch
 
 from .. import ops, parallel_state
+from ..utils import REF_ATTENTION, nvtx_range_pop, nvtx_range_push
 from .spec_utils import ModuleSpec, build_module
 
 
@@ -37,11 +38,12 @@ def _sm_count() -> int:
 
 def choose_attention_splits(num_rows: int, num_kv_heads: int, max_sequence_length: int, chunk_size: int) -> int:
     """Context splits per row (flash-decoding).  A function of capture-time constants only, so that a
-    CUDA graph can replay it: enough (row, KV head, split) units for two CTAs per SM, no split shorter
-    than 1024 tokens at the longest context."""
+    CUDA graph can replay it: enough (row, KV head, split) units for two CTAs per SM, and - contexts differ by
+    large factors inside a batch, and a CTA runs for a time proportional to its share - no split longer than 8192
+    tokens at the longest context; never shorter than 1024 tokens there."""
     sms = _sm_count()
     units = max(1, num_rows * num_kv_heads)
-    want = -(-2 * sms // units)
+    want = max(-(-2 * sms // units), -(-max_sequence_length // 8192))
     cap = max(1, max_sequence_length // 1024)
     return int(max(1, min(want, cap, 64)))
 
@@ -138,16 +140,25 @@ class SelfAttention(torch.nn.Module):
                      and getattr(self.linear_qkv, "supports_deferred_reduction", False)
                      and getattr(self.core_attention, "accepts_gemm_partials", False)
                      and not getattr(inference_context, "kv_cache_fp8", False))  # the E4M3-pool kernel reads bf16 qkv
+        nvtx_range_push(REF_ATTENTION, "qkv")
         if defer_qkv:  # decode: the attention kernel sums the QKV GEMM's split-K partial sums itself
             mixed_qkv, _ = self.linear_qkv(hidden_states, defer_reduction=True)
         else:
             mixed_qkv, _ = self.linear_qkv(hidden_states)
+        nvtx_range_pop(REF_ATTENTION, "qkv")
+        # adjust_key_value (KV append), rotary_pos_emb and core_attention of the reference are one fused op here
+        nvtx_range_push(REF_ATTENTION, "core_attention")
         fp8 = getattr(self.linear_proj, "fp8", None)
         if fp8 and getattr(self.config, "fuse_attention_output_quantization", True) \
                 and getattr(self.core_attention, "quantizes_output", False):
             core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin, quantize_output=fp8)
         else:
             core = self.core_attention(mixed_qkv, inference_context, rotary_pos_cos, rotary_pos_sin)
+        nvtx_range_pop(REF_ATTENTION, "core_attention")
+        nvtx_range_push(REF_ATTENTION, "linear_proj")
         if defer_output_reduction and getattr(self.linear_proj, "supports_deferred_reduction", False):
-            return self.linear_proj(core, defer_reduction=True)
-        return self.linear_proj(core)
+            out = self.linear_proj(core, defer_reduction=True)
+        else:
+            out = self.linear_proj(core)
+        nvtx_range_pop(REF_ATTENTION, "linear_proj")
+        return out

@@ -8,6 +8,7 @@ from typing import Union
 import torch
 
 from .. import ops
+from ..utils import REF_MLP, nvtx_range_pop, nvtx_range_push
 from .spec_utils import ModuleSpec, build_module
 
 
@@ -37,24 +38,27 @@ class MLP(torch.nn.Module):
             self.linear_fc1.gate_up_interleaved = True
 
     def forward(self, hidden_states, defer_output_reduction: bool = False):
+        # ranges as in the reference (mlp.py:143-226); where fc1 and the activation are one kernel, "linear_fc1" covers both
+        nvtx_range_push(REF_MLP, "linear_fc1")
+        inter = self._fc1_and_activation(hidden_states)
+        nvtx_range_pop(REF_MLP, "linear_fc1")
+        nvtx_range_push(REF_MLP, "linear_fc2")
+        if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
+            out = self.linear_fc2(inter, defer_reduction=True)
+        else:
+            out = self.linear_fc2(inter)
+        nvtx_range_pop(REF_MLP, "linear_fc2")
+        return out
+
+    def _fc1_and_activation(self, hidden_states):
         if getattr(self.linear_fc1, "_layout_interleaved", False):
-            inter = self.linear_fc1.forward_swiglu(hidden_states)
-            if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
-                return self.linear_fc2(inter, defer_reduction=True)
-            return self.linear_fc2(inter)
+            return self.linear_fc1.forward_swiglu(hidden_states)
         if self.config.gated_linear_unit and self.linear_fc1.bias is None and hasattr(self.linear_fc1, "forward_gated"):
-            inter = self.linear_fc1.forward_gated(hidden_states)
-            if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
-                return self.linear_fc2(inter, defer_reduction=True)
-            return self.linear_fc2(inter)
+            return self.linear_fc1.forward_gated(hidden_states)
         inter, bias = self.linear_fc1(hidden_states)
         act = {None: ops.activation, "mxfp8": ops.activation_mxfp8, "blockwise": ops.activation_fp8_rowblock}[self.config.fp8]
         if self.config.gated_linear_unit:
             if bias is not None:
                 raise NotImplementedError("SwiGLU with an fc1 bias")
-            inter = act(inter, "swiglu")
-        else:
-            inter = act(inter, "gelu", bias)
-        if defer_output_reduction and getattr(self.linear_fc2, "supports_deferred_reduction", False):
-            return self.linear_fc2(inter, defer_reduction=True)
-        return self.linear_fc2(inter)
+            return act(inter, "swiglu")
+        return act(inter, "gelu", bias)

@@ -411,3 +411,36 @@ def test_rejected_admission_leaves_the_state_version_alone():
     assert c.state_version == v
     c.add_request(2, torch.zeros(10, dtype=torch.int64))
     assert c.state_version == v + 1
+
+
+def test_debug_validation_accepts_real_steps_and_names_corruptions():
+    from megatron_mixtera_b200.inference.contexts.dynamic_context import AttentionStateError
+
+    set_rounder(4)
+    c = make_ctx(debug_validate=True, max_requests_override=8, max_tokens_override=600)
+    rng = np.random.RandomState(0)
+    for i, n in enumerate((130, 5, 127)):
+        c.add_request(i, torch.from_numpy(rng.randint(0, 50, size=n)), 40)
+    for step in range(12):  # prefill, then decode steps that cross a chunk boundary: every step validates itself
+        c.initialize_attention_state()
+        n = c.total_request_count - c.paused_request_count
+        c.update_requests(np.ones(n, dtype=np.uint8), rng.randint(0, 50, size=n))
+    c.initialize_attention_state()
+    c.validate_attention_state()
+
+    def corrupted(mutate, match):
+        c.initialize_attention_state()
+        saved = [a.copy() for a in (c._h_bt_np, c._h_len_np, c._h_tok_np)]
+        mutate()
+        with pytest.raises(AttentionStateError, match=match):
+            c.validate_attention_state()
+        for a, b in zip((c._h_bt_np, c._h_len_np, c._h_tok_np), saved):  # (an unchanged block table is not staged again)
+            a[...] = b
+
+    corrupted(lambda: c._h_bt_np.__setitem__((0, 0), c.chunk_allocator.chunk_count_total), "chunk id")
+    corrupted(lambda: c._h_bt_np.__setitem__((1, 0), -1), "chunk id")
+    corrupted(lambda: c._h_len_np.__setitem__((1, 0), c.max_sequence_length + 1), "kv_seq_lengths")
+    corrupted(lambda: c._h_len_np.__setitem__((2, 0), c._h_len_np[2, 1]), "permutation")
+    corrupted(lambda: c._h_tok_np.__setitem__((5, 0), c.chunk_size_tokens), "KV slot")
+    corrupted(lambda: c._h_tok_np.__setitem__((3, 0), c.dummy_chunk_idx), "dummy chunk")
+    c.initialize_attention_state()  # a fresh step is clean again
