@@ -375,8 +375,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 // launch it sizes.
 static std::atomic<int> g_split_ctas_per_sm{2}, g_split_min_k_blocks{4}, g_split_max{kMaxSplits};
 
-static int choose_splits(int tiles, int num_k_blocks) {
-  const int slots = g_split_ctas_per_sm.load(std::memory_order_relaxed) * sm_count();
+// `resident_ctas_per_sm`: 0 = the policy's value; a kernel of which only one CTA fits an SM passes 1.
+static int choose_splits(int tiles, int num_k_blocks, int resident_ctas_per_sm = 0) {
+  const int per_sm = resident_ctas_per_sm > 0 ? resident_ctas_per_sm : g_split_ctas_per_sm.load(std::memory_order_relaxed);
+  const int slots = per_sm * sm_count();
   const int min_kb = g_split_min_k_blocks.load(std::memory_order_relaxed);
   if (tiles * 2 > slots) return 1;
   int s = slots / tiles;

@@ -280,10 +280,14 @@ static int launch_fp8_block(const void* xq, const float* x_scale, int m_pad, con
   return launch_splitk_reduce(p, stream);
 }
 
-static int pick_bt_block(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
+// Token block per CTA: up to 64 tokens the weight-major kernel above; 128 and 256 tokens the token-major kernel of
+// gemm_fp8_block_tok.cu.
+static int pick_bt_block(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)); }
 
 }  // namespace gemm
 }  // namespace b200
+
+#include "gemm_fp8_block_tok.cu"
 
 extern "C" {
 
@@ -292,7 +296,7 @@ size_t b200_gemm_fp8_block_splitk_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int bt = pick_bt_block(M);
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
-  return static_cast<size_t>(choose_splits(tiles, K / 128)) * M * N * sizeof(float);
+  return static_cast<size_t>(choose_splits(tiles, K / 128, bt >= 128 ? 1 : 0)) * M * N * sizeof(float);
 }
 
 int b200_gemm_fp8_block_splitk(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
@@ -309,8 +313,10 @@ int b200_gemm_fp8_block_splitk(const void* xq, const float* x_scale, int m_pad, 
       return gemm::launch_fp8_block<32>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
     case 64:
       return gemm::launch_fp8_block<64>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+    case 128:
+      return gemm::launch_fp8_block_tok<1>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
     default:
-      return gemm::launch_fp8_block<128>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
+      return gemm::launch_fp8_block_tok<2>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
   }
 }
 
@@ -319,7 +325,7 @@ size_t b200_gemm_fp8_block_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int bt = pick_bt_block(M);
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + bt - 1) / bt);
-  const int splits = choose_splits(tiles, K / 128);
+  const int splits = choose_splits(tiles, K / 128, bt >= 128 ? 1 : 0);
   if (splits == 1) return 0;
   return static_cast<size_t>(splits) * static_cast<size_t>(M) * N * sizeof(float);
 }
@@ -337,8 +343,10 @@ int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const v
       return gemm::launch_fp8_block<32>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
     case 64:
       return gemm::launch_fp8_block<64>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+    case 128:
+      return gemm::launch_fp8_block_tok<1>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s, nullptr, 0, nullptr);
     default:
-      return gemm::launch_fp8_block<128>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);
+      return gemm::launch_fp8_block_tok<2>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s, nullptr, 0, nullptr);
   }
 }
 
