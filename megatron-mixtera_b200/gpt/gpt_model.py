@@ -8,7 +8,8 @@ Module tree and ``state_dict`` keys follow the reference's ``GPTModel``
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from dataclasses import dataclass
+from typing import Dict, List, Optional
 
 import torch
 
@@ -147,6 +148,76 @@ class GPTModel(torch.nn.Module):
         self._weights_are_canonical()
         self.quantize_weights()
 
+    def load_tensor_parallel_checkpoint(self, shards: List[Dict[str, torch.Tensor]]) -> None:
+        """Load a checkpoint that was written at ANY tensor-parallel size (``shards[r]`` = rank r's ``state_dict``, the
+        layout of the reference's ``mp_rank_XX`` files): the shards are merged with the reference's partition rules
+        and re-sharded for this model's tensor-parallel size."""
+        self.load_full_state_dict(merge_tensor_parallel_shards(shards, gated=self.config.gated_linear_unit))
+
+    def sharded_state_dict(self, prefix: str = "") -> Dict[str, List[ShardedTensorInfo]]:
+        """``state_dict`` key -> the piece(s) of the unsharded tensor this rank holds (see `ShardedTensorInfo`).
+        Weights come out in the reference's row order (`ColumnParallelLinear.canonical_weight`)."""
+        tp, rank = parallel_state.get_tensor_model_parallel_world_size(), parallel_state.get_tensor_model_parallel_rank()
+        canonical = {n + ".weight": m.canonical_weight() for n, m in self.named_modules() if hasattr(m, "canonical_weight") and m.weight is not None}
+        out = {}
+        full = self.full_parameter_shapes()
+        for k, v in self.state_dict().items():
+            if v is None or k.endswith("_extra_state"):
+                continue
+            v = canonical.get(k, v)
+            dim, gshape = _partition_dim(k), full[k]
+            if dim is None or tp == 1:
+                out[prefix + k] = [ShardedTensorInfo(prefix + k, v, gshape, (0,) * v.dim(), replica_id=rank if dim is None else 0)]
+            elif self.config.gated_linear_unit and k.endswith(("linear_fc1.weight", "linear_fc1.bias")):
+                gate, up = torch.chunk(v, 2, dim=0)
+                per, F = gate.shape[0], gshape[0] // 2
+                rest = (0,) * (v.dim() - 1)
+                out[prefix + k] = [ShardedTensorInfo(prefix + k, gate, gshape, (rank * per, *rest)),
+                                   ShardedTensorInfo(prefix + k, up, gshape, (F + rank * per, *rest))]
+            else:
+                off = [0] * v.dim()
+                off[dim] = rank * v.shape[dim]
+                out[prefix + k] = [ShardedTensorInfo(prefix + k, v, gshape, tuple(off))]
+        return out
+
+    # ---- offline quantisation: serve from FP8 weights without ever holding the bf16 ones ----
+    def quantized_state_dict(self) -> Dict[str, torch.Tensor]:
+        """The FP8 copies of this rank's linear weights (what `quantize_weights` built), as plain tensors:
+        ``<module>.weight_fp8`` (tile-major E4M3 bytes) and ``<module>.weight_scales`` (E8M0 tile bytes for "mxfp8",
+        fp32 ``[N/128, K/128]`` for "blockwise"), plus every tensor that is not an FP8 linear weight.  Written once by
+        an offline job; `load_quantized_state_dict` is the matching loader."""
+        out = {}
+        fp8_weights = set()
+        for n, m in self.named_modules():
+            if getattr(m, "fp8", None) and getattr(m, "weight", None) is not None:
+                if m._wq is None:
+                    m.quantize_weights()
+                out[n + ".weight_fp8"] = m._wq.q
+                out[n + ".weight_scales"] = m._wq.sf if m.fp8 == "mxfp8" else m._wq.scale
+                fp8_weights.add(n + ".weight")
+        for k, v in self.state_dict().items():
+            if v is not None and not k.endswith("_extra_state") and k not in fp8_weights:
+                out[k] = v
+        return out
+
+    def load_quantized_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        """Counterpart of `quantized_state_dict` (same tensor-parallel size and recipe): FP8 linears take their
+        quantised weights as they are and release the bf16 parameter; everything else is copied."""
+        from .. import ops
+
+        own = self.state_dict()
+        for n, m in self.named_modules():
+            if getattr(m, "fp8", None) and getattr(m, "weight", None) is not None:
+                q, sc = sd[n + ".weight_fp8"].to(m.weight.device), sd[n + ".weight_scales"].to(m.weight.device)
+                shape = m.weight_shape
+                m._wq = ops.Mxfp8Tensor(q, sc, shape, packed=True) if m.fp8 == "mxfp8" else ops.Fp8BlockTensor(q, sc, shape)
+                m._weight_shape = tuple(shape)
+                m.weight.data = torch.empty(0, dtype=m.weight.dtype, device=m.weight.device)
+                own.pop(n + ".weight", None)
+        for k, dst in own.items():
+            if dst is not None and not k.endswith("_extra_state"):
+                dst.copy_(sd[k])
+
     def _weights_are_canonical(self) -> None:
         """Called after the parameters were overwritten with weights in the reference's layout."""
         for m in self.modules():
@@ -178,6 +249,40 @@ class GPTModel(torch.nn.Module):
             del full
         self._weights_are_canonical()
         self.quantize_weights()
+
+
+@dataclass(frozen=True)
+class ShardedTensorInfo:
+    """What the reference's ``ShardedTensor`` records about one local tensor (``dist_checkpointing/mapping.py``; built by
+    ``make_sharded_tensors_for_checkpoint`` from ``ColumnParallelLinear.sharded_state_dict`` / ``RowParallelLinear.
+    sharded_state_dict``, ``megatron/core/tensor_parallel/layers.py:1045-1050, 1283-1288``): the checkpoint key, the
+    local data, the shape of the whole tensor and where the local piece sits in it.  A gated fc1 is two pieces per rank
+    - the rank's gate rows and its up rows - exactly as ``apply_swiglu_sharded_factory`` (``mlp.py:260-297``) writes it."""
+
+    key: str
+    data: torch.Tensor
+    global_shape: tuple
+    global_offset: tuple
+    replica_id: int = 0
+
+
+def merge_tensor_parallel_shards(shards, *, gated: bool) -> Dict[str, torch.Tensor]:
+    """Inverse of `shard_for_rank`: the per-rank state dicts of a checkpoint written at tensor-parallel size
+    ``len(shards)`` (rank order) -> unsharded tensors.  Replicated tensors are taken from rank 0."""
+    tp = len(shards)
+    out = {}
+    for k, first in shards[0].items():
+        if first is None or k.endswith("_extra_state"):
+            continue
+        dim = _partition_dim(k)
+        if dim is None or tp == 1:
+            out[k] = first
+        elif gated and k.endswith(("linear_fc1.weight", "linear_fc1.bias")):
+            halves = [torch.chunk(sd[k], 2, dim=0) for sd in shards]
+            out[k] = torch.cat([h[0] for h in halves] + [h[1] for h in halves], dim=0)
+        else:
+            out[k] = torch.cat([sd[k] for sd in shards], dim=dim)
+    return out
 
 
 def _partition_dim(key: str) -> Optional[int]:

@@ -444,3 +444,70 @@ def test_debug_validation_accepts_real_steps_and_names_corruptions():
     corrupted(lambda: c._h_tok_np.__setitem__((5, 0), c.chunk_size_tokens), "KV slot")
     corrupted(lambda: c._h_tok_np.__setitem__((3, 0), c.dummy_chunk_idx), "dummy chunk")
     c.initialize_attention_state()  # a fresh step is clean again
+
+
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_checkpoint_shards_merge_back_to_the_full_tensors(tp):
+    # the partition rules of the reference (QKV by KV group, gated fc1 as [gate_r ; up_r], row-parallel along the
+    # input, vocabulary contiguous): sharding for `tp` ranks and merging the ranks' state dicts is the identity
+    from megatron_mixtera_b200.gpt.gpt_model import merge_tensor_parallel_shards, shard_for_rank
+
+    g = torch.Generator().manual_seed(tp)
+    H, F, V = 64, 32 * 8, 16 * 8
+    full = {
+        "embedding.word_embeddings.weight": torch.randn(V, H, generator=g),
+        "decoder.layers.0.input_layernorm.weight": torch.randn(H, generator=g),
+        "decoder.layers.0.self_attention.linear_qkv.weight": torch.randn(8 * 3 * 16, H, generator=g),
+        "decoder.layers.0.self_attention.linear_proj.weight": torch.randn(H, 8 * 16, generator=g),
+        "decoder.layers.0.mlp.linear_fc1.weight": torch.randn(2 * F, H, generator=g),
+        "decoder.layers.0.mlp.linear_fc2.weight": torch.randn(H, F, generator=g),
+        "output_layer.weight": torch.randn(V, H, generator=g),
+    }
+    shards = [{k: shard_for_rank(k, v, r, tp, gated=True) for k, v in full.items()} for r in range(tp)]
+    if tp > 1:
+        gate_r = shards[1]["decoder.layers.0.mlp.linear_fc1.weight"][: F // tp]
+        assert torch.equal(gate_r, full["decoder.layers.0.mlp.linear_fc1.weight"][F // tp: 2 * F // tp])
+    merged = merge_tensor_parallel_shards(shards, gated=True)
+    assert set(merged) == set(full)
+    for k in full:
+        assert torch.equal(merged[k], full[k]), k
+    # re-sharding a checkpoint written at another size: merge the `tp` shards, cut for 2 ranks
+    again = [shard_for_rank(k, merged[k], 1, 2, gated=True) for k in full]
+    direct = [shard_for_rank(k, full[k], 1, 2, gated=True) for k in full]
+    assert all(torch.equal(a, b) for a, b in zip(again, direct))
+
+
+def test_sharded_state_dict_pieces_tile_the_full_tensors():
+    # every rank's `sharded_state_dict` says where its pieces sit in the unsharded tensors (a gated fc1: two pieces, the
+    # rank's gate rows and its up rows); pasting the pieces of both ranks reproduces the checkpoint
+    from megatron_mixtera_b200 import parallel_state
+    from megatron_mixtera_b200.gpt.gpt_model import GPTModel
+    from megatron_mixtera_b200.synthetic import canonical_tensor
+    from megatron_mixtera_b200.transformer.transformer_config import TransformerConfig
+
+    tp = 2
+    pasted, full = {}, None
+    try:
+        for rank in range(tp):
+            parallel_state._TP_SIZE, parallel_state._TP_RANK, parallel_state._INITIALIZED = tp, rank, True
+            cfg = TransformerConfig(num_layers=1, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=32,
+                                    ffn_hidden_size=256, normalization="RMSNorm", gated_linear_unit=True, activation="silu",
+                                    add_bias_linear=False, tensor_model_parallel_size=tp)
+            model = GPTModel(cfg, vocab_size=64, max_sequence_length=32, position_embedding_type="rope")
+            if full is None:
+                full = {k: canonical_tensor(k, s, dtype=torch.bfloat16) for k, s in model.full_parameter_shapes().items()}
+            model.load_full_state_dict(full)
+            assert model.decoder.layers[0].mlp.linear_fc1._layout_interleaved  # stored rearranged, exported canonical
+            for k, pieces in model.sharded_state_dict().items():
+                dst = pasted.setdefault(k, torch.zeros(pieces[0].global_shape, dtype=torch.bfloat16))
+                assert len(pieces) == (2 if k.endswith("linear_fc1.weight") else 1)
+                for pc in pieces:
+                    assert pc.global_shape == tuple(full[k].shape)
+                    idx = tuple(slice(o, o + n) for o, n in zip(pc.global_offset, pc.data.shape))
+                    if pc.replica_id == 0 or rank == 0:
+                        dst[idx] = pc.data
+    finally:
+        parallel_state.destroy_model_parallel()
+    assert set(pasted) == set(full)
+    for k in full:
+        assert torch.equal(pasted[k], full[k]), k

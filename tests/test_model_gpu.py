@@ -360,3 +360,29 @@ def test_waiting_request_does_not_cost_a_second_forward_per_step():
         runs[extra] = (tokens, wrapper.graph_replays - replays0, decode_steps)
     assert runs[0][0] == runs[1][0]
     assert runs[1][1] == runs[0][1] <= runs[0][2] + 1, runs
+
+
+@pytest.mark.parametrize("recipe", ["mxfp8", "blockwise"])
+def test_offline_quantised_state_dict_serves_the_same_logits(recipe):
+    # an offline job writes the FP8 weights (tile-major bytes + scales); a serving process loads them without ever
+    # holding the bf16 weights and produces the same logits bit for bit
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = dict(json.loads(str(z["meta"])), fp8=recipe)
+    n = len(meta["prompt_lengths"])
+
+    def first_logits(model, ctx, wrapper):
+        for i in range(n):
+            ctx.add_request(i, torch.from_numpy(z[f"prompt_{i}"]), 4)
+        ctx.initialize_attention_state()
+        ids, pos = ctx.current_input_and_position_ids()
+        return wrapper.run_one_forward_step({"tokens": ids, "position_ids": pos, "attention_mask": None}).float().cpu()
+
+    model, ctx, wrapper, _ = build_cuda_stack(meta)
+    ref = first_logits(model, ctx, wrapper)
+    sd = {k: v.clone() for k, v in model.quantized_state_dict().items()}
+    assert any(k.endswith("weight_fp8") for k in sd) and not any(k.endswith("linear_fc1.weight") for k in sd)
+    model2, ctx2, wrapper2, _ = build_cuda_stack(dict(meta, weight_seed=meta["weight_seed"] + 1))  # other weights ...
+    model2.load_quantized_state_dict(sd)                                                        # ... replaced by the file's
+    assert model2.decoder.layers[0].mlp.linear_fc1.weight.numel() == 0  # no bf16 copy is kept
+    got = first_logits(model2, ctx2, wrapper2)
+    assert torch.equal(got, ref)
