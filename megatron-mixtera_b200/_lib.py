@@ -9,7 +9,7 @@ import ctypes
 import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
-from .build import LIB_PATH
+from .build import LIB_PATH, TORCH_LIB_PATH
 
 EXPORTED_SYMBOLS = (
     "b200_version",
@@ -266,6 +266,36 @@ def load() -> ctypes.CDLL:
             fn.restype = c_int
     _lib = lib
     return lib
+
+
+_torch_ops = None
+
+
+def load_torch_ops():
+    """Register (once) the torch custom ops of ``libb200_decode_torch.so`` and return ``torch.ops.b200_decode``.
+
+    The front links ``libb200_decode.so``; loading the C-ABI library first with its full path makes the dynamic
+    linker reuse that copy.  Raises if either library has not been built: there is no fallback."""
+    global _torch_ops
+    if _torch_ops is not None:
+        return _torch_ops
+    load()
+    if not os.path.exists(TORCH_LIB_PATH):
+        raise ImportError(
+            f"{TORCH_LIB_PATH} is missing: build it with `python -m megatron_mixtera_b200.build` "
+            "(the decode operators have no CPU or PyTorch fallback)"
+        )
+    import torch
+
+    torch.ops.load_library(TORCH_LIB_PATH)
+    _torch_ops = torch.ops.b200_decode
+    return _torch_ops
+
+
+TORCH_OPS = (
+    "gather_rows", "add_norm", "activation", "quantize", "gemm", "gemm_splitk", "gemm_bf16_swiglu", "gemm_mxfp8_swiglu",
+    "attention", "argmax", "argmax_shard", "argmax_merge", "filtered_probs", "allreduce_add_norm",
+)
 
 
 def check(fn_name: str, code: int) -> None:

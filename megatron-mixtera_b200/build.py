@@ -1,6 +1,9 @@
-"""Builds ``libb200_decode.so`` (all sm_100a kernels + the C ABI) in-tree with nvcc.
+"""Builds ``libb200_decode.so`` (all sm_100a kernels + the C ABI) in-tree with nvcc, and
+``libb200_decode_torch.so`` (the torch custom-op front, ``TORCH_LIBRARY(b200_decode, ...)``) with g++.
 
-nvcc cross-compiles for sm_100a without a GPU, so this also runs on CPU-only build machines.
+nvcc cross-compiles for sm_100a without a GPU, so this also runs on CPU-only build machines.  The torch front holds
+no kernels: it links the C-ABI library (found next to it through ``$ORIGIN``) and the torch libraries of the
+interpreter that builds it.
 """
 from __future__ import annotations
 
@@ -12,6 +15,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200_decode.so")
+TORCH_LIB_PATH = os.path.join(PKG_DIR, "libb200_decode_torch.so")
+TORCH_SRC = os.path.join(CSRC, "torch_binding.cpp")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -55,5 +60,41 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def torch_ops_need_build() -> bool:
+    if not os.path.exists(TORCH_LIB_PATH):
+        return True
+    t = os.path.getmtime(TORCH_LIB_PATH)
+    deps = [TORCH_SRC, os.path.join(PKG_DIR, "..", "include", "b200_decode.h")]
+    return any(os.path.getmtime(s) > t for s in deps)
+
+
+def build_torch_ops(force: bool = False) -> str:
+    """Compile the torch custom-op front if it is missing or older than its source; returns its path."""
+    build()
+    if not force and not torch_ops_need_build():
+        return TORCH_LIB_PATH
+    import torch
+    from torch.utils import cpp_extension
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        raise RuntimeError("g++ not found: cannot build libb200_decode_torch.so")
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    for inc in cpp_extension.include_paths() + [os.path.join(cuda_home, "include")]:
+        cmd += ["-isystem", inc]
+    tmp = TORCH_LIB_PATH + ".tmp%d" % os.getpid()
+    cmd += [TORCH_SRC, "-o", tmp, "-L" + PKG_DIR, "-lb200_decode", "-L" + torch_lib, "-ltorch", "-ltorch_cpu",
+            "-ltorch_cuda", "-lc10", "-lc10_cuda", "-Wl,-rpath,$ORIGIN"]
+    proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("g++ failed on torch_binding.cpp:\n" + proc.stdout + proc.stderr)
+    os.replace(tmp, TORCH_LIB_PATH)
+    return TORCH_LIB_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_torch_ops(force="--force" in sys.argv))

@@ -1,8 +1,10 @@
-"""Tensor-level wrappers over the C ABI (``include/b200_decode.h``).
+"""Tensor-level wrappers over the library's torch custom ops (``torch.ops.b200_decode.*``).
 
-Each function checks dtype / device / contiguity on the host, passes raw device pointers and
-the current CUDA stream to the library and raises `B200Error` on a non-zero return code.
-Nothing here computes on the CPU or through PyTorch kernels.
+The ops are registered by ``libb200_decode_torch.so`` (``csrc/torch_binding.cpp``), a thin front of the C ABI in
+``include/b200_decode.h``: each checks device / dtype / contiguity, takes the current CUDA stream and raises on a
+non-zero return code; the wrappers here allocate the outputs, keep the split-K workspace and re-raise failures as
+`B200Error`.  Calls that launch nothing (size queries, the status word, the wait limit) and the 2-D host copy go to
+the C ABI directly through ctypes.  Nothing here computes on the CPU or through PyTorch kernels.
 """
 from __future__ import annotations
 
@@ -92,6 +94,31 @@ def check(fn_name: str, code: int) -> None:
         launch_count += 1
 
 
+_ops = None
+
+
+def _launch(name: str, *args):
+    """Call ``torch.ops.b200_decode.<name>`` (one kernel launch); a failed check or return code becomes `B200Error`."""
+    global launch_count, _ops
+    if _ops is None:
+        _ops = _lib.load_torch_ops()
+    try:
+        out = getattr(_ops, name)(*args)
+    except (RuntimeError, NotImplementedError) as e:
+        raise B200Error(name, -1, str(e).split("\nException raised from")[0]) from None
+    launch_count += 1
+    return out
+
+
+def _blob(struct) -> torch.Tensor:
+    """The bytes of a ctypes argument struct as a CPU uint8 tensor sharing its memory (made once per struct)."""
+    t = getattr(struct, "_as_tensor", None)
+    if t is None:
+        t = torch.frombuffer(struct, dtype=torch.uint8)
+        struct._as_tensor = t
+    return t
+
+
 def set_wait_limit_ns(limit_ns: int) -> None:
     """Bound of the library's device-side waits on the current device (default 2 s)."""
     check("b200_set_wait_limit_ns", _lib.load().b200_set_wait_limit_ns(int(limit_ns)))
@@ -126,9 +153,7 @@ def gather_rows(table, ids, *, vocab_start: int = 0, vocab_end: Optional[int] = 
         _need(add_table, BF16, "add_table")
         _need(add_ids, torch.int64, "add_ids")
     hi = vocab_start + table.shape[0] if vocab_end is None else vocab_end
-    check("b200_gather_rows_bf16", _lib.load().b200_gather_rows_bf16(
-        table.data_ptr(), ids.data_ptr(), out.data_ptr(), n, width, vocab_start, hi, _p(add_table), _p(add_ids),
-        _stream()))
+    _launch("gather_rows", table, ids, out, vocab_start, hi, add_table, add_ids)
     return out
 
 
@@ -140,8 +165,7 @@ def add_norm(x, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5
     rows = x.numel() // hidden
     h = torch.empty_like(x) if want_hidden else None
     y = torch.empty_like(x) if want_normed else None
-    check("b200_add_norm_bf16", _lib.load().b200_add_norm_bf16(
-        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps, _stream()))
+    _launch("add_norm", x, None, 0, bias, residual, gamma, beta, h, y, None, None, 0, 0, rows, hidden, eps)
     return h, y
 
 
@@ -161,8 +185,7 @@ def activation(x, kind: str, bias=None):
     rows = x.numel() // x.shape[-1]
     F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.device)
-    check("b200_activation_bf16", _lib.load().b200_activation_bf16(
-        x.data_ptr(), _p(bias), out.data_ptr(), rows, F, _act_kind(kind), _stream()))
+    _launch("activation", x, None, 0, bias, out, None, None, 0, 0, rows, F, _act_kind(kind))
     return out
 
 
@@ -193,8 +216,7 @@ def gemm_swiglu(x, w_interleaved, out=None):
     M, N = x.numel() // K, w_interleaved.shape[0]
     if out is None:
         out = torch.empty((*x.shape[:-1], N // 2), dtype=BF16, device=x.device)
-    check("b200_gemm_bf16_swiglu", _lib.load().b200_gemm_bf16_swiglu(
-        x.data_ptr(), K, w_interleaved.data_ptr(), out.data_ptr(), N // 2, M, N, K, _stream()))
+    _launch("gemm_bf16_swiglu", x, w_interleaved, out)
     return out
 
 
@@ -212,8 +234,7 @@ def gemm(x, w, bias=None, out=None):
     lib = _lib.load()
     nbytes = lib.b200_gemm_bf16_workspace_bytes(M, N, K)
     ws = _gemm_workspace(x.device, nbytes, True)
-    check("b200_gemm_bf16", lib.b200_gemm_bf16(x.data_ptr(), K, w.data_ptr(), _p(bias), out.data_ptr(), N, M, N, K,
-                                               ws.data_ptr(), ws.numel(), _stream()))
+    _launch("gemm", 0, x, None, 0, w, None, bias, out, ws, M, N, K)
     return out
 
 
@@ -240,8 +261,7 @@ def quantize_mxfp8_weight(w) -> Mxfp8Tensor:
     lib = _lib.load()
     q = torch.zeros((lib.b200_fp8_weight_bytes(N, K),), dtype=torch.uint8, device=w.device)
     sf = torch.empty((lib.b200_mxfp8_scale_bytes(N, K),), dtype=torch.uint8, device=w.device)
-    check("b200_quantize_mxfp8_weight", lib.b200_quantize_mxfp8_weight(w.data_ptr(), q.data_ptr(), sf.data_ptr(), N, K,
-                                                                       _stream()))
+    _launch("quantize", 3, w, q, sf, N, K, 0)
     return Mxfp8Tensor(q, sf, w.shape, packed=True)
 
 
@@ -257,8 +277,7 @@ def quantize_mxfp8(x) -> Mxfp8Tensor:
     K = x.shape[-1]
     rows = x.numel() // K
     q, sf = _mx_buffers(rows, K, x.device)
-    check("b200_quantize_mxfp8", _lib.load().b200_quantize_mxfp8(x.data_ptr(), K, q.data_ptr(), sf.data_ptr(), rows, K,
-                                                                 _stream()))
+    _launch("quantize", 1, x, q, sf, rows, K, 0)
     return Mxfp8Tensor(q, sf, x.shape)
 
 
@@ -269,9 +288,7 @@ def add_norm_mxfp8(x, gamma, *, bias=None, residual=None, beta=None, eps: float 
     rows = x.numel() // hidden
     h = torch.empty_like(x) if want_hidden else None
     q, sf = _mx_buffers(rows, hidden, x.device)
-    check("b200_add_norm_mxfp8", _lib.load().b200_add_norm_mxfp8(
-        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(), rows, hidden, eps,
-        _stream()))
+    _launch("add_norm", x, None, 0, bias, residual, gamma, beta, h, None, q, sf, 1, 0, rows, hidden, eps)
     return h, Mxfp8Tensor(q, sf, x.shape)
 
 
@@ -281,8 +298,7 @@ def activation_mxfp8(x, kind: str, bias=None) -> Mxfp8Tensor:
     rows = x.numel() // x.shape[-1]
     F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     q, sf = _mx_buffers(rows, F, x.device)
-    check("b200_activation_mxfp8", _lib.load().b200_activation_mxfp8(
-        x.data_ptr(), _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, _act_kind(kind), _stream()))
+    _launch("activation", x, None, 0, bias, None, q, sf, 1, 0, rows, F, _act_kind(kind))
     return Mxfp8Tensor(q, sf, (*x.shape[:-1], F))
 
 
@@ -297,8 +313,7 @@ def gemm_mxfp8(x: Mxfp8Tensor, w: Mxfp8Tensor, bias=None, out=None):
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
     ws = _gemm_workspace(x.q.device, lib.b200_gemm_mxfp8_workspace_bytes(M, N, K), True)
-    check("b200_gemm_mxfp8", lib.b200_gemm_mxfp8(x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), _p(bias),
-                                                 out.data_ptr(), N, M, N, K, ws.data_ptr(), ws.numel(), _stream()))
+    _launch("gemm", 1, x.q, x.sf, 0, w.q, w.sf, bias, out, ws, M, N, K)
     return out
 
 
@@ -309,16 +324,12 @@ def gemm_mxfp8_swiglu(x: Mxfp8Tensor, w: Mxfp8Tensor, quantize: bool = True):
     M, F = x.q.shape[0], w.shape[0] // 2
     if w.shape[1] != K or not w.packed:
         raise B200Error("gemm_mxfp8_swiglu", -1, f"x[..., {K}] vs w{tuple(w.shape)} (tile-major, `quantize_mxfp8_weight`)")
-    lib = _lib.load()
     if quantize:
         q, sf = _mx_buffers(M, F, x.q.device)
-        check("b200_gemm_mxfp8_swiglu", lib.b200_gemm_mxfp8_swiglu(
-            x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), q.data_ptr(), sf.data_ptr(), None, 0, M, F, K,
-            _stream()))
+        _launch("gemm_mxfp8_swiglu", x.q, x.sf, w.q, w.sf, q, sf, None, M, F, K)
         return Mxfp8Tensor(q, sf, (*x.shape[:-1], F))
     out = torch.empty((*x.shape[:-1], F), dtype=BF16, device=x.q.device)
-    check("b200_gemm_mxfp8_swiglu", lib.b200_gemm_mxfp8_swiglu(
-        x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), None, None, out.data_ptr(), F, M, F, K, _stream()))
+    _launch("gemm_mxfp8_swiglu", x.q, x.sf, w.q, w.sf, None, None, out, M, F, K)
     return out
 
 
@@ -341,21 +352,17 @@ def activation_splitk(p: "GemmPartials", kind: str, bias=None, quantize=None):
     for d in p.shape[:-1]:
         rows *= d
     dev = p.device
-    lib = _lib.load()
     shape = (*p.shape[:-1], F)
     if quantize == "mxfp8":
         q, sf = _mx_buffers(rows, F, dev)
-        check("b200_activation_splitk_mxfp8", lib.b200_activation_splitk_mxfp8(
-            p.buf.data_ptr(), p.num_splits, _p(bias), q.data_ptr(), sf.data_ptr(), rows, F, k, _stream()))
+        _launch("activation", None, p.buf, p.num_splits, bias, None, q, sf, 1, 0, rows, F, k)
         return Mxfp8Tensor(q, sf, shape)
     if quantize == "blockwise":
         q, scale, m_pad = _rowblock_buffers(rows, F, dev)
-        check("b200_activation_splitk_fp8_rowblock", lib.b200_activation_splitk_fp8_rowblock(
-            p.buf.data_ptr(), p.num_splits, _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, k, _stream()))
+        _launch("activation", None, p.buf, p.num_splits, bias, None, q, scale, 2, m_pad, rows, F, k)
         return Fp8BlockTensor(q, scale, shape, m_pad)
     out = torch.empty(shape, dtype=BF16, device=dev)
-    check("b200_activation_splitk_bf16", lib.b200_activation_splitk_bf16(
-        p.buf.data_ptr(), p.num_splits, _p(bias), out.data_ptr(), rows, F, k, _stream()))
+    _launch("activation", None, p.buf, p.num_splits, bias, out, None, None, 0, 0, rows, F, k)
     return out
 
 
@@ -381,8 +388,7 @@ def quantize_fp8_weight_block128(w) -> Fp8BlockTensor:
     N, K = w.shape
     q = torch.zeros((_lib.load().b200_fp8_weight_bytes(N, K),), dtype=torch.uint8, device=w.device)  # tile-major
     scale = torch.empty(((N + 127) // 128, K // 128), dtype=torch.float32, device=w.device)
-    check("b200_quantize_fp8_weight_block128", _lib.load().b200_quantize_fp8_weight_block128(
-        w.data_ptr(), q.data_ptr(), scale.data_ptr(), N, K, _stream()))
+    _launch("quantize", 4, w, q, scale, N, K, 0)
     return Fp8BlockTensor(q, scale, w.shape)
 
 
@@ -391,8 +397,7 @@ def quantize_fp8_rowblock(x) -> Fp8BlockTensor:
     K = x.shape[-1]
     rows = x.numel() // K
     q, scale, m_pad = _rowblock_buffers(rows, K, x.device)
-    check("b200_quantize_fp8_rowblock", _lib.load().b200_quantize_fp8_rowblock(
-        x.data_ptr(), K, q.data_ptr(), scale.data_ptr(), rows, K, m_pad, _stream()))
+    _launch("quantize", 2, x, q, scale, rows, K, m_pad)
     return Fp8BlockTensor(q, scale, x.shape, m_pad)
 
 
@@ -403,9 +408,7 @@ def add_norm_fp8_rowblock(x, gamma, *, bias=None, residual=None, beta=None, eps:
     rows = x.numel() // hidden
     h = torch.empty_like(x) if want_hidden else None
     q, scale, m_pad = _rowblock_buffers(rows, hidden, x.device)
-    check("b200_add_norm_fp8_rowblock", _lib.load().b200_add_norm_fp8_rowblock(
-        x.data_ptr(), _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), scale.data_ptr(), m_pad, rows,
-        hidden, eps, _stream()))
+    _launch("add_norm", x, None, 0, bias, residual, gamma, beta, h, None, q, scale, 2, m_pad, rows, hidden, eps)
     return h, Fp8BlockTensor(q, scale, x.shape, m_pad)
 
 
@@ -414,8 +417,7 @@ def activation_fp8_rowblock(x, kind: str, bias=None) -> Fp8BlockTensor:
     rows = x.numel() // x.shape[-1]
     F = x.shape[-1] if _act_kind(kind) == 1 else x.shape[-1] // 2
     q, scale, m_pad = _rowblock_buffers(rows, F, x.device)
-    check("b200_activation_fp8_rowblock", _lib.load().b200_activation_fp8_rowblock(
-        x.data_ptr(), _p(bias), q.data_ptr(), scale.data_ptr(), m_pad, rows, F, _act_kind(kind), _stream()))
+    _launch("activation", x, None, 0, bias, None, q, scale, 2, m_pad, rows, F, _act_kind(kind))
     return Fp8BlockTensor(q, scale, (*x.shape[:-1], F), m_pad)
 
 
@@ -429,9 +431,7 @@ def gemm_fp8_block(x: Fp8BlockTensor, w: Fp8BlockTensor, bias=None, out=None):
         out = torch.empty((*x.shape[:-1], N), dtype=BF16, device=x.q.device)
     lib = _lib.load()
     ws = _gemm_workspace(x.q.device, lib.b200_gemm_fp8_block_workspace_bytes(M, N, K), True)
-    check("b200_gemm_fp8_block", lib.b200_gemm_fp8_block(
-        x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), _p(bias), out.data_ptr(), N, M, N,
-        K, ws.data_ptr(), ws.numel(), _stream()))
+    _launch("gemm", 2, x.q, x.scale, x.m_pad, w.q, w.scale, bias, out, ws, M, N, K)
     return out
 
 
@@ -461,21 +461,16 @@ def gemm_splitk(x, w) -> GemmPartials:
     """x @ w.T as split-K partial sums (no reduction launch, no bias); x bf16, `Mxfp8Tensor` or `Fp8BlockTensor`
     with `w` of the same kind."""
     lib = _lib.load()
-    n = ctypes.c_int(0)
     if isinstance(x, Mxfp8Tensor):
         K, M, N, dev = x.shape[-1], x.q.shape[0], w.shape[0], x.q.device
         if not w.packed:
             raise B200Error("gemm_splitk", -1, "MXFP8 weights must be tile-major (`quantize_mxfp8_weight`)")
         ws = _gemm_workspace(dev, lib.b200_gemm_mxfp8_splitk_bytes(M, N, K))
-        check("b200_gemm_mxfp8_splitk", lib.b200_gemm_mxfp8_splitk(
-            x.q.data_ptr(), x.sf.data_ptr(), w.q.data_ptr(), w.sf.data_ptr(), M, N, K, ws.data_ptr(), ws.numel(),
-            ctypes.byref(n), _stream()))
+        n = _launch("gemm_splitk", 1, x.q, x.sf, 0, w.q, w.sf, ws, M, N, K)
     elif isinstance(x, Fp8BlockTensor):
         K, M, N, dev = x.shape[-1], x.q.shape[0], w.shape[0], x.q.device
         ws = _gemm_workspace(dev, lib.b200_gemm_fp8_block_splitk_bytes(M, N, K))
-        check("b200_gemm_fp8_block_splitk", lib.b200_gemm_fp8_block_splitk(
-            x.q.data_ptr(), x.scale.data_ptr(), x.m_pad, w.q.data_ptr(), w.scale.data_ptr(), M, N, K, ws.data_ptr(),
-            ws.numel(), ctypes.byref(n), _stream()))
+        n = _launch("gemm_splitk", 2, x.q, x.scale, x.m_pad, w.q, w.scale, ws, M, N, K)
     else:
         _need(x, BF16, "x")
         _need(w, BF16, "w")
@@ -484,9 +479,8 @@ def gemm_splitk(x, w) -> GemmPartials:
         if w.shape[1] != K:
             raise B200Error("gemm_splitk", -1, f"shape mismatch x[..., {K}] vs w{tuple(w.shape)}")
         ws = _gemm_workspace(dev, lib.b200_gemm_bf16_splitk_bytes(M, N, K))
-        check("b200_gemm_bf16_splitk", lib.b200_gemm_bf16_splitk(
-            x.data_ptr(), K, w.data_ptr(), M, N, K, ws.data_ptr(), ws.numel(), ctypes.byref(n), _stream()))
-    return GemmPartials(ws, n.value, (*x.shape[:-1], N))
+        n = _launch("gemm_splitk", 0, x, None, 0, w, None, ws, M, N, K)
+    return GemmPartials(ws, int(n), (*x.shape[:-1], N))
 
 
 def add_norm_splitk(p: GemmPartials, gamma, *, bias=None, residual=None, beta=None, eps: float = 1e-5,
@@ -500,23 +494,17 @@ def add_norm_splitk(p: GemmPartials, gamma, *, bias=None, residual=None, beta=No
         rows *= d
     dev = p.device
     h = torch.empty(p.shape, dtype=BF16, device=dev) if want_hidden else None
-    lib = _lib.load()
     if quantize == "mxfp8":
         q, sf = _mx_buffers(rows, hidden, dev)
-        check("b200_add_norm_splitk_mxfp8", lib.b200_add_norm_splitk_mxfp8(
-            p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(),
-            rows, hidden, eps, _stream()))
+        _launch("add_norm", None, p.buf, p.num_splits, bias, residual, gamma, beta, h, None, q, sf, 1, 0, rows, hidden, eps)
         return h, Mxfp8Tensor(q, sf, p.shape)
     if quantize == "blockwise":
         q, scale, m_pad = _rowblock_buffers(rows, hidden, dev)
-        check("b200_add_norm_splitk_fp8_rowblock", lib.b200_add_norm_splitk_fp8_rowblock(
-            p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(),
-            scale.data_ptr(), m_pad, rows, hidden, eps, _stream()))
+        _launch("add_norm", None, p.buf, p.num_splits, bias, residual, gamma, beta, h, None, q, scale, 2, m_pad, rows, hidden,
+                eps)
         return h, Fp8BlockTensor(q, scale, p.shape, m_pad)
     y = torch.empty(p.shape, dtype=BF16, device=dev) if want_normed else None
-    check("b200_add_norm_splitk_bf16", lib.b200_add_norm_splitk_bf16(
-        p.buf.data_ptr(), p.num_splits, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps,
-        _stream()))
+    _launch("add_norm", None, p.buf, p.num_splits, bias, residual, gamma, beta, h, y, None, None, 0, 0, rows, hidden, eps)
     return h, y
 
 
@@ -534,27 +522,22 @@ def allreduce_add_norm(pending, gamma, *, bias=None, residual=None, beta=None, e
         # every rank finishes its share of the rows and stores them into all ranks' buffers: the results are views of
         # this rank's buffers (valid until the next call through the same communicator)
         q_mode = {None: 0, "mxfp8": 1, "blockwise": 2}[quantize]
-        check("b200_allreduce2_add_norm", _lib.load().b200_allreduce2_add_norm(
-            ctypes.byref(comm.comm), _p(bias), _p(residual), _p(gamma), _p(beta), q_mode, rows, hidden, eps, _stream()))
+        _launch("allreduce_add_norm", _blob(comm.comm), 1, 0, bias, residual, gamma, beta, None, None, None, None, q_mode, 0,
+                rows, hidden, eps)
         return comm.hidden_view(pending.shape), comm.normed_view(rows, quantize, pending.shape)
     h = torch.empty(pending.shape, dtype=BF16, device=dev) if want_hidden else None
-    lib = _lib.load()
-    c = ctypes.byref(comm.comm)
+    c = _blob(comm.comm)
     if quantize == "mxfp8":
         q, sf = _mx_buffers(rows, hidden, dev)
-        check("b200_allreduce_add_norm_mxfp8", lib.b200_allreduce_add_norm_mxfp8(
-            c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), sf.data_ptr(), rows, hidden,
-            eps, _stream()))
+        _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, None, q, sf, 1, 0, rows, hidden, eps)
         return h, Mxfp8Tensor(q, sf, pending.shape)
     if quantize == "blockwise":
         q, scale, m_pad = _rowblock_buffers(rows, hidden, dev)
-        check("b200_allreduce_add_norm_fp8_rowblock", lib.b200_allreduce_add_norm_fp8_rowblock(
-            c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), q.data_ptr(), scale.data_ptr(), m_pad,
-            rows, hidden, eps, _stream()))
+        _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, None, q, scale, 2, m_pad, rows,
+                hidden, eps)
         return h, Fp8BlockTensor(q, scale, pending.shape, m_pad)
     y = torch.empty(pending.shape, dtype=BF16, device=dev) if want_normed else None
-    check("b200_allreduce_add_norm_bf16", lib.b200_allreduce_add_norm_bf16(
-        c, pending.slot, _p(bias), _p(residual), _p(gamma), _p(beta), _p(h), _p(y), rows, hidden, eps, _stream()))
+    _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, y, None, None, 0, 0, rows, hidden, eps)
     return h, y
 
 
@@ -618,6 +601,7 @@ def make_attention_args(*, qkv, k_cache, v_cache, block_table, kv_seq_lengths, o
     ws = attention_workspace(device, T, num_q_heads, head_dim, num_splits) if (out is not None or out_quantized is not None) else None
     a.workspace = _p(ws)
     a.workspace_bytes = 0 if ws is None else ws.numel()
+    a._anchor = k_cache  # device + stream of the launches that take this struct
     return a
 
 
@@ -633,12 +617,12 @@ def quantized_like(kind: str, rows: int, K: int, device, lead_shape=None):
 
 
 def rope_append(args: AttentionArgs) -> None:
-    check("b200_rope_append", _lib.load().b200_rope_append(ctypes.byref(args), _stream()))
+    _launch("attention", _blob(args), args._anchor, 0, None, 0)
 
 
 def paged_attention(args: AttentionArgs) -> None:
     global launch_count
-    check("b200_paged_attention", _lib.load().b200_paged_attention(ctypes.byref(args), _stream()))
+    _launch("attention", _blob(args), args._anchor, 1, None, 0)
     if args.num_splits > 1:
         launch_count += 1  # the split-combine kernel
 
@@ -668,8 +652,7 @@ def fp8_values_from_pool_layout(p: torch.Tensor) -> torch.Tensor:
 def paged_prefill_attention(args: AttentionArgs, units: torch.Tensor, num_units: int) -> None:
     """Prefill attention over ``units`` int32 [>= num_units, 4] = (block-table row, first token, token count, 0)."""
     _need(units, torch.int32, "units")
-    check("b200_paged_prefill_attention", _lib.load().b200_paged_prefill_attention(
-        ctypes.byref(args), units.data_ptr(), int(num_units), _stream()))
+    _launch("attention", _blob(args), args._anchor, 2, units, int(num_units))
 
 
 def prefill_q_block(num_q_heads: int, num_kv_heads: int) -> int:
@@ -683,8 +666,7 @@ def argmax(logits):
     _need(logits, BF16, "logits")
     rows, vocab = logits.shape
     out = torch.empty((rows,), dtype=torch.int64, device=logits.device)
-    check("b200_argmax_bf16", _lib.load().b200_argmax_bf16(logits.data_ptr(), logits.stride(0), out.data_ptr(), rows,
-                                                            vocab, _stream()))
+    _launch("argmax", logits, out)
     return out
 
 
@@ -695,8 +677,7 @@ def argmax_shard(logits, index_offset: int, keys=None):
     rows, vocab = logits.shape
     if keys is None:
         keys = torch.empty((rows,), dtype=torch.int64, device=logits.device)
-    check("b200_argmax_shard_bf16", _lib.load().b200_argmax_shard_bf16(
-        logits.data_ptr(), logits.stride(0), keys.data_ptr(), rows, vocab, int(index_offset), _stream()))
+    _launch("argmax_shard", logits, keys, int(index_offset))
     return keys
 
 
@@ -705,7 +686,7 @@ def argmax_merge(keys):
     _need(keys, torch.int64, "keys")
     shards, rows = keys.shape
     out = torch.empty((rows,), dtype=torch.int64, device=keys.device)
-    check("b200_argmax_merge", _lib.load().b200_argmax_merge(keys.data_ptr(), shards, rows, out.data_ptr(), _stream()))
+    _launch("argmax_merge", keys, shards, rows, out)
     return out
 
 
@@ -714,8 +695,9 @@ def topk_probs(logits, top_k: int, temperature: float = 1.0):
     _need(logits, BF16, "logits")
     rows, vocab = logits.shape
     probs = torch.empty((rows, vocab), dtype=torch.float32, device=logits.device)
-    check("b200_topk_probs_bf16", _lib.load().b200_topk_probs_bf16(
-        logits.data_ptr(), logits.stride(0), probs.data_ptr(), rows, vocab, top_k, float(temperature), _stream()))
+    if top_k <= 0:
+        raise B200Error("topk_probs", -1, f"top_k must be positive, got {top_k}")
+    _launch("filtered_probs", logits, probs, int(top_k), 0.0, float(temperature))
     return probs
 
 
@@ -724,6 +706,5 @@ def topp_probs(logits, top_p: float, temperature: float = 1.0):
     _need(logits, BF16, "logits")
     rows, vocab = logits.shape
     probs = torch.empty((rows, vocab), dtype=torch.float32, device=logits.device)
-    check("b200_topp_probs_bf16", _lib.load().b200_topp_probs_bf16(
-        logits.data_ptr(), logits.stride(0), probs.data_ptr(), rows, vocab, float(top_p), float(temperature), _stream()))
+    _launch("filtered_probs", logits, probs, 0, float(top_p), float(temperature))
     return probs
