@@ -1,0 +1,83 @@
+"""The reference engine's view of this package's context and controller.
+
+The reference's `DynamicInferenceEngine` (megatron/core/inference/engines/dynamic_engine.py) asserts the classes of
+the controller and context it is given (:107-108) and then uses a fixed set of their attributes and methods.  In a
+child process that imports the reference (it cannot travel, so the test is skipped where the checkout is absent):
+  * `reference_subclasses()` yields classes that pass those isinstance checks and resolve every method to this
+    package's implementation;
+  * every `context.<name>` / `controller.<name>` the reference engine's source uses exists here, and where it is a
+    method the parameter lists agree (names, order, defaults);
+  * the dict the controller returns per step has the keys the engine reads (:576-582).
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+REFERENCE = os.environ.get("MEGATRON_REFERENCE", "/root/reference")
+
+CHILD = r'''
+import inspect, json, os, re, sys
+ref, root = sys.argv[1], sys.argv[2]
+sys.path.insert(0, ref); sys.path.insert(0, root)
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+import torch
+torch.cuda.current_device = lambda: torch.device("cpu")
+from megatron.core.inference.contexts.dynamic_context import DynamicInferenceContext as RefCtx
+from megatron.core.inference.text_generation_controllers.simple_text_generation_controller import SimpleTextGenerationController as RefCtl
+from megatron_mixtera_b200.inference.contexts.dynamic_context import DynamicInferenceContext as Ctx
+from megatron_mixtera_b200.inference.text_generation_controllers.text_generation_controller import TextGenerationController as Ctl
+from megatron_mixtera_b200.reference_seam import reference_subclasses
+
+C, T = reference_subclasses()
+out = {"sub": [issubclass(C, RefCtx), issubclass(C, Ctx), issubclass(T, RefCtl), issubclass(T, Ctl)],
+       "same": reference_subclasses()[0] is C, "shadowed": [], "missing": [], "signature": []}
+# every attribute the reference classes define resolves to this package's implementation when this package has one
+for cls, ours in ((C, Ctx), (T, Ctl)):
+    for name in dir(ours):
+        if not name.startswith("__") and inspect.getattr_static(cls, name) is not inspect.getattr_static(ours, name):
+            out["shadowed"].append(name)
+src = open(os.path.join(ref, "megatron/core/inference/engines/dynamic_engine.py")).read()
+def sig(f):
+    return [(p.name, p.kind.name, repr(p.default)) for p in inspect.signature(f).parameters.values()]
+for pattern, ours, theirs in ((r"(?<![\w.])(?:self\.)?context\.([a-z_]\w*)", Ctx, RefCtx), (r"controller\.([a-z_]\w*)", Ctl, RefCtl)):
+    ours_src = inspect.getsource(ours)
+    for name in sorted(set(re.findall(pattern, src))):
+        if not (hasattr(ours, name) or re.search(r"self\.%s\b\s*(?::[^=\n]+)?=" % name, ours_src)):
+            out["missing"].append(name)
+        elif inspect.isfunction(getattr(theirs, name, None)) and sig(getattr(theirs, name)) != sig(getattr(ours, name)):
+            out["signature"].append(name)
+step = src[src.index("controller.async_generate_output_tokens_dynamic_batch("):]
+keys = set(re.findall(r'= result\["(\w+)"\]', step[:step.index("schedule_waiting_requests")]))
+out["result_keys_missing"] = sorted(k for k in keys if ('"%s":' % k) not in inspect.getsource(Ctl))
+out["n_result_keys"] = len(keys)
+print("RESULT " + json.dumps(out))
+'''
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "megatron", "core")), reason="reference checkout absent")
+def test_reference_engine_accepts_our_classes():
+    import json
+
+    proc = subprocess.run([sys.executable, "-c", CHILD, REFERENCE, ROOT], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    out = json.loads(line[len("RESULT "):])
+    assert out["sub"] == [True, True, True, True] and out["same"]
+    assert out["shadowed"] == []
+    assert out["missing"] == []
+    assert out["signature"] == []
+    assert out["n_result_keys"] >= 6 and out["result_keys_missing"] == []
+
+
+def test_seam_needs_the_reference():
+    """Without the reference on the path the helper fails with ImportError: nothing is stubbed."""
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from megatron_mixtera_b200.reference_seam import reference_subclasses\n"
+            "try:\n    reference_subclasses()\nexcept ImportError:\n    print('IMPORTERROR')\n" % ROOT)
+    env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
+    proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env, cwd="/tmp")
+    assert "IMPORTERROR" in proc.stdout, proc.stdout + proc.stderr[-2000:]
