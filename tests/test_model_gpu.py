@@ -129,12 +129,12 @@ def run_teacher_forced(meta, trace, *, enable_cuda_graph=False, check_ctx=None):
     return state, gen, wrapper
 
 
-def assert_flips_are_near_ties(flips, n_decisions, resolution=2.0**-7):
+def assert_flips_are_near_ties(flips, n_decisions, resolution=2.0**-7, max_fraction=0.1):
     # a flip is legitimate only where the reference's own top-1/top-2 margin is within the arithmetic's
     # resolution of the logit magnitude (2^-7 relative for bf16); everything else is a real error
     for step, row, margin, scale in flips:
         assert margin <= 2 * scale * resolution, (step, row, margin, scale)
-    assert len(flips) <= max(2, n_decisions // 10), (len(flips), n_decisions)
+    assert len(flips) <= max(2, int(n_decisions * max_fraction)), (len(flips), n_decisions)
 
 
 def test_llama_tiny_bf16_matches_reference_trace():
