@@ -737,6 +737,9 @@ def main():
     ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
+    ap.add_argument("--synthesize-kv", action="store_true",
+                    help="skip the prefill forward passes: admit the requests through the bookkeeping only and fill the KV "
+                         "pool with seeded noise (decode timing does not depend on the pool's contents)")
     ap.add_argument("--deadline", type=int, default=1500,
                     help="seconds after which a stuck run dumps every thread's stack and exits instead of waiting to be killed")
     args = ap.parse_args()
@@ -745,6 +748,11 @@ def main():
     faulthandler.dump_traceback_later(args.deadline, exit=True)
     protect_stdout()
     w = configs.WORKLOADS[args.workload]
+    if args.synthesize_kv and not w.synthesize_kv:
+        import dataclasses
+
+        w = dataclasses.replace(w, synthesize_kv=True, max_prefill_tokens=0,
+                                name=w.name + " (KV pool filled with seeded noise instead of a prefill)")
     if args.impl == "reference":
         run_reference(args, w)
     else:

@@ -84,12 +84,22 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 1
 
 using attn::Params;
 
-// kTwoTerms: queries and probabilities as hi + lo E4M3 terms (the kernel then adds nothing measurable to the
-// pool's own quantisation error: 1.3e-3 against 4e-2 relative); false: one term each, half the tensor-core work
-// (the usual FP8-attention trade: total error 5.2e-2 instead of 4.0e-2, 1.6x the speed).
-template <bool kTwoTerms>
+// kMode 1, 2: queries and probabilities as hi + lo E4M3 terms (the kernel then adds nothing measurable to the
+// pool's own quantisation error: 1.3e-3 against 4e-2 relative); kMode 0: one term each (the usual FP8-attention
+// trade: total error 5.2e-2 instead of 4.0e-2).
+// kMode 2 ("stacked", groups of at most 8 query heads - every Llama shape): the hi terms of the group's heads are rows
+// 0..7 of the 16-row A operand and the lo terms of the same heads rows 8..15, so ONE mma yields both partial products
+// and the thread that owns row g also owns row g + 8: S = S_hi + S_lo and O = O_hi + O_lo are register adds.  Two
+// terms then cost the tensor-core work of one, and the softmax runs on one row per thread instead of two.
+// kMode 1 (groups of 9..16 heads): the terms as separate mma instructions into the same accumulators.
+// kMode 3: one term for groups of at most 8 heads - rows 8..15 are padding, so their softmax is skipped.
+template <int kMode>
 __global__ void __launch_bounds__(kThreads, 2)
 paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, Params p) {
+  constexpr bool kTwoTerms = kMode == 1 || kMode == 2;
+  constexpr bool kStacked = kMode == 2;
+  constexpr bool kLowerRowsOnly = kMode == 3;
+  constexpr int kRows = (kStacked || kLowerRowsOnly) ? 1 : 2;  // accumulator rows (g, g + 8) with a softmax state of their own
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -237,6 +247,10 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     ql[s][1] = *reinterpret_cast<const uint32_t*>(q8_lo + (gid + 8) * kQ8Stride + c0);
     ql[s][2] = *reinterpret_cast<const uint32_t*>(q8_lo + gid * kQ8Stride + c0 + 16);
     ql[s][3] = *reinterpret_cast<const uint32_t*>(q8_lo + (gid + 8) * kQ8Stride + c0 + 16);
+    if constexpr (kStacked) {  // rows 8..15 of the A operand = the lo terms of rows 0..7
+      qh[s][1] = ql[s][0];
+      qh[s][3] = ql[s][2];
+    }
   }
   // logits in the log2 domain: acc * (query scale * key scale * softmax scale * log2 e), per row
   const float row_scale[2] = {q_scale[gid] * p.k_scale[h] * p.scale_log2, q_scale[gid + 8] * p.k_scale[h] * p.scale_log2};
@@ -316,9 +330,9 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4(kbase + trow * 128 + ((c16 ^ (trow & 7)) << 4), b0, b1, b2, b3);
           mma_e4m3_16832(sacc[pair * 2], qh[ks], b0, b1);
-          if constexpr (kTwoTerms) mma_e4m3_16832(sacc[pair * 2], ql[ks], b0, b1);
+          if constexpr (kTwoTerms && !kStacked) mma_e4m3_16832(sacc[pair * 2], ql[ks], b0, b1);
           mma_e4m3_16832(sacc[pair * 2 + 1], qh[ks], b2, b3);
-          if constexpr (kTwoTerms) mma_e4m3_16832(sacc[pair * 2 + 1], ql[ks], b2, b3);
+          if constexpr (kTwoTerms && !kStacked) mma_e4m3_16832(sacc[pair * 2 + 1], ql[ks], b2, b3);
         }
       }
       // ---- online softmax (log2 domain) ----
@@ -326,9 +340,9 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2 * kRows; ++c) {
           const int tok = tok0 + r0 + nt * 8 + tig * 2 + (c & 1);
-          float v = sacc[nt][c] * row_scale[c >> 1];
+          float v = kStacked ? (sacc[nt][c] + sacc[nt][c + 2]) * row_scale[0] : sacc[nt][c] * row_scale[c >> 1];
           if (tok >= end) v = -INFINITY;
           sacc[nt][c] = v;
           mx[c >> 1] = fmaxf(mx[c >> 1], v);
@@ -336,7 +350,7 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       }
       float alpha[2], m_use[2];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
+      for (int r = 0; r < kRows; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m_run[r], mx[r]);
@@ -353,7 +367,7 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2 * kRows; ++c) {
             const float pv = exp2f(sacc[nt][c] - m_use[c >> 1]);
             l_run[c >> 1] += pv;
             const float ps = pv * kPScale;
@@ -362,14 +376,22 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
           }
         }
         ph[0] = pack_e4m3x4(hi[0][0], hi[0][1], hi[1][0], hi[1][1]);
-        ph[1] = pack_e4m3x4(hi[0][2], hi[0][3], hi[1][2], hi[1][3]);
         ph[2] = pack_e4m3x4(hi[2][0], hi[2][1], hi[3][0], hi[3][1]);
-        ph[3] = pack_e4m3x4(hi[2][2], hi[2][3], hi[3][2], hi[3][3]);
         pl[0] = pack_e4m3x4(lo[0][0], lo[0][1], lo[1][0], lo[1][1]);
-        pl[1] = pack_e4m3x4(lo[0][2], lo[0][3], lo[1][2], lo[1][3]);
         pl[2] = pack_e4m3x4(lo[2][0], lo[2][1], lo[3][0], lo[3][1]);
-        pl[3] = pack_e4m3x4(lo[2][2], lo[2][3], lo[3][2], lo[3][3]);
+        if constexpr (kStacked) {  // rows 8..15 of the A operand = the lo terms of rows 0..7
+          ph[1] = pl[0];
+          ph[3] = pl[2];
+        } else if constexpr (kLowerRowsOnly) {
+          ph[1] = ph[3] = 0u;
+        } else {
+          ph[1] = pack_e4m3x4(hi[0][2], hi[0][3], hi[1][2], hi[1][3]);
+          ph[3] = pack_e4m3x4(hi[2][2], hi[2][3], hi[3][2], hi[3][3]);
+          pl[1] = pack_e4m3x4(lo[0][2], lo[0][3], lo[1][2], lo[1][3]);
+          pl[3] = pack_e4m3x4(lo[2][2], lo[2][3], lo[3][2], lo[3][3]);
+        }
       }
+      if constexpr (kRows == 1) alpha[1] = alpha[0];  // stacked: the O_lo rows follow their head's running maximum
 #pragma unroll
       for (int i2 = 0; i2 < D / 8; ++i2) {
         oacc[i2][0] *= alpha[0];
@@ -387,9 +409,9 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(vbase + drow * 128 + ((c16 ^ (drow & 7)) << 4), b0, b1, b2, b3);
         mma_e4m3_16832(oacc[dn * 2], ph, b0, b1);
-        if constexpr (kTwoTerms) mma_e4m3_16832(oacc[dn * 2], pl, b0, b1);
+        if constexpr (kTwoTerms && !kStacked) mma_e4m3_16832(oacc[dn * 2], pl, b0, b1);
         mma_e4m3_16832(oacc[dn * 2 + 1], ph, b2, b3);
-        if constexpr (kTwoTerms) mma_e4m3_16832(oacc[dn * 2 + 1], pl, b2, b3);
+        if constexpr (kTwoTerms && !kStacked) mma_e4m3_16832(oacc[dn * 2 + 1], pl, b2, b3);
       }
     }
     __syncwarp();
@@ -398,7 +420,7 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
 
   // ------------------------------ merge the four warps ------------------------------
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < kRows; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
@@ -411,16 +433,25 @@ paged_attention_fp8_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     const int col = i2 * 8 + tig * 2;
     float* o0 = mo + (warp * 16 + gid) * D + col;
     float* o1 = mo + (warp * 16 + gid + 8) * D + col;
-    o0[0] = oacc[i2][0];
-    o0[1] = oacc[i2][1];
-    o1[0] = oacc[i2][2];
-    o1[1] = oacc[i2][3];
+    if constexpr (kStacked) {  // O = O_hi + O_lo; rows 8..15 are not heads
+      o0[0] = oacc[i2][0] + oacc[i2][2];
+      o0[1] = oacc[i2][1] + oacc[i2][3];
+    } else {
+      o0[0] = oacc[i2][0];
+      o0[1] = oacc[i2][1];
+      if constexpr (!kLowerRowsOnly) {
+        o1[0] = oacc[i2][2];
+        o1[1] = oacc[i2][3];
+      }
+    }
   }
   if (tig == 0) {
     mm[warp * 16 + gid] = m_run[0];
-    mm[warp * 16 + gid + 8] = m_run[1];
     ml[warp * 16 + gid] = l_run[0];
-    ml[warp * 16 + gid + 8] = l_run[1];
+    if constexpr (kRows == 2) {
+      mm[warp * 16 + gid + 8] = m_run[1];
+      ml[warp * 16 + gid + 8] = l_run[1];
+    }
   }
   consumer_barrier();
   for (int i = tid; i < G * D; i += kConsumerThreads) {
@@ -523,16 +554,20 @@ static int launch_attention_fp8(Params& p, bool two_terms, cudaStream_t stream) 
   const CUtensorMap* mv = get_tensor_map(p.v_cache, 3, vdims, vstr, vbox, CU_TENSOR_MAP_SWIZZLE_128B,
                                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_DATA_TYPE_UINT8);
   if (!mk || !mv) return B200_ERR_DRIVER;
-  static std::atomic<uint64_t> smem_attr_done2{0}, smem_attr_done1{0};
-  if (ensure_dynamic_smem(paged_attention_fp8_kernel<true>, kSmemBytes, smem_attr_done2) != B200_OK ||
-      ensure_dynamic_smem(paged_attention_fp8_kernel<false>, kSmemBytes, smem_attr_done1) != B200_OK)
+  static std::atomic<uint64_t> smem_attr_done0{0}, smem_attr_done1{0}, smem_attr_done2{0}, smem_attr_done3{0};
+  if (ensure_dynamic_smem(paged_attention_fp8_kernel<0>, kSmemBytes, smem_attr_done0) != B200_OK ||
+      ensure_dynamic_smem(paged_attention_fp8_kernel<1>, kSmemBytes, smem_attr_done1) != B200_OK ||
+      ensure_dynamic_smem(paged_attention_fp8_kernel<2>, kSmemBytes, smem_attr_done2) != B200_OK ||
+      ensure_dynamic_smem(paged_attention_fp8_kernel<3>, kSmemBytes, smem_attr_done3) != B200_OK)
     return B200_ERR_LAUNCH;
   const int64_t units = static_cast<int64_t>(p.T) * p.nkv * p.num_splits;
   if (units > 0x7fffffff) return B200_ERR_INVALID_ARGUMENT;
-  int rc = two_terms ? launch_pdl(paged_attention_fp8_kernel<true>, dim3(static_cast<unsigned>(units)), dim3(kThreads),
-                                  kSmemBytes, stream, *mk, *mv, p)
-                     : launch_pdl(paged_attention_fp8_kernel<false>, dim3(static_cast<unsigned>(units)), dim3(kThreads),
-                                  kSmemBytes, stream, *mk, *mv, p);
+  const int mode = two_terms ? (p.G <= 8 ? 2 : 1) : (p.G <= 8 ? 3 : 0);
+  const dim3 grid(static_cast<unsigned>(units)), block(kThreads);
+  int rc = mode == 0   ? launch_pdl(paged_attention_fp8_kernel<0>, grid, block, kSmemBytes, stream, *mk, *mv, p)
+           : mode == 1 ? launch_pdl(paged_attention_fp8_kernel<1>, grid, block, kSmemBytes, stream, *mk, *mv, p)
+           : mode == 2 ? launch_pdl(paged_attention_fp8_kernel<2>, grid, block, kSmemBytes, stream, *mk, *mv, p)
+                       : launch_pdl(paged_attention_fp8_kernel<3>, grid, block, kSmemBytes, stream, *mk, *mv, p);
   if (rc != B200_OK) return rc;
   if (p.num_splits > 1) rc = launch_pdl(combine_fp8_kernel, dim3(p.T * p.nq), dim3(D), 0, stream, p);
   return rc;

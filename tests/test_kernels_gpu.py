@@ -604,6 +604,7 @@ def test_attention_split_invariance_at_long_context(ops):
     "nkv,G,chunk,kv_lens,splits",
     [(2, 4, 128, [1, 64, 65, 130, 0, 300, 17, 256, 128, 129], 1), (2, 4, 128, [1, 64, 65, 130, 0, 300, 17, 256], 3),
      (8, 4, 256, [2304, 128, 700, 1216, 0], 2), (1, 8, 256, [5000, 257], 4), (2, 1, 128, [33, 500], 1),
+     (1, 16, 128, [700, 129, 1], 2),  # a group of more than 8 heads: the two terms as separate tensor-core instructions
      (1, 4, 256, [131072, 33000, 40001], 16)],  # the long-context stress: 513-column block table, 16 context splits
 )
 @pytest.mark.parametrize("fused,single_term", [(True, False), (False, False), (True, True)])
