@@ -7,6 +7,7 @@ interpreter that builds it.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import shutil
 import subprocess
@@ -33,6 +34,18 @@ def _sources():
     return out
 
 
+@contextlib.contextmanager
+def _build_lock():
+    import fcntl
+
+    with open(os.path.join(PKG_DIR, ".build.lock"), "w") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
+
+
 def needs_build() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
@@ -44,19 +57,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not needs_build():
         return LIB_PATH
-    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    if not os.path.exists(nvcc):
-        raise RuntimeError("nvcc not found: cannot build libb200_decode.so")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(CSRC, "b200_decode.cu")]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd), file=sys.stderr)
-    proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-    if verbose:
-        print(proc.stderr, file=sys.stderr)
+    with _build_lock():  # several ranks of one job may get here at once: one compiles, the others find it done
+        if not force and not needs_build():
+            return LIB_PATH
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        if not os.path.exists(nvcc):
+            raise RuntimeError("nvcc not found: cannot build libb200_decode.so")
+        tmp = LIB_PATH + ".tmp%d" % os.getpid()
+        cmd = [nvcc, *NVCC_FLAGS, "-o", tmp, os.path.join(CSRC, "b200_decode.cu")]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+            print(" ".join(cmd), file=sys.stderr)
+        proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        os.replace(tmp, LIB_PATH)
+        if verbose:
+            print(proc.stderr, file=sys.stderr)
     return LIB_PATH
 
 
@@ -73,6 +91,13 @@ def build_torch_ops(force: bool = False) -> str:
     build()
     if not force and not torch_ops_need_build():
         return TORCH_LIB_PATH
+    with _build_lock():
+        if not force and not torch_ops_need_build():
+            return TORCH_LIB_PATH
+        return _compile_torch_ops()
+
+
+def _compile_torch_ops() -> str:
     import torch
     from torch.utils import cpp_extension
 

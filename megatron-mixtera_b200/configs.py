@@ -63,20 +63,20 @@ LLAMA3_8B_MXFP8_SHAPE_2LAYER = Workload(
     num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336, vocab_size=128256,
     num_requests=128, prompt_len_range=(256, 4096), num_tokens_to_generate=24, fp8="mxfp8")
 
-# MXFP8 linears and an E4M3 KV pool (per-head scales; one-term attention arithmetic), 128 requests: the single-GPU form of
-# the "FP8 weights + FP8 KV" configuration.
+# MXFP8 linears and an E4M3 KV pool (per-head scales; two-term attention arithmetic, the one inside the FP8 logit
+# tolerance), 128 requests: the short-context form of the "FP8 weights + FP8 KV" configuration.
 LLAMA3_8B_MXFP8_FP8KV_128REQ = Workload(
-    name="llama3-8b-shape MXFP8 linears + E4M3 KV (one-term attention) decode, 128 requests, prompt U[256,4096], 256 greedy tokens, KV chunk 256",
+    name="llama3-8b-shape MXFP8 linears + E4M3 KV (two-term attention) decode, 128 requests, prompt U[256,4096], 256 greedy tokens, KV chunk 256",
     num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
     ffn_hidden_size=14336, vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096),
-    num_tokens_to_generate=256, fp8="mxfp8", kv_fp8="one_term")
+    num_tokens_to_generate=256, fp8="mxfp8", kv_fp8="two_term")
 
 # Two-layer cut of it for profiler captures.
 LLAMA3_8B_MXFP8_FP8KV_SHAPE_2LAYER = Workload(
-    name="llama3-8b-shape MXFP8 + E4M3 KV (one-term attention) cut to 2 layers, 128 requests, prompt U[256,4096]",
+    name="llama3-8b-shape MXFP8 + E4M3 KV (two-term attention) cut to 2 layers, 128 requests, prompt U[256,4096]",
     num_layers=2, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=14336,
     vocab_size=128256, num_requests=128, prompt_len_range=(256, 4096), num_tokens_to_generate=24, fp8="mxfp8",
-    kv_fp8="one_term")
+    kv_fp8="two_term")
 
 # Llama-3-70B-shaped FP8 decode: E4M3 weights with 128 x 128 block scales, 1 x 128 per-token activation scales,
 # bf16 KV cache, 256 concurrent requests, prompts uniform in [512, 8192], 512 output tokens; tensor parallel 2 / 4 / 8.

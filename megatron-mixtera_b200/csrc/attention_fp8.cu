@@ -9,10 +9,11 @@
 //               (v_position below) to the order in which the S accumulators of a thread hold the tokens:
 //               the P fragment is then built from the thread's own registers, without shuffles.
 // One CTA = (row, KV head, context split) as in the 16-bit kernel; a tile is 128 tokens (K 16 KB + V^T 16 KB),
-// every consumer warp takes 32 of them.  Neither HBM nor the tensor pipe is saturated (profiler: 61 % / 29 % with one
-// term): the per-tile chain ldmatrix -> mma -> softmax -> pack -> ldmatrix -> mma of the eight consumer warps an SM holds
-// is latency bound.  With two terms the kernel reads E4M3 bytes at ~4 TB/s (1.16x the tokens per second of the 16-bit
-// kernel), with one term at ~6.5 TB/s (1.8x).  (Two stages and three CTAs per SM were tried: registers spill, no gain.)
+// every consumer warp takes 32 of them.  The per-tile chain ldmatrix -> mma -> softmax -> pack -> ldmatrix -> mma of the
+// eight consumer warps an SM holds is latency bound, so what counts is the number of mma and exp2 per tile: with the two
+// terms as separate instructions the kernel read E4M3 bytes at ~4 TB/s; stacked in one 16-row operand (kMode 2 below)
+// it reads them at 6.3-6.4 TB/s, the measured HBM copy rate (32 requests x 68 k tokens, 16 context splits), twice the
+// tokens per second of the 16-bit kernel.  (Two stages and three CTAs per SM were tried: registers spill, no gain.)
 #include <cuda_fp8.h>
 
 #include "common.cuh"
