@@ -302,7 +302,7 @@ int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, con
  * finished rows into EVERY rank's output buffers (peer stores): `hidden_out` [max_rows][hidden] bf16, `normed_out`
  * ([max_rows][hidden] bf16, or E4M3 bytes) and `scales_out` (MXFP8 tile-layout scale bytes of a [max_rows, hidden]
  * matrix, or fp32 [hidden / 128][m_pad]).  Each row is computed exactly once, so all ranks hold identical bits.
- * `flags[r]`: 16 int32 of rank r (zero-initialised, peer-mapped); `counters`: 2 local int32 (zeroed).  Two flag
+ * `flags[r]`: 16 int32 of rank r (zero-initialised, peer-mapped); `counters`: 4 local int32 (zeroed).  Two flag
  * exchanges per call (inputs complete / outputs stored), each wait bounded by b200_set_wait_limit_ns (device status
  * 4 on expiry); the kernel completes only after every rank's rows have arrived, so later kernels on the stream may
  * read the local output buffers.  `residual` is local memory and may be this rank's `hidden_out` buffer itself.
@@ -321,6 +321,13 @@ typedef struct {
 } b200_tp_exchange;
 int b200_allreduce2_add_norm(const b200_tp_exchange* comm, const void* bias, const void* residual, const void* gamma,
                              const void* beta, int q_mode, int rows, int hidden, float eps, b200_stream_t stream);
+/* The same with the row-parallel GEMM's split-K partial sums as input (b200_gemm_*_splitk: `partials`
+ * [num_splits][rows][hidden] fp32, local memory): the kernel first sums them in split order into this rank's `in` buffer
+ * (what the GEMM's own reduction kernel would have written there) and then proceeds as above - one launch fewer per
+ * linear, bit-identical results. */
+int b200_allreduce2_add_norm_splitk(const b200_tp_exchange* comm, const float* partials, int num_splits, const void* bias,
+                                    const void* residual, const void* gamma, const void* beta, int q_mode, int rows,
+                                    int hidden, float eps, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Paged-KV attention for the dynamic context.

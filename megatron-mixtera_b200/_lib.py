@@ -62,6 +62,7 @@ EXPORTED_SYMBOLS = (
     "b200_allreduce_add_norm_mxfp8",
     "b200_allreduce_add_norm_fp8_rowblock",
     "b200_allreduce2_add_norm",
+    "b200_allreduce2_add_norm_splitk",
     "b200_paged_attention_workspace_bytes",
     "b200_rope_append",
     "b200_paged_attention",
@@ -248,6 +249,8 @@ def load() -> ctypes.CDLL:
                                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.b200_allreduce2_add_norm.argtypes = [POINTER(TpExchange), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_float, c_void_p]
+    lib.b200_allreduce2_add_norm_splitk.argtypes = [POINTER(TpExchange), c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                    c_int, c_int, c_int, c_float, c_void_p]
     lib.b200_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     lib.b200_paged_attention_workspace_bytes.restype = c_size_t
     lib.b200_paged_attention_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]

@@ -345,7 +345,9 @@ void filtered_probs(const Tensor& logits, Tensor probs, int64_t top_k, double to
 void allreduce_add_norm(const Tensor& comm, int64_t two_shot, int64_t slot, const OptTensor& bias, const OptTensor& residual,
                         const Tensor& gamma, const OptTensor& beta, const OptTensor& hidden_out, const OptTensor& normed_out,
                         const OptTensor& q_out, const OptTensor& scales_out, int64_t q_mode, int64_t m_pad, int64_t rows,
-                        int64_t hidden, double eps) {
+                        int64_t hidden, double eps, const OptTensor& partials, int64_t num_splits) {
+  need_partials(partials);
+  TORCH_CHECK(!partials.has_value() || two_shot, "b200_decode.allreduce_add_norm: split-K input needs the two-shot form");
   const int64_t want = two_shot ? sizeof(b200_tp_exchange) : sizeof(b200_tp_comm);
   TORCH_CHECK(comm.is_cpu() && comm.scalar_type() == U8 && comm.is_contiguous() && comm.numel() == want,
               "b200_decode.allreduce_add_norm: comm must be a CPU uint8 tensor of ", want, " bytes");
@@ -362,8 +364,11 @@ void allreduce_add_norm(const Tensor& comm, int64_t two_shot, int64_t slot, cons
   const float e = static_cast<float>(eps);
   int rc;
   if (two_shot) {
-    rc = b200_allreduce2_add_norm(static_cast<const b200_tp_exchange*>(comm.data_ptr()), ptr(bias), ptr(residual), ptr(gamma),
-                                  ptr(beta), static_cast<int>(q_mode), r, h, e, s);
+    const auto* x = static_cast<const b200_tp_exchange*>(comm.data_ptr());
+    rc = partials.has_value()
+             ? b200_allreduce2_add_norm_splitk(x, static_cast<const float*>(ptr(partials)), static_cast<int>(num_splits),
+                                               ptr(bias), ptr(residual), ptr(gamma), ptr(beta), static_cast<int>(q_mode), r, h, e, s)
+             : b200_allreduce2_add_norm(x, ptr(bias), ptr(residual), ptr(gamma), ptr(beta), static_cast<int>(q_mode), r, h, e, s);
   } else {
     const auto* c = static_cast<const b200_tp_comm*>(comm.data_ptr());
     const int sl = static_cast<int>(slot);
@@ -411,7 +416,7 @@ TORCH_LIBRARY(b200_decode, m) {
   m.def("filtered_probs(Tensor logits, Tensor(a!) probs, int top_k, float top_p, float temperature) -> ()");
   m.def("allreduce_add_norm(Tensor comm, int two_shot, int slot, Tensor? bias, Tensor? residual, Tensor gamma, Tensor? beta, "
         "Tensor(a!)? hidden_out, Tensor(b!)? normed_out, Tensor(c!)? q_out, Tensor(d!)? scales_out, int q_mode, int m_pad, "
-        "int rows, int hidden, float eps) -> ()");
+        "int rows, int hidden, float eps, Tensor? partials, int num_splits) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(b200_decode, CUDA, m) {

@@ -24,6 +24,10 @@
 // inputs; and output rows are written only after exchange A of the same call, when every rank has finished the
 // kernels that read the previous call's outputs.  Rows of the hidden state are owned by one rank per call, which is
 // why the residual may live in the very buffer the new hidden state is written to.
+// Split-K inputs: when the row-parallel GEMM was split along K its fp32 partial sums [splits][rows][hidden] can be
+// handed over as they are.  The kernel's CTAs then first sum them in split order (the arithmetic of the GEMM's own
+// reduction kernel: fp32, one bf16 rounding) into this rank's input buffer - each CTA a strided share of ALL rows - and
+// the CTA that finishes last sends exchange A.  One launch fewer per linear, same bits.
 // No TMA, no multicast, no multimem: plain loads and stores.
 #include "common.cuh"
 #include "quant.cuh"
@@ -37,7 +41,8 @@ struct Exchange {
   void* normed_out[8];
   void* scales_out[8];
   int32_t* flags[8];  // per rank: [2][8] int32 - [0][q]: exchange A from rank q, [1][q]: exchange B from rank q
-  int32_t* counters;  // local: [0] calls completed, [1] CTAs of the running call that are done
+  int32_t* counters;  // local: [0] calls completed, [1] CTAs of the running call that are done, [2] CTAs whose share of
+                      // the split-K sums is written
   int world, rank, m_pad;
 };
 
@@ -83,17 +88,43 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void __launch_bounds__(1024)
 allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
                            const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta, int rows,
-                           int hidden, float eps, int q_mode) {
+                           int hidden, float eps, int q_mode, const float* __restrict__ partials, int splits) {
   __shared__ float red[32];
   __shared__ int s_last;
+  __shared__ int s_announce;
   pdl_launch_dependents();
   pdl_wait();
   // every CTA reads the same value: the counter moves only when the last CTA of this launch is done
   const int32_t call = ld_acquire_sys(x.counters) + 1;
-  // ---- exchange A: this rank's partial output (written by the kernel before this one) is complete ----
+  bool announce = blockIdx.x == 0;
+  if (partials != nullptr) {
+    // ---- split-K sums of this rank's GEMM into its input buffer: rows blockIdx.x, blockIdx.x + gridDim.x, ... ----
+    __nv_bfloat16* mine = const_cast<__nv_bfloat16*>(x.in[x.rank]);
+    const int64_t split_stride = static_cast<int64_t>(rows) * hidden;
+    if (static_cast<int>(threadIdx.x) < hidden / 8) {
+      for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int64_t o = static_cast<int64_t>(r) * hidden + threadIdx.x * 8;
+        const ew::Vec8 v = ew::sum_partials8(partials + o, splits, split_stride);
+        *reinterpret_cast<uint4*>(mine + o) = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]);
+      }
+    }
+    // the CTA barrier orders every thread's stores before thread 0's system-scope fence, and that fence before the
+    // arrival count: the CTA that counts last (and then announces) sends the flag after all rows are visible
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const bool last = atomicAdd(&x.counters[2], 1) == static_cast<int>(gridDim.x) - 1;
+      if (last) x.counters[2] = 0;  // nobody touches it again before the next call (which starts after this kernel)
+      __threadfence();
+      s_announce = last;
+    }
+    __syncthreads();
+    announce = s_announce != 0;
+  }
+  // ---- exchange A: this rank's partial output (written by the kernel before this one, or just above) is complete ----
   if (threadIdx.x < 8) {
     __threadfence_system();
-    exchange(x, 0, call, blockIdx.x == 0);
+    exchange(x, 0, call, announce);
   }
   __syncthreads();
 
@@ -271,9 +302,14 @@ allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, c
 
 extern "C" {
 
-int b200_allreduce2_add_norm(const b200_tp_exchange* c, const void* bias, const void* residual, const void* gamma,
-                             const void* beta, int q_mode, int rows, int hidden, float eps, b200_stream_t stream) {
+static int allreduce2_impl(const b200_tp_exchange* c, const float* partials, int num_splits, const void* bias,
+                           const void* residual, const void* gamma, const void* beta, int q_mode, int rows, int hidden,
+                           float eps, b200_stream_t stream) {
   using namespace b200;
+  if (partials != nullptr && (num_splits < 1 || num_splits > 32 || !aligned16(partials))) return B200_ERR_INVALID_ARGUMENT;
+  // With split-K input the peers wait for ALL CTAs of this launch (the last one to finish its sums announces), so the
+  // whole grid must be resident at once: one CTA per SM always is.
+  if (partials != nullptr && c && (rows + c->world_size - 1) / c->world_size > 128) return B200_ERR_INVALID_ARGUMENT;
   if (!c || c->world_size < 2 || c->world_size > 8 || c->rank < 0 || c->rank >= c->world_size) return B200_ERR_INVALID_ARGUMENT;
   if (rows <= 0 || rows > c->max_rows || hidden != c->hidden || hidden <= 0 || hidden > 8192 || !gamma || !c->counters)
     return B200_ERR_INVALID_ARGUMENT;
@@ -304,7 +340,20 @@ int b200_allreduce2_add_norm(const b200_tp_exchange* c, const void* bias, const 
   const int per_rank = (rows + c->world_size - 1) / c->world_size;
   return launch_pdl(tpx::allreduce2_add_norm_kernel, dim3(per_rank), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
                     x, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual),
-                    static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), rows, hidden, eps, q_mode);
+                    static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), rows, hidden, eps, q_mode,
+                    partials, num_splits);
+}
+
+int b200_allreduce2_add_norm(const b200_tp_exchange* c, const void* bias, const void* residual, const void* gamma,
+                             const void* beta, int q_mode, int rows, int hidden, float eps, b200_stream_t stream) {
+  return allreduce2_impl(c, nullptr, 0, bias, residual, gamma, beta, q_mode, rows, hidden, eps, stream);
+}
+
+int b200_allreduce2_add_norm_splitk(const b200_tp_exchange* c, const float* partials, int num_splits, const void* bias,
+                                    const void* residual, const void* gamma, const void* beta, int q_mode, int rows,
+                                    int hidden, float eps, b200_stream_t stream) {
+  if (!partials) return B200_ERR_INVALID_ARGUMENT;
+  return allreduce2_impl(c, partials, num_splits, bias, residual, gamma, beta, q_mode, rows, hidden, eps, stream);
 }
 
 }  // extern "C"

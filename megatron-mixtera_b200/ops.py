@@ -73,6 +73,8 @@ _workspace = _Workspace()
 launch_count = 0
 # Number of GEMMs that have used the shared split-K workspace: a `GemmPartials` is only valid while this has not moved.
 _gemm_epoch = 0
+# Tensor-parallel exchanges that were handed split-K partial sums (instead of a reduced bf16 output) since import.
+tp_splitk_exchanges = 0
 
 
 def _gemm_workspace(device, nbytes: int, count_reduction: bool = False) -> torch.Tensor:
@@ -522,22 +524,30 @@ def allreduce_add_norm(pending, gamma, *, bias=None, residual=None, beta=None, e
         # every rank finishes its share of the rows and stores them into all ranks' buffers: the results are views of
         # this rank's buffers (valid until the next call through the same communicator)
         q_mode = {None: 0, "mxfp8": 1, "blockwise": 2}[quantize]
+        global tp_splitk_exchanges
+        parts = getattr(pending, "partials", None)
+        if parts is not None:
+            if parts.epoch != _gemm_epoch:
+                raise B200Error("allreduce_add_norm", -1, "another GEMM has reused the workspace that held these partial sums")
+            tp_splitk_exchanges += 1
         _launch("allreduce_add_norm", _blob(comm.comm), 1, 0, bias, residual, gamma, beta, None, None, None, None, q_mode, 0,
-                rows, hidden, eps)
+                rows, hidden, eps, None if parts is None else parts.buf, 0 if parts is None else parts.num_splits)
         return comm.hidden_view(pending.shape), comm.normed_view(rows, quantize, pending.shape)
     h = torch.empty(pending.shape, dtype=BF16, device=dev) if want_hidden else None
     c = _blob(comm.comm)
     if quantize == "mxfp8":
         q, sf = _mx_buffers(rows, hidden, dev)
-        _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, None, q, sf, 1, 0, rows, hidden, eps)
+        _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, None, q, sf, 1, 0, rows, hidden, eps,
+                None, 0)
         return h, Mxfp8Tensor(q, sf, pending.shape)
     if quantize == "blockwise":
         q, scale, m_pad = _rowblock_buffers(rows, hidden, dev)
         _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, None, q, scale, 2, m_pad, rows,
-                hidden, eps)
+                hidden, eps, None, 0)
         return h, Fp8BlockTensor(q, scale, pending.shape, m_pad)
     y = torch.empty(pending.shape, dtype=BF16, device=dev) if want_normed else None
-    _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, y, None, None, 0, 0, rows, hidden, eps)
+    _launch("allreduce_add_norm", c, 0, pending.slot, bias, residual, gamma, beta, h, y, None, None, 0, 0, rows, hidden, eps,
+            None, 0)
     return h, y
 
 

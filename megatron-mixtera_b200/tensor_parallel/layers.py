@@ -266,9 +266,18 @@ class RowParallelLinear(_ParallelLinearBase):
             rows = (input_.q.shape[0] if hasattr(input_, "q") else input_.numel() // input_.shape[-1])
             comm = get_peer_allreduce(self.output_size, rows)
             if comm is not None:
+                lead = input_.shape[:-1]
+                fp8 = self.fp8
+                if getattr(comm, "two_shot", False) and comm.accepts_partials(rows) \
+                        and getattr(self.config, "fuse_splitk_reduction_into_norm", True) \
+                        and ops.gemm_num_splits(fp8, rows, self.output_size, self.weight_shape[1]) > 1:
+                    # split-K GEMM: its partial sums go to the exchange kernel, which sums them into the peer-visible
+                    # buffer itself (no reduction launch)
+                    parts = self._matmul(input_, self.weight, None, defer_reduction=True)
+                    return (TpPending(comm, 0, (*lead, self.output_size), partials=parts),
+                            (self.bias if self.skip_bias_add else None))
                 slot, view = comm.output_slot(rows)
                 self._matmul(input_, self.weight, None, out=view)
-                lead = input_.shape[:-1]
                 return TpPending(comm, slot, (*lead, self.output_size)), (self.bias if self.skip_bias_add else None)
         out = self._matmul(input_, self.weight, fuse_bias)
         if tp > 1:

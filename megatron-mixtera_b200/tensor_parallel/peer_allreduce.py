@@ -25,12 +25,14 @@ class _DeviceBytes:
 
 
 class TpPending:
-    """A row-parallel output that still has to be summed over the ranks: lives in slot ``slot`` of the peer buffers."""
+    """A row-parallel output that still has to be summed over the ranks: lives in slot ``slot`` of the peer buffers, or
+    (two-shot form, ``partials``) is still the GEMM's split-K partial sums, which the exchange kernel sums into the
+    buffer itself."""
 
-    __slots__ = ("comm", "slot", "shape")
+    __slots__ = ("comm", "slot", "shape", "partials")
 
-    def __init__(self, comm: "PeerAllReduce", slot: int, shape):
-        self.comm, self.slot, self.shape = comm, slot, tuple(shape)
+    def __init__(self, comm: "PeerAllReduce", slot: int, shape, partials=None):
+        self.comm, self.slot, self.shape, self.partials = comm, slot, tuple(shape), partials
 
 
 class PeerAllReduce:
@@ -159,7 +161,7 @@ class PeerExchange:
                     ptrs.append(ptr.value)
                     self._opened.append(ptr.value)
             comm.in_[r], comm.hidden_out[r], comm.normed_out[r], comm.scales_out[r], comm.flags[r] = ptrs
-        self._counters = torch.zeros(2, dtype=torch.int32, device=device)
+        self._counters = torch.zeros(4, dtype=torch.int32, device=device)
         comm.counters = self._counters.data_ptr()
         self.comm = comm
         wrap = lambda i: torch.as_tensor(_DeviceBytes(self._own[i], self._sizes[i]), device=device)
@@ -174,6 +176,11 @@ class PeerExchange:
         """(0, [rows, hidden] bf16 view of this rank's input buffer): where the row-parallel GEMM writes."""
         assert rows <= self.max_rows
         return 0, self._in[: rows * self.hidden].view(rows, self.hidden)
+
+    def accepts_partials(self, rows: int) -> bool:
+        """Whether the exchange kernel may be given split-K partial sums for this many rows: its grid (one CTA per owned
+        row) must be resident at once, because the peers wait for all of its CTAs."""
+        return -(-rows // self.world_size) <= 128
 
     def hidden_view(self, shape):
         n = 1

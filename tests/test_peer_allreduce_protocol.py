@@ -183,3 +183,118 @@ def test_two_shot_exchange_needs_one_buffer_only(world, rows):
             steps += 1
             assert steps < 2000000, "deadlock"
         assert len(log) == world * rows * calls
+
+
+def two_shot_splitk_rank(rank, world, calls, rows, inp, flags_a, flags_b, counters, rng, log):
+    """The split-K form of csrc/tp_exchange.cu at CTA granularity: a launch is `per` CTAs; each first writes a strided share
+    of ALL rows of this rank's input buffer (the sums of its GEMM's partial products), the CTA that counts last on
+    counters[2] sends exchange A, every CTA waits for the peers' A flags before it reads their rows, and the CTA that counts
+    last on counters[1] runs exchange B.  A launch starts only when the previous one has ended (stream order)."""
+    per = -(-rows // world)
+
+    def cta(b, k):
+        for r in range(b, rows, per):                       # split-K sums -> this rank's input rows
+            inp[rank][r] = (rank, k, r)
+            yield
+        counters[rank][2] += 1                              # atomicAdd after the CTA's fence
+        last = counters[rank][2] == per
+        if last:
+            counters[rank][2] = 0
+        yield
+        if last:
+            for q in range(world):                          # exchange A, sent once all rows are written
+                if q != rank:
+                    flags_a[q][rank] = k
+                    yield
+        while any(flags_a[rank][q] < k for q in range(world) if q != rank):
+            yield
+        row = rank * per + b
+        if row < rows:
+            for q in range(world):
+                got = inp[q][row]
+                assert got == (q, k, row), f"rank {rank} call {k}: input row {row} of rank {q} holds {got}"
+                log.append((rank, k, row, q))
+                yield
+        counters[rank][1] += 1
+        if counters[rank][1] == per:                        # exchange B by the CTA that finishes last
+            counters[rank][1] = 0
+            for q in range(world):
+                if q != rank:
+                    flags_b[q][rank] = k
+                    yield
+            while any(flags_b[rank][q] < k for q in range(world) if q != rank):
+                yield
+            counters[rank][0] = k
+
+    for k in range(1, calls + 1):
+        ctas = [cta(b, k) for b in range(per)]
+        while ctas:                                         # all CTAs of a launch are resident: any interleaving
+            c = rng.choice(ctas)
+            try:
+                next(c)
+            except StopIteration:
+                ctas.remove(c)
+            yield
+        assert counters[rank][0] == k
+
+
+@pytest.mark.parametrize("world,rows", [(2, 5), (3, 7), (4, 8), (8, 16), (8, 3)])
+def test_two_shot_exchange_with_split_k_input(world, rows):
+    rng = random.Random(100 * world + rows)
+    for trial in range(60):
+        calls = rng.randint(1, 5)
+        inp = [[None] * rows for _ in range(world)]
+        fa = [[0] * world for _ in range(world)]
+        fb = [[0] * world for _ in range(world)]
+        counters = [[0, 0, 0] for _ in range(world)]
+        log = []
+        progs = [two_shot_splitk_rank(r, world, calls, rows, inp, fa, fb, counters, rng, log) for r in range(world)]
+        live = list(range(world))
+        favourite = rng.randrange(world)
+        steps = 0
+        while live:
+            r = favourite if (favourite in live and rng.random() < 0.7) else rng.choice(live)
+            try:
+                next(progs[r])
+            except StopIteration:
+                live.remove(r)
+            steps += 1
+            assert steps < 4000000, "deadlock"
+        assert len(log) == world * rows * calls
+
+
+def test_split_k_input_announced_by_the_first_cta_would_read_unfinished_rows():
+    """Why the announcement waits for the arrival count: if CTA 0 announced as soon as ITS rows were written (as the
+    plain form does, where the GEMM before the kernel has written everything), a peer could read a row that another CTA
+    has not summed yet."""
+    world, rows = 2, 6
+    rng = random.Random(3)
+    failures = 0
+    for trial in range(200):
+        inp = [[None] * rows for _ in range(world)]
+        flag = [0] * world
+        per = rows // world
+
+        def cta(rank, b):
+            for r in range(b, rows, per):
+                inp[rank][r] = (rank, r)
+                yield
+            if b == 0:
+                flag[rank] = 1
+            yield
+            while not flag[1 - rank]:
+                yield
+            row = rank * per + b
+            assert inp[1 - rank][row] == (1 - rank, row)
+
+        ctas = [cta(r, b) for r in range(world) for b in range(per)]
+        try:
+            while ctas:
+                c = rng.choice(ctas)
+                try:
+                    next(c)
+                except StopIteration:
+                    ctas.remove(c)
+        except AssertionError:
+            failures += 1
+    assert failures > 0

@@ -104,6 +104,11 @@ def cuda_mode(out_path):
         from megatron_mixtera_b200.tensor_parallel import peer_allreduce
 
         peer_allreduce.ONE_SHOT_MAX_WORLD = 1
+    if os.environ.get("TP_WORKER_SPLIT_POLICY"):  # "ctas per SM,min K blocks per split,max splits": force split-K GEMMs
+        from megatron_mixtera_b200 import _lib
+
+        a, b, c = (int(v) for v in os.environ["TP_WORKER_SPLIT_POLICY"].split(","))
+        assert _lib.load().b200_set_gemm_split_policy(a, b, c) == 0
     if os.environ.get("TP_WORKER_FP8"):
         meta["fp8"] = os.environ["TP_WORKER_FP8"]  # "mxfp8" | "blockwise": FP8 linears, sharded per rank
     model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=True)
@@ -151,7 +156,7 @@ def cuda_mode(out_path):
             dist.all_reduce(hi, op=dist.ReduceOp.MAX)
             assert torch.equal(lo, hi), k
     if int(os.environ.get("RANK", "0")) == 0:
-        np.savez(out_path, replays=wrapper.graph_replays, **out)
+        np.savez(out_path, replays=wrapper.graph_replays, tp_splitk_exchanges=ops.tp_splitk_exchanges, **out)
     if world > 1:
         dist.barrier()
         # Not destroy_process_group(): tearing the NCCL communicator down while captured CUDA graphs still
