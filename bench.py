@@ -291,6 +291,33 @@ def kernel_rooflines(model, ctx, T, peak_gbs):
     out["paged_attention"] = {"us": sec * 1e6, "GB/s": kv_bytes / sec / 1e9, "frac": kv_bytes / sec / 1e9 / peak_gbs,
                               "kv_tokens": int(kv_lens.sum()), "bytes": kv_bytes}
     out["_gemm_total"] = {"bytes": gemm_bytes, "sec": gemm_time}
+    # tensor parallel: the out-projection -> all-reduce -> residual add -> norm (-> quantise) edge as the layer runs it
+    # (every rank executes the same sweep, so the exchange kernels meet their peers); minus the GEMM alone = what the
+    # collective + norm costs.  bytes = what one rank moves over NVLink for the two-shot exchange.
+    from megatron_mixtera_b200 import parallel_state
+
+    tp = parallel_state.get_tensor_model_parallel_world_size()
+    if tp > 1 and (len(layers) * reps_of_stack) % 2 == 0:  # (the one-shot form needs an even number of calls per replay)
+        proj = [l.self_attention.linear_proj for l in layers]
+        K = proj[0].weight_shape[1]
+        fp8 = proj[0].fp8
+        x = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+        if fp8 == "mxfp8":
+            x = ops.quantize_mxfp8(x)
+        elif fp8 == "blockwise":
+            x = ops.quantize_fp8_rowblock(x)
+        H = proj[0].output_size
+        res = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+
+        def edge():
+            for l in layers:
+                y, _ = l.self_attention.linear_proj(x, defer_reduction=True)
+                l.pre_mlp_layernorm.add_and_norm(y, res, quantize=fp8)
+
+        sec = sweep(edge)
+        out["proj_allreduce_norm"] = {
+            "us": sec * 1e6, "gemm_alone_us": out["linear_proj"]["us"], "collective_and_norm_us": sec * 1e6 - out["linear_proj"]["us"],
+            "rows": T, "hidden": H, "nvlink_bytes_per_rank": 2.0 * (tp - 1) / tp * T * H * 2}
     return out
 
 
@@ -486,6 +513,10 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.splitk_into_exchange:
+        from megatron_mixtera_b200.tensor_parallel import peer_allreduce as _pa
+
+        _pa.SPLITK_INTO_EXCHANGE = True
     if args.one_shot_max_world is not None:
         from megatron_mixtera_b200.tensor_parallel import peer_allreduce
 
@@ -737,6 +768,8 @@ def main():
     ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
+    ap.add_argument("--splitk-into-exchange", action="store_true",
+                    help="ablation: the two-shot exchange kernel sums the row-parallel GEMMs' split-K partial sums itself")
     ap.add_argument("--synthesize-kv", action="store_true",
                     help="skip the prefill forward passes: admit the requests through the bookkeeping only and fill the KV "
                          "pool with seeded noise (decode timing does not depend on the pool's contents)")

@@ -120,15 +120,26 @@ allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, c
     }
     __syncthreads();
     announce = s_announce != 0;
+    // CTAs beyond this rank's share of the rows were launched for the sums only; the one that counted last still has
+    // to deliver exchange A (it does not wait: nothing it does afterwards depends on the peers)
+    if (static_cast<int>(blockIdx.x) >= (rows + x.world - 1) / x.world) {
+      if (announce && threadIdx.x < 8 && static_cast<int>(threadIdx.x) < x.world && static_cast<int>(threadIdx.x) != x.rank) {
+        __threadfence_system();
+        st_release_sys(x.flags[threadIdx.x] + x.rank, call);
+      }
+      announce = false;
+    }
   }
   // ---- exchange A: this rank's partial output (written by the kernel before this one, or just above) is complete ----
-  if (threadIdx.x < 8) {
-    __threadfence_system();
-    exchange(x, 0, call, announce);
-  }
-  __syncthreads();
-
   const int per_rank = (rows + x.world - 1) / x.world;
+  if (static_cast<int>(blockIdx.x) < per_rank) {
+    if (threadIdx.x < 8) {
+      __threadfence_system();
+      exchange(x, 0, call, announce);
+    }
+    __syncthreads();
+  }
+
   const int row = x.rank * per_rank + blockIdx.x;
   const int nvec = hidden / 8;
   const int i = threadIdx.x;
@@ -338,7 +349,9 @@ static int allreduce2_impl(const b200_tp_exchange* c, const float* partials, int
   int threads = ((nvec + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int per_rank = (rows + c->world_size - 1) / c->world_size;
-  return launch_pdl(tpx::allreduce2_add_norm_kernel, dim3(per_rank), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
+  // split-K input: up to 128 CTAs share the sums (all rows); the first `per_rank` of them go on with the exchange
+  const int grid = partials != nullptr ? (rows < 128 ? (rows > per_rank ? rows : per_rank) : 128) : per_rank;
+  return launch_pdl(tpx::allreduce2_add_norm_kernel, dim3(grid), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
                     x, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual),
                     static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), rows, hidden, eps, q_mode,
                     partials, num_splits);

@@ -180,7 +180,7 @@ class PeerExchange:
     def accepts_partials(self, rows: int) -> bool:
         """Whether the exchange kernel may be given split-K partial sums for this many rows: its grid (one CTA per owned
         row) must be resident at once, because the peers wait for all of its CTAs."""
-        return -(-rows // self.world_size) <= 128
+        return SPLITK_INTO_EXCHANGE and -(-rows // self.world_size) <= 128
 
     def hidden_view(self, shape):
         n = 1
@@ -212,6 +212,11 @@ class PeerExchange:
 
 _COMM = None
 
+
+# Hand the split-K partial sums of a row-parallel GEMM to the two-shot exchange kernel instead of launching the GEMM's
+# reduction kernel.  Same bits, one launch fewer; off by default: measured slower at 4 ranks (the sums then sit on the
+# critical path in front of the first flag exchange instead of overlapping with the GEMM's tail).
+SPLITK_INTO_EXCHANGE = False
 
 # Groups of up to this many ranks use the one-shot form (every rank pulls every peer's rows: one flag exchange, w - 1
 # times the data per rank), larger ones the two-shot form (two exchanges, 2 (w - 1) / w of the data per rank).

@@ -47,7 +47,7 @@ def test_tp2_cuda_stack_matches_tp1(tmp_path):
     # they are and sums them itself - the same bits as the one-shot form behind the GEMM's own reduction kernel
     forced, forced2 = str(tmp_path / "tp2_split.npz"), str(tmp_path / "tp2_split_two_shot.npz")
     _torchrun(2, "cuda", forced, 29625, TP_WORKER_SPLIT_POLICY="4,1,8")
-    _torchrun(2, "cuda", forced2, 29626, TP_WORKER_SPLIT_POLICY="4,1,8", TP_WORKER_TWO_SHOT="1")
+    _torchrun(2, "cuda", forced2, 29626, TP_WORKER_SPLIT_POLICY="4,1,8", TP_WORKER_TWO_SHOT="1", TP_WORKER_SPLITK_EXCHANGE="1")
     e, f = np.load(forced), np.load(forced2)
     assert int(f["tp_splitk_exchanges"]) > 0 and int(e["tp_splitk_exchanges"]) == 0
     for k in e.files:
@@ -103,7 +103,7 @@ def test_tp2_mxfp8_matches_the_fp8_oracle_at_tp2(tmp_path):
             out3, out4 = str(tmp_path / "tp2_split.npz"), str(tmp_path / "tp2_split_two_shot.npz")
             common = dict(TP_WORKER_FP8="mxfp8", TP_WORKER_TRACE=trace_path, TP_WORKER_SPLIT_POLICY="4,1,8")
             _torchrun(tp, "cuda", out3, port + 20, **common)
-            _torchrun(tp, "cuda", out4, port + 30, TP_WORKER_TWO_SHOT="1", **common)
+            _torchrun(tp, "cuda", out4, port + 30, TP_WORKER_TWO_SHOT="1", TP_WORKER_SPLITK_EXCHANGE="1", **common)
             got3, got4 = np.load(out3), np.load(out4)
             assert int(got4["tp_splitk_exchanges"]) > 0
             for k in got3.files:

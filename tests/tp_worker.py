@@ -104,6 +104,10 @@ def cuda_mode(out_path):
         from megatron_mixtera_b200.tensor_parallel import peer_allreduce
 
         peer_allreduce.ONE_SHOT_MAX_WORLD = 1
+    if os.environ.get("TP_WORKER_SPLITK_EXCHANGE") == "1":  # split-K partial sums straight into the two-shot exchange
+        from megatron_mixtera_b200.tensor_parallel import peer_allreduce
+
+        peer_allreduce.SPLITK_INTO_EXCHANGE = True
     if os.environ.get("TP_WORKER_SPLIT_POLICY"):  # "ctas per SM,min K blocks per split,max splits": force split-K GEMMs
         from megatron_mixtera_b200 import _lib
 
