@@ -513,6 +513,11 @@ def run_ours(args, w):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.split_policy:
+        from megatron_mixtera_b200 import _lib as _l
+
+        a_, b_, c_ = (int(v) for v in args.split_policy.split(","))
+        _l.check("b200_set_gemm_split_policy", _l.load().b200_set_gemm_split_policy(a_, b_, c_))
     if args.splitk_into_exchange:
         from megatron_mixtera_b200.tensor_parallel import peer_allreduce as _pa
 
@@ -768,6 +773,8 @@ def main():
     ap.add_argument("--unfused-swiglu", action="store_true", help="ablation: fc1 and SwiGLU as two kernels")
     ap.add_argument("--unfused-splitk", action="store_true",
                     help="ablation: reduce the split-K partial sums of out-proj / fc2 in a kernel of their own")
+    ap.add_argument("--split-policy", default=None,
+                    help="GEMM split-K policy 'CTAs per SM wanted,min K blocks per split,max splits' (default 2,4,32)")
     ap.add_argument("--splitk-into-exchange", action="store_true",
                     help="ablation: the two-shot exchange kernel sums the row-parallel GEMMs' split-K partial sums itself")
     ap.add_argument("--synthesize-kv", action="store_true",

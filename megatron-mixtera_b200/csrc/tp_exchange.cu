@@ -57,13 +57,23 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
 
 // Called by threads 0 .. world-1 of a CTA (thread q talks to rank q): announce `call` in slot `which` of every peer
 // (if `announce`), then wait until every peer has announced it here.
+// kRelaxed: relaxed system-scope flag accesses without fences.  Right for exchange A when the input was written by an
+// earlier kernel of this stream: griddepcontrol.wait has awaited that kernel's completion, memory included, so the rows
+// are in this GPU's L2 - where a peer's load is served - before the flag store is issued.  A release store would add a
+// system-scope fence in front of the first NVLink hop of every call (measured 23.5 -> 17.7 us per call, 2 ranks,
+// 128 x 4096).  Exchange B announces rows this kernel has just stored into the peers' memory and keeps release /
+// acquire behind the CTAs' system-scope fences.
+template <bool kRelaxed = false>
 __device__ __forceinline__ void exchange(const Exchange& x, int which, int32_t call, bool announce) {
   const int q = threadIdx.x;
   if (q >= x.world || q == x.rank) return;
-  if (announce) st_release_sys(x.flags[q] + which * 8 + x.rank, call);
+  if (announce) {
+    if (kRelaxed) ew::st_relaxed_sys(x.flags[q] + which * 8 + x.rank, call);
+    else st_release_sys(x.flags[q] + which * 8 + x.rank, call);
+  }
   const int32_t* mine = x.flags[x.rank] + which * 8 + q;
   const uint64_t t0 = global_timer_ns();
-  while (ld_acquire_sys(mine) < call) {
+  while ((kRelaxed ? ew::ld_relaxed_sys(mine) : ld_acquire_sys(mine)) < call) {
     if (global_timer_ns() - t0 > g_wait_limit_ns) {
       atomicOr(&g_device_status, kStatusPeerTimeout);
       return;
@@ -95,7 +105,7 @@ allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, c
   pdl_launch_dependents();
   pdl_wait();
   // every CTA reads the same value: the counter moves only when the last CTA of this launch is done
-  const int32_t call = ld_acquire_sys(x.counters) + 1;
+  const int32_t call = ew::ld_relaxed_sys(x.counters) + 1;  // written by the previous call's kernel
   bool announce = blockIdx.x == 0;
   if (partials != nullptr) {
     // ---- split-K sums of this rank's GEMM into its input buffer: rows blockIdx.x, blockIdx.x + gridDim.x, ... ----
@@ -134,8 +144,12 @@ allreduce2_add_norm_kernel(Exchange x, const __nv_bfloat16* __restrict__ bias, c
   const int per_rank = (rows + x.world - 1) / x.world;
   if (static_cast<int>(blockIdx.x) < per_rank) {
     if (threadIdx.x < 8) {
-      __threadfence_system();
-      exchange(x, 0, call, announce);
+      if (partials != nullptr) {  // the input rows were written by this kernel's own CTAs: fence + release
+        __threadfence_system();
+        exchange(x, 0, call, announce);
+      } else {
+        exchange<true>(x, 0, call, announce);
+      }
     }
     __syncthreads();
   }
