@@ -88,15 +88,11 @@ class GPTModel(torch.nn.Module):
         (int64 device tensor) of the final hidden states."""
         from ..tensor_parallel import peer_allreduce
 
-        comm = peer_allreduce._COMM
-        if comm is not None:
-            comm.begin_forward()
+        comms_at_entry = peer_allreduce.begin_forward()
         hidden = self.embedding(input_ids.reshape(-1), position_ids)
         hidden = self.decoder(hidden, inference_context=inference_context, rotary_pos_cos=self.rotary_pos_cos,
                               rotary_pos_sin=self.rotary_pos_sin)
-        comm = peer_allreduce._COMM if comm is None else comm  # created during this forward: it started on slot 0
-        if comm is not None:
-            comm.end_forward()
+        peer_allreduce.end_forward(comms_at_entry)
         if row_indices is not None:
             hidden = ops.gather_rows(hidden, row_indices)
         weight = self.embedding.word_embeddings.weight if self.share_embeddings_and_output_weights else None

@@ -210,7 +210,7 @@ class PeerExchange:
         self._opened, self._own = [], []
 
 
-_COMM = None
+_COMMS = {}  # form ("one_shot" | "two_shot") -> communicator of the tensor-parallel group
 
 
 # Hand the split-K partial sums of a row-parallel GEMM to the two-shot exchange kernel instead of launching the GEMM's
@@ -218,33 +218,57 @@ _COMM = None
 # critical path in front of the first flag exchange instead of overlapping with the GEMM's tail).
 SPLITK_INTO_EXCHANGE = False
 
-# Groups of up to this many ranks use the one-shot form (every rank pulls every peer's rows: one flag exchange, w - 1
-# times the data per rank), larger ones the two-shot form (two exchanges, 2 (w - 1) / w of the data per rank).
-ONE_SHOT_MAX_WORLD = 2
+# One-shot form (every rank pulls every peer's rows: one flag exchange, no end-of-call exchange, w - 1 times the data per
+# rank) or two-shot form (two exchanges, 2 (w - 1) / w of the data per rank)?  One-shot for groups of up to
+# ONE_SHOT_MAX_WORLD ranks while a rank pulls at most ONE_SHOT_MAX_BYTES per call.  Measured per call (collective + add +
+# norm, B200, NVLink 5): 128 x 4096 bf16 at 2 ranks 8 us one-shot / 18 us two-shot, at 4 ranks 12 / 17 us (3 MB pulled);
+# 256 x 8192 at 2 ranks 17 / 22 us (4 MB), at 4 ranks 29 / 27 us (12 MB).
+ONE_SHOT_MAX_WORLD = 8
+ONE_SHOT_MAX_BYTES = 8 << 20
+
+
+def use_one_shot(world: int, rows: int, hidden: int) -> bool:
+    return world <= ONE_SHOT_MAX_WORLD and (world - 1) * rows * hidden * 2 <= ONE_SHOT_MAX_BYTES
 
 
 def get_peer_allreduce(hidden: int, rows: int, max_rows: int = 512):
-    """The group's communicator (created on first use: a collective, so every rank must get here together), or None
-    when this output cannot go through it (more rows than a buffer holds, a different width, capture in progress
-    before the first eager use)."""
+    """The group's communicator for this output (created on first use: a collective, so every rank must get here
+    together - the choice of form depends only on sizes every rank knows), or None when this output cannot go through
+    one (more rows than a buffer holds, a different width, capture in progress before the first eager use)."""
     from .. import parallel_state
 
-    global _COMM
     tp = parallel_state.get_tensor_model_parallel_world_size()
     if tp < 2 or tp > 8 or rows > max_rows or hidden > 8192 or hidden % 8 != 0 or not torch.cuda.is_available():
         return None
-    if _COMM is None:
+    form = "one_shot" if use_one_shot(tp, rows, hidden) else "two_shot"
+    comm = _COMMS.get(form)
+    if comm is None:
         if torch.cuda.is_current_stream_capturing():
             return None
         dev = torch.device("cuda", torch.cuda.current_device())
-        cls = PeerAllReduce if tp <= ONE_SHOT_MAX_WORLD else PeerExchange
-        _COMM = cls(parallel_state.get_tensor_model_parallel_group(), parallel_state.get_tensor_model_parallel_rank(), tp,
-                    max_rows, hidden, dev)
-    return _COMM if _COMM.hidden == hidden else None
+        cls = PeerAllReduce if form == "one_shot" else PeerExchange
+        comm = _COMMS[form] = cls(parallel_state.get_tensor_model_parallel_group(),
+                                  parallel_state.get_tensor_model_parallel_rank(), tp, max_rows, hidden, dev)
+    return comm if comm.hidden == hidden else None
+
+
+def begin_forward() -> dict:
+    """Called where a forward pass (and its CUDA graph, if any) starts; returns what `end_forward` needs."""
+    for comm in _COMMS.values():
+        comm.begin_forward()
+    return dict(_COMMS)
+
+
+def end_forward(at_entry: dict) -> None:
+    """Checks the slot discipline of the communicators that existed when the forward started (one created during the
+    forward started on slot 0 and is checked against that)."""
+    for form, comm in _COMMS.items():
+        if form not in at_entry:
+            comm._slot_at_entry = 0
+        comm.end_forward()
 
 
 def destroy_peer_allreduce() -> None:
-    global _COMM
-    if _COMM is not None:
-        _COMM.close()
-        _COMM = None
+    for comm in list(_COMMS.values()):
+        comm.close()
+    _COMMS.clear()
