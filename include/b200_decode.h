@@ -271,6 +271,8 @@ int b200_activation_splitk_fp8_rowblock(const float* partials, int num_splits, c
  * are, reads all ranks' rows with peer loads and uses x = bf16(sum in rank order, fp32) exactly like
  * b200_add_norm_*'s x.  All ranks obtain identical bits.  Consecutive calls must alternate the slot (0, 1, 0, ...)
  * and every rank must issue the same sequence of calls.  hidden <= 8192, world_size 2..8; plain peer loads and stores only.
+ * The slot must have been written by an EARLIER kernel launch on the same stream (the GEMM): the ready flags are relaxed
+ * stores that rely on that kernel's completion for the visibility of the rows.
  */
 typedef struct {
   int32_t world_size, rank;
@@ -306,7 +308,8 @@ int b200_allreduce_add_norm_fp8_rowblock(const b200_tp_comm* comm, int slot, con
  * exchanges per call (inputs complete / outputs stored), each wait bounded by b200_set_wait_limit_ns (device status
  * 4 on expiry); the kernel completes only after every rank's rows have arrived, so later kernels on the stream may
  * read the local output buffers.  `residual` is local memory and may be this rank's `hidden_out` buffer itself.
- * One buffer of each kind is enough (no slot alternation); every rank must issue the same sequence of calls.
+ * One buffer of each kind is enough (no slot alternation); every rank must issue the same sequence of calls.  `in[rank]`
+ * must have been written by an EARLIER kernel launch on the same stream (see above).
  */
 typedef struct {
   int32_t world_size, rank;
