@@ -298,3 +298,49 @@ def test_split_k_input_announced_by_the_first_cta_would_read_unfinished_rows():
         except AssertionError:
             failures += 1
     assert failures > 0
+
+
+def test_choice_of_exchange_form_depends_on_sizes_every_rank_knows():
+    """`use_one_shot` (tensor_parallel/peer_allreduce.py): one-shot while a rank pulls at most 8 MB per call."""
+    from megatron_mixtera_b200.tensor_parallel import peer_allreduce as P
+
+    assert P.use_one_shot(2, 128, 4096) and P.use_one_shot(4, 128, 4096) and P.use_one_shot(8, 128, 4096)
+    assert P.use_one_shot(2, 256, 8192) and not P.use_one_shot(4, 256, 8192) and not P.use_one_shot(8, 256, 8192)
+    assert not P.use_one_shot(4, 512, 4096)  # a large prefill step goes through the two-shot exchange
+    old = P.ONE_SHOT_MAX_WORLD
+    try:
+        P.ONE_SHOT_MAX_WORLD = 1            # what the tests and the bench ablation use to force the two-shot form
+        assert not P.use_one_shot(2, 8, 512)
+    finally:
+        P.ONE_SHOT_MAX_WORLD = old
+
+
+def test_forward_guard_covers_every_communicator():
+    """`begin_forward` / `end_forward` apply the one-shot form's even-number-of-calls rule to whichever communicators
+    exist, including one that was created during the forward (it started on slot 0)."""
+    from megatron_mixtera_b200.tensor_parallel import peer_allreduce as P
+
+    class Fake:
+        def __init__(self):
+            self._next_slot = 0
+
+        begin_forward = P.PeerAllReduce.begin_forward
+        end_forward = P.PeerAllReduce.end_forward
+
+        def call(self):
+            self._next_slot ^= 1
+
+    saved = dict(P._COMMS)
+    try:
+        P._COMMS.clear()
+        at_entry = P.begin_forward()
+        c = P._COMMS["one_shot"] = Fake()   # created by the first fused reduction of this forward
+        c.call(); c.call()
+        P.end_forward(at_entry)              # two calls: fine
+        at_entry = P.begin_forward()
+        c.call()
+        with pytest.raises(RuntimeError):
+            P.end_forward(at_entry)          # an odd number of calls would reuse a slot on replay
+    finally:
+        P._COMMS.clear()
+        P._COMMS.update(saved)
