@@ -212,6 +212,11 @@ int b200_add_norm_fp8_rowblock(const void* x, const void* bias, const void* resi
                                int hidden, float eps, b200_stream_t stream);
 int b200_activation_fp8_rowblock(const void* in, const void* bias, void* q_out, float* scale_out, int m_pad, int rows,
                                  int F, int kind, b200_stream_t stream);
+/* 129..256 tokens and N a multiple of 256: optionally (off by default; process-wide switch) the GEMM runs as pairs of
+ * CTAs on two SMs that share one tcgen05.mma.cta_group::2 per K step over a 256-token x 256-row output tile - each CTA
+ * stages its 128 tokens and its 128 weight rows, so the SMs take in two instead of three times the weight bytes.  Same
+ * arithmetic, same split-K workspace sizes, bit-identical results. */
+int b200_set_fp8_block_cta_pairs(int enable);
 size_t b200_gemm_fp8_block_workspace_bytes(int M, int N, int K);
 int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const void* wq, const float* w_scale,
                         const void* bias, void* y, int64_t ldy, int M, int N, int K, void* workspace,

@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "b200_quantize_fp8_rowblock",
     "b200_add_norm_fp8_rowblock",
     "b200_activation_fp8_rowblock",
+    "b200_set_fp8_block_cta_pairs",
     "b200_gemm_fp8_block_workspace_bytes",
     "b200_gemm_fp8_block",
     "b200_gemm_bf16_swiglu_supported",
@@ -183,6 +184,7 @@ def load() -> ctypes.CDLL:
                                        c_int, c_float, c_void_p]
     lib.b200_activation_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.b200_set_gemm_split_policy.argtypes = [c_int, c_int, c_int]
+    lib.b200_set_fp8_block_cta_pairs.argtypes = [c_int]
     lib.b200_gemm_bf16_workspace_bytes.restype = c_size_t
     lib.b200_gemm_bf16_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.b200_gemm_bf16.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,

@@ -288,8 +288,14 @@ static int pick_bt_block(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 12
 }  // namespace b200
 
 #include "gemm_fp8_block_tok.cu"
+#include "gemm_fp8_block_pair.cu"
 
 extern "C" {
+
+int b200_set_fp8_block_cta_pairs(int enable) {
+  b200::gemm::g_fp8_block_cta_pairs.store(enable != 0 ? 1 : 0, std::memory_order_relaxed);
+  return B200_OK;
+}
 
 size_t b200_gemm_fp8_block_splitk_bytes(int M, int N, int K) {
   using namespace b200::gemm;
@@ -308,6 +314,9 @@ int b200_gemm_fp8_block_splitk(const void* xq, const float* x_scale, int m_pad, 
   if (K % 128 != 0 || m_pad < M || m_pad % 4 != 0) return B200_ERR_ALIGNMENT;
   if (!aligned16(xq) || !aligned16(wq) || !aligned16(x_scale) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gemm::fp8_block_pair_applicable(M, N))
+    return gemm::launch_fp8_block_pair(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials,
+                                       partials_bytes, num_splits);
   switch (gemm::pick_bt_block(M)) {
     case 32:
       return gemm::launch_fp8_block<32>(xq, x_scale, m_pad, wq, w_scale, nullptr, nullptr, N, M, N, K, nullptr, 0, s, partials, partials_bytes, num_splits);
@@ -338,6 +347,9 @@ int b200_gemm_fp8_block(const void* xq, const float* x_scale, int m_pad, const v
   if (K % 128 != 0 || ldy < N || m_pad < M || m_pad % 4 != 0) return B200_ERR_ALIGNMENT;
   if (!aligned16(xq) || !aligned16(wq) || !aligned16(x_scale)) return B200_ERR_ALIGNMENT;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gemm::fp8_block_pair_applicable(M, N))
+    return gemm::launch_fp8_block_pair(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s,
+                                       nullptr, 0, nullptr);
   switch (gemm::pick_bt_block(M)) {
     case 32:
       return gemm::launch_fp8_block<32>(xq, x_scale, m_pad, wq, w_scale, bias, y, ldy, M, N, K, workspace, workspace_bytes, s);

@@ -289,3 +289,32 @@ def test_activation_reduces_fc1_split_k_partials(recipe, M, F, K):
             idx = _sf_indices(M, F).to(got.sf.device)
             assert torch.equal(got.sf[idx], ref.sf[idx])
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (256, 512, 1024), (200, 2560, 4096), (130, 1024, 2048), (256, 8192, 2048)])
+def test_blockwise_gemm_as_cta_pairs_equals_the_single_cta_kernel(ops, M, N, K):
+    """The opt-in `tcgen05.mma.cta_group::2` form of the 256-token blockwise GEMM (csrc/gemm_fp8_block_pair.cu: two CTAs
+    on two SMs share one 256 x 256 output tile) accumulates and promotes every 128-wide K block exactly like the
+    single-CTA kernel: outputs and split-K partial sums must be identical bit for bit."""
+    from megatron_mixtera_b200 import _lib
+
+    lib = _lib.load()
+    x = randn((M, K), 31).cuda()
+    w = randn((N, K), 32, 0.05).cuda()
+    bias = randn((N,), 33).cuda()
+    xq, wq = ops.quantize_fp8_rowblock(x), ops.quantize_fp8_weight_block128(w)
+    got = {}
+    try:
+        for pairs in (0, 1):
+            assert lib.b200_set_fp8_block_cta_pairs(pairs) == 0
+            y = ops.gemm_fp8_block(xq, wq, bias)
+            p = ops.gemm_splitk(xq, wq)
+            parts = p.buf[: p.num_splits * M * N * 4].view(torch.float32).clone()
+            got[pairs] = (y, parts, p.num_splits)
+    finally:
+        lib.b200_set_fp8_block_cta_pairs(0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert got[0][2] == got[1][2]
+    assert torch.equal(got[0][0], got[1][0])
+    assert torch.equal(got[0][1], got[1][1])
