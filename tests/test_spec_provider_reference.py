@@ -17,7 +17,7 @@ import pytest
 
 from conftest import ROOT
 
-REFERENCE = os.environ.get("MEGATRON_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("MEGATRON_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))  # a sibling checkout
 
 CHILD = r'''
 import contextlib, json, os, sys
