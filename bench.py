@@ -540,7 +540,13 @@ def run_ours(args, w):
         n = ctx.total_request_count
         ctx.update_requests(np.ones(n, dtype=np.uint8), np.zeros(n, dtype=np.int64))
     prefill_steps = 0
-    while not ctx.is_decode_only() or engine.waiting_request_ids:
+    waiting_before = None
+    while True:
+        if ctx.is_decode_only():
+            waiting = len(engine.waiting_request_ids)
+            if waiting == 0 or waiting == waiting_before:
+                break  # everybody is in, or the pool admits no more: the rest stays queued (see `concurrent_requests`)
+            waiting_before = waiting
         engine.step_modern(sp)  # prefill / admission (excluded from the timed region)
         prefill_steps += 1
         if prefill_steps > 4 * w.num_requests:
