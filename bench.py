@@ -165,6 +165,7 @@ def build_stack(w, tp: int, prompts, seed: int = 0, fuse_splitk: bool = True, fu
     chunks_per_req = -(-w.max_sequence_length // w.chunk_size_tokens)
     want = int(need_chunks * 1.03) + chunks_per_req + 2
     torch.cuda.synchronize()
+    torch.cuda.empty_cache()  # the released bf16 weights are still in torch's cache: hand them back before measuring
     free, _total = torch.cuda.mem_get_info()
     # headroom: activations of the largest prefill step, logits, workspaces, CUDA graphs
     prefill_tokens = w.num_requests if w.synthesize_kv else (w.max_prefill_tokens or sum(len(p) for p in prompts))
