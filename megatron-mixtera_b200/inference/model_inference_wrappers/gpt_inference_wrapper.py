@@ -36,8 +36,9 @@ class GPTInferenceWrapper:
         self.inference_wrapper_config = inference_wrapper_config
         self.inference_context = inference_context
         self.model_is_pipeline_parallel = False
-        self._graphs: Dict[int, Any] = {}
+        self._graphs: Dict[Any, Any] = {}
         self.graph_replays = 0
+        self.non_decode_graph_replays = 0
         model.eval()
         cfg = getattr(model, "config", None)
         if inference_context is not None and cfg is not None and hasattr(inference_context, "set_prefill_q_block"):
@@ -64,16 +65,56 @@ class GPTInferenceWrapper:
         ctx = self.inference_context
         return self.model.forward_rows(ctx.token_to_input_ids[:T], ctx.token_to_pos_ids[:T], ctx, None, self._gather_mode())
 
+    def _mixed_rows(self, T: int, last_rows: torch.Tensor):
+        ctx = self.inference_context
+        return self.model.forward_rows(ctx.token_to_input_ids[:T], ctx.token_to_pos_ids[:T], ctx, last_rows, self._gather_mode())
+
+    def _run_mixed_step_graph(self, T: int, n_req: int) -> torch.Tensor:
+        """A prefill / mixed step whose token count the context padded to a CUDA-graph size (the reference's non-decode
+        CUDA graphs, ``dynamic_context.py:354-356, 691-697``): every shape is then a function of ``T`` alone - the
+        prefill work list has a fixed capacity with empty entries, padding tokens write to the dummy chunk - except
+        which rows are the requests' last tokens.  Those indices live in a buffer of ``T`` entries at a fixed address
+        that is refreshed before each replay (unused entries point at row 0; their logits are dropped)."""
+        ctx = self.inference_context
+        entry = self._graphs.get(("mixed", T))
+        if entry is None:
+            dev = ctx.token_to_input_ids.device
+            last_rows = torch.zeros(T, dtype=torch.int64, device=dev)
+            host_rows = torch.zeros(T, dtype=torch.int64, pin_memory=True)
+            entry = [None, None, last_rows, host_rows]
+        _, _, last_rows, host_rows = entry
+        host_rows.zero_()
+        host_rows[:n_req] = torch.from_numpy(ctx.last_token_indices())
+        last_rows.copy_(host_rows, non_blocking=True)
+        if entry[0] is None:
+            # One eager pass sizes every workspace; the step is idempotent (it rewrites the same KV slots and its
+            # attention reads only what the step itself and earlier steps wrote), so running it again under capture
+            # and replay changes nothing.
+            self._mixed_rows(T, last_rows)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._mixed_rows(T, last_rows)
+            entry[0], entry[1] = graph, out
+            self._graphs[("mixed", T)] = entry
+        entry[0].replay()
+        self.graph_replays += 1
+        self.non_decode_graph_replays += 1
+        return entry[1][:n_req].unsqueeze(0)
+
     @torch.inference_mode()
     def run_one_forward_step(self, inference_input: Dict[str, Any]) -> torch.Tensor:
         """Logits ``[1, active requests, vocab]`` of the context's current step."""
         ctx = self.inference_context
-        use_graph = (getattr(self.model.config, "enable_cuda_graph", False) and ctx.is_decode_only()
-                     and ctx.materialize_only_last_token_logits and torch.cuda.is_available())
+        graphs_on = (getattr(self.model.config, "enable_cuda_graph", False) and ctx.materialize_only_last_token_logits
+                     and torch.cuda.is_available())
+        n_req = ctx.total_request_count - ctx.paused_request_count
+        if graphs_on and not ctx.is_decode_only() and ctx.using_cuda_graph_this_step() and n_req > 0:
+            return self._run_mixed_step_graph(ctx.padded_active_token_count, n_req)
+        use_graph = graphs_on and ctx.is_decode_only()
         if not use_graph:
             return self._forward(inference_input)
         T = ctx.padded_active_token_count
-        n_req = ctx.total_request_count - ctx.paused_request_count
         entry = self._graphs.get(T)
         if entry is None:
             # One eager pass sizes every workspace; the decode step is idempotent (it rewrites the same

@@ -386,3 +386,57 @@ def test_offline_quantised_state_dict_serves_the_same_logits(recipe):
     assert model2.decoder.layers[0].mlp.linear_fc1.weight.numel() == 0  # no bf16 copy is kept
     got = first_logits(model2, ctx2, wrapper2)
     assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("fp8", [None, "mxfp8"])
+def test_padded_mixed_steps_replay_cuda_graphs_bit_identically(fp8):
+    """Prefill / mixed steps whose token count the context pads to a CUDA-graph size (the reference's non-decode CUDA
+    graphs, dynamic_context.py:354-356, 691-697) run as graph replays here too: same logits, bit for bit, as the same
+    padded steps run eagerly, and the same generated tokens."""
+    from megatron_mixtera_b200.inference.sampling_params import SamplingParams
+
+    z = np.load(os.path.join(GOLDEN, "llama_tiny_bf16.npz"))
+    meta = dict(json.loads(str(z["meta"])), max_requests=16, fp8=fp8)
+    g = torch.Generator().manual_seed(11)
+    prompts = {0: 20, 1: 9, 2: 33, 3: 5, 4: 9, 5: 3}
+    prompts = {i: torch.randint(0, meta["vocab_size"], (n,), generator=g, dtype=torch.int64) for i, n in prompts.items()}
+    arrival = {0: 0, 1: 0, 2: 0, 3: 4, 4: 7, 5: 7}   # steps 4 and 7 mix decoding requests with short new prompts
+    runs = {}
+    for graphs in (False, True):
+        model, ctx, wrapper, Controller = build_cuda_stack(meta, enable_cuda_graph=graphs, num_cuda_graphs=2)
+        assert ctx.non_decode_cuda_graphs and sorted(ctx.cuda_graph_token_counts) == [8, 16]
+        logits_per_step, mixed_graph_steps = [], []
+
+        class Recording(Controller):
+            def sample_from_logits(self, last_token_logits, sampling_params=None, vocab_size=None, **kw):
+                logits_per_step.append(last_token_logits.float().cpu())
+                return super().sample_from_logits(last_token_logits, sampling_params, vocab_size, **kw)
+
+        ctl = Recording(wrapper, types.SimpleNamespace(vocab_size=meta["vocab_size"]))
+        sp = SamplingParams(top_k=1, num_tokens_to_generate=12)
+        gen = {i: [] for i in prompts}
+        step = added = 0
+        while added < len(prompts) or ctx.has_unfinished_requests():
+            for i, when in arrival.items():
+                if when == step:
+                    ctx.add_request(i, prompts[i], 12)
+                    added += 1
+            if ctx.active_token_count > 0:
+                before = wrapper.non_decode_graph_replays
+                r = ctl.generate_output_tokens_dynamic_batch(sp, -1)
+                if wrapper.non_decode_graph_replays > before:
+                    mixed_graph_steps.append(step)
+                for rid, tok in zip(r["active_request_ids"].tolist(), r["sample"].tolist()):
+                    gen[rid].append(tok)
+            step += 1
+            assert step < 200
+        from megatron_mixtera_b200 import ops
+
+        assert ops.device_status() == 0
+        runs[graphs] = (logits_per_step, gen, mixed_graph_steps, wrapper.graph_replays)
+    assert runs[False][2] == [] and runs[False][3] == 0
+    assert runs[True][2] == [4, 7], runs[True][2]       # both short mixed steps were graph replays (sizes 8 and 16)
+    assert runs[True][1] == runs[False][1]
+    assert len(runs[True][0]) == len(runs[False][0])
+    for a, b in zip(runs[True][0], runs[False][0]):
+        assert torch.equal(a, b)
