@@ -51,17 +51,25 @@ class DynamicInferenceEngine:
         self.enable_cuda_graph = model.config.enable_cuda_graph
         self.capture_stats = None
         if self.enable_cuda_graph and context.cuda_graph_token_counts is not None and self._cuda:
-            # Warm up and capture one whole-model decode graph per token count (reference :143-227
-            # captures per-layer graphs for the same sizes).
+            # Warm up and capture one whole-model graph per token count, for decode steps and - when the context
+            # pads short prefill / mixed steps to the same sizes - for those as well (reference :143-227 captures
+            # per-layer graphs for the same sizes and modes; a mixed step needs at least two tokens).
             t0 = time.time()
-            for n in context.cuda_graph_token_counts:
-                context.initialize_attention_state(num_warmup_tokens=n, warmup_engine_mode=WarmupEngineMode.DECODE)
-                assert n == context.padded_active_token_count
-                ids, pos = context.current_input_and_position_ids(num_warmup_tokens=n)
-                controller.inference_wrapped_model.run_one_forward_step(
-                    {"tokens": ids, "position_ids": pos, "attention_mask": None})
-                context.reset()
-            self.capture_stats = {"time": time.time() - t0, "graphs": len(context.cuda_graph_token_counts)}
+            captured = 0
+            for mode in (WarmupEngineMode.DECODE, WarmupEngineMode.NON_DECODE):
+                if mode == WarmupEngineMode.NON_DECODE and not context.non_decode_cuda_graphs:
+                    continue
+                for n in context.cuda_graph_token_counts:
+                    if n == 1 and mode == WarmupEngineMode.NON_DECODE:
+                        continue
+                    context.initialize_attention_state(num_warmup_tokens=n, warmup_engine_mode=mode)
+                    assert n == context.padded_active_token_count
+                    ids, pos = context.current_input_and_position_ids(num_warmup_tokens=n)
+                    controller.inference_wrapped_model.run_one_forward_step(
+                        {"tokens": ids, "position_ids": pos, "attention_mask": None})
+                    context.reset()
+                    captured += 1
+            self.capture_stats = {"time": time.time() - t0, "graphs": captured}
 
     # ------------------------------------------------------------------------------------------
     def has_unfinished_requests(self) -> bool:

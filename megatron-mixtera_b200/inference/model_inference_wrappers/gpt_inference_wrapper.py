@@ -84,7 +84,7 @@ class GPTInferenceWrapper:
             entry = [None, None, last_rows, host_rows]
         _, _, last_rows, host_rows = entry
         host_rows.zero_()
-        host_rows[:n_req] = torch.from_numpy(ctx.last_token_indices())
+        host_rows[:n_req] = torch.from_numpy(ctx.last_token_indices()).clamp_(min=0)  # (a warm-up step has no tokens)
         last_rows.copy_(host_rows, non_blocking=True)
         if entry[0] is None:
             # One eager pass sizes every workspace; the step is idempotent (it rewrites the same KV slots and its

@@ -413,6 +413,16 @@ def test_padded_mixed_steps_replay_cuda_graphs_bit_identically(fp8):
                 return super().sample_from_logits(last_token_logits, sampling_params, vocab_size, **kw)
 
         ctl = Recording(wrapper, types.SimpleNamespace(vocab_size=meta["vocab_size"]))
+        if graphs:
+            # the engine captures every graph up front on an all-padding warm-up step (decode and non-decode sizes, as
+            # the reference's engine does); the replays below then run on real requests
+            from megatron_mixtera_b200.inference.engines.dynamic_engine import DynamicInferenceEngine
+
+            engine = DynamicInferenceEngine(ctl, ctx, termination_id=-1, random_seed=0)
+            assert engine.capture_stats["graphs"] == 4
+            assert {("mixed", 8), ("mixed", 16), 8, 16} <= set(wrapper._graphs)
+            logits_per_step.clear()
+            wrapper.graph_replays = wrapper.non_decode_graph_replays = 0
         sp = SamplingParams(top_k=1, num_tokens_to_generate=12)
         gen = {i: [] for i in prompts}
         step = added = 0
