@@ -70,7 +70,7 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
 
 // Row handshake of one all-reduce call: tell every peer that this rank's row is complete, then wait (bounded)
 // until every peer has said the same.  Flags carry the call number (monotonic), so nothing is ever reset; a
-// peer can be at most one call ahead, which only makes its flag larger.  Called by one thread per CTA.
+// peer can be at most one call ahead, which only makes its flag larger.
 // The flag accesses are relaxed (system scope), without fences: the row a flag announces was written by an EARLIER
 // kernel of this stream, whose completion - memory included - griddepcontrol.wait has awaited before this code runs;
 // it sits in this GPU's L2, which is where a peer's load over NVLink is served.  A release store here would add a
@@ -85,16 +85,17 @@ __device__ __forceinline__ int32_t ld_relaxed_sys(const int32_t* p) {
   asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Called by every thread of the CTA; thread q < world talks to rank q (its flag store and its polls are then one
+// NVLink / L2 round trip in parallel with the other peers', not `world - 1` of them in a row), the caller's CTA barrier
+// ends the handshake.
 __device__ __forceinline__ void peer_row_handshake(const PeerSrc& ps, int row) {
+  const int q = threadIdx.x;
+  if (q >= ps.world || q == ps.rank) return;
   const int32_t call = ld_relaxed_sys(ps.counters) + 1;  // every CTA reads the same value: it moves when all are done
-  for (int q = 0; q < ps.world; ++q)
-    if (q != ps.rank) st_relaxed_sys(ps.flags[q] + ps.rank * ps.max_rows + row, call);
+  st_relaxed_sys(ps.flags[q] + ps.rank * ps.max_rows + row, call);
+  const int32_t* mine = ps.flags[ps.rank] + q * ps.max_rows + row;
   const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    bool all = true;
-    for (int q = 0; q < ps.world; ++q)
-      if (q != ps.rank && ld_relaxed_sys(ps.flags[ps.rank] + q * ps.max_rows + row) < call) all = false;
-    if (all) return;
+  while (ld_relaxed_sys(mine) < call) {
     if (global_timer_ns() - t0 > g_wait_limit_ns) {  // give up, flag it, carry on with what is there
       atomicOr(&g_device_status, kStatusPeerTimeout);
       return;
@@ -122,7 +123,7 @@ add_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   pdl_launch_dependents();
   pdl_wait();
   if constexpr (kSrc == 2) {
-    if (threadIdx.x == 0) peer_row_handshake(ps, blockIdx.x);
+    peer_row_handshake(ps, blockIdx.x);
     __syncthreads();
   }
   // peers: the call counter moves on when the last CTA of this launch is done with the peers' rows
