@@ -64,7 +64,11 @@ def host_threads() -> int:
 # clocks
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """One `nvidia-smi` process for the whole measured part (it needs a few hundred milliseconds to start, longer than a
+    short timed region): every 20 ms a line with a timestamp; `window(t0, t1)` summarises the lines whose timestamp
+    falls inside a timed region (host clock read after a synchronise on either side of it)."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -73,54 +77,71 @@ class ClockSampler:
         self.proc = None
         self.path = None
 
-    def __enter__(self):
+    def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.device_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-            time.sleep(0.15)  # let the first samples land inside the region
         except Exception:
             self.proc = None
         return self
 
-    def __exit__(self, *exc):
+    def stop(self):
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except Exception:
                 self.proc.kill()
+            self.proc = None
 
-    def summary(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    def _rows(self):
+        import datetime
+
+        rows = []
         if not self.path or not os.path.exists(self.path):
-            return out
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            return rows
         for line in open(self.path):
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), parts[6:10]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
+        return rows
+
+    def window(self, t0: float, t1: float):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        rows = self._rows()
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        if not inside and rows:  # a region shorter than the sampling period: the samples nearest to it (same load: the
+            mid = 0.5 * (t0 + t1)  # warm-up steps before it and the next region after it run the same kernels)
+            inside = sorted(rows, key=lambda r: abs(r[0] - mid))[:3]
+            out["note"] = "no sample fell inside the region; nearest samples used"
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = set()
+        for _, _, _, flags in inside:
+            for name, val in zip(names, flags):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        try:
-            os.unlink(self.path)
-        except OSError:
-            pass
-        if sm:
-            out["sm_mhz"] = statistics.median(sm)
-            out["sm_max_mhz"] = max(mx)
-            out["samples"] = len(sm)
+        if inside:
+            out["sm_mhz"] = statistics.median(r[1] for r in inside)
+            out["sm_max_mhz"] = max(r[2] for r in inside)
+            out["samples"] = len(inside)
         out["reasons"] = sorted(reasons)
         return out
+
+    def close(self):
+        self.stop()
+        try:
+            if self.path:
+                os.unlink(self.path)
+        except OSError:
+            pass
 
 
 # ---------------------------------------------------------------------------------------------
@@ -565,22 +586,24 @@ def run_ours(args, w):
         raise SystemExit(f"--steps/--warmup too large for {w.num_tokens_to_generate} output tokens per request")
 
     # ---- e2e: the public API, host<->device copies inside the timed region ----
+    sampler = ClockSampler(local_rank).start()  # runs through both timed regions
     for _ in range(warmup):
         engine.step_modern(sp)
     B = ctx.total_request_count - ctx.paused_request_count
     launches0, h2d0 = ops.launch_count, ctx.h2d_bytes
     step_ms, step_tokens, sampled = [], 0, []
     barrier()
-    with ClockSampler(local_rank) as clk_e2e:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            r = engine.step_modern(sp)
-            step_ms.append(r["step_time"] * 1e3)
-            step_tokens += len(r["active_requests"]) + len(r["finished_requests"])
-            sampled.append([req.generated_tokens[-1] for req in r["active_requests"]])
-        e1.record()
-        barrier()
+    t_e2e0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        r = engine.step_modern(sp)
+        step_ms.append(r["step_time"] * 1e3)
+        step_tokens += len(r["active_requests"]) + len(r["finished_requests"])
+        sampled.append([req.generated_tokens[-1] for req in r["active_requests"]])
+    e1.record()
+    barrier()
+    t_e2e1 = time.time()
     e2e_s = e0.elapsed_time(e1) / 1e3
     h2d_per_step = (ctx.h2d_bytes - h2d0) / steps
     eager_launches_per_step = (ops.launch_count - launches0) / steps  # sampling only: the forward is a graph
@@ -601,14 +624,15 @@ def run_ours(args, w):
     barrier()
     torch.cuda.synchronize()
     torch.cuda.profiler.start()  # a profiler started with "--profile-from-start off" sees the timed launches only
-    with ClockSampler(local_rank) as clk:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            ctl.sample_from_logits(wrapper.run_one_forward_step(inp).squeeze(0), sp, vocab_size=w.vocab_size)
-        e1.record()
-        barrier()
+    t_dev0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ctl.sample_from_logits(wrapper.run_one_forward_step(inp).squeeze(0), sp, vocab_size=w.vocab_size)
+    e1.record()
+    barrier()
     torch.cuda.synchronize()
+    t_dev1 = time.time()
     torch.cuda.profiler.stop()
     dev_s = e0.elapsed_time(e1) / 1e3
     times = torch.tensor([dev_s, e2e_s], device="cuda", dtype=torch.float64)
@@ -646,8 +670,9 @@ def run_ours(args, w):
     gemm_us = sum(kern[k]["us"] for k in ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"))
     attn = kern["paged_attention"]
     layer_us = gemm_us + attn["us"]
-    clocks = clk.summary()
-    clocks["e2e_region"] = clk_e2e.summary()
+    clocks = sampler.window(t_dev0, t_dev1)
+    clocks["e2e_region"] = sampler.window(t_e2e0, t_e2e1)
+    sampler.close()
     gemm_name = {None: "gemm_bf16_kernel", "mxfp8": "gemm_mxfp8_kernel", "blockwise": "gemm_fp8_block_kernel"}[w.fp8]
     attn_name = "paged_attention_fp8_kernel" if w.kv_fp8 else "paged_attention_kernel"
     roof_gemm = {"bound": "hbm", "kernel": f"{gemm_name} (tcgen05, {len(model.decoder.layers)} layers x qkv/proj/fc1/fc2)",
