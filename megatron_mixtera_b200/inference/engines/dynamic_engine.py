@@ -35,6 +35,8 @@ class DynamicInferenceEngine:
         controller.enqueue_next_forward_early = bool(overlap_host_and_device)
         self.step_count = 0
         self.finished_request_count = 0
+        self.paused = False   # set by PAUSE / UNPAUSE / STOP messages of the data-parallel coordinator
+        self.stopped = False
         self.waiting_request_ids = deque()
         self.failed_request_ids: List[int] = []
         self.request_counter = count()
@@ -161,7 +163,11 @@ class DynamicInferenceEngine:
             except Exception:
                 break
 
-    async def async_step(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False) -> Dict:
+    async def async_step(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False,
+                         post_process_requests_locally: bool = True):
+        """One engine step.  With ``post_process_requests_locally=False`` (serving under the data-parallel coordinator,
+        which keeps the request records) the step returns ``(request ids, finished ids, tokens, log probs)`` or None
+        instead of request objects (reference ``dynamic_engine.py:596-605``)."""
         prev_decode = self.context.is_decode_only()
         nvtx_range_push("Decode" if prev_decode else "Prefill")  # reference :562
         # The controller returns after reading the sampled tokens back, i.e. after the step's device work is done:
@@ -182,8 +188,19 @@ class DynamicInferenceEngine:
             self.schedule_waiting_requests()
             for i in result["finished_request_ids"].tolist():
                 self.requests[i].add_event_finish()
+            if not post_process_requests_locally:
+                for i in result["finished_request_ids"].tolist():  # the coordinator owns the record; drop ours
+                    self.requests.pop(i, None)
+                    self.request_completion_futures.pop(i, None)
+                self.finished_request_count += int(result["finished_request_ids"].numel())
+                self.step_count += 1
+                nvtx_range_pop()
+                return result["active_request_ids"], result["finished_request_ids"], result["sample"], result["log_probs"]
             active_requests, finished_requests = self.post_process_requests(
                 result["active_request_ids"], result["finished_request_ids"], step_time, result["sample"], result["log_probs"])
+        elif not post_process_requests_locally:
+            nvtx_range_pop()
+            return None
         for failed_id in self.failed_request_ids:
             failed = self.requests.pop(failed_id)
             failed.status = Status.FAILED
@@ -229,3 +246,153 @@ class DynamicInferenceEngine:
         while self.has_unfinished_requests():
             finished.extend(self.step_modern(sampling_params)["finished_requests"])
         return finished
+
+    # ------------------------------------------------------------------------------------------
+    # Serving under the data-parallel coordinator (reference ``dynamic_engine.py:229-356, 708-872``)
+    # ------------------------------------------------------------------------------------------
+    async def start_listening_to_data_parallel_coordinator(self, sampling_params: SamplingParams,
+                                                           inference_coordinator_port: int,
+                                                           launch_inference_coordinator: bool = True):
+        """Connect this replica to the coordinator and start the serving loop as a background task.
+
+        The first rank of every tensor-parallel group talks to the coordinator (DEALER socket with the identity
+        ``tp-coord-<data-parallel rank>``, registered with an empty frame) and republishes what it receives to the
+        other ranks of its group over a PUB / SUB pair on an ``ipc`` endpoint (one node per tensor-parallel group, as
+        in the reference), so that every rank adds the same requests before the same step.  With
+        ``launch_inference_coordinator`` global rank 0 spawns the coordinator process first."""
+        import multiprocessing
+        import os
+        import tempfile
+
+        import zmq
+
+        from ... import parallel_state
+        from ..data_parallel_inference_coordinator import DataParallelInferenceCoordinator
+
+        dist_rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
+        ready = None
+        if launch_inference_coordinator and dist_rank == 0:
+            spawn = multiprocessing.get_context("spawn")
+            ready = spawn.Event()
+            self.inference_coordinator_process = spawn.Process(
+                target=DataParallelInferenceCoordinator.entrypoint,
+                args=(ready, self.controller.tokenizer, inference_coordinator_port,
+                      parallel_state.get_data_parallel_world_size()), daemon=True)
+            self.inference_coordinator_process.start()
+        self.zmq_context = zmq.Context()
+        self.zmq_sockets = []
+        address = os.getenv("MASTER_ADDR", "127.0.0.1")
+        identity = f"tp-coord-{parallel_state.get_data_parallel_rank()}"
+        base = os.path.join(tempfile.gettempdir(), f"b200-{inference_coordinator_port}-{identity}")
+        self._is_tp_coordinator = parallel_state.get_tensor_model_parallel_rank() == 0
+        self._tp_fanout = parallel_state.get_tensor_model_parallel_world_size() > 1
+        if self._is_tp_coordinator:
+            self.socket_for_receiving_requests = self.zmq_context.socket(zmq.DEALER)
+            self.socket_for_receiving_requests.setsockopt(zmq.IDENTITY, identity.encode())
+            self.socket_for_receiving_requests.connect(f"tcp://{address}:{inference_coordinator_port}")
+            self.socket_for_receiving_requests.send(b"")  # registration
+            self.zmq_sockets.append(self.socket_for_receiving_requests)
+            if self._tp_fanout:
+                self.tensor_parallel_publisher_socket = self.zmq_context.socket(zmq.PUB)
+                self.tensor_parallel_publisher_socket.bind(f"ipc://{base}-req")
+                self.tensor_parallel_num_msgs_publisher_socket = self.zmq_context.socket(zmq.PUB)
+                self.tensor_parallel_num_msgs_publisher_socket.bind(f"ipc://{base}-len")
+                self.zmq_sockets += [self.tensor_parallel_publisher_socket, self.tensor_parallel_num_msgs_publisher_socket]
+        elif self._tp_fanout:
+            self.tensor_parallel_subscriber_socket = self.zmq_context.socket(zmq.SUB)
+            self.tensor_parallel_subscriber_socket.connect(f"ipc://{base}-req")
+            self.tensor_parallel_subscriber_socket.setsockopt_string(zmq.SUBSCRIBE, "")
+            self.tensor_parallel_num_msgs_subscriber_socket = self.zmq_context.socket(zmq.SUB)
+            self.tensor_parallel_num_msgs_subscriber_socket.connect(f"ipc://{base}-len")
+            self.tensor_parallel_num_msgs_subscriber_socket.setsockopt_string(zmq.SUBSCRIBE, "")
+            self.zmq_sockets += [self.tensor_parallel_subscriber_socket, self.tensor_parallel_num_msgs_subscriber_socket]
+        if self._tp_fanout:  # every subscriber is connected before the first publication
+            torch.distributed.barrier(parallel_state.get_tensor_model_parallel_group())
+        if ready is not None:
+            ready.wait()
+        self.engine_loop_task = asyncio.create_task(self.run_engine_with_coordinator(sampling_params))
+
+    def schedule_requests(self) -> int:
+        """Drain the messages that have arrived from the coordinator and apply them: new requests are queued, PAUSE /
+        UNPAUSE / STOP set the engine's flags.  Collective over the tensor-parallel group: its first rank drains its
+        socket, publishes the count and then the messages; the others receive exactly that many, so that all ranks
+        see the same batch before the same step (reference ``dynamic_engine.py:708-789``).  Returns the count."""
+        import struct
+
+        import msgpack
+        import zmq
+
+        from ..headers import Headers
+
+        messages = []
+        if self._is_tp_coordinator:
+            while True:
+                try:
+                    messages.append(self.socket_for_receiving_requests.recv(flags=zmq.NOBLOCK))
+                except zmq.Again:
+                    break
+            if self._tp_fanout:
+                self.tensor_parallel_num_msgs_publisher_socket.send(struct.pack("!i", len(messages)))
+                for m in messages:
+                    self.tensor_parallel_publisher_socket.send(m)
+        else:
+            n = struct.unpack("!i", self.tensor_parallel_num_msgs_subscriber_socket.recv())[0]
+            messages = [self.tensor_parallel_subscriber_socket.recv() for _ in range(n)]
+        for m in messages:
+            data = msgpack.unpackb(m, raw=False)
+            header = Headers(data[0])
+            if header == Headers.SUBMIT_REQUEST:
+                request_id, prompt, params = data[1:]
+                params = SamplingParams.deserialize(params)
+                self.add_request(request_id, prompt, params.num_tokens_to_generate)
+            elif header == Headers.PAUSE:
+                self.paused = True
+            elif header == Headers.UNPAUSE:
+                self.paused = False
+            elif header == Headers.STOP:
+                self.stopped = True
+        return len(messages)
+
+    async def run_engine_with_coordinator(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False,
+                                          idle_sleep_s: float = 0.02):
+        """Serving loop of one replica: apply the coordinator's messages, step while there is work, and after every step
+        send ``[ENGINE_REPLY, ids, finished ids, tokens, log probs]`` back (first tensor-parallel rank only)."""
+        import msgpack
+
+        from ..headers import Headers
+
+        try:
+            while True:
+                self.schedule_requests()
+                if self.stopped:
+                    self.stop()
+                    return
+                if self.paused or (self.context.get_active_request_count() == 0 and not self.waiting_request_ids):
+                    await asyncio.sleep(idle_sleep_s)
+                    continue
+                if self.context.get_active_request_count() == 0:
+                    self.schedule_waiting_requests()
+                out = await self.async_step(sampling_params=sampling_params, verbose=verbose,
+                                            post_process_requests_locally=False)
+                if self._is_tp_coordinator and out is not None:
+                    request_ids, finished_ids, sample, log_probs = out
+                    self.socket_for_receiving_requests.send(msgpack.packb(
+                        [Headers.ENGINE_REPLY.value, request_ids.tolist(), finished_ids.tolist(), sample.tolist(), log_probs],
+                        use_bin_type=True))
+                await asyncio.sleep(0)
+        except asyncio.CancelledError:
+            pass
+
+    def stop(self) -> None:
+        """Leave the serving set-up: end the coordinator process this engine spawned (if any) and close the sockets."""
+        proc = getattr(self, "inference_coordinator_process", None)
+        if proc is not None:
+            proc.terminate()
+        for sock in getattr(self, "zmq_sockets", []):
+            sock.close(linger=0)
+        self.zmq_sockets = []
+        ctx = getattr(self, "zmq_context", None)
+        if ctx is not None:
+            ctx.term()
+            self.zmq_context = None
+

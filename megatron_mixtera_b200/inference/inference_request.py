@@ -86,3 +86,36 @@ class DynamicInferenceRequest:
 
     def failed(self) -> bool:
         return self.status == Status.FAILED
+
+    def serializable(self) -> dict:
+        """Plain-data form for the serving protocol (msgpack): tensors as lists, enums by name, events as strings
+        (reference ``inference_request.py:58-77``)."""
+        out = {}
+        for key, value in self.__dict__.items():
+            if isinstance(value, torch.Tensor):
+                value = value.tolist()
+            elif isinstance(value, Enum):
+                value = value.name
+            elif isinstance(value, SamplingParams):
+                value = value.serializable()
+            elif key == "events":
+                value = [str(e) for e in value]
+            out[key] = value
+        return out
+
+    @classmethod
+    def deserialize(cls, data: dict) -> "DynamicInferenceRequest":
+        """Inverse of `serializable` as far as a client needs it: events stay strings, extra keys become attributes."""
+        data = dict(data)
+        tokens = data.pop("prompt_tokens", None)
+        status = data.pop("status", None)
+        params = data.pop("sampling_params", None)
+        events = data.pop("events", None) or []
+        known = {k: data.pop(k) for k in list(data) if k in cls.__dataclass_fields__}
+        obj = cls(prompt_tokens=torch.tensor(tokens if tokens is not None else [], dtype=torch.int64),
+                  status=Status[status] if isinstance(status, str) else status,
+                  sampling_params=SamplingParams.deserialize(params) if isinstance(params, dict) else params, **known)
+        obj.events = events
+        for key, value in data.items():
+            setattr(obj, key, value)
+        return obj

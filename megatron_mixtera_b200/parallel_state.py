@@ -57,3 +57,27 @@ def get_tensor_model_parallel_rank() -> int:
 
 def get_tensor_model_parallel_group():
     return _TP_GROUP
+
+
+def _world_and_rank():
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(), dist.get_rank()
+    return 1, 0
+
+
+def get_data_parallel_world_size() -> int:
+    """Number of model replicas: the ranks that are not inside one tensor-parallel group (serving plumbing only)."""
+    world, _ = _world_and_rank()
+    return max(1, world // _TP_SIZE)
+
+
+def get_data_parallel_rank() -> int:
+    """Index of this rank's replica (ranks are grouped contiguously into tensor-parallel groups)."""
+    _, rank = _world_and_rank()
+    return rank // _TP_SIZE
+
+
+def get_pipeline_model_parallel_rank() -> int:
+    return 0
