@@ -12,6 +12,7 @@ from typing import Dict, List, Optional, Union
 import torch
 from torch import Tensor
 
+from ... import parallel_state
 from ..contexts.dynamic_context import ContextOverflowError, DynamicInferenceContext, WarmupEngineMode
 from ..inference_request import DynamicInferenceRequest, Status
 from ..sampling_params import SamplingParams
@@ -266,7 +267,6 @@ class DynamicInferenceEngine:
 
         import zmq
 
-        from ... import parallel_state
         from ..data_parallel_inference_coordinator import DataParallelInferenceCoordinator
 
         dist_rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
@@ -306,11 +306,47 @@ class DynamicInferenceEngine:
             self.tensor_parallel_num_msgs_subscriber_socket.connect(f"ipc://{base}-len")
             self.tensor_parallel_num_msgs_subscriber_socket.setsockopt_string(zmq.SUBSCRIBE, "")
             self.zmq_sockets += [self.tensor_parallel_subscriber_socket, self.tensor_parallel_num_msgs_subscriber_socket]
-        if self._tp_fanout:  # every subscriber is connected before the first publication
-            torch.distributed.barrier(parallel_state.get_tensor_model_parallel_group())
+        if self._tp_fanout:
+            self._await_tensor_parallel_subscriptions()
         if ready is not None:
             ready.wait()
         self.engine_loop_task = asyncio.create_task(self.run_engine_with_coordinator(sampling_params))
+
+    def _await_tensor_parallel_subscriptions(self, poll_ms: int = 100) -> None:
+        """Collective over the tensor-parallel group: returns once every subscriber provably receives what the group's
+        first rank publishes.  A SUB socket's subscription reaches the publisher some time after ``connect`` returns,
+        and a PUB socket drops what it has nobody to send to; a barrier after ``connect`` therefore does not keep the
+        first request batch from being lost on a rank, which would then step without it.  The publisher sends a probe
+        on both sockets per round, the ranks agree (all-reduce, minimum) on whether everybody has seen one on both, and
+        a closing marker lets the subscribers discard probes that arrived late."""
+        group = parallel_state.get_tensor_model_parallel_group()
+        device = "cuda" if torch.distributed.get_backend(group) == "nccl" else "cpu"
+        probe, ready = b"\x00probe", b"\x00ready"
+        if self._is_tp_coordinator:
+            socks = (self.tensor_parallel_num_msgs_publisher_socket, self.tensor_parallel_publisher_socket)
+        else:
+            socks = (self.tensor_parallel_num_msgs_subscriber_socket, self.tensor_parallel_subscriber_socket)
+        live = [False, False]
+        while True:
+            if self._is_tp_coordinator:
+                for sock in socks:
+                    sock.send(probe)
+                live = [True, True]
+            else:
+                for i, sock in enumerate(socks):
+                    if sock.poll(poll_ms):
+                        sock.recv()
+                        live[i] = True
+            flag = torch.tensor([int(all(live))], dtype=torch.int32, device=device)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN, group=group)
+            if int(flag.item()) == 1:
+                break
+        for sock in socks:
+            if self._is_tp_coordinator:
+                sock.send(ready)
+            else:
+                while sock.recv() != ready:
+                    pass
 
     def schedule_requests(self) -> int:
         """Drain the messages that have arrived from the coordinator and apply them: new requests are queued, PAUSE /
@@ -365,6 +401,10 @@ class DynamicInferenceEngine:
             while True:
                 self.schedule_requests()
                 if self.stopped:
+                    if self._tp_fanout:
+                        # every rank of the group has the STOP message (it arrived in the same batch on all of them)
+                        # before the publisher's sockets close and drop what they have not delivered yet
+                        torch.distributed.barrier(parallel_state.get_tensor_model_parallel_group())
                     self.stop()
                     return
                 if self.paused or (self.context.get_active_request_count() == 0 and not self.waiting_request_ids):

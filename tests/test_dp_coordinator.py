@@ -176,3 +176,56 @@ def test_unknown_clients_and_duplicate_connects_are_ignored():
 def test_registration_times_out_instead_of_waiting_for_ever():
     with pytest.raises(TimeoutError):
         DataParallelInferenceCoordinator(CharTokenizer(), free_port(), 1, registration_timeout_s=0.2, bind_address="127.0.0.1")
+
+
+def test_messages_fan_out_inside_a_tensor_parallel_group(tmp_path):
+    """One replica of two tensor-parallel ranks (gloo processes running the engine's own serving loop over a stand-in
+    model step): only the group's first rank talks to the coordinator; the other rank must see the same requests before
+    the same steps, and STOP must reach both (reference dynamic_engine.py:708-789)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    port, out = free_port(), str(tmp_path / "ranks.json")
+    box = {}
+
+    def serve():
+        box["c"] = DataParallelInferenceCoordinator(CharTokenizer(), port, 1, registration_timeout_s=180, bind_address="127.0.0.1")
+        box["c"].start(poll_ms=10)
+
+    threading.Thread(target=serve, daemon=True).start()
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", TORCHDYNAMO_DISABLE="1")
+    ranks = subprocess.Popen(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", str(free_port()), os.path.join(ROOT, "tests", "serving_tp_worker.py"), str(port), out],
+        env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+
+    async def scenario():
+        client = InferenceClient(port)
+        await client.start()  # acknowledged once the replica has registered
+        sp = SamplingParams(top_k=1, num_tokens_to_generate=3)
+        first = await asyncio.wait_for(asyncio.gather(client.add_request("ab", sp), client.add_request([4, 5], sp)), timeout=120)
+        client.pause_engines()
+        client.unpause_engines()
+        second = await asyncio.wait_for(client.add_request([9], sp), timeout=60)
+        client.stop_engines()
+        await asyncio.sleep(0.2)
+        client.stop()
+        return first + [second]
+
+    try:
+        done = asyncio.new_event_loop().run_until_complete(scenario())
+        log, _ = ranks.communicate(timeout=90)
+    finally:
+        if ranks.poll() is None:
+            ranks.kill()
+        box["c"].stop()
+    assert ranks.returncode == 0, log[-3000:]
+    assert [list(r.generated_tokens) for r in done] == [[0, 1, 2], [100, 101, 102], [200, 201, 202]]
+    a, b = json.load(open(out))
+    assert (a["rank"], b["rank"]) == (0, 1)
+    assert [x[1:] for x in a["added"]] == [[0, [97, 98]], [1, [4, 5]], [2, [9]]]
+    assert a["added"] == b["added"] and a["steps"] == b["steps"]  # same requests before the same steps on both ranks
