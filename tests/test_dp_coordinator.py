@@ -184,6 +184,7 @@ def test_messages_fan_out_inside_a_tensor_parallel_group(tmp_path):
     the same steps, and STOP must reach both (reference dynamic_engine.py:708-789)."""
     import json
     import os
+    import signal
     import subprocess
     import sys
 
@@ -201,7 +202,7 @@ def test_messages_fan_out_inside_a_tensor_parallel_group(tmp_path):
     ranks = subprocess.Popen(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
          "--master-port", str(free_port()), os.path.join(ROOT, "tests", "serving_tp_worker.py"), str(port), out],
-        env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
 
     async def scenario():
         client = InferenceClient(port)
@@ -217,12 +218,17 @@ def test_messages_fan_out_inside_a_tensor_parallel_group(tmp_path):
         return first + [second]
 
     try:
+        deadline = time.time() + 170  # the ranks import torch first; the coordinator exists once they have registered
+        while "c" not in box and ranks.poll() is None and time.time() < deadline:
+            time.sleep(0.1)
+        assert "c" in box, "the replica did not register"
         done = asyncio.new_event_loop().run_until_complete(scenario())
         log, _ = ranks.communicate(timeout=90)
     finally:
         if ranks.poll() is None:
-            ranks.kill()
-        box["c"].stop()
+            os.killpg(ranks.pid, signal.SIGKILL)  # the launcher and its ranks: the process group this test started
+        if "c" in box:
+            box["c"].stop()
     assert ranks.returncode == 0, log[-3000:]
     assert [list(r.generated_tokens) for r in done] == [[0, 1, 2], [100, 101, 102], [200, 201, 202]]
     a, b = json.load(open(out))
