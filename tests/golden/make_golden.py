@@ -375,6 +375,48 @@ LLAMA_TINY = dict(
 )
 
 
+SAMPLING_CASES = [  # (top_k, top_p, temperature)
+    (1, 0.0, 1.0), (4, 0.0, 1.0), (50, 0.0, 0.7), (0, 0.9, 1.0), (0, 0.5, 1.3), (0, 0.0, 0.8),
+]
+
+
+def case_sampling(path):
+    """The reference's `sample_from_logits` (text_generation_controller.py:172-315) on seeded logits: the token of the
+    greedy case and, for the others, the probability vector it hands to `torch.multinomial` (captured by wrapping that
+    one call; the draw itself is torch's and needs no pin)."""
+
+    from megatron.core.inference.sampling_params import SamplingParams
+    from megatron.core.inference.text_generation_controllers.text_generation_controller import TextGenerationController
+
+    gen = torch.Generator().manual_seed(11)
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        logits = (torch.randn(6, 512, generator=gen) * 3.0).to(getattr(torch, dtype))
+        out[f"{dtype}_logits"] = logits.float().numpy()
+        stub = types.SimpleNamespace(sampling_rng=torch.Generator().manual_seed(0))
+        for i, (top_k, top_p, temperature) in enumerate(SAMPLING_CASES):
+            seen = []
+            real = torch.multinomial
+
+            def capture(probabilities, num_samples=1, generator=None, _seen=seen):
+                _seen.append(probabilities.clone())
+                return real(probabilities, num_samples=num_samples, generator=generator)
+
+            torch.multinomial = capture
+            try:
+                tokens = TextGenerationController.sample_from_logits(
+                    stub, logits.clone(), SamplingParams(top_k=top_k, top_p=top_p, temperature=temperature), vocab_size=512)
+            finally:
+                torch.multinomial = real
+            out[f"{dtype}_case{i}_params"] = np.array([top_k, top_p, temperature], dtype=np.float64)
+            if top_k == 1:
+                assert not seen
+                out[f"{dtype}_case{i}_tokens"] = tokens.numpy()
+            else:
+                out[f"{dtype}_case{i}_probs"] = seen[0].float().numpy()
+    np.savez_compressed(path, **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="checkout of the reference (the directory that holds megatron/)")
@@ -391,6 +433,7 @@ def main():
         "c0_fp32": lambda p: case_model_decode(p, C0),
         "llama_tiny_bf16": lambda p: case_model_decode(p, LLAMA_TINY),
         "llama_tiny_fp32": lambda p: case_model_decode(p, dict(LLAMA_TINY, dtype="float32")),
+        "sampling": case_sampling,
     }
     for name, fn in cases.items():
         if args.only and name != args.only:

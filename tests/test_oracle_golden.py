@@ -265,3 +265,34 @@ def test_oracle_tensor_parallel_arithmetic_is_a_small_perturbation():
         rel = float((logits[1] - logits[2]).norm() / logits[1].norm())
         assert rel < bound, (dtype, rel)
         assert dtype == torch.float32 or rel > 0  # bf16: the partial roundings are really there
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sampling_oracle_matches_reference(dtype):
+    """`O.sample` / `O.filtered_probabilities` against the reference's `sample_from_logits`: the greedy token and the
+    exact probability vector handed to `torch.multinomial` (top-k, top-p with its shift-by-one, plain temperature)."""
+    z = np.load(os.path.join(GOLDEN, "sampling.npz"))
+    logits = torch.from_numpy(z[f"{dtype}_logits"]).to(getattr(torch, dtype))
+    cases = 0
+    while f"{dtype}_case{cases}_params" in z.files:
+        top_k, top_p, temperature = z[f"{dtype}_case{cases}_params"].tolist()
+        if int(top_k) == 1:
+            assert np.array_equal(O.sample(logits, top_k=1).numpy(), z[f"{dtype}_case{cases}_tokens"])
+        else:
+            probs = O.filtered_probabilities(logits, int(top_k), float(top_p), float(temperature))
+            ref = z[f"{dtype}_case{cases}_probs"]
+            got = probs.float().numpy()
+            if np.array_equal(got, ref):
+                cases += 1
+                continue
+            # Only where equal logits straddle the nucleus boundary may the two differ: the reference's sort is not
+            # stable, so WHICH of the tied tokens it keeps is arbitrary; the oracle keeps the lower index.  The kept
+            # values are the same multiset, and every token whose state differs is tied with one in the opposite state.
+            assert dtype == "bfloat16" and top_p > 0, (dtype, cases, np.abs(got - ref).max())
+            assert np.array_equal(np.sort(got, axis=1), np.sort(ref, axis=1)), (dtype, cases)
+            x = logits.float().numpy()
+            for r, c in zip(*np.nonzero((got > 0) != (ref > 0))):
+                opposite = ((got[r] > 0) != (got[r, c] > 0)) & (x[r] == x[r, c])
+                assert opposite.any(), (dtype, cases, r, c)
+        cases += 1
+    assert cases == 6
