@@ -375,6 +375,46 @@ LLAMA_TINY = dict(
 )
 
 
+LOG_PROB_CFG = dict(num_layers=2, kv_channels=8, num_attention_heads=2, max_sequence_length=64, buffer_size_gb=0.0002,
+                    buffer_guaranteed_fraction=0.1, chunk_size_tokens=16, max_requests_override=8, max_tokens_override=64,
+                    tensor_model_parallel_size=1)
+LOG_PROB_VOCAB = 48
+# (prompt lengths admitted before the step, then the step is taken): a prefill step, a decode step, a mixed step
+LOG_PROB_STEPS = [[5, 3], [], [6]]
+
+
+def case_log_probs(path):
+    """The reference context's `calculate_log_probs` (dynamic_context.py:1300-1365) before each `update_requests`: all
+    tokens' logits on a prefill step and on a mixed step (per-request lists, prompt tokens shifted by one), last-token
+    logits on a decode step and with ``only_last_token_logits``."""
+    from megatron.core.inference.contexts.dynamic_context import DynamicInferenceContext as C
+
+    C.TOKEN_ROUNDER = 4
+    C.REQUEST_ROUNDER = 4
+    ctx = C(params_dtype=torch.float32, **LOG_PROB_CFG)
+    gen = torch.Generator().manual_seed(5)
+    out, next_id = {}, 0
+    for step, prompts in enumerate(LOG_PROB_STEPS):
+        for plen in prompts:
+            ctx.add_request(next_id, torch.randint(0, LOG_PROB_VOCAB, (plen,), generator=gen), 8)
+            next_id += 1
+        ctx.initialize_attention_state()
+        n_req = ctx.total_request_count - ctx.paused_request_count
+        new_tokens = torch.randint(0, LOG_PROB_VOCAB, (n_req,), generator=gen)
+        logits = torch.randn(1, ctx.padded_active_token_count, LOG_PROB_VOCAB, generator=gen)
+        out[f"s{step}_input_ids"] = ctx.token_to_input_ids[: ctx.active_token_count].numpy().copy()
+        out[f"s{step}_new_tokens"] = new_tokens.numpy()
+        out[f"s{step}_logits"] = logits.numpy()
+        full = ctx.calculate_log_probs(logits, new_tokens)
+        out[f"s{step}_lengths"] = np.array([len(x) for x in full], dtype=np.int64)
+        out[f"s{step}_log_probs"] = np.array([v for x in full for v in x], dtype=np.float64)
+        last = ctx.last_token_logits(logits)
+        only_last = ctx.calculate_log_probs(last.unsqueeze(0), new_tokens, only_last_token_logits=True)
+        out[f"s{step}_last_log_probs"] = np.array([v for x in only_last for v in x], dtype=np.float64)
+        ctx.update_requests(torch.ones(n_req, dtype=torch.uint8), new_tokens.clone())
+    np.savez_compressed(path, **out)
+
+
 SAMPLING_CASES = [  # (top_k, top_p, temperature)
     (1, 0.0, 1.0), (4, 0.0, 1.0), (50, 0.0, 0.7), (0, 0.9, 1.0), (0, 0.5, 1.3), (0, 0.0, 0.8),
 ]
@@ -434,6 +474,7 @@ def main():
         "llama_tiny_bf16": lambda p: case_model_decode(p, LLAMA_TINY),
         "llama_tiny_fp32": lambda p: case_model_decode(p, dict(LLAMA_TINY, dtype="float32")),
         "sampling": case_sampling,
+        "log_probs": case_log_probs,
     }
     for name, fn in cases.items():
         if args.only and name != args.only:

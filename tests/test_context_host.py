@@ -511,3 +511,32 @@ def test_sharded_state_dict_pieces_tile_the_full_tensors():
     assert set(pasted) == set(full)
     for k in full:
         assert torch.equal(pasted[k], full[k]), k
+
+
+def test_log_probs_match_the_reference_context():
+    """`calculate_log_probs` / `last_token_logits` before each `update_requests` of a prefill, a decode and a mixed step
+    (fixture: the reference context's own results on the same prompts, logits and sampled tokens)."""
+    z = np.load(os.path.join(GOLDEN, "log_probs.npz"))
+    set_rounder(4)
+    ctx = make_ctx(num_layers=2, max_sequence_length=64, buffer_size_gb=0.0002, chunk_size_tokens=16,
+                   max_requests_override=8, max_tokens_override=64)
+    gen = torch.Generator().manual_seed(5)
+    next_id = 0
+    for step, prompts in enumerate([[5, 3], [], [6]]):
+        for plen in prompts:
+            ctx.add_request(next_id, torch.randint(0, 48, (plen,), generator=gen), 8)
+            next_id += 1
+        ctx.initialize_attention_state()
+        n_req = ctx.total_request_count - ctx.paused_request_count
+        new_tokens = torch.randint(0, 48, (n_req,), generator=gen)
+        logits = torch.randn(1, ctx.padded_active_token_count, 48, generator=gen)
+        assert np.array_equal(ctx.token_to_input_ids[: ctx.active_token_count].numpy(), z[f"s{step}_input_ids"])
+        assert np.array_equal(new_tokens.numpy(), z[f"s{step}_new_tokens"]) and np.array_equal(logits.numpy(), z[f"s{step}_logits"])
+        full = ctx.calculate_log_probs(logits, new_tokens)
+        assert [len(x) for x in full] == z[f"s{step}_lengths"].tolist()
+        assert np.array_equal(np.array([v for x in full for v in x]), z[f"s{step}_log_probs"]), step
+        last = ctx.last_token_logits(logits)
+        only_last = ctx.calculate_log_probs(last.unsqueeze(0), new_tokens, only_last_token_logits=True)
+        assert np.array_equal(np.array([v for x in only_last for v in x]), z[f"s{step}_last_log_probs"]), step
+        ctx.update_requests(np.ones(n_req, dtype=np.uint8), new_tokens.numpy())
+    assert z["s2_lengths"].tolist() == [1, 1, 6]  # the mixed step: two decoding requests and one prompt
