@@ -24,8 +24,12 @@ from megatron.core.inference.sampling_params import SamplingParams as RefSamplin
 from megatron_mixtera_b200.inference.data_parallel_inference_coordinator import DataParallelInferenceCoordinator
 from megatron_mixtera_b200.inference.inference_client import InferenceClient
 from megatron_mixtera_b200.inference.sampling_params import SamplingParams
+from megatron.core.inference.headers import Headers as RefHeaders
+from megatron_mixtera_b200.inference.headers import Headers
 from serving_helpers import CharTokenizer, free_port
 from test_dp_coordinator import FakeReplica
+
+assert {h.name: h.value for h in RefHeaders} == {h.name: h.value for h in Headers}
 
 KEEP = []
 
