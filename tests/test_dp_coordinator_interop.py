@@ -39,7 +39,7 @@ def run(coordinator_cls, client_cls, params):
     replica = FakeReplica(port, 0)
     threading.Thread(target=lambda: coordinator_cls(CharTokenizer(), port, 1).start(), daemon=True).start()
     replica.start()
-    time.sleep(0.5)  # (the reference's coordinator must have its replica before a client speaks)
+    time.sleep(1.5)  # (the reference's coordinator must have its replica before a client speaks)
     async def scenario():
         client = client_cls(port)
         KEEP.append(client)  # (a collected client would terminate its ZMQ context inside the loop and block on it)
