@@ -359,6 +359,14 @@ class DynamicInferenceContext(BaseInferenceContext):
         return rounder * int(math.ceil(int(value) / rounder))
 
     @classmethod
+    def round_up(cls, value):
+        """Deprecated predecessor of `round_up_tokens` / `round_up_requests` (reference :458-466): multiples of
+        ``ROUNDER`` (64 unless a subclass sets it), no tensor-parallel divisibility."""
+        warnings.warn("`round_up` is deprecated in favor of `round_up_tokens` or `round_up_requests`")
+        rounder = getattr(cls, "ROUNDER", 64)
+        return rounder * int(math.ceil(int(value) / rounder))
+
+    @classmethod
     def round_up_requests(cls, value, tp_size=None):
         """Next multiple of ``REQUEST_ROUNDER`` that is divisible by the tensor-parallel size."""
         if tp_size is None:
@@ -405,10 +413,13 @@ class DynamicInferenceContext(BaseInferenceContext):
             "b200_rope_append for prefill steps); see SelfAttention.forward"
         )
 
-    def apply_rotary_emb_query(self, *args, **kwargs):
+    def apply_rotary_emb_query(self, query, query_emb, config, cu_seqlens_q, cp_group, mscale=1.0):
+        """Not a separate step here: the attention kernel rotates the query as it loads it (reference :566-600)."""
         raise NotImplementedError("RoPE is applied inside the fused attention op; see SelfAttention.forward")
 
-    apply_rotary_emb_key = apply_rotary_emb_query
+    def apply_rotary_emb_key(self, key, key_emb, config, cp_group, mscale=1.0):
+        """Not a separate step here: the append kernel rotates the key before it stores it (reference :602-631)."""
+        raise NotImplementedError("RoPE is applied inside the fused attention op; see SelfAttention.forward")
 
     # ------------------------------------------------------------------ host -> device mirroring
     def _wait_copies(self) -> None:

@@ -38,6 +38,7 @@ class DynamicInferenceEngine:
         self.finished_request_count = 0
         self.paused = False   # set by PAUSE / UNPAUSE / STOP messages of the data-parallel coordinator
         self.stopped = False
+        self._cond = asyncio.Condition()  # `run_engine` sleeps on it; `add_request` inside a running loop wakes it
         self.waiting_request_ids = deque()
         self.failed_request_ids: List[int] = []
         self.request_counter = count()
@@ -102,7 +103,15 @@ class DynamicInferenceEngine:
                 self.failed_request_ids.append(request_id)
                 request.add_event_error_nontransient(e)
         self.request_completion_futures[request_id] = self._loop.create_future()
+        try:  # wake `run_engine` if it is waiting for work (reference :385-391); nothing to wake outside a running loop
+            asyncio.get_running_loop().create_task(self._notify_cond_for_new_request())
+        except RuntimeError:
+            pass
         return self.request_completion_futures[request_id]
+
+    async def _notify_cond_for_new_request(self):
+        async with self._cond:
+            self._cond.notify_all()
 
     def add_request(self, request_id: int, prompt: Union[str, List[int], Tensor],
                     num_tokens_to_generate: Optional[int] = None) -> asyncio.Future:
@@ -247,6 +256,18 @@ class DynamicInferenceEngine:
         while self.has_unfinished_requests():
             finished.extend(self.step_modern(sampling_params)["finished_requests"])
         return finished
+
+    async def run_engine(self, sampling_params: SamplingParams, *, verbose: Optional[bool] = False):
+        """Step for as long as the task lives: sleeps until a request is active, steps, repeats (reference :803-813).
+        Requests still queued because the context is full count as work too: a step retries them."""
+        try:
+            while True:
+                async with self._cond:
+                    await self._cond.wait_for(
+                        lambda: self.context.get_active_request_count() > 0 or len(self.waiting_request_ids) > 0)
+                await self.async_step(sampling_params=sampling_params, verbose=verbose)
+        except asyncio.CancelledError:
+            pass
 
     # ------------------------------------------------------------------------------------------
     # Serving under the data-parallel coordinator (reference ``dynamic_engine.py:229-356, 708-872``)

@@ -62,6 +62,17 @@ class DynamicInferenceRequest:
     generated_log_probs: Optional[List[float]] = None
     tpot: Optional[List[float]] = None
     events: List[DynamicInferenceEvent] = field(default_factory=list)
+    latency: Optional[float] = None  # set by the client: submission to completion
+    # Fields of the reference's record that only its static-batching engine fills (reference :33-51); they are kept so that
+    # a serialised record has the reference's keys and either side's client can rebuild the other side's record.
+    inference_parameters: Optional[SamplingParams] = None  # the reference's deprecated name of `sampling_params`
+    arrival_time: Optional[float] = None
+    encoder_prompt: Optional[str] = None
+    segments: Optional[List[str]] = None
+    generated_segments: Optional[List[str]] = None
+    generated_sequence_lengths: Optional[List[int]] = None
+    prompt_top_n_logprobs: Optional[list] = None
+    generated_top_n_logprobs: Optional[list] = None
 
     def add_event(self, type: DynamicInferenceEventType, payload: Optional[Any] = None) -> None:
         self.events.append(DynamicInferenceEvent(type=type, payload=payload))

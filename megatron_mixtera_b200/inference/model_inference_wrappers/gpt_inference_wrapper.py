@@ -103,8 +103,9 @@ class GPTInferenceWrapper:
         return entry[1][:n_req].unsqueeze(0)
 
     @torch.inference_mode()
-    def run_one_forward_step(self, inference_input: Dict[str, Any]) -> torch.Tensor:
-        """Logits ``[1, active requests, vocab]`` of the context's current step."""
+    def run_one_forward_step(self, inference_input: Dict[str, Any], recv_buffer_seq_len: Optional[int] = None) -> torch.Tensor:
+        """Logits ``[1, active requests, vocab]`` of the context's current step (``recv_buffer_seq_len`` is the reference's
+        pipeline-parallel receive size: accepted, unused)."""
         ctx = self.inference_context
         graphs_on = (getattr(self.model.config, "enable_cuda_graph", False) and ctx.materialize_only_last_token_logits
                      and torch.cuda.is_available())

@@ -48,7 +48,8 @@ class TextGenerationController:
 
     # --------------------------------------------------------------------------------------------
     def sample_from_logits(self, last_token_logits: torch.Tensor, sampling_params: Optional[SamplingParams] = None,
-                           vocab_size: Optional[int] = None, **kwargs) -> torch.Tensor:
+                           vocab_size: Optional[int] = None, generation_started: Optional[torch.Tensor] = None,
+                           top_n_logprobs_dict=None, logits: Optional[torch.Tensor] = None, **kwargs) -> torch.Tensor:
         """Sample one token per row of ``last_token_logits [batch, vocab]`` (bf16, on the device).
 
         ``top_k == 1``: greedy, the argmax kernel (ties go to the smallest index).  ``top_k > 1``: the
@@ -56,6 +57,8 @@ class TextGenerationController:
         draws from them with the controller's generator, as the reference does (:292-309).  ``top_k == 0``
         with ``top_p == 0`` keeps the whole vocabulary.  ``top_p > 0``: the nucleus kernel (the reference's
         sort + cumulative sum + shift-by-one rule, :221-240, evaluated in fp32 without a sort).
+        ``generation_started``, ``top_n_logprobs_dict`` and ``logits`` serve the reference's top-n log-probabilities
+        (static batching only); they are accepted for the signature and unused.
         """
         if kwargs.get("common_inference_params"):
             sampling_params = kwargs["common_inference_params"]

@@ -81,3 +81,69 @@ def test_seam_needs_the_reference():
     env = {k: v for k, v in os.environ.items() if k != "PYTHONPATH"}
     proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env, cwd="/tmp")
     assert "IMPORTERROR" in proc.stdout, proc.stdout + proc.stderr[-2000:]
+
+
+API_CHILD = r'''
+import dataclasses, importlib, inspect, json, os, sys
+ref, root = sys.argv[1], sys.argv[2]
+sys.path.insert(0, ref); sys.path.insert(0, root)
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+import torch
+torch.cuda.current_device = lambda: torch.device("cpu")
+R, O = "megatron.core.inference.", "megatron_mixtera_b200.inference."
+CLASSES = [
+    ("engines.dynamic_engine", "engines.dynamic_engine", "DynamicInferenceEngine"),
+    ("inference_client", "inference_client", "InferenceClient"),
+    ("data_parallel_inference_coordinator", "data_parallel_inference_coordinator", "DataParallelInferenceCoordinator"),
+    ("contexts.dynamic_context", "contexts.dynamic_context", "DynamicInferenceContext"),
+    ("contexts.dynamic_chunk_allocator", "contexts.dynamic_chunk_allocator", "ChunkAllocator"),
+    ("text_generation_controllers.text_generation_controller", "text_generation_controllers.text_generation_controller", "TextGenerationController"),
+    ("model_inference_wrappers.gpt.gpt_inference_wrapper", "model_inference_wrappers.gpt_inference_wrapper", "GPTInferenceWrapper"),
+]
+RECORDS = [("sampling_params", "SamplingParams"), ("inference_request", "DynamicInferenceRequest")]
+def sig(f):
+    return [(p.name, p.kind.name, repr(p.default)) for p in inspect.signature(f).parameters.values()]
+out = {"missing": {}, "incompatible": {}, "fields": {}}
+for rm, om, name in CLASSES:
+    theirs, ours = getattr(importlib.import_module(R + rm), name), getattr(importlib.import_module(O + om), name)
+    for n, f in inspect.getmembers(theirs, predicate=inspect.isfunction):
+        if n.startswith("_") and n != "__init__":
+            continue
+        g = getattr(ours, n, None)
+        if g is None:
+            out["missing"].setdefault(name, []).append(n)
+            continue
+        a, b = sig(f), sig(g)
+        extras = b[len(a):]
+        # a call written for the reference must mean the same here: same leading parameters, additions optional
+        if b[:len(a)] != a or any(d == repr(inspect.Parameter.empty) and k not in ("VAR_POSITIONAL", "VAR_KEYWORD") for _, k, d in extras):
+            out["incompatible"].setdefault(name, []).append(n)
+for module, name in RECORDS:
+    theirs, ours = getattr(importlib.import_module(R + module), name), getattr(importlib.import_module(O + module), name)
+    a = {f.name for f in dataclasses.fields(theirs)}
+    b = {f.name for f in dataclasses.fields(ours)}
+    out["fields"][name] = [sorted(a - b), sorted(b - a)]
+print("RESULT " + json.dumps(out))
+'''
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "megatron", "core")), reason="reference checkout absent")
+def test_public_methods_and_records_cover_the_reference_api():
+    """Every public method of the reference's classes on the dynamic-inference path exists here under the same name, and
+    a call written against the reference binds the same way (same leading parameters; what this package adds is optional).
+    What is absent is listed: static batching and pipeline parallelism, which are outside this path."""
+    import json
+
+    proc = subprocess.run([sys.executable, "-c", API_CHILD, REFERENCE, ROOT], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    out = json.loads([l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert out["incompatible"] == {}, out["incompatible"]
+    assert out["missing"] == {
+        "TextGenerationController": [  # the static-batching generation loop and its helpers
+            "detokenize_generations", "generate_all_output_tokens_static_batch", "pad_input_prompt_tokens",
+            "prep_inference_input", "stream_tokens", "unpad_input_prompt_tokens", "update_generation_status"],
+        "GPTInferenceWrapper": [  # static batching and pipeline-parallel forward passes
+            "forward_pass_with_pipeline_parallel_large_input_batch", "forward_pass_with_pipeline_parallel_small_input_batch",
+            "forward_pass_without_pipeline_parallel", "get_batch_for_context_window", "prep_inference_input"],
+    }, out["missing"]
+    assert out["fields"] == {"SamplingParams": [[], []], "DynamicInferenceRequest": [[], []]}, out["fields"]
