@@ -24,6 +24,10 @@ class InferenceWrapperConfig:
     inference_max_seq_length: int = 2560
     fp32_residual_connection: bool = False
     nccl_all_reduce_for_prefill: bool = False
+    # The reference wraps the forward in Transformer Engine's FP8 autocast when this is set.  Here the FP8 recipe belongs
+    # to the model (`TransformerConfig.fp8`, weights quantised when they are loaded); a value here is only checked
+    # against it.
+    fp8: Optional[str] = None
 
     def add_attributes(self, attribute_value_pair: dict):
         for key, value in attribute_value_pair.items():
@@ -41,6 +45,9 @@ class GPTInferenceWrapper:
         self.non_decode_graph_replays = 0
         model.eval()
         cfg = getattr(model, "config", None)
+        if getattr(inference_wrapper_config, "fp8", None) is not None and getattr(cfg, "fp8", None) is None:
+            raise ValueError("InferenceWrapperConfig.fp8 is set but the model was built without an FP8 recipe "
+                             "(TransformerConfig.fp8 = 'mxfp8' or 'blockwise')")
         if inference_context is not None and cfg is not None and hasattr(inference_context, "set_prefill_q_block"):
             from ... import ops
 

@@ -91,27 +91,34 @@ os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 import torch
 torch.cuda.current_device = lambda: torch.device("cpu")
 R, O = "megatron.core.inference.", "megatron_mixtera_b200.inference."
-CLASSES = [
-    ("engines.dynamic_engine", "engines.dynamic_engine", "DynamicInferenceEngine"),
-    ("inference_client", "inference_client", "InferenceClient"),
-    ("data_parallel_inference_coordinator", "data_parallel_inference_coordinator", "DataParallelInferenceCoordinator"),
-    ("contexts.dynamic_context", "contexts.dynamic_context", "DynamicInferenceContext"),
-    ("contexts.dynamic_chunk_allocator", "contexts.dynamic_chunk_allocator", "ChunkAllocator"),
-    ("text_generation_controllers.text_generation_controller", "text_generation_controllers.text_generation_controller", "TextGenerationController"),
-    ("model_inference_wrappers.gpt.gpt_inference_wrapper", "model_inference_wrappers.gpt_inference_wrapper", "GPTInferenceWrapper"),
+CLASSES = [  # (module path below the inference package - the same in both trees -, class)
+    ("engines.dynamic_engine", "DynamicInferenceEngine"),
+    ("inference_client", "InferenceClient"),
+    ("data_parallel_inference_coordinator", "DataParallelInferenceCoordinator"),
+    ("contexts.dynamic_context", "DynamicInferenceContext"),
+    ("contexts.dynamic_chunk_allocator", "ChunkAllocator"),
+    ("text_generation_controllers.text_generation_controller", "TextGenerationController"),
+    ("text_generation_controllers.simple_text_generation_controller", "SimpleTextGenerationController"),
+    ("model_inference_wrappers.gpt.gpt_inference_wrapper", "GPTInferenceWrapper"),
 ]
-RECORDS = [("sampling_params", "SamplingParams"), ("inference_request", "DynamicInferenceRequest")]
+RECORDS = [("sampling_params", "SamplingParams"), ("common_inference_params", "CommonInferenceParams"),
+           ("inference_request", "DynamicInferenceRequest"),
+           ("model_inference_wrappers.inference_wrapper_config", "InferenceWrapperConfig")]
 def sig(f):
     return [(p.name, p.kind.name, repr(p.default)) for p in inspect.signature(f).parameters.values()]
 out = {"missing": {}, "incompatible": {}, "fields": {}}
-for rm, om, name in CLASSES:
-    theirs, ours = getattr(importlib.import_module(R + rm), name), getattr(importlib.import_module(O + om), name)
+for module, name in CLASSES:
+    theirs, ours = getattr(importlib.import_module(R + module), name), getattr(importlib.import_module(O + module), name)
+    if name != theirs.__name__:  # a second name of a class compared above: it only has to resolve to the same class
+        assert ours.__name__ == theirs.__name__, (name, ours, theirs)
+        continue
     for n, f in inspect.getmembers(theirs, predicate=inspect.isfunction):
         if n.startswith("_") and n != "__init__":
             continue
         g = getattr(ours, n, None)
         if g is None:
-            out["missing"].setdefault(name, []).append(n)
+            if n not in out["missing"].setdefault(name, []):
+                out["missing"][name].append(n)
             continue
         a, b = sig(f), sig(g)
         extras = b[len(a):]
@@ -146,4 +153,5 @@ def test_public_methods_and_records_cover_the_reference_api():
             "forward_pass_with_pipeline_parallel_large_input_batch", "forward_pass_with_pipeline_parallel_small_input_batch",
             "forward_pass_without_pipeline_parallel", "get_batch_for_context_window", "prep_inference_input"],
     }, out["missing"]
-    assert out["fields"] == {"SamplingParams": [[], []], "DynamicInferenceRequest": [[], []]}, out["fields"]
+    assert out["fields"] == {name: [[], []] for name in ("SamplingParams", "CommonInferenceParams", "DynamicInferenceRequest",
+                                                        "InferenceWrapperConfig")}, out["fields"]
