@@ -81,3 +81,26 @@ def get_data_parallel_rank() -> int:
 
 def get_pipeline_model_parallel_rank() -> int:
     return 0
+
+
+def get_pipeline_model_parallel_world_size() -> int:
+    return 1
+
+
+def is_pipeline_first_stage(*_, **__) -> bool:
+    """There is one pipeline stage (pipeline parallelism is outside this path): it is first and last."""
+    return True
+
+
+def is_pipeline_last_stage(*_, **__) -> bool:
+    return True
+
+
+def model_parallel_is_initialized() -> bool:
+    """The reference's older name of `is_initialized`."""
+    return _INITIALIZED
+
+
+def get_pipeline_model_parallel_group():
+    """No process group: a single pipeline stage has nobody to talk to."""
+    return None

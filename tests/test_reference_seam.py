@@ -130,6 +130,14 @@ for module, name in RECORDS:
     a = {f.name for f in dataclasses.fields(theirs)}
     b = {f.name for f in dataclasses.fields(ours)}
     out["fields"][name] = [sorted(a - b), sorted(b - a)]
+# parallel_state functions the reference's dynamic-inference modules call
+import re
+import megatron_mixtera_b200.parallel_state as ours_ps
+used = set()
+for rel in ("engines/dynamic_engine.py", "contexts/dynamic_context.py", "text_generation_controllers/text_generation_controller.py",
+            "model_inference_wrappers/abstract_model_inference_wrapper.py", "model_inference_wrappers/gpt/gpt_inference_wrapper.py"):
+    used |= set(re.findall(r"parallel_state\.([a-z_]+)", open(os.path.join(ref, "megatron/core/inference", rel)).read()))
+out["parallel_state_missing"] = sorted(n for n in used if not hasattr(ours_ps, n))
 print("RESULT " + json.dumps(out))
 '''
 
@@ -145,6 +153,7 @@ def test_public_methods_and_records_cover_the_reference_api():
     assert proc.returncode == 0, proc.stderr[-3000:]
     out = json.loads([l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
     assert out["incompatible"] == {}, out["incompatible"]
+    assert out["parallel_state_missing"] == [], out["parallel_state_missing"]
     assert out["missing"] == {
         "TextGenerationController": [  # the static-batching generation loop and its helpers
             "detokenize_generations", "generate_all_output_tokens_static_batch", "pad_input_prompt_tokens",
