@@ -162,7 +162,12 @@ class DynamicInferenceEngine:
         return active_requests, finished_requests
 
     def schedule_waiting_requests(self) -> None:
-        """Retry queued requests in arrival order; stop at the first that still does not fit."""
+        """Retry queued requests in arrival order; stop at the first that still does not fit.
+
+        A queued request that can never fit is failed instead of being retried for ever: one whose retry raises a
+        non-transient overflow (it was queued because a transient limit was hit first), and one that does not fit a
+        context that holds no other request.  The reference swallows both and leaves the request queued
+        (``dynamic_engine.py:518-531``), so its `generate` never returns for such a prompt."""
         for request_id in list(self.waiting_request_ids):
             request = self.requests[request_id]
             try:
@@ -170,6 +175,13 @@ class DynamicInferenceEngine:
                 request.add_event_add()
                 request.status = Status.ACTIVE_AND_GENERATING_TOKENS
                 self.waiting_request_ids.popleft()
+            except ContextOverflowError as e:
+                if e.is_transient and self.context.total_request_count > 0:
+                    break  # room will appear when running requests finish
+                self.waiting_request_ids.popleft()
+                request.status = Status.FAILED
+                self.failed_request_ids.append(request_id)
+                request.add_event_error_nontransient(e)
             except Exception:
                 break
 
@@ -208,9 +220,12 @@ class DynamicInferenceEngine:
                 return result["active_request_ids"], result["finished_request_ids"], result["sample"], result["log_probs"]
             active_requests, finished_requests = self.post_process_requests(
                 result["active_request_ids"], result["finished_request_ids"], step_time, result["sample"], result["log_probs"])
-        elif not post_process_requests_locally:
-            nvtx_range_pop()
-            return None
+        else:
+            if self.waiting_request_ids:
+                self.schedule_waiting_requests()  # nothing ran: the queue's head gets the empty context (or fails)
+            if not post_process_requests_locally:
+                nvtx_range_pop()
+                return None
         for failed_id in self.failed_request_ids:
             failed = self.requests.pop(failed_id)
             failed.status = Status.FAILED
