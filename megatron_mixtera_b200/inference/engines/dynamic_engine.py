@@ -433,9 +433,24 @@ class DynamicInferenceEngine:
 
         from ..headers import Headers
 
+        def report_failed_requests():
+            # Requests this replica had to give up (they can never fit its context) are reported as finished without
+            # tokens, so that the client's future resolves (with an empty completion) instead of waiting for ever; the
+            # reference's loop never mentions them to the coordinator.
+            if not self.failed_request_ids:
+                return
+            failed, self.failed_request_ids = list(self.failed_request_ids), []
+            for i in failed:
+                self.requests.pop(i, None)
+                self.request_completion_futures.pop(i, None)
+            if self._is_tp_coordinator:
+                self.socket_for_receiving_requests.send(msgpack.packb(
+                    [Headers.ENGINE_REPLY.value, [], failed, [], None], use_bin_type=True))
+
         try:
             while True:
                 self.schedule_requests()
+                report_failed_requests()
                 if self.stopped:
                     if self._tp_fanout:
                         # every rank of the group has the STOP message (it arrived in the same batch on all of them)
@@ -455,6 +470,7 @@ class DynamicInferenceEngine:
                     self.socket_for_receiving_requests.send(msgpack.packb(
                         [Headers.ENGINE_REPLY.value, request_ids.tolist(), finished_ids.tolist(), sample.tolist(), log_probs],
                         use_bin_type=True))
+                report_failed_requests()
                 await asyncio.sleep(0)
         except asyncio.CancelledError:
             pass

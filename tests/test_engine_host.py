@@ -176,3 +176,54 @@ def test_enqueueing_the_next_forward_early_changes_no_token_and_repeats_few_forw
     assert steps == len(plain_model.steps)
     repeated = len(model.steps) - steps
     assert 0 <= repeated <= admissions + 1, (repeated, admissions, steps)
+
+
+def test_engine_serves_a_client_through_the_coordinator_on_the_cpu():
+    """The engine's serving loop (registration, message intake, ENGINE_REPLY after every step, PAUSE / STOP) with the real
+    context and controller step around the stand-in model; a prompt the replica can never hold comes back empty."""
+    import asyncio
+    import threading
+
+    pytest.importorskip("zmq")
+    pytest.importorskip("msgpack")
+    from megatron_mixtera_b200.inference.data_parallel_inference_coordinator import DataParallelInferenceCoordinator
+    from megatron_mixtera_b200.inference.inference_client import InferenceClient
+    from serving_helpers import CharTokenizer, free_port
+
+    engine, ctx, model = make_engine(0.01)
+    port, box = free_port(), {}
+
+    def serve():
+        box["c"] = DataParallelInferenceCoordinator(CharTokenizer(VOCAB), port, 1, registration_timeout_s=60, bind_address="127.0.0.1")
+        box["c"].start(poll_ms=10)
+
+    threading.Thread(target=serve, daemon=True).start()
+    prompts = prompts_of(3, 6) + ["hello"]
+    sp = SamplingParams(top_k=1, num_tokens_to_generate=12)
+
+    async def scenario():
+        await engine.start_listening_to_data_parallel_coordinator(sp, port, launch_inference_coordinator=False)
+        client = InferenceClient(port)
+        await client.start()
+        futures = [client.add_request(p, sp) for p in prompts]
+        hopeless = client.add_request(list(range(6, 96)) + list(range(6, 96)), sp)
+        records = await asyncio.wait_for(asyncio.gather(*futures), timeout=60)
+        empty = await asyncio.wait_for(hopeless, timeout=60)
+        client.pause_engines()
+        await asyncio.sleep(0.2)
+        assert engine.paused
+        client.stop_engines()
+        await asyncio.wait_for(engine.engine_loop_task, timeout=30)
+        client.stop()
+        return records, empty
+
+    try:
+        records, empty = asyncio.new_event_loop().run_until_complete(scenario())
+    finally:
+        if "c" in box:
+            box["c"].stop()
+    assert engine.stopped and not engine.requests
+    tokenised = prompts[:-1] + [CharTokenizer(VOCAB).tokenize("hello")]
+    for prompt, record in zip(tokenised, records):
+        assert list(record.generated_tokens) == expected_completion(prompt, 12)
+    assert records[-1].prompt == "hello" and list(empty.generated_tokens) == [] and empty.generated_length == 0
