@@ -35,7 +35,8 @@ def main(port: int, out_path: str) -> None:
     class StubEngine(DynamicInferenceEngine):
         def __init__(self):
             self.paused = self.stopped = False
-            self.waiting_request_ids = deque()
+            self.waiting_request_ids, self.failed_request_ids = deque(), []
+            self.requests, self.request_completion_futures = {}, {}
             self.context = Context(self)
             self.active = {}     # request id -> [tokens still to emit, position]
             self.steps = 0

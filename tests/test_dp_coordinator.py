@@ -105,6 +105,7 @@ def test_coordinator_routes_requests_round_robin_and_results_to_their_clients():
         await asyncio.sleep(0.2)
         a.stop()
         b.stop()
+        await asyncio.sleep(0)  # lets the cancelled listener task finish before the loop goes away
         return done
 
     done = asyncio.new_event_loop().run_until_complete(scenario())
@@ -215,6 +216,7 @@ def test_messages_fan_out_inside_a_tensor_parallel_group(tmp_path):
         client.stop_engines()
         await asyncio.sleep(0.2)
         client.stop()
+        await asyncio.sleep(0)  # lets the cancelled listener task finish before the loop goes away
         return first + [second]
 
     try:

@@ -215,6 +215,7 @@ def test_engine_serves_a_client_through_the_coordinator_on_the_cpu():
         client.stop_engines()
         await asyncio.wait_for(engine.engine_loop_task, timeout=30)
         client.stop()
+        await asyncio.sleep(0)  # lets the cancelled listener task finish before the loop goes away
         return records, empty
 
     try:
