@@ -15,6 +15,12 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    # A test that stops making progress fails after a generous limit instead of blocking the run (pytest-timeout, where
+    # it is installed; the slowest tests - full-width oracle comparisons - take a few minutes).
+    if config.pluginmanager.hasplugin("timeout"):
+        for item in items:
+            if item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(1800))
     # Tests marked gpu are skipped (not failed) when no device is visible, so that an
     # unfiltered `pytest tests/` still passes on a CPU-only machine.
     try:
