@@ -67,7 +67,7 @@ def test_reference_engine_accepts_our_classes():
     line = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1]
     out = json.loads(line[len("RESULT "):])
     assert out["sub"] == [True, True, True, True] and out["same"]
-    assert out["shadowed"] == []
+    assert out["shadowed"] == ["add_request"]  # the wrapper that re-raises overflow errors as both families' (see the seam)
     assert out["missing"] == []
     assert out["signature"] == []
     assert out["n_result_keys"] >= 6 and out["result_keys_missing"] == []
@@ -164,3 +164,77 @@ def test_public_methods_and_records_cover_the_reference_api():
     }, out["missing"]
     assert out["fields"] == {name: [[], []] for name in ("SamplingParams", "CommonInferenceParams", "DynamicInferenceRequest",
                                                         "InferenceWrapperConfig")}, out["fields"]
+
+
+ENGINE_CHILD = r'''
+import json, os, sys, time
+ref, root = sys.argv[1], sys.argv[2]
+sys.path.insert(0, ref); sys.path.insert(0, root); sys.path.insert(0, os.path.join(root, "tests"))
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+import torch
+torch.cuda.current_device = lambda: torch.device("cpu")
+
+
+class HostEvent:  # the reference engine times a step with CUDA events
+    def __init__(self, *a, **k):
+        self.t = 0.0
+    def record(self):
+        self.t = time.perf_counter()
+    def synchronize(self):
+        pass
+    def elapsed_time(self, other):
+        return (other.t - self.t) * 1e3
+
+
+torch.cuda.Event = HostEvent
+import megatron.core.inference.engines.dynamic_engine as ref_engine
+ref_engine.range_push = lambda *a, **k: None
+ref_engine.range_pop = lambda *a, **k: None
+from megatron.core.inference.sampling_params import SamplingParams as RefSamplingParams
+from megatron_mixtera_b200.reference_seam import reference_subclasses
+import test_engine_host as H
+
+Context, Controller = reference_subclasses()
+
+
+class HostController(Controller):
+    def sample_from_logits(self, last_token_logits, sampling_params=None, vocab_size=None, **kwargs):
+        return torch.argmax(last_token_logits, dim=-1)
+
+
+def run(buffer_size_gb):
+    Context.TOKEN_ROUNDER, Context.REQUEST_ROUNDER = 4, 4
+    ctx = Context(params_dtype=torch.float32, num_layers=2, kv_channels=8, num_attention_heads=2, max_sequence_length=96,
+                  buffer_size_gb=buffer_size_gb, buffer_guaranteed_fraction=0.1, chunk_size_tokens=16,
+                  tensor_model_parallel_size=1, max_requests_override=8, max_tokens_override=128, device="cpu",
+                  allocate_memory_buffer=False)
+    model = H.StandInModel(ctx)
+    engine = ref_engine.DynamicInferenceEngine(HostController(model, tokenizer=__import__("serving_helpers").CharTokenizer(H.VOCAB)), ctx, termination_id=H.EOD, random_seed=0)
+    prompts = H.prompts_of(0, 14)
+    finished = engine.generate(list(prompts), RefSamplingParams(top_k=1, num_tokens_to_generate=24))
+    got = {r.request_id: [int(t) for t in r.generated_tokens] for r in finished}
+    want = {i: H.expected_completion(p, 24) for i, p in enumerate(prompts)}
+    return {"equal": got == want, "n": len(got), "steps": len(model.steps), "paused_seen": any(p for _, _, p in model.steps),
+            "engine": type(engine).__module__}
+
+
+print("RESULT " + json.dumps({"roomy": run(0.01), "starved": run(0.0001)}))
+'''
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "megatron", "core")), reason="reference checkout absent")
+def test_reference_engine_drives_our_context_and_controller():
+    """The REFERENCE's `DynamicInferenceEngine` (its queueing, stepping and post-processing, unmodified) around this
+    package's context and controller step, on the CPU: the model is the stand-in of `test_engine_host` (next token from
+    the request's own last token and position), CUDA events and NVTX ranges are replaced by host stand-ins.  Every request
+    must complete with its own tokens through a roomy pool and through one so small that requests wait and are paused -
+    which needs the overflow errors of `add_request` to be the ones the reference engine catches."""
+    import json
+
+    proc = subprocess.run([sys.executable, "-c", ENGINE_CHILD, REFERENCE, ROOT], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    out = json.loads([l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    for case in ("roomy", "starved"):
+        assert out[case]["engine"] == "megatron.core.inference.engines.dynamic_engine"
+        assert out[case]["equal"] and out[case]["n"] == 14, out
+    assert out["starved"]["paused_seen"] and not out["roomy"]["paused_seen"]
