@@ -1,5 +1,6 @@
 """Wire compatibility of the serving plumbing with the reference's: this package's client against the REFERENCE's
-coordinator, and the reference's client against this package's coordinator (engine replicas are protocol stand-ins).
+coordinator, the reference's client against this package's coordinator (engine replicas are protocol stand-ins), and this
+package's engine - its own serving loop around a stand-in model - as the replica of the reference's coordinator and client.
 Runs in a child process that imports the reference checkout; skipped where it is absent (it cannot travel)."""
 import os
 import subprocess
@@ -52,7 +53,32 @@ def run(coordinator_cls, client_cls, params):
     out = asyncio.new_event_loop().run_until_complete(scenario())
     return {"records": out, "received": replica.received, "signals": [s.name for s in replica.signals]}
 
+def run_engine(coordinator_cls, client_cls, params):
+    """This package's ENGINE (its serving loop, context and controller step around the stand-in model of
+    test_engine_host) as the replica of the given coordinator, driven by the given client."""
+    import test_engine_host as H
+
+    engine, ctx, model = H.make_engine(0.01)
+    port = free_port()
+    threading.Thread(target=lambda: coordinator_cls(CharTokenizer(H.VOCAB), port, 1).start(), daemon=True).start()
+    prompts = H.prompts_of(4, 5)
+    async def scenario():
+        await engine.start_listening_to_data_parallel_coordinator(
+            SamplingParams(top_k=1, num_tokens_to_generate=8), port, launch_inference_coordinator=False)
+        await asyncio.sleep(1.5)  # (the reference's coordinator must have its replica before a client speaks)
+        client = client_cls(port)
+        KEEP.append(client)
+        await client.start()
+        records = await asyncio.wait_for(asyncio.gather(*[client.add_request(p, params) for p in prompts]), timeout=60)
+        client.stop_engines()
+        await asyncio.wait_for(engine.engine_loop_task, timeout=30)
+        return [[int(t) for t in r.generated_tokens] for r in records]
+    got = asyncio.new_event_loop().run_until_complete(scenario())
+    return {"equal": got == [H.expected_completion(p, 8) for p in prompts], "n": len(got), "stopped": engine.stopped}
+
+
 result = {
+    "our_engine_ref_coordinator_ref_client": run_engine(RefCoordinator, RefClient, RefSamplingParams(top_k=1, num_tokens_to_generate=8)),
     "our_client_ref_coordinator": run(RefCoordinator, InferenceClient, SamplingParams(top_k=1, num_tokens_to_generate=2)),
     "ref_client_our_coordinator": run(DataParallelInferenceCoordinator, RefClient, RefSamplingParams(top_k=1, num_tokens_to_generate=2)),
 }
@@ -69,6 +95,7 @@ def test_client_and_coordinator_interoperate_with_the_reference():
     lines = [l for l in proc.stdout.splitlines() if l.startswith("RESULT ")]
     assert lines, proc.stdout[-2000:] + proc.stderr[-3000:]
     out = json.loads(lines[-1][len("RESULT "):])
+    assert out["our_engine_ref_coordinator_ref_client"] == {"equal": True, "n": 5, "stopped": True}, out
     for case in ("our_client_ref_coordinator", "ref_client_our_coordinator"):
         got = out[case]
         assert [r[0] for r in got["records"]] == [0, 1], (case, got)
